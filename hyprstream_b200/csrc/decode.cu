@@ -1,0 +1,404 @@
+// Decode attention (one query token per sequence) over a bf16 / int8 / 4-bit KV cache view, with a
+// flat split-KV partition over all sequences and a log-sum-exp merge.
+//
+// Fused replacement of cache.get() -> GQA expansion -> transposes -> fp32 upcast -> q@K^T*scale ->
+// softmax -> @V (architectures/llama.rs:605-640,847-872,1023-1119; the batched ragged form
+// llama.rs:710-844 with its padding mask 2540-2572; qwen3_5.rs:992-1059 for the gated variant).
+// The cache is read exactly once, in its stored precision, and dequantised in registers.
+//
+// This file holds the shape-generic CUDA-core kernel (any supported kind, head_dim 64/128/256,
+// group 1/2/4/8) and the merge kernel.  It is HBM-bound: per cached token and kv head it moves
+// 2*head_dim code bytes plus the scales, and does 2*group*head_dim FMAs.
+#include "hs_common.cuh"
+
+namespace hs {
+
+constexpr int kDecTile = 64;  // tokens per tile of the flat partition
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kKind4Bit = HS_KV_NF4;  // NF4 and FP4 share one instantiation (table chosen at run time)
+
+__device__ __forceinline__ int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
+
+// Raw (unscaled) values of EPL consecutive elements starting at element `e` of a page.
+template <int KIND, int EPL>
+struct Chunk {
+    static constexpr int kWords = KIND == HS_KV_BF16 ? EPL / 2 : (KIND == HS_KV_INT8 ? EPL / 4 : EPL / 8);
+    uint32_t w[kWords];
+
+    __device__ __forceinline__ void load(const void *page, int64_t e) {
+        if constexpr (kWords == 8) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(page) + e);
+            uint4 a = p[0], b = p[1];
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        } else {
+            const char *base = reinterpret_cast<const char *>(page) +
+                               (KIND == HS_KV_BF16 ? e * 2 : (KIND == HS_KV_INT8 ? e : e / 2));
+            if constexpr (kWords == 4) {
+                uint4 a = *reinterpret_cast<const uint4 *>(base);
+                w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+            } else if constexpr (kWords == 2) {
+                uint2 a = *reinterpret_cast<const uint2 *>(base);
+                w[0] = a.x; w[1] = a.y;
+            } else {
+                w[0] = *reinterpret_cast<const uint32_t *>(base);
+            }
+        }
+    }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) w[i] = 0;
+    }
+    // element i as a float before the block scale is applied (int8: code - 127; 4-bit: table value)
+    __device__ __forceinline__ float get(int i, const float *stab) const {
+        if constexpr (KIND == HS_KV_BF16) {
+            return (i & 1) ? bf16hi(w[i >> 1]) : bf16lo(w[i >> 1]);
+        } else if constexpr (KIND == HS_KV_INT8) {
+            // 2^23 + byte, built with one byte permute, minus (2^23 + 127): exact
+            return __uint_as_float(__byte_perm(w[i >> 2], 0x4B000000u, 0x7650 + (i & 3))) - 8388735.0f;
+        } else {
+            uint32_t byte = (w[i >> 3] >> (8 * ((i >> 1) & 3))) & 0xffu;
+            return stab[(i & 1) ? (byte & 0xfu) : (byte >> 4)];
+        }
+    }
+};
+
+template <int KIND, int D, int G, int EPL>
+__global__ void __launch_bounds__(kDecThreads)
+decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_t *__restrict__ seq_lens, int n_seqs,
+                      int n_q_heads, float scale_log2, float *__restrict__ o_part, float *__restrict__ lse_part,
+                      int *__restrict__ err) {
+    constexpr int LPT = D / EPL;         // lanes per token
+    constexpr int TPW = 32 / LPT;        // tokens per warp step
+    constexpr int NG = kDecWarps * TPW;  // lane groups per CTA
+    constexpr int U = 2;                 // tokens in flight per lane group
+    extern __shared__ float smem[];      // [NG][G][D + 2] merge buffer
+    __shared__ float stab[16];
+    if (KIND == kKind4Bit && threadIdx.x < 16) stab[threadIdx.x] = view.kind == HS_KV_NF4 ? c_nf4[threadIdx.x] : c_fp4[threadIdx.x];
+    __syncthreads();
+
+    const int kvh = blockIdx.y, H = view.n_kv_heads;
+    const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
+    int64_t total = 0;
+    for (int r = 0; r < n_seqs; ++r) total += ceil_div_i(max(seq_lens[r], 0), kDecTile);
+    const int64_t t_begin = part_begin(cta, total, n_ctas), t_end = part_begin(cta + 1, total, n_ctas);
+    if (t_begin >= t_end) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPT, li = lane % LPT, d0 = li * EPL;
+    const int grp = warp * TPW + sub;
+    const int bpr = D / view.block;  // scale blocks per (token, head) row
+    const int sblk = d0 / view.block;
+    const float kscale_mul = KIND == HS_KV_INT8 ? (1.0f / 127.0f) : 1.0f;
+
+    int64_t acc_tiles = 0;
+    for (int r = 0; r < n_seqs && acc_tiles < t_end; ++r) {
+        const int L = max(seq_lens[r], 0);
+        const int nt = ceil_div_i(L, kDecTile);
+        const int64_t lo = max(t_begin, acc_tiles), hi = min(t_end, acc_tiles + nt);
+        const int64_t seq_tile0 = acc_tiles;
+        acc_tiles += nt;
+        if (lo >= hi) continue;
+        const int tok_begin = static_cast<int>(lo - seq_tile0) * kDecTile;
+        int tok_end = min(L, static_cast<int>(hi - seq_tile0) * kDecTile);
+        const int cap = view.page_tokens * view.pages_per_seq;
+        if (tok_end > cap) {  // recorded; tokens past the view's pages are ignored
+            if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
+            tok_end = cap;
+        }
+        // query of this group's heads, packed bf16 pairs
+        uint32_t qw[G][EPL / 2];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const uint16_t *qp = q + (static_cast<int64_t>(r) * n_q_heads + kvh * G + g) * D + d0;
+#pragma unroll
+            for (int i = 0; i < EPL / 8; ++i) {
+                uint4 a = reinterpret_cast<const uint4 *>(qp)[i];
+                qw[g][4 * i] = a.x; qw[g][4 * i + 1] = a.y; qw[g][4 * i + 2] = a.z; qw[g][4 * i + 3] = a.w;
+            }
+        }
+        float m[G], l[G], o[G][EPL];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[g][i] = 0.0f;
+        }
+        void *const *kp = view.k_pages + static_cast<int64_t>(r) * view.pages_per_seq;
+        void *const *vp = view.v_pages + static_cast<int64_t>(r) * view.pages_per_seq;
+        void *const *ksp = KIND == HS_KV_BF16 ? nullptr : view.k_scale_pages + static_cast<int64_t>(r) * view.pages_per_seq;
+        void *const *vsp = KIND == HS_KV_BF16 ? nullptr : view.v_scale_pages + static_cast<int64_t>(r) * view.pages_per_seq;
+
+        for (int tb = tok_begin; tb < tok_end; tb += NG * U) {  // warp-uniform trip count
+            Chunk<KIND, EPL> kc[U], vc[U];
+            float ks[U], vs[U];
+            bool valid[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = tb + u * NG + grp;
+                valid[u] = t < tok_end;
+                ks[u] = 1.0f; vs[u] = 1.0f;
+                if (valid[u]) {
+                    const int page = view.pages_per_seq == 1 ? 0 : t / view.page_tokens;
+                    const int64_t row = static_cast<int64_t>(t - page * view.page_tokens) * H + kvh;
+                    kc[u].load(kp[page], row * D + d0);
+                    vc[u].load(vp[page], row * D + d0);
+                    if constexpr (KIND != HS_KV_BF16) {
+                        ks[u] = load_scale(ksp[page], row * bpr + sblk, view.scale_dtype) * kscale_mul;
+                        vs[u] = load_scale(vsp[page], row * bpr + sblk, view.scale_dtype) * kscale_mul;
+                    }
+                } else {
+                    kc[u].zero(); vc[u].zero();
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float s[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) s[g] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    const float kf = kc[u].get(i, stab);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float qf = (i & 1) ? bf16hi(qw[g][i >> 1]) : bf16lo(qw[g][i >> 1]);
+                        s[g] = fmaf(qf, kf, s[g]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float v = s[g] * ks[u];
+#pragma unroll
+                    for (int off = 1; off < LPT; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    s[g] = valid[u] ? v * scale_log2 : -INFINITY;
+                }
+                float p[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float mn = fmaxf(m[g], s[g]);
+                    const float corr = (mn == -INFINITY) ? 1.0f : exp2f(m[g] - mn);
+                    p[g] = (mn == -INFINITY) ? 0.0f : exp2f(s[g] - mn);
+                    l[g] = l[g] * corr + p[g];
+                    m[g] = mn;
+                    if (corr != 1.0f) {
+#pragma unroll
+                        for (int i = 0; i < EPL; ++i) o[g][i] *= corr;
+                    }
+                    p[g] *= vs[u];
+                }
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    const float vf = vc[u].get(i, stab);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) o[g][i] = fmaf(p[g], vf, o[g][i]);
+                }
+            }
+        }
+        // ---- merge the NG lane groups through shared memory ----
+        __syncthreads();  // previous segment's readers are done
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float *dst = smem + (static_cast<int64_t>(grp) * G + g) * (D + 2);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) dst[d0 + i] = o[g][i];
+            if (li == 0) { dst[D] = m[g]; dst[D + 1] = l[g]; }
+        }
+        __syncthreads();
+        const int slot = static_cast<int>(cta) + r;
+        for (int idx = threadIdx.x; idx < G * D; idx += kDecThreads) {
+            const int g = idx / D, d = idx % D;
+            float M = -INFINITY;
+            for (int j = 0; j < NG; ++j) M = fmaxf(M, smem[(static_cast<int64_t>(j) * G + g) * (D + 2) + D]);
+            float num = 0.0f, den = 0.0f;
+            for (int j = 0; j < NG; ++j) {
+                const float *src = smem + (static_cast<int64_t>(j) * G + g) * (D + 2);
+                const float wgt = src[D] == -INFINITY ? 0.0f : exp2f(src[D] - M);
+                num = fmaf(wgt, src[d], num);
+                den = fmaf(wgt, src[D + 1], den);
+            }
+            const int64_t hrow = static_cast<int64_t>(slot) * n_q_heads + kvh * G + g;
+            o_part[hrow * D + d] = den > 0.0f ? num / den : 0.0f;
+            if (d == 0) lse_part[hrow] = den > 0.0f ? (M + log2f(den)) * 0.6931471805599453f : -INFINITY;
+        }
+    }
+}
+
+// Merge the split-KV partials of every (sequence, head).  One CTA per (sequence, head), one thread per
+// output element.  The slot range of a sequence is recomputed from seq_lens with the same partition
+// arithmetic the decode kernel used.
+__global__ void decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_heads, int D, int n_ctas,
+                                    int tile, const float *__restrict__ o_part, const float *__restrict__ lse_part,
+                                    uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, float *__restrict__ o_shard,
+                                    float *__restrict__ lse_shard) {
+    const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    int64_t total = 0, before = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        if (i == r) before = total;
+        total += ceil_div_i(max(seq_lens[i], 0), tile);
+    }
+    const int64_t nt = ceil_div_i(max(seq_lens[r], 0), tile);
+    const int64_t row = static_cast<int64_t>(r) * n_q_heads + h;
+    float num = 0.0f, den = 0.0f, M = -INFINITY;
+    if (nt > 0) {
+        // first / last CTA whose tile range overlaps [before, before + nt)
+        int64_t c_lo = before * n_ctas / total;
+        while (c_lo > 0 && part_begin(c_lo, total, n_ctas) > before) --c_lo;
+        while (part_begin(c_lo + 1, total, n_ctas) <= before) ++c_lo;
+        int64_t c_hi = (before + nt - 1) * n_ctas / total;
+        while (c_hi > 0 && part_begin(c_hi, total, n_ctas) > before + nt - 1) --c_hi;
+        while (part_begin(c_hi + 1, total, n_ctas) <= before + nt - 1) ++c_hi;
+        for (int64_t c = c_lo; c <= c_hi; ++c) M = fmaxf(M, lse_part[(c + r) * n_q_heads + h]);
+        for (int64_t c = c_lo; c <= c_hi; ++c) {
+            const int64_t prow = (c + r) * n_q_heads + h;
+            const float ls = lse_part[prow];
+            const float wgt = ls == -INFINITY ? 0.0f : __expf(ls - M);
+            num = fmaf(wgt, o_part[prow * D + d], num);
+            den += wgt;
+        }
+    }
+    const float o = den > 0.0f ? num / den : 0.0f;
+    if (o_shard != nullptr) {
+        o_shard[row * D + d] = o;
+        if (d == 0) lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
+        return;
+    }
+    float res = o;
+    if (gate != nullptr) {
+        const float gv = bf16_bits_to_f32(gate[row * D + d]);
+        res = bf16_round(o) * bf16_round(1.0f / (1.0f + __expf(-gv)));  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
+    }
+    out[row * D + d] = f32_to_bf16_bits(res);
+}
+
+// Merge of externally produced partials (KV-length shards from several GPUs, or a caller's own split).
+__global__ void merge_parts_kernel(const float *__restrict__ o_parts, const float *__restrict__ lse_parts, int n_parts,
+                                   int64_t n_rows, int D, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate) {
+    const int64_t row = blockIdx.x;
+    const int d = threadIdx.x;
+    float M = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, lse_parts[p * n_rows + row]);
+    float num = 0.0f, den = 0.0f;
+    for (int p = 0; p < n_parts; ++p) {
+        const float ls = lse_parts[p * n_rows + row];
+        const float wgt = ls == -INFINITY ? 0.0f : __expf(ls - M);
+        num = fmaf(wgt, o_parts[(p * n_rows + row) * D + d], num);
+        den += wgt;
+    }
+    float res = den > 0.0f ? num / den : 0.0f;
+    if (gate != nullptr) {
+        const float gv = bf16_bits_to_f32(gate[row * D + d]);
+        res = bf16_round(res) * bf16_round(1.0f / (1.0f + __expf(-gv)));
+    }
+    out[row * D + d] = f32_to_bf16_bits(res);
+}
+
+static int decode_max_ctas() { return 4 * sm_count(); }
+
+template <int KIND, int D, int G>
+static int32_t launch_generic(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
+                              float scale_log2, float *o_part, float *lse_part, int *err, int n_ctas, cudaStream_t s) {
+    constexpr int EPL = (G == 8) ? 8 : 16;
+    constexpr int NG = kDecWarps * (32 / (D / EPL));
+    const size_t smem = static_cast<size_t>(NG) * G * (D + 2) * sizeof(float);
+    auto kern = decode_generic_kernel<KIND, D, G, EPL>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode: %s", cudaGetErrorString(e));
+    }
+    dim3 grid(n_ctas, v.n_kv_heads);
+    kern<<<grid, kDecThreads, smem, s>>>(v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err);
+    return HS_OK;
+}
+
+template <int KIND, int D>
+static int32_t dispatch_g(int G, const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
+                          float scale_log2, float *o_part, float *lse_part, int *err, int n_ctas, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_generic<KIND, D, 1>(v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        case 2: return launch_generic<KIND, D, 2>(v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        case 4: return launch_generic<KIND, D, 4>(v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        case 8: return launch_generic<KIND, D, 8>(v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        default: return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode: n_q_heads / n_kv_heads = %d (supported: 1, 2, 4, 8)", G);
+    }
+}
+
+template <int KIND>
+static int32_t dispatch_d(int D, int G, const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs,
+                          int n_q_heads, float scale_log2, float *o_part, float *lse_part, int *err, int n_ctas,
+                          cudaStream_t s) {
+    switch (D) {
+        case 64: return dispatch_g<KIND, 64>(G, v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        case 128: return dispatch_g<KIND, 128>(G, v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        case 256: return dispatch_g<KIND, 256>(G, v, q, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s);
+        default: return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode: head_dim %d", D);
+    }
+}
+
+}  // namespace hs
+
+using namespace hs;
+
+extern "C" {
+
+int64_t hs_attn_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, int32_t head_dim) {
+    if (n_seqs < 0 || n_q_heads <= 0 || head_dim <= 0) return HS_ERR_ARG;
+    const int64_t slots = static_cast<int64_t>(decode_max_ctas()) + n_seqs;
+    return slots * n_q_heads * (static_cast<int64_t>(head_dim) + 1) * 4;
+}
+
+int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                       float softmax_scale, void *out, const void *gate, void *workspace, int64_t workspace_bytes,
+                       float *o_shard, float *lse_shard, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (int32_t st = validate_view(view)) return st;
+    if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode: bad sizes");
+    if (n_seqs == 0) return HS_OK;
+    if (n_q_heads % view->n_kv_heads != 0) return fail(HS_ERR_ARG, "hs_attn_decode: n_q_heads %d not a multiple of n_kv_heads %d", n_q_heads, view->n_kv_heads);
+    if (!q || !seq_lens || !workspace) return fail(HS_ERR_ARG, "hs_attn_decode: NULL pointer");
+    if ((o_shard == nullptr) != (lse_shard == nullptr)) return fail(HS_ERR_ARG, "hs_attn_decode: o_shard and lse_shard go together");
+    if (!o_shard && !out) return fail(HS_ERR_ARG, "hs_attn_decode: no output");
+    if (!aligned(q, 16) || !aligned(workspace, 16) || (out && !aligned(out, 2)) || (gate && !aligned(gate, 2)) || !aligned(seq_lens, 4))
+        return fail(HS_ERR_ARG, "hs_attn_decode: q and workspace must be 16-byte aligned");
+    const int D = view->head_dim, G = n_q_heads / view->n_kv_heads;
+    const int64_t need = hs_attn_decode_workspace_bytes(n_seqs, n_q_heads, D);
+    if (workspace_bytes < need) return fail(HS_ERR_WORKSPACE, "hs_attn_decode: workspace %lld < %lld bytes", (long long)workspace_bytes, (long long)need);
+    int *err = device_error_word();
+    if (!err) return fail(HS_ERR_DEVICE, "hs_attn_decode: device error word unavailable");
+
+    ViewDev v = to_dev(view);
+    int n_ctas = (3 * sm_count() + v.n_kv_heads - 1) / v.n_kv_heads;
+    n_ctas = max(1, min(n_ctas, decode_max_ctas()));
+    const int64_t slots = static_cast<int64_t>(decode_max_ctas()) + n_seqs;
+    float *o_part = reinterpret_cast<float *>(workspace);
+    float *lse_part = o_part + slots * n_q_heads * D;
+    const float scale_log2 = softmax_scale * 1.4426950408889634f;
+    cudaStream_t s = as_stream(stream);
+    const uint16_t *qp = reinterpret_cast<const uint16_t *>(q);
+    int32_t st;
+    switch (view->kind) {
+        case HS_KV_BF16: st = dispatch_d<HS_KV_BF16>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+        case HS_KV_INT8: st = dispatch_d<HS_KV_INT8>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+        default: st = dispatch_d<kKind4Bit>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+    }
+    if (st != HS_OK) return st;
+    if (int32_t e = check_launch("hs_attn_decode")) return e;
+    dim3 mgrid(n_seqs, n_q_heads);
+    decode_merge_kernel<<<mgrid, D, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, kDecTile, o_part, lse_part,
+                                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard,
+                                            lse_shard);
+    return check_launch("hs_attn_decode (merge)");
+}
+
+int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows, int32_t head_dim,
+                               void *out, const void *gate, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (n_parts <= 0 || n_rows < 0 || head_dim <= 0 || head_dim > 1024) return fail(HS_ERR_ARG, "hs_attn_merge_partials: bad sizes");
+    if (n_rows == 0) return HS_OK;
+    if (!o_parts || !lse_parts || !out) return fail(HS_ERR_ARG, "hs_attn_merge_partials: NULL pointer");
+    if (n_rows > 0x7fffffffLL) return fail(HS_ERR_ARG, "hs_attn_merge_partials: too many rows");
+    merge_parts_kernel<<<static_cast<unsigned>(n_rows), head_dim, 0, as_stream(stream)>>>(
+        o_parts, lse_parts, n_parts, n_rows, head_dim, reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate));
+    return check_launch("hs_attn_merge_partials");
+}
+
+}  // extern "C"

@@ -1,0 +1,76 @@
+// Shared host/device helpers for the sm_100a attention + KV-cache kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/hs_attn.h"
+
+namespace hs {
+
+// ---- host-side status plumbing --------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int32_t fail(int32_t code, const char *fmt, ...);
+int32_t check_device();             // HS_OK on compute capability 10.x, else HS_ERR_DEVICE
+int32_t check_launch(const char *what);  // cudaGetLastError -> status
+int sm_count();
+// Address (on the current device) of the error word that kernels set instead of faulting when they
+// meet an out-of-range index; hs_attn_take_device_error() reads and clears it.
+int *device_error_word();
+
+static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+static inline cudaStream_t as_stream(hs_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int32_t validate_view(const hs_kv_view *v);
+
+// Kernel-argument copy of hs_kv_view (passed by value).
+struct ViewDev {
+    void *const *k_pages, *const *v_pages, *const *k_scale_pages, *const *v_scale_pages;
+    int kind, scale_dtype, block, n_kv_heads, head_dim, page_tokens, pages_per_seq;
+};
+
+static inline ViewDev to_dev(const hs_kv_view *v) {
+    ViewDev d;
+    d.k_pages = v->k_pages; d.v_pages = v->v_pages; d.k_scale_pages = v->k_scale_pages; d.v_scale_pages = v->v_scale_pages;
+    d.kind = v->kind; d.scale_dtype = v->scale_dtype; d.block = v->kind == HS_KV_BF16 ? v->head_dim : v->block;
+    d.n_kv_heads = v->n_kv_heads; d.head_dim = v->head_dim; d.page_tokens = v->page_tokens; d.pages_per_seq = v->pages_per_seq;
+    return d;
+}
+
+// ---- device helpers --------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    return static_cast<uint32_t>(f32_to_bf16_bits(lo)) | (static_cast<uint32_t>(f32_to_bf16_bits(hi)) << 16);
+}
+// a (op) b rounded to bf16, as libtorch's bf16 elementwise kernels do (f32 op, then round).
+__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+__device__ __forceinline__ float load_scale(const void *p, int64_t idx, int scale_dtype) {
+    return scale_dtype == HS_SCALE_F16 ? __half2float(reinterpret_cast<const __half *>(p)[idx])
+                                       : reinterpret_cast<const float *>(p)[idx];
+}
+
+// NF4 / FP4 codebooks (bitsandbytes-sys/src/lib.rs:131-148,152-169)
+static __device__ __constant__ float c_nf4[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230945587158f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+static __device__ __constant__ float c_fp4[16] = {0.0f,  0.0625f, 0.125f, 0.1875f, 0.25f,  0.3125f, 0.375f, 0.4375f,
+                                                  0.5f,  0.5625f, 0.625f, 0.6875f, 0.75f,  0.8125f, 0.875f, 1.0f};
+
+// ---- flat split-KV partition -------------------------------------------------------------------
+// The KV tokens of all sequences are cut into tiles of `tile` tokens; the concatenated tile list is
+// divided evenly over `n_ctas` CTAs.  CTA c owns tiles [c*total/n_ctas, (c+1)*total/n_ctas).  A
+// (cta, sequence) pair that overlaps writes one partial into slot cta + sequence (unique because
+// both indices are non-decreasing along the tile list).
+__device__ __forceinline__ int64_t part_begin(int64_t c, int64_t total, int64_t n_ctas) { return c * total / n_ctas; }
+
+}  // namespace hs

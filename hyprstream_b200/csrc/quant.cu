@@ -1,0 +1,447 @@
+// Blockwise KV quantiser for sm_100a: flat quantise / dequantise, RoPE, quantise-on-write into a
+// (paged) cache view, and the gather-dequantise compatibility read.
+//
+// Arithmetic contract (bit-exact with the CPU specification used by the parity tests):
+//   absmax = max|x| over the block in f32; in f16-scale mode it is rounded to f16 (nearest even,
+//   saturating at 65504) before use;  y = x * (1/absmax), one IEEE rounding each;
+//   index = number of f32 codeword midpoints 0.5*(c[j]+c[j+1]) strictly below y;
+//   an all-zero block stores absmax 0 and the index of the codeword 0;
+//   4-bit codes pack the even element into the high nibble.
+// Codebooks and block geometry follow bitsandbytes-sys/src/lib.rs:104-181 and
+// crates/hyprstream/src/runtime/kv_cache.rs:704,741-957.
+//
+// All kernels here are HBM-streaming: one thread owns 8 consecutive elements (one 16-byte bf16
+// load, one 8-byte int8 store), a block's absmax is reduced with warp shuffles, nothing is staged.
+#include "hs_common.cuh"
+
+namespace hs {
+
+constexpr int kQThreads = 256;
+
+__device__ __forceinline__ float code8(int i) { return __fdiv_rn(static_cast<float>(i) - 127.0f, 127.0f); }
+__device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(code8(j), code8(j + 1))); }
+
+// Index of y in the 8-bit linear codebook.  The candidate round(y*127)+127 is exact unless y*127 sits
+// within 1e-3 of a half-integer; only then are the true f32 midpoints consulted.
+__device__ __forceinline__ int index_int8(float y) {
+    float t = __fmul_rn(y, 127.0f);
+    int c = __float2int_rn(t) + 127;
+    c = max(0, min(255, c));
+    float fr = t - floorf(t);
+    if (fabsf(fr - 0.5f) < 1e-3f) {
+        if (c > 0 && !(y > mid8(c - 1))) c--;
+        else if (c < 255 && y > mid8(c)) c++;
+    }
+    return c;
+}
+
+// Index of y in a 16-entry ascending codebook whose 15 midpoints are in shared memory.
+__device__ __forceinline__ int index_4bit(float y, const float *smid) {
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < 15; ++j) c += (y > smid[j]) ? 1 : 0;
+    return c;
+}
+
+__device__ __forceinline__ void fill_midpoints(int kind, float *smid) {
+    if (kind != HS_KV_INT8 && threadIdx.x < 15) {
+        const float *t = kind == HS_KV_NF4 ? c_nf4 : c_fp4;
+        smid[threadIdx.x] = __fmul_rn(0.5f, __fadd_rn(t[threadIdx.x], t[threadIdx.x + 1]));
+    }
+}
+
+__device__ __forceinline__ float f16_sat_round(float a) {
+    // nearest-even to f16, saturating: anything that would round past 65504 stays 65504
+    return a >= 65520.0f ? 65504.0f : __half2float(__float2half_rn(a));
+}
+
+// Quantise the 8 values of this thread; `tpb` consecutive lanes (a power of two <= 32) share a block.
+// Returns the stored scale (already rounded in f16 mode); codes[] receives 8 indices.
+template <int KIND>
+__device__ __forceinline__ float quantize8(const float (&x)[8], int tpb, int scale_dtype, const float *smid,
+                                           int (&codes)[8]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    for (int o = 1; o < tpb; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float a = scale_dtype == HS_SCALE_F16 ? f16_sat_round(amax) : amax;
+    if (a == 0.0f) {
+        const int zc = KIND == HS_KV_INT8 ? 127 : (KIND == HS_KV_NF4 ? 7 : 0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) codes[i] = zc;
+        return a;
+    }
+    float inv = __fdiv_rn(1.0f, a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float y = __fmul_rn(x[i], inv);
+        codes[i] = KIND == HS_KV_INT8 ? index_int8(y) : index_4bit(y, smid);
+    }
+    return a;
+}
+
+__device__ __forceinline__ void store_scale(void *p, int64_t idx, int scale_dtype, float a) {
+    if (scale_dtype == HS_SCALE_F16) reinterpret_cast<__half *>(p)[idx] = __float2half_rn(a);
+    else reinterpret_cast<float *>(p)[idx] = a;
+}
+
+__device__ __forceinline__ float load_elem(const void *src, int dtype, int64_t i) {
+    if (dtype == HS_DTYPE_BF16) return bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(src)[i]);
+    if (dtype == HS_DTYPE_F16) return __half2float(reinterpret_cast<const __half *>(src)[i]);
+    return reinterpret_cast<const float *>(src)[i];
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4 &w, float (&x)[8]) {
+    x[0] = bf16lo(w.x); x[1] = bf16hi(w.x); x[2] = bf16lo(w.y); x[3] = bf16hi(w.y);
+    x[4] = bf16lo(w.z); x[5] = bf16hi(w.z); x[6] = bf16lo(w.w); x[7] = bf16hi(w.w);
+}
+
+template <int KIND>
+__device__ __forceinline__ void store_codes8(uint8_t *codes, int64_t e0, int64_t n, const int (&c)[8], bool full) {
+    if (KIND == HS_KV_INT8) {
+        if (full) {
+            uint2 w;
+            w.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+            w.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+            *reinterpret_cast<uint2 *>(codes + e0) = w;
+        } else {
+            for (int i = 0; i < 8 && e0 + i < n; ++i) codes[e0 + i] = static_cast<uint8_t>(c[i]);
+        }
+    } else {
+        if (full) {
+            uint32_t w = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8) | (((c[4] << 4) | c[5]) << 16) |
+                         (((c[6] << 4) | c[7]) << 24);
+            *reinterpret_cast<uint32_t *>(codes + (e0 >> 1)) = w;
+        } else {
+            for (int i = 0; i < 8 && e0 + i < n; i += 2) {
+                int lo = (e0 + i + 1 < n) ? c[i + 1] : 0;
+                codes[(e0 + i) >> 1] = static_cast<uint8_t>((c[i] << 4) | lo);
+            }
+        }
+    }
+}
+
+// ---- flat quantise ----------------------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(kQThreads) quantize_flat_kernel(const void *__restrict__ src, int dtype, int64_t n,
+                                                                  int block, int scale_dtype, uint8_t *__restrict__ codes,
+                                                                  void *__restrict__ absmax, int vec_ok) {
+    __shared__ float smid[16];
+    fill_midpoints(KIND, smid);
+    __syncthreads();
+    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
+    const int64_t e0 = chunk * 8;
+    float x[8];
+    const bool full = e0 + 8 <= n;
+    if (full && vec_ok && dtype == HS_DTYPE_BF16) {
+        unpack8_bf16(*reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(src) + e0), x);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (e0 + i < n) ? load_elem(src, dtype, e0 + i) : 0.0f;
+    }
+    int c[8];
+    const int tpb = block / 8;
+    float a = quantize8<KIND>(x, tpb, scale_dtype, smid, c);
+    if (e0 < n) {
+        if ((chunk % tpb) == 0) store_scale(absmax, e0 / block, scale_dtype, a);
+        store_codes8<KIND>(codes, e0, n, c, full);
+    }
+}
+
+// ---- flat dequantise ----------------------------------------------------------------------------
+__device__ __forceinline__ float table_value(int kind, int c, const float *stab) {
+    return kind == HS_KV_INT8 ? code8(c) : stab[c];
+}
+
+__device__ __forceinline__ void store_elem(void *out, int dtype, int64_t i, float v) {
+    if (dtype == HS_DTYPE_BF16) reinterpret_cast<uint16_t *>(out)[i] = f32_to_bf16_bits(v);
+    else if (dtype == HS_DTYPE_F16) reinterpret_cast<__half *>(out)[i] = __float2half_rn(v);
+    else reinterpret_cast<float *>(out)[i] = v;
+}
+
+__global__ void __launch_bounds__(kQThreads) dequantize_flat_kernel(int kind, const uint8_t *__restrict__ codes,
+                                                                    const void *__restrict__ absmax, int64_t n, int block,
+                                                                    int scale_dtype, void *__restrict__ out, int dtype) {
+    __shared__ float stab[16];
+    if (kind != HS_KV_INT8 && threadIdx.x < 16) stab[threadIdx.x] = kind == HS_KV_NF4 ? c_nf4[threadIdx.x] : c_fp4[threadIdx.x];
+    __syncthreads();
+    const int64_t e0 = (static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x) * 8;
+    if (e0 >= n) return;
+    const float a = load_scale(absmax, e0 / block, scale_dtype);
+    for (int i = 0; i < 8 && e0 + i < n; ++i) {
+        int64_t e = e0 + i;
+        int c = kind == HS_KV_INT8 ? codes[e] : ((e & 1) ? (codes[e >> 1] & 0xf) : (codes[e >> 1] >> 4));
+        store_elem(out, dtype, e, __fmul_rn(table_value(kind, c, stab), a));
+    }
+}
+
+// ---- RoPE ------------------------------------------------------------------------------------------
+// Rotated value of element d of a row, given the row's unrotated elements `own` (at d) and `partner`
+// (at d +- rotary_dim/2).  Every product, difference and sum is rounded to bf16 (rope.rs:243-244).
+__device__ __forceinline__ float rope_elem(float own, float partner, float s, float c, bool first_half) {
+    if (first_half) return bf16_round(bf16_round(own * c) - bf16_round(partner * s));  // x1*cos - x2*sin
+    return bf16_round(bf16_round(partner * s) + bf16_round(own * c));                 // x1*sin + x2*cos
+}
+
+// Loads the 8 bf16 elements [d0, d0+8) of a row, rotated when sin != NULL.
+__device__ __forceinline__ void load_row8_rope(const uint16_t *row, int d0, const uint16_t *sin, const uint16_t *cos,
+                                               int pos, int rotary_dim, float (&x)[8]) {
+    unpack8_bf16(*reinterpret_cast<const uint4 *>(row + d0), x);
+    if (sin != nullptr && d0 < rotary_dim) {
+        const int half = rotary_dim >> 1;
+        const bool first = d0 < half;
+        float p[8];
+        unpack8_bf16(*reinterpret_cast<const uint4 *>(row + (first ? d0 + half : d0 - half)), p);
+        const int j0 = first ? d0 : d0 - half;
+        const uint16_t *srow = sin + static_cast<int64_t>(pos) * half + j0;
+        const uint16_t *crow = cos + static_cast<int64_t>(pos) * half + j0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = rope_elem(x[i], p[i], bf16_bits_to_f32(srow[i]), bf16_bits_to_f32(crow[i]), first);
+    }
+}
+
+__global__ void __launch_bounds__(kQThreads) rope_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out,
+                                                         const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
+                                                         const int32_t *__restrict__ positions, int64_t n_rows, int n_heads,
+                                                         int head_dim, int rotary_dim, int n_positions, int *__restrict__ err) {
+    const int cpr = head_dim / 8;  // chunks per (row, head)
+    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
+    const int64_t total = n_rows * n_heads * cpr;
+    if (chunk >= total) return;
+    const int d0 = static_cast<int>(chunk % cpr) * 8;
+    const int64_t rh = chunk / cpr;
+    const int64_t r = rh / n_heads;
+    float v[8];
+    const int pos = positions[r];
+    const bool in_table = pos >= 0 && pos < n_positions;
+    if (!in_table) atomicExch(err, HS_DEVERR_ROPE_RANGE);  // recorded; the row is copied unrotated
+    load_row8_rope(x + rh * head_dim, d0, in_table ? sin : nullptr, cos, in_table ? pos : 0, rotary_dim, v);
+    uint4 w;
+    w.x = pack_bf16(v[0], v[1]); w.y = pack_bf16(v[2], v[3]); w.z = pack_bf16(v[4], v[5]); w.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4 *>(out + rh * head_dim + d0) = w;
+}
+
+// ---- quantise-on-write into a cache view ----------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const uint16_t *__restrict__ k_new,
+                                                             const uint16_t *__restrict__ v_new, int n_seqs, int n_tokens,
+                                                             const int32_t *__restrict__ dst_pos,
+                                                             const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
+                                                             int rotary_dim, int n_positions, int *__restrict__ err) {
+    __shared__ float smid[16];
+    fill_midpoints(KIND, smid);
+    __syncthreads();
+    const bool is_v = blockIdx.y == 1;
+    const int D = view.head_dim, H = view.n_kv_heads;
+    const int cpr = D / 8;
+    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
+    const int64_t total = static_cast<int64_t>(n_seqs) * n_tokens * H * cpr;
+    const bool live = chunk < total;
+    const int64_t cc = live ? chunk : 0;  // dead lanes still take part in the shuffles
+    const int d0 = static_cast<int>(cc % cpr) * 8;
+    const int64_t row = cc / cpr;  // (seq, token, head)
+    const int h = static_cast<int>(row % H);
+    const int64_t st = row / H;
+    const int t = static_cast<int>(st % n_tokens);
+    const int s = static_cast<int>(st / n_tokens);
+    const int pos = dst_pos ? dst_pos[s] + t : t;
+    const int page = pos / view.page_tokens;
+    bool ok = live && pos >= 0 && page < view.pages_per_seq;
+    if (!is_v && sin != nullptr && (pos < 0 || pos >= n_positions)) ok = false;
+    if (live && !ok) atomicExch(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
+    const uint16_t *src = (is_v ? v_new : k_new) + row * D;
+    float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (ok) load_row8_rope(src, d0, is_v ? nullptr : sin, cos, pos, rotary_dim, x);
+    const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + h;  // (token, head) row inside the page
+    const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
+    if (KIND == HS_KV_BF16) {
+        if (ok) {
+            uint16_t *dst = reinterpret_cast<uint16_t *>((is_v ? view.v_pages : view.k_pages)[pidx]) + in_page * D + d0;
+            uint4 w;
+            w.x = pack_bf16(x[0], x[1]); w.y = pack_bf16(x[2], x[3]); w.z = pack_bf16(x[4], x[5]); w.w = pack_bf16(x[6], x[7]);
+            *reinterpret_cast<uint4 *>(dst) = w;
+        }
+        return;
+    }
+    constexpr int QK = KIND == HS_KV_BF16 ? HS_KV_INT8 : KIND;
+    int c[8];
+    const int tpb = view.block / 8;
+    float a = quantize8<QK>(x, tpb, view.scale_dtype, smid, c);
+    if (!ok) return;
+    uint8_t *codes = reinterpret_cast<uint8_t *>((is_v ? view.v_pages : view.k_pages)[pidx]);
+    void *scales = (is_v ? view.v_scale_pages : view.k_scale_pages)[pidx];
+    const int bpr = D / view.block;  // blocks per (token, head) row
+    if ((d0 % view.block) == 0) store_scale(scales, in_page * bpr + d0 / view.block, view.scale_dtype, a);
+    const int64_t e0 = in_page * D + d0;
+    store_codes8<QK>(codes, e0, e0 + 8, c, true);
+}
+
+// ---- gather-dequantise (LayerKVCache::get compatibility read) ------------------------------------------------
+__global__ void __launch_bounds__(kQThreads) kv_gather_kernel(ViewDev view, const int32_t *__restrict__ seq_lens, int n_seqs,
+                                                              int out_tokens, uint16_t *__restrict__ k_out,
+                                                              uint16_t *__restrict__ v_out) {
+    __shared__ float stab[16];
+    if (view.kind >= HS_KV_NF4 && threadIdx.x < 16) stab[threadIdx.x] = view.kind == HS_KV_NF4 ? c_nf4[threadIdx.x] : c_fp4[threadIdx.x];
+    __syncthreads();
+    const bool is_v = blockIdx.y == 1;
+    const int D = view.head_dim, H = view.n_kv_heads;
+    const int cpr = D / 8;
+    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
+    const int64_t total = static_cast<int64_t>(n_seqs) * out_tokens * H * cpr;
+    if (chunk >= total) return;
+    const int d0 = static_cast<int>(chunk % cpr) * 8;
+    const int64_t row = chunk / cpr;
+    const int h = static_cast<int>(row % H);
+    const int64_t st = row / H;
+    const int t = static_cast<int>(st % out_tokens);
+    const int s = static_cast<int>(st / out_tokens);
+    uint4 w = make_uint4(0, 0, 0, 0);
+    const int page = t / view.page_tokens;
+    if (t < seq_lens[s] && page < view.pages_per_seq) {
+        const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
+        const int64_t in_page = static_cast<int64_t>(t - page * view.page_tokens) * H + h;
+        const void *data = (is_v ? view.v_pages : view.k_pages)[pidx];
+        if (view.kind == HS_KV_BF16) {
+            w = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(data) + in_page * D + d0);
+        } else {
+            const void *scales = (is_v ? view.v_scale_pages : view.k_scale_pages)[pidx];
+            const float a = load_scale(scales, in_page * (D / view.block) + d0 / view.block, view.scale_dtype);
+            float v[8];
+            const uint8_t *codes = reinterpret_cast<const uint8_t *>(data);
+            if (view.kind == HS_KV_INT8) {
+                uint2 cw = *reinterpret_cast<const uint2 *>(codes + in_page * D + d0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(code8(((i < 4 ? cw.x : cw.y) >> (8 * (i & 3))) & 0xff), a);
+            } else {
+                uint32_t cw = *reinterpret_cast<const uint32_t *>(codes + ((in_page * D + d0) >> 1));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    int byte = (cw >> (8 * (i >> 1))) & 0xff;
+                    v[i] = __fmul_rn(stab[(i & 1) ? (byte & 0xf) : (byte >> 4)], a);
+                }
+            }
+            w.x = pack_bf16(v[0], v[1]); w.y = pack_bf16(v[2], v[3]); w.z = pack_bf16(v[4], v[5]); w.w = pack_bf16(v[6], v[7]);
+        }
+    }
+    *reinterpret_cast<uint4 *>((is_v ? v_out : k_out) + row * D + d0) = w;
+}
+
+}  // namespace hs
+
+using namespace hs;
+
+extern "C" {
+
+int32_t hs_quantize_blockwise(int32_t kind, const void *src, int32_t dtype, int64_t n, int32_t block, int32_t scale_dtype,
+                              uint8_t *codes, void *absmax, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (kind < HS_KV_INT8 || kind > HS_KV_FP4) return fail(HS_ERR_ARG, "hs_quantize_blockwise: unknown kind %d", kind);
+    if (dtype < HS_DTYPE_BF16 || dtype > HS_DTYPE_F32) return fail(HS_ERR_ARG, "hs_quantize_blockwise: unknown dtype %d", dtype);
+    if (block != 64 && block != 128 && block != 256) return fail(HS_ERR_UNSUPPORTED, "hs_quantize_blockwise: block %d (supported: 64, 128, 256)", block);
+    if (scale_dtype != HS_SCALE_F32 && scale_dtype != HS_SCALE_F16) return fail(HS_ERR_ARG, "hs_quantize_blockwise: unknown scale dtype %d", scale_dtype);
+    if (n < 0) return fail(HS_ERR_ARG, "hs_quantize_blockwise: negative n");
+    if (n == 0) return HS_OK;
+    if (!src || !codes || !absmax) return fail(HS_ERR_ARG, "hs_quantize_blockwise: NULL pointer");
+    const size_t esz = dtype == HS_DTYPE_F32 ? 4 : 2;
+    if (!aligned(src, esz) || !aligned(absmax, scale_dtype == HS_SCALE_F16 ? 2 : 4))
+        return fail(HS_ERR_ARG, "hs_quantize_blockwise: misaligned pointer");
+    if (!aligned(codes, kind == HS_KV_INT8 ? 8 : 4)) return fail(HS_ERR_ARG, "hs_quantize_blockwise: codes must be 8-byte aligned");
+    const int vec_ok = aligned(src, 16) ? 1 : 0;
+    const int64_t chunks = (n + 7) / 8;
+    // whole quantisation blocks per CTA: kQThreads*8 elements is a multiple of every supported block
+    const unsigned grid = static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads);
+    cudaStream_t s = as_stream(stream);
+    if (kind == HS_KV_INT8) quantize_flat_kernel<HS_KV_INT8><<<grid, kQThreads, 0, s>>>(src, dtype, n, block, scale_dtype, codes, absmax, vec_ok);
+    else if (kind == HS_KV_NF4) quantize_flat_kernel<HS_KV_NF4><<<grid, kQThreads, 0, s>>>(src, dtype, n, block, scale_dtype, codes, absmax, vec_ok);
+    else quantize_flat_kernel<HS_KV_FP4><<<grid, kQThreads, 0, s>>>(src, dtype, n, block, scale_dtype, codes, absmax, vec_ok);
+    return check_launch("hs_quantize_blockwise");
+}
+
+int32_t hs_dequantize_blockwise(int32_t kind, const uint8_t *codes, const void *absmax, int64_t n, int32_t block,
+                                int32_t scale_dtype, void *out, int32_t dtype, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (kind < HS_KV_INT8 || kind > HS_KV_FP4) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: unknown kind %d", kind);
+    if (dtype < HS_DTYPE_BF16 || dtype > HS_DTYPE_F32) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: unknown dtype %d", dtype);
+    if (block <= 0) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: block must be positive");
+    if (scale_dtype != HS_SCALE_F32 && scale_dtype != HS_SCALE_F16) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: unknown scale dtype %d", scale_dtype);
+    if (n < 0) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: negative n");
+    if (n == 0) return HS_OK;
+    if (!codes || !absmax || !out) return fail(HS_ERR_ARG, "hs_dequantize_blockwise: NULL pointer");
+    if (block % 8 != 0) return fail(HS_ERR_UNSUPPORTED, "hs_dequantize_blockwise: block must be a multiple of 8");
+    if (!aligned(out, dtype == HS_DTYPE_F32 ? 4 : 2) || !aligned(absmax, scale_dtype == HS_SCALE_F16 ? 2 : 4))
+        return fail(HS_ERR_ARG, "hs_dequantize_blockwise: misaligned pointer");
+    const int64_t chunks = (n + 7) / 8;
+    const unsigned grid = static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads);
+    dequantize_flat_kernel<<<grid, kQThreads, 0, as_stream(stream)>>>(kind, codes, absmax, n, block, scale_dtype, out, dtype);
+    return check_launch("hs_dequantize_blockwise");
+}
+
+int32_t hs_rope_apply(const void *x, void *out, const void *sin, const void *cos, const int32_t *positions, int64_t n_rows,
+                      int32_t n_heads, int32_t head_dim, int32_t rotary_dim, int32_t n_positions, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (n_rows < 0 || n_heads <= 0 || head_dim <= 0 || n_positions <= 0) return fail(HS_ERR_ARG, "hs_rope_apply: bad sizes");
+    if (head_dim % 8 != 0 || rotary_dim % 16 != 0 || rotary_dim < 0 || rotary_dim > head_dim)
+        return fail(HS_ERR_UNSUPPORTED, "hs_rope_apply: head_dim %% 8 and rotary_dim %% 16 must be 0, rotary_dim <= head_dim");
+    if (n_rows == 0) return HS_OK;
+    if (!x || !out || !sin || !cos || !positions) return fail(HS_ERR_ARG, "hs_rope_apply: NULL pointer");
+    if (!aligned(x, 16) || !aligned(out, 16) || !aligned(sin, 2) || !aligned(cos, 2) || !aligned(positions, 4))
+        return fail(HS_ERR_ARG, "hs_rope_apply: x and out must be 16-byte aligned");
+    if (x == out && rotary_dim > 0) return fail(HS_ERR_ARG, "hs_rope_apply: in-place rotation is not supported (a lane reads its partner half)");
+    int *err = device_error_word();
+    if (!err) return fail(HS_ERR_DEVICE, "hs_rope_apply: device error word unavailable");
+    const int64_t chunks = n_rows * n_heads * (head_dim / 8);
+    const unsigned grid = static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads);
+    rope_kernel<<<grid, kQThreads, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint16_t *>(x), reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(sin),
+        reinterpret_cast<const uint16_t *>(cos), positions, n_rows, n_heads, head_dim, rotary_dim, n_positions, err);
+    return check_launch("hs_rope_apply");
+}
+
+int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, int32_t n_tokens,
+                             const int32_t *dst_pos, const void *sin, const void *cos, int32_t rotary_dim,
+                             int32_t n_positions, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (int32_t st = validate_view(view)) return st;
+    if (n_seqs < 0 || n_tokens < 0) return fail(HS_ERR_ARG, "hs_kv_quantize_write: negative sizes");
+    if (n_seqs == 0 || n_tokens == 0) return HS_OK;
+    if (!k_new || !v_new) return fail(HS_ERR_ARG, "hs_kv_quantize_write: NULL input");
+    if (!aligned(k_new, 16) || !aligned(v_new, 16)) return fail(HS_ERR_ARG, "hs_kv_quantize_write: inputs must be 16-byte aligned");
+    if (sin != nullptr) {
+        if (!cos) return fail(HS_ERR_ARG, "hs_kv_quantize_write: sin given without cos");
+        if (rotary_dim <= 0 || rotary_dim % 16 != 0 || rotary_dim > view->head_dim || n_positions <= 0)
+            return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: rotary_dim must be a positive multiple of 16 <= head_dim");
+    }
+    ViewDev d = to_dev(view);
+    const int64_t chunks = static_cast<int64_t>(n_seqs) * n_tokens * d.n_kv_heads * (d.head_dim / 8);
+    dim3 grid(static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads), 2);
+    cudaStream_t s = as_stream(stream);
+    int *err = device_error_word();
+    if (!err) return fail(HS_ERR_DEVICE, "hs_kv_quantize_write: device error word unavailable");
+    const uint16_t *k = reinterpret_cast<const uint16_t *>(k_new), *v = reinterpret_cast<const uint16_t *>(v_new);
+    const uint16_t *sn = reinterpret_cast<const uint16_t *>(sin), *cs = reinterpret_cast<const uint16_t *>(cos);
+    switch (view->kind) {
+        case HS_KV_BF16: kv_write_kernel<HS_KV_BF16><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
+        case HS_KV_INT8: kv_write_kernel<HS_KV_INT8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
+        case HS_KV_NF4: kv_write_kernel<HS_KV_NF4><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
+        default: kv_write_kernel<HS_KV_FP4><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
+    }
+    return check_launch("hs_kv_quantize_write");
+}
+
+int32_t hs_kv_gather_dequantize(const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t out_tokens,
+                                void *k_out, void *v_out, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (int32_t st = validate_view(view)) return st;
+    if (n_seqs < 0 || out_tokens < 0) return fail(HS_ERR_ARG, "hs_kv_gather_dequantize: negative sizes");
+    if (n_seqs == 0 || out_tokens == 0) return HS_OK;
+    if (!seq_lens || !k_out || !v_out) return fail(HS_ERR_ARG, "hs_kv_gather_dequantize: NULL pointer");
+    if (!aligned(k_out, 16) || !aligned(v_out, 16)) return fail(HS_ERR_ARG, "hs_kv_gather_dequantize: outputs must be 16-byte aligned");
+    ViewDev d = to_dev(view);
+    const int64_t chunks = static_cast<int64_t>(n_seqs) * out_tokens * d.n_kv_heads * (d.head_dim / 8);
+    dim3 grid(static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads), 2);
+    kv_gather_kernel<<<grid, kQThreads, 0, as_stream(stream)>>>(d, seq_lens, n_seqs, out_tokens,
+                                                               reinterpret_cast<uint16_t *>(k_out), reinterpret_cast<uint16_t *>(v_out));
+    return check_launch("hs_kv_gather_dequantize");
+}
+
+}  // extern "C"

@@ -1,0 +1,85 @@
+"""ctypes binding of libhs_attn.so — the same C ABI (include/hs_attn.h) a Rust `-sys` crate would bind.
+
+There is no fallback: if the shared library is missing, importing this module raises.  Build it
+with ``python hyprstream_b200/csrc/build.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhs_attn.so")
+
+HS_OK = 0
+HS_ERR_ARG, HS_ERR_UNSUPPORTED, HS_ERR_DEVICE, HS_ERR_WORKSPACE = -1, -2, -3, -4
+KV_BF16, KV_INT8, KV_NF4, KV_FP4 = 0, 1, 2, 3
+SCALE_F32, SCALE_F16 = 0, 1
+DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
+DEVERR_KV_WRITE_RANGE, DEVERR_ROPE_RANGE, DEVERR_DECODE_RANGE, DEVERR_WAIT_TIMEOUT = 1, 2, 4, 8
+
+
+class HsError(RuntimeError):
+    """A non-zero status from the C ABI; `.status` holds the code (negative: argument, positive: CUDA)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"hs_attn status {status}: {message}")
+        self.status = status
+
+
+class KVView(ctypes.Structure):
+    """struct hs_kv_view."""
+    _fields_ = [
+        ("kind", c_int32), ("scale_dtype", c_int32), ("block", c_int32), ("n_kv_heads", c_int32),
+        ("head_dim", c_int32), ("page_tokens", c_int32), ("pages_per_seq", c_int32), ("reserved", c_int32),
+        ("k_pages", c_void_p), ("v_pages", c_void_p), ("k_scale_pages", c_void_p), ("v_scale_pages", c_void_p),
+    ]
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} is missing: build it with `python hyprstream_b200/csrc/build.py` (there is no CPU fallback)")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_SIGS = {
+    "hs_attn_version": (c_int32, []),
+    "hs_attn_device_check": (c_int32, [c_int32]),
+    "hs_attn_last_error": (c_char_p, []),
+    "hs_attn_take_device_error": (c_int32, [POINTER(c_int32)]),
+    "hs_quantize_blockwise": (c_int32, [c_int32, c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
+    "hs_dequantize_blockwise": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32, c_void_p]),
+    "hs_rope_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "hs_kv_quantize_write": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    "hs_kv_gather_dequantize": (c_int32, [POINTER(KVView), c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_decode_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),
+    "hs_attn_decode": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_merge_partials": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
+}
+
+
+def exported_symbols() -> list[str]:
+    """Every entry point include/hs_attn.h declares (checked against the header by the CPU tests)."""
+    return sorted(_SIGS)
+
+
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    msg = lib.hs_attn_last_error()
+    return msg.decode() if msg else ""
+
+
+def check(status: int) -> None:
+    if status != HS_OK:
+        raise HsError(status, last_error())
+
+
+def take_device_error() -> int:
+    flags = c_int32(0)
+    check(lib.hs_attn_take_device_error(ctypes.byref(flags)))
+    return flags.value

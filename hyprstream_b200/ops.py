@@ -1,0 +1,138 @@
+"""Thin functional wrappers over the C ABI: torch tensors supply device memory and the stream, nothing else.
+
+Every function launches on torch's current CUDA stream and returns without synchronising.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import ffi
+from .ffi import KVView, check, lib
+
+_DTYPES = {torch.bfloat16: ffi.DTYPE_BF16, torch.float16: ffi.DTYPE_F16, torch.float32: ffi.DTYPE_F32}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("hyprstream_b200 ops take CUDA tensors; there is no CPU path")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("hyprstream_b200 ops take contiguous tensors")
+
+
+def n_code_bytes(kind: int, n: int) -> int:
+    return n if kind == ffi.KV_INT8 else (n + 1) // 2
+
+
+def quantize_blockwise(x: torch.Tensor, kind: int, block: int = 64, scale_dtype: int = ffi.SCALE_F32
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """QuantizedTensor::from_tensor (kv_cache.rs:741-865): flat blockwise quantisation -> (codes u8, absmax)."""
+    _need_cuda(x)
+    n = x.numel()
+    nb = (n + block - 1) // block
+    # code buffers are allocated in whole 8-byte words (the kernel stores 8 codes at a time)
+    codes = torch.empty((n_code_bytes(kind, n) + 7) // 8 * 8, dtype=torch.uint8, device=x.device)
+    absmax = torch.empty(nb, dtype=torch.float16 if scale_dtype == ffi.SCALE_F16 else torch.float32, device=x.device)
+    check(lib.hs_quantize_blockwise(kind, _ptr(x), _DTYPES[x.dtype], n, block, scale_dtype, _ptr(codes), _ptr(absmax), _stream()))
+    return codes[: n_code_bytes(kind, n)], absmax
+
+
+def dequantize_blockwise(codes: torch.Tensor, absmax: torch.Tensor, kind: int, n: int, block: int = 64,
+                         dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """QuantizedTensor::to_tensor (kv_cache.rs:871-957)."""
+    _need_cuda(codes, absmax)
+    out = torch.empty(n, dtype=dtype, device=codes.device)
+    sd = ffi.SCALE_F16 if absmax.dtype == torch.float16 else ffi.SCALE_F32
+    check(lib.hs_dequantize_blockwise(kind, _ptr(codes), _ptr(absmax), n, block, sd, _ptr(out), _DTYPES[dtype], _stream()))
+    return out
+
+
+def rope_apply(x: torch.Tensor, sin: torch.Tensor, cos: torch.Tensor, positions: torch.Tensor,
+               rotary_dim: Optional[int] = None) -> torch.Tensor:
+    """RoPE::apply_rotary_pos_emb (rope.rs:206-248) on x [rows, heads, dim] bf16 with int32 positions [rows]."""
+    _need_cuda(x, sin, cos, positions)
+    rows, heads, dim = x.shape
+    rd = dim if rotary_dim is None else rotary_dim
+    out = torch.empty_like(x)
+    check(lib.hs_rope_apply(_ptr(x), _ptr(out), _ptr(sin), _ptr(cos), _ptr(positions), rows, heads, dim, rd,
+                            sin.shape[0], _stream()))
+    return out
+
+
+def kv_quantize_write(view: KVView, k_new: torch.Tensor, v_new: torch.Tensor, dst_pos: Optional[torch.Tensor],
+                      sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                      rotary_dim: int = 0) -> None:
+    """LayerKVCache::update (kv_cache.rs:1275-1496) into device-resident (quantised) storage."""
+    _need_cuda(k_new, v_new, dst_pos, sin, cos)
+    n_seqs, n_tokens = k_new.shape[0], k_new.shape[1]
+    check(lib.hs_kv_quantize_write(ctypes.byref(view), _ptr(k_new), _ptr(v_new), n_seqs, n_tokens, _ptr(dst_pos),
+                                   _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0], _stream()))
+
+
+def kv_gather_dequantize(view: KVView, seq_lens: torch.Tensor, out_tokens: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """LayerKVCache::get (kv_cache.rs:1499-1643): bf16 [n_seqs, out_tokens, Hkv, D], zero past each length."""
+    _need_cuda(seq_lens)
+    n = seq_lens.numel()
+    shape = (n, out_tokens, view.n_kv_heads, view.head_dim)
+    k = torch.empty(shape, dtype=torch.bfloat16, device=seq_lens.device)
+    v = torch.empty(shape, dtype=torch.bfloat16, device=seq_lens.device)
+    check(lib.hs_kv_gather_dequantize(ctypes.byref(view), _ptr(seq_lens), n, out_tokens, _ptr(k), _ptr(v), _stream()))
+    return k, v
+
+
+_workspaces: dict = {}
+
+
+def decode_workspace(n_seqs: int, n_q_heads: int, head_dim: int, device: torch.device) -> torch.Tensor:
+    need = lib.hs_attn_decode_workspace_bytes(n_seqs, n_q_heads, head_dim)
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def decode_attention(q: torch.Tensor, view: KVView, seq_lens: torch.Tensor, softmax_scale: Optional[float] = None,
+                     gate: Optional[torch.Tensor] = None, shard: bool = False, out: Optional[torch.Tensor] = None,
+                     workspace: Optional[torch.Tensor] = None):
+    """Fused decode attention (llama.rs:605-640,710-844,1023-1119; qwen3_5.rs:992-1059).
+
+    q bf16 [n_seqs, Hq, D], seq_lens int32 [n_seqs].  Returns bf16 [n_seqs, Hq, D], or with
+    ``shard=True`` the fp32 pair (o [n_seqs, Hq, D], lse [n_seqs, Hq]) of a KV-length shard."""
+    _need_cuda(q, seq_lens, gate)
+    n_seqs, hq, d = q.shape
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
+    ws = decode_workspace(n_seqs, hq, d, q.device) if workspace is None else workspace
+    if shard:
+        o = torch.empty(n_seqs, hq, d, dtype=torch.float32, device=q.device)
+        lse = torch.empty(n_seqs, hq, dtype=torch.float32, device=q.device)
+        check(lib.hs_attn_decode(_ptr(q), ctypes.byref(view), _ptr(seq_lens), n_seqs, hq, scale, None, None, _ptr(ws),
+                                 ws.numel(), _ptr(o), _ptr(lse), _stream()))
+        return o, lse
+    if out is None:
+        out = torch.empty_like(q)
+    check(lib.hs_attn_decode(_ptr(q), ctypes.byref(view), _ptr(seq_lens), n_seqs, hq, scale, _ptr(out), _ptr(gate), _ptr(ws),
+                             ws.numel(), None, None, _stream()))
+    return out
+
+
+def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LSE merge of partials: o_parts fp32 [P, n_seqs, Hq, D], lse_parts fp32 [P, n_seqs, Hq] -> bf16 [n_seqs, Hq, D]."""
+    _need_cuda(o_parts, lse_parts, gate)
+    p, n_seqs, hq, d = o_parts.shape
+    out = torch.empty(n_seqs, hq, d, dtype=torch.bfloat16, device=o_parts.device)
+    check(lib.hs_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), p, n_seqs * hq, d, _ptr(out), _ptr(gate), _stream()))
+    return out

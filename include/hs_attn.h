@@ -1,0 +1,159 @@
+/*
+ * hs_attn.h — C ABI of the B200-native (sm_100a) attention + quantised KV-cache kernels.
+ *
+ * This is the boundary a `hyprstream-attn-sys` crate (a sibling of the reference's
+ * crates/bitsandbytes-sys) binds.  It follows that crate's conventions
+ * (crates/bitsandbytes-sys/src/bindings.rs:10-334): one extern "C" block, plain C scalars and raw
+ * pointers, `void*` for bf16 buffers, an opaque stream handle where NULL means the default stream,
+ * and caller-owned memory — no function here allocates, frees or retains device memory
+ * (the reference allocates every buffer with libtorch and passes data_ptr(),
+ * crates/hyprstream/src/runtime/kv_cache.rs:804-839).
+ *
+ * Deliberate tightenings over bitsandbytes' `void` entry points: every function returns an int32
+ * status (0 = ok, < 0 = argument error found on the host before any launch, > 0 = a cudaError_t),
+ * `hs_attn_last_error()` returns a thread-local message, sizes are 64-bit, and every launch takes a
+ * stream.  All launches are asynchronous.  There is no CPU fallback: on a device that is not
+ * compute capability 10.x every compute entry point returns HS_ERR_DEVICE.
+ *
+ * Logical K/V geometry is the reference's: [tokens, kv_heads, head_dim], token-major, head_dim
+ * contiguous, K stored after RoPE (kv_cache.rs:1160-1164,1281-1285; architectures/llama.rs:598-607).
+ * Quantised storage keeps the reference's block geometry (a block is `block` consecutive elements
+ * of that flattened tensor, one absmax per block, bitsandbytes-sys/src/lib.rs:104-105) but lives
+ * in device memory instead of host Vec<u8> (kv_cache.rs:721-732).
+ */
+#ifndef HS_ATTN_H
+#define HS_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *hs_stream_t; /* a cudaStream_t; NULL = default stream (cf. bnb_stream_t, bindings.rs:10-13) */
+
+/* status codes */
+#define HS_OK 0
+#define HS_ERR_ARG (-1)       /* null / misaligned pointer, negative size, inconsistent geometry */
+#define HS_ERR_UNSUPPORTED (-2) /* head_dim / group / block combination with no kernel */
+#define HS_ERR_DEVICE (-3)    /* current device is not sm_100 */
+#define HS_ERR_WORKSPACE (-4) /* workspace too small */
+
+/* storage kinds: mirrors KVQuantType {None, Int8, Nf4, Fp4}
+ * (crates/hyprstream-rpc-std/schema/model.capnp:252-257; kv_cache.rs:741-788) */
+#define HS_KV_BF16 0
+#define HS_KV_INT8 1 /* u8 index into code[i] = (i-127)/127, bitsandbytes-sys/src/lib.rs:108-111 */
+#define HS_KV_NF4 2  /* lib.rs:131-148; two elements per byte, even element in the high nibble */
+#define HS_KV_FP4 3  /* lib.rs:152-169 (the reference's unsigned table) */
+
+#define HS_SCALE_F32 0 /* reference layout: f32 absmax (lib.rs:89) */
+#define HS_SCALE_F16 1 /* absmax rounded to f16 before it normalises the block */
+
+#define HS_DTYPE_BF16 0
+#define HS_DTYPE_F16 1
+#define HS_DTYPE_F32 2
+
+/*
+ * A view of one layer's K/V cache for `n_seqs` sequences.  Every sequence owns `pages_per_seq`
+ * consecutive entries of the four page-pointer tables (device arrays of device pointers).
+ * A page holds `page_tokens` tokens: K/V data [page_tokens, n_kv_heads, head_dim] (bf16, or u8
+ * codes, or packed 4-bit codes of head_dim/2 bytes per row) and scales
+ * [page_tokens, n_kv_heads, head_dim/block].  A contiguous per-sequence cache
+ * (KVStorage::FullPrecision / Quantized, kv_cache.rs:967-996) is pages_per_seq = 1 with
+ * page_tokens = its capacity; the paged pool (BlockPool, kv_cache.rs:477,515-680) is
+ * page_tokens = 256.  Token t of sequence s lives in page s*pages_per_seq + t/page_tokens.
+ */
+typedef struct hs_kv_view {
+    int32_t kind;        /* HS_KV_* */
+    int32_t scale_dtype; /* HS_SCALE_*; ignored for HS_KV_BF16 */
+    int32_t block;       /* elements per quantisation block: 64 (reference), 128 or 256; must divide head_dim */
+    int32_t n_kv_heads;
+    int32_t head_dim;    /* 64, 128 or 256 */
+    int32_t page_tokens;
+    int32_t pages_per_seq;
+    int32_t reserved;
+    void *const *k_pages;
+    void *const *v_pages;
+    void *const *k_scale_pages; /* NULL for HS_KV_BF16 */
+    void *const *v_scale_pages;
+} hs_kv_view;
+
+/* ---- library ---------------------------------------------------------------------------- */
+int32_t hs_attn_version(void);
+/* 0 if `device` (or the current device when < 0) is compute capability 10.x, else HS_ERR_DEVICE. */
+int32_t hs_attn_device_check(int32_t device);
+const char *hs_attn_last_error(void);
+/* Kernels never fault on a bad index: an out-of-range token position, page or RoPE row is skipped
+ * and recorded in a per-device word.  This call synchronises with the device, returns the recorded
+ * flags (0 = none) and clears them. */
+#define HS_DEVERR_KV_WRITE_RANGE 1 /* hs_kv_quantize_write: position outside the view's pages or the RoPE table */
+#define HS_DEVERR_ROPE_RANGE 2     /* hs_rope_apply: position outside the table; row copied unrotated */
+#define HS_DEVERR_DECODE_RANGE 4   /* hs_attn_decode: seq_len beyond the view's pages; tokens past them ignored */
+#define HS_DEVERR_WAIT_TIMEOUT 8   /* a bounded device-side wait ran out */
+int32_t hs_attn_take_device_error(int32_t *flags);
+
+/* ---- blockwise quantiser (flat tensors) --------------------------------------------------
+ * Replaces cquantize_blockwise_{bf16,fp16,fp32}[_nf4,_fp4] and cdequantize_blockwise_*
+ * (bitsandbytes-sys/src/bindings.rs:20-197; called from kv_cache.rs:771-779,823-840,882-899,929-946).
+ * `src`/`out` hold n elements of `dtype`; `codes` holds n bytes (INT8) or (n+1)/2 bytes (4-bit);
+ * `absmax` holds ceil(n/block) f32 or f16 values.  All pointers are device pointers. */
+int32_t hs_quantize_blockwise(int32_t kind, const void *src, int32_t dtype, int64_t n, int32_t block,
+                              int32_t scale_dtype, uint8_t *codes, void *absmax, hs_stream_t stream);
+int32_t hs_dequantize_blockwise(int32_t kind, const uint8_t *codes, const void *absmax, int64_t n, int32_t block,
+                                int32_t scale_dtype, void *out, int32_t dtype, hs_stream_t stream);
+
+/* ---- RoPE ---------------------------------------------------------------------------------
+ * RoPE::apply_rotary_pos_emb (runtime/rope.rs:206-248) on x [n_rows, n_heads, head_dim] bf16, out
+ * of place (out != x): half-split rotation of the first `rotary_dim` dims, every multiply, subtract
+ * and add rounded to bf16 as libtorch does; `sin`/`cos` are the caller's bf16 tables
+ * [n_positions, rotary_dim/2] (rope.rs:100-122) and `positions` int32 [n_rows]. */
+int32_t hs_rope_apply(const void *x, void *out, const void *sin, const void *cos, const int32_t *positions,
+                      int64_t n_rows, int32_t n_heads, int32_t head_dim, int32_t rotary_dim, int32_t n_positions,
+                      hs_stream_t stream);
+
+/* ---- KV quantise-on-write -----------------------------------------------------------------
+ * LayerKVCache::update (kv_cache.rs:1275-1496) for device-resident storage: appends
+ * k_new/v_new [n_seqs, n_tokens, n_kv_heads, head_dim] bf16 to the caches in `view`, sequence s at
+ * token positions dst_pos[s] .. dst_pos[s]+n_tokens-1 (dst_pos: device int32 [n_seqs]).
+ * HS_KV_BF16 copies; the quantised kinds write codes + scales bit-identical to
+ * hs_quantize_blockwise on the same rows.  If `sin` is non-NULL, K is rotated first exactly as
+ * hs_rope_apply would with position dst_pos[s]+t (V is never rotated). */
+int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs,
+                             int32_t n_tokens, const int32_t *dst_pos, const void *sin, const void *cos,
+                             int32_t rotary_dim, int32_t n_positions, hs_stream_t stream);
+
+/* LayerKVCache::get (kv_cache.rs:1499-1643) compatibility path: dequantise (or copy) tokens
+ * [0, seq_lens[s]) of every sequence into k_out/v_out [n_seqs, out_tokens, n_kv_heads, head_dim] bf16;
+ * rows past seq_lens[s] are zero-filled like the reference's right padding (llama.rs:787-813). */
+int32_t hs_kv_gather_dequantize(const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t out_tokens,
+                                void *k_out, void *v_out, hs_stream_t stream);
+
+/* ---- decode attention ---------------------------------------------------------------------
+ * One query token per sequence against its cache: the fused replacement of cache.get() + GQA
+ * expansion + compute_attention_masked for q_len == 1 (llama.rs:605-640,710-844,847-872,1023-1119)
+ * and of Qwen3_5FullAttention's decode branch (qwen3_5.rs:992-1059).
+ *   q        bf16 [n_seqs, n_q_heads, head_dim]      seq_lens  device int32 [n_seqs] (ragged; no padding)
+ *   out      bf16 [n_seqs, n_q_heads, head_dim]      gate      optional bf16, same shape: out *= sigmoid(gate)
+ *   softmax_scale  normally 1/sqrt(head_dim)
+ * Query head h reads kv head h / (n_q_heads / n_kv_heads).  The KV range is split across CTAs and the
+ * partials are merged by log-sum-exp inside the call; `workspace` (>= hs_attn_decode_workspace_bytes)
+ * is scratch for those partials.  If `o_shard`/`lse_shard` are non-NULL the call instead writes the
+ * merged, normalised fp32 result [n_seqs, n_q_heads, head_dim] and its log-sum-exp
+ * [n_seqs, n_q_heads] (natural log, scaled scores) for a KV-length shard, to be combined across
+ * GPUs with hs_attn_merge_partials; `out` may then be NULL. */
+int64_t hs_attn_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, int32_t head_dim);
+int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs,
+                       int32_t n_q_heads, float softmax_scale, void *out, const void *gate, void *workspace,
+                       int64_t workspace_bytes, float *o_shard, float *lse_shard, hs_stream_t stream);
+
+/* Log-sum-exp merge of `n_parts` partial results: o_parts fp32 [n_parts, n_rows, head_dim],
+ * lse_parts fp32 [n_parts, n_rows] (n_rows = n_seqs * n_q_heads) -> out bf16 [n_rows, head_dim],
+ * optionally times sigmoid(gate).  A part with lse = -inf contributes nothing. */
+int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows,
+                               int32_t head_dim, void *out, const void *gate, hs_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HS_ATTN_H */
