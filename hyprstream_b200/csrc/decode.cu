@@ -247,8 +247,11 @@ __global__ void decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_
         int64_t c_hi = (before + nt - 1) * n_ctas / total;
         while (c_hi > 0 && part_begin(c_hi, total, n_ctas) > before + nt - 1) --c_hi;
         while (part_begin(c_hi + 1, total, n_ctas) <= before + nt - 1) ++c_hi;
-        for (int64_t c = c_lo; c <= c_hi; ++c) M = fmaxf(M, lse_part[(c + r) * n_q_heads + h]);
+        // CTAs with an empty tile range (more CTAs than tiles) wrote nothing: skip their slots
+        for (int64_t c = c_lo; c <= c_hi; ++c)
+            if (part_begin(c, total, n_ctas) < part_begin(c + 1, total, n_ctas)) M = fmaxf(M, lse_part[(c + r) * n_q_heads + h]);
         for (int64_t c = c_lo; c <= c_hi; ++c) {
+            if (part_begin(c, total, n_ctas) >= part_begin(c + 1, total, n_ctas)) continue;
             const int64_t prow = (c + r) * n_q_heads + h;
             const float ls = lse_part[prow];
             const float wgt = ls == -INFINITY ? 0.0f : __expf(ls - M);
@@ -375,11 +378,13 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     cudaStream_t s = as_stream(stream);
     const uint16_t *qp = reinterpret_cast<const uint16_t *>(q);
     int32_t st;
+    prof_begin(s);
     switch (view->kind) {
         case HS_KV_BF16: st = dispatch_d<HS_KV_BF16>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
         case HS_KV_INT8: st = dispatch_d<HS_KV_INT8>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
         default: st = dispatch_d<kKind4Bit>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
     }
+    prof_end(s);
     if (st != HS_OK) return st;
     if (int32_t e = check_launch("hs_attn_decode")) return e;
     dim3 mgrid(n_seqs, n_q_heads);

@@ -26,6 +26,9 @@ static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<u
 static inline cudaStream_t as_stream(hs_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int32_t validate_view(const hs_kv_view *v);
+// Bracket the dominant kernel of an entry point; records CUDA events only while profiling is on.
+void prof_begin(cudaStream_t s);
+void prof_end(cudaStream_t s);
 
 // Kernel-argument copy of hs_kv_view (passed by value).
 struct ViewDev {

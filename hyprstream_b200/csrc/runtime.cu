@@ -69,6 +69,21 @@ int32_t check_launch(const char *what) {
     return HS_OK;
 }
 
+// ---- optional per-kernel timing (off by default) -------------------------------------------------
+static bool g_prof_on = false;
+static bool g_prof_valid = false;
+static cudaEvent_t g_prof_ev[2] = {nullptr, nullptr};
+
+void prof_begin(cudaStream_t s) {
+    if (g_prof_on) cudaEventRecord(g_prof_ev[0], s);
+}
+void prof_end(cudaStream_t s) {
+    if (g_prof_on) {
+        cudaEventRecord(g_prof_ev[1], s);
+        g_prof_valid = true;
+    }
+}
+
 int32_t validate_view(const hs_kv_view *v) {
     if (!v) return fail(HS_ERR_ARG, "kv view is NULL");
     if (v->kind < HS_KV_BF16 || v->kind > HS_KV_FP4) return fail(HS_ERR_ARG, "kv view: unknown kind %d", v->kind);
@@ -101,6 +116,28 @@ int32_t hs_attn_device_check(int32_t device) {
 }
 
 const char *hs_attn_last_error(void) { return hs::g_err; }
+
+int32_t hs_attn_set_profiling(int32_t on) {
+    if (int32_t st = hs::check_device()) return st;
+    if (on && !hs::g_prof_ev[0]) {
+        for (int i = 0; i < 2; ++i) {
+            cudaError_t e = cudaEventCreate(&hs::g_prof_ev[i]);
+            if (e != cudaSuccess) return hs::fail(static_cast<int32_t>(e), "hs_attn_set_profiling: %s", cudaGetErrorString(e));
+        }
+    }
+    hs::g_prof_on = on != 0;
+    hs::g_prof_valid = false;
+    return HS_OK;
+}
+
+int32_t hs_attn_last_kernel_ms(float *ms) {
+    if (!ms) return hs::fail(HS_ERR_ARG, "hs_attn_last_kernel_ms: NULL output");
+    if (!hs::g_prof_valid) return hs::fail(HS_ERR_ARG, "hs_attn_last_kernel_ms: no profiled launch since profiling was switched on");
+    cudaError_t e = cudaEventSynchronize(hs::g_prof_ev[1]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(ms, hs::g_prof_ev[0], hs::g_prof_ev[1]);
+    if (e != cudaSuccess) return hs::fail(static_cast<int32_t>(e), "hs_attn_last_kernel_ms: %s", cudaGetErrorString(e));
+    return HS_OK;
+}
 
 int32_t hs_attn_take_device_error(int32_t *flags) {
     if (!flags) return hs::fail(HS_ERR_ARG, "hs_attn_take_device_error: NULL output");

@@ -47,6 +47,8 @@ _SIGS = {
     "hs_attn_device_check": (c_int32, [c_int32]),
     "hs_attn_last_error": (c_char_p, []),
     "hs_attn_take_device_error": (c_int32, [POINTER(c_int32)]),
+    "hs_attn_set_profiling": (c_int32, [c_int32]),
+    "hs_attn_last_kernel_ms": (c_int32, [POINTER(c_float)]),
     "hs_quantize_blockwise": (c_int32, [c_int32, c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "hs_dequantize_blockwise": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32, c_void_p]),
     "hs_rope_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
@@ -83,3 +85,13 @@ def take_device_error() -> int:
     flags = c_int32(0)
     check(lib.hs_attn_take_device_error(ctypes.byref(flags)))
     return flags.value
+
+
+def set_profiling(on: bool) -> None:
+    check(lib.hs_attn_set_profiling(1 if on else 0))
+
+
+def last_kernel_ms() -> float:
+    ms = c_float(0.0)
+    check(lib.hs_attn_last_kernel_ms(ctypes.byref(ms)))
+    return ms.value

@@ -17,6 +17,7 @@ torch is used only to own device memory.
 from __future__ import annotations
 
 import enum
+import math
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -242,9 +243,21 @@ def make_view(caches: Sequence[LayerKVCache]) -> Tuple[KVView, list]:
     rows = [c.page_rows() for c in caches]
     page_tokens = {pt for pt, _ in rows}
     if c0.pool is None:
-        # contiguous caches: one page per sequence; the view's page_tokens is the smallest capacity
-        pt = min(page_tokens)
-        pps = 1
+        # contiguous caches of different capacities: cut each into pages of gcd(capacities) tokens
+        pt = 0
+        for cap in page_tokens:
+            pt = math.gcd(pt, cap)
+        rb = _row_bytes(c0.kind, c0.n_kv_heads, c0.head_dim)
+        sb = c0.n_kv_heads * (c0.head_dim // c0.block) * (2 if c0.scale_dtype == ffi.SCALE_F16 else 4)
+        cut = []
+        for cap, pages in rows:
+            ptrs = []
+            for (k, v, ks, vs) in pages:
+                for j in range(cap // pt):
+                    ptrs.append((k + j * pt * rb, v + j * pt * rb, ks + j * pt * sb if ks else 0, vs + j * pt * sb if vs else 0))
+            cut.append((pt, ptrs))
+        rows = cut
+        pps = max(1, max(len(p) for _, p in rows))
     else:
         if len(page_tokens) != 1:
             raise ValueError("paged caches of one batch must share a page size")

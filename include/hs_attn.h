@@ -93,6 +93,12 @@ const char *hs_attn_last_error(void);
 #define HS_DEVERR_WAIT_TIMEOUT 8   /* a bounded device-side wait ran out */
 int32_t hs_attn_take_device_error(int32_t *flags);
 
+/* Tracing hook: while profiling is on, each compute entry point brackets its dominant kernel with two
+ * CUDA events on the launch stream; hs_attn_last_kernel_ms() waits for the latest pair and returns the
+ * elapsed device time.  Off by default; one set of events per process, so profile one stream at a time. */
+int32_t hs_attn_set_profiling(int32_t on);
+int32_t hs_attn_last_kernel_ms(float *ms);
+
 /* ---- blockwise quantiser (flat tensors) --------------------------------------------------
  * Replaces cquantize_blockwise_{bf16,fp16,fp32}[_nf4,_fp4] and cdequantize_blockwise_*
  * (bitsandbytes-sys/src/bindings.rs:20-197; called from kv_cache.rs:771-779,823-840,882-899,929-946).
