@@ -79,8 +79,14 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 
     const int kvh = blockIdx.y, H = view.n_kv_heads;
     const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
+    const int cap = view.page_tokens * view.pages_per_seq;  // lengths beyond the view's pages are cut (and recorded)
     int64_t total = 0;
-    for (int r = 0; r < n_seqs; ++r) total += ceil_div_i(max(seq_lens[r], 0), kDecTile);
+    bool over = false;
+    for (int r = 0; r < n_seqs; ++r) {
+        over |= seq_lens[r] > cap;
+        total += ceil_div_i(min(max(seq_lens[r], 0), cap), kDecTile);
+    }
+    if (over && threadIdx.x == 0 && cta == 0 && kvh == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
     const int64_t t_begin = part_begin(cta, total, n_ctas), t_end = part_begin(cta + 1, total, n_ctas);
     if (t_begin >= t_end) return;
 
@@ -93,19 +99,14 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 
     int64_t acc_tiles = 0;
     for (int r = 0; r < n_seqs && acc_tiles < t_end; ++r) {
-        const int L = max(seq_lens[r], 0);
+        const int L = min(max(seq_lens[r], 0), cap);
         const int nt = ceil_div_i(L, kDecTile);
         const int64_t lo = max(t_begin, acc_tiles), hi = min(t_end, acc_tiles + nt);
         const int64_t seq_tile0 = acc_tiles;
         acc_tiles += nt;
         if (lo >= hi) continue;
         const int tok_begin = static_cast<int>(lo - seq_tile0) * kDecTile;
-        int tok_end = min(L, static_cast<int>(hi - seq_tile0) * kDecTile);
-        const int cap = view.page_tokens * view.pages_per_seq;
-        if (tok_end > cap) {  // recorded; tokens past the view's pages are ignored
-            if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
-            tok_end = cap;
-        }
+        const int tok_end = min(L, static_cast<int>(hi - seq_tile0) * kDecTile);
         // query of this group's heads, packed bf16 pairs
         uint32_t qw[G][EPL / 2];
 #pragma unroll
@@ -227,16 +228,16 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 // output element.  The slot range of a sequence is recomputed from seq_lens with the same partition
 // arithmetic the decode kernel used.
 __global__ void decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_heads, int D, int n_ctas,
-                                    int tile, const float *__restrict__ o_part, const float *__restrict__ lse_part,
+                                    int tile, int cap, const float *__restrict__ o_part, const float *__restrict__ lse_part,
                                     uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, float *__restrict__ o_shard,
                                     float *__restrict__ lse_shard) {
     const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     int64_t total = 0, before = 0;
     for (int i = 0; i < n_seqs; ++i) {
         if (i == r) before = total;
-        total += ceil_div_i(max(seq_lens[i], 0), tile);
+        total += ceil_div_i(min(max(seq_lens[i], 0), cap), tile);
     }
-    const int64_t nt = ceil_div_i(max(seq_lens[r], 0), tile);
+    const int64_t nt = ceil_div_i(min(max(seq_lens[r], 0), cap), tile);
     const int64_t row = static_cast<int64_t>(r) * n_q_heads + h;
     float num = 0.0f, den = 0.0f, M = -INFINITY;
     if (nt > 0) {
@@ -296,6 +297,10 @@ __global__ void merge_parts_kernel(const float *__restrict__ o_parts, const floa
 }
 
 static int decode_max_ctas() { return 4 * sm_count(); }
+
+// decode_tc.cu: tensor-core kernel for the int8 / head_dim 128 / 8 kv heads / group 4 shape
+int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
+                           float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out);
 
 template <int KIND, int D, int G>
 static int32_t launch_generic(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
@@ -378,19 +383,26 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     cudaStream_t s = as_stream(stream);
     const uint16_t *qp = reinterpret_cast<const uint16_t *>(q);
     int32_t st;
+    int tile = kDecTile, tc_ctas = 0;
     prof_begin(s);
-    switch (view->kind) {
-        case HS_KV_BF16: st = dispatch_d<HS_KV_BF16>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
-        case HS_KV_INT8: st = dispatch_d<HS_KV_INT8>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
-        default: st = dispatch_d<kKind4Bit>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+    st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas);
+    if (st == HS_OK && tc_ctas > 0) {
+        n_ctas = tc_ctas;
+        tile = 32;
+    } else if (st == HS_OK) {
+        switch (view->kind) {
+            case HS_KV_BF16: st = dispatch_d<HS_KV_BF16>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+            case HS_KV_INT8: st = dispatch_d<HS_KV_INT8>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+            default: st = dispatch_d<kKind4Bit>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
+        }
     }
     prof_end(s);
     if (st != HS_OK) return st;
     if (int32_t e = check_launch("hs_attn_decode")) return e;
     dim3 mgrid(n_seqs, n_q_heads);
-    decode_merge_kernel<<<mgrid, D, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, kDecTile, o_part, lse_part,
-                                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard,
-                                            lse_shard);
+    decode_merge_kernel<<<mgrid, D, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, tile, v.page_tokens * v.pages_per_seq, o_part,
+                                            lse_part, reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate),
+                                            o_shard, lse_shard);
     return check_launch("hs_attn_decode (merge)");
 }
 
