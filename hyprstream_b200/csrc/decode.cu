@@ -224,54 +224,95 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     }
 }
 
-// Merge the split-KV partials of every (sequence, head).  One CTA per (sequence, head), one thread per
-// output element.  The slot range of a sequence is recomputed from seq_lens with the same partition
-// arithmetic the decode kernel used.
-__global__ void decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_heads, int D, int n_ctas,
-                                    int tile, int cap, const float *__restrict__ o_part, const float *__restrict__ lse_part,
-                                    uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, float *__restrict__ o_shard,
-                                    float *__restrict__ lse_shard) {
-    const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    int64_t total = 0, before = 0;
-    for (int i = 0; i < n_seqs; ++i) {
-        if (i == r) before = total;
-        total += ceil_div_i(min(max(seq_lens[i], 0), cap), tile);
+// Merge the split-KV partials of one sequence, kMergeHeads query heads per CTA.  The slot range of the
+// sequence is recomputed from seq_lens with the same partition arithmetic the decode kernel used: CTA c
+// and sequence r share slots (c + r) * ppp + k, k < ppp (ppp = partials each pair writes).
+constexpr int kMergeThreads = 256;
+constexpr int kMergeHeads = 4;
+constexpr int kMergeMaxParts = 1280;  // >= decode_max_ctas() * kMaxPartsPerPair on a 148-SM part (checked on the host)
+__global__ void __launch_bounds__(kMergeThreads)
+decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_heads, int D, int n_ctas, int tile, int cap,
+                    int ppp, const float *__restrict__ o_part, const float *__restrict__ lse_part, uint16_t *__restrict__ out,
+                    const uint16_t *__restrict__ gate, float *__restrict__ o_shard, float *__restrict__ lse_shard) {
+    __shared__ int s_slot[kMergeMaxParts];
+    __shared__ float s_w[kMergeMaxParts * kMergeHeads];
+    __shared__ float s_den[kMergeHeads], s_max[kMergeHeads];
+    __shared__ int s_nparts;
+    const int r = blockIdx.x, h0 = blockIdx.y * kMergeHeads, lane = threadIdx.x & 31;
+    const int nh = min(kMergeHeads, n_q_heads - h0);
+    // every warp computes the tile prefix redundantly, one coalesced load per 32 sequences
+    long long total = 0, before = 0;
+    for (int base = 0; base < n_seqs; base += 32) {
+        const int i = base + lane;
+        const int t = i < n_seqs ? ceil_div_i(min(max(seq_lens[i], 0), cap), tile) : 0;
+        total += t;
+        before += i < r ? t : 0;
     }
-    const int64_t nt = ceil_div_i(min(max(seq_lens[r], 0), cap), tile);
-    const int64_t row = static_cast<int64_t>(r) * n_q_heads + h;
-    float num = 0.0f, den = 0.0f, M = -INFINITY;
-    if (nt > 0) {
-        // first / last CTA whose tile range overlaps [before, before + nt)
-        int64_t c_lo = before * n_ctas / total;
-        while (c_lo > 0 && part_begin(c_lo, total, n_ctas) > before) --c_lo;
-        while (part_begin(c_lo + 1, total, n_ctas) <= before) ++c_lo;
-        int64_t c_hi = (before + nt - 1) * n_ctas / total;
-        while (c_hi > 0 && part_begin(c_hi, total, n_ctas) > before + nt - 1) --c_hi;
-        while (part_begin(c_hi + 1, total, n_ctas) <= before + nt - 1) ++c_hi;
-        // CTAs with an empty tile range (more CTAs than tiles) wrote nothing: skip their slots
-        for (int64_t c = c_lo; c <= c_hi; ++c)
-            if (part_begin(c, total, n_ctas) < part_begin(c + 1, total, n_ctas)) M = fmaxf(M, lse_part[(c + r) * n_q_heads + h]);
-        for (int64_t c = c_lo; c <= c_hi; ++c) {
-            if (part_begin(c, total, n_ctas) >= part_begin(c + 1, total, n_ctas)) continue;
-            const int64_t prow = (c + r) * n_q_heads + h;
-            const float ls = lse_part[prow];
-            const float wgt = ls == -INFINITY ? 0.0f : __expf(ls - M);
-            num = fmaf(wgt, o_part[prow * D + d], num);
-            den += wgt;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        total += __shfl_xor_sync(0xffffffffu, total, off);
+        before += __shfl_xor_sync(0xffffffffu, before, off);
+    }
+    const long long nt = ceil_div_i(min(max(seq_lens[r], 0), cap), tile);
+    if (threadIdx.x == 0) {
+        // CTAs whose tile range overlaps [before, before + nt); a CTA with an empty range wrote nothing
+        int n = 0;
+        if (nt > 0) {
+            long long c = before * n_ctas / total;
+            while (c > 0 && part_begin(c, total, n_ctas) > before) --c;
+            while (part_begin(c + 1, total, n_ctas) <= before) ++c;
+            for (; c < n_ctas && part_begin(c, total, n_ctas) < before + nt; ++c) {
+                if (part_begin(c, total, n_ctas) >= part_begin(c + 1, total, n_ctas)) continue;
+                for (int k = 0; k < ppp && n < kMergeMaxParts; ++k) s_slot[n++] = static_cast<int>((c + r) * ppp + k);
+            }
         }
+        s_nparts = n;
     }
-    const float o = den > 0.0f ? num / den : 0.0f;
-    if (o_shard != nullptr) {
-        o_shard[row * D + d] = o;
-        if (d == 0) lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
-        return;
+    __syncthreads();
+    const int np = s_nparts;
+    for (int i = threadIdx.x; i < np * nh; i += kMergeThreads) {
+        const int pi = i / nh, hh = i - pi * nh;
+        s_w[pi * kMergeHeads + hh] = lse_part[static_cast<int64_t>(s_slot[pi]) * n_q_heads + h0 + hh];
     }
-    float res = o;
-    if (gate != nullptr) {
-        const float gv = bf16_bits_to_f32(gate[row * D + d]);
-        res = bf16_round(o) * bf16_round(1.0f / (1.0f + __expf(-gv)));  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
+    __syncthreads();
+    if (threadIdx.x < nh) {
+        float M = -INFINITY;
+        for (int pi = 0; pi < np; ++pi) M = fmaxf(M, s_w[pi * kMergeHeads + threadIdx.x]);
+        s_max[threadIdx.x] = M;
     }
-    out[row * D + d] = f32_to_bf16_bits(res);
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * nh; i += kMergeThreads) {
+        const int pi = i / nh, hh = i - pi * nh;
+        const float ls = s_w[pi * kMergeHeads + hh];
+        s_w[pi * kMergeHeads + hh] = ls == -INFINITY ? 0.0f : __expf(ls - s_max[hh]);
+    }
+    __syncthreads();
+    if (threadIdx.x < nh) {
+        float den = 0.0f;
+        for (int pi = 0; pi < np; ++pi) den += s_w[pi * kMergeHeads + threadIdx.x];
+        s_den[threadIdx.x] = den;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nh * D; idx += kMergeThreads) {
+        const int hh = idx / D, d = idx - hh * D;
+        const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
+        float num = 0.0f;
+        for (int pi = 0; pi < np; ++pi)
+            num = fmaf(s_w[pi * kMergeHeads + hh], o_part[(static_cast<int64_t>(s_slot[pi]) * n_q_heads + h0 + hh) * D + d], num);
+        const float den = s_den[hh];
+        const float o = den > 0.0f ? num / den : 0.0f;
+        if (o_shard != nullptr) {
+            o_shard[row * D + d] = o;
+            if (d == 0) lse_shard[row] = den > 0.0f ? s_max[hh] + __logf(den) : -INFINITY;
+            continue;
+        }
+        float res = o;
+        if (gate != nullptr) {
+            const float gv = bf16_bits_to_f32(gate[row * D + d]);
+            res = bf16_round(o) * bf16_round(1.0f / (1.0f + __expf(-gv)));  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
+        }
+        out[row * D + d] = f32_to_bf16_bits(res);
+    }
 }
 
 // Merge of externally produced partials (KV-length shards from several GPUs, or a caller's own split).
@@ -297,6 +338,7 @@ __global__ void merge_parts_kernel(const float *__restrict__ o_parts, const floa
 }
 
 static int decode_max_ctas() { return 4 * sm_count(); }
+constexpr int kMaxPartsPerPair = 2;
 
 // decode_tc.cu: tensor-core kernel for the int8 / head_dim 128 / 8 kv heads / group 4 shape
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
@@ -350,7 +392,7 @@ extern "C" {
 
 int64_t hs_attn_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, int32_t head_dim) {
     if (n_seqs < 0 || n_q_heads <= 0 || head_dim <= 0) return HS_ERR_ARG;
-    const int64_t slots = static_cast<int64_t>(decode_max_ctas()) + n_seqs;
+    const int64_t slots = (static_cast<int64_t>(decode_max_ctas()) + n_seqs) * kMaxPartsPerPair;
     return slots * n_q_heads * (static_cast<int64_t>(head_dim) + 1) * 4;
 }
 
@@ -376,19 +418,19 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     ViewDev v = to_dev(view);
     int n_ctas = (3 * sm_count() + v.n_kv_heads - 1) / v.n_kv_heads;
     n_ctas = max(1, min(n_ctas, decode_max_ctas()));
-    const int64_t slots = static_cast<int64_t>(decode_max_ctas()) + n_seqs;
+    const int64_t slots = (static_cast<int64_t>(decode_max_ctas()) + n_seqs) * kMaxPartsPerPair;
     float *o_part = reinterpret_cast<float *>(workspace);
     float *lse_part = o_part + slots * n_q_heads * D;
     const float scale_log2 = softmax_scale * 1.4426950408889634f;
     cudaStream_t s = as_stream(stream);
     const uint16_t *qp = reinterpret_cast<const uint16_t *>(q);
     int32_t st;
-    int tile = kDecTile, tc_ctas = 0;
+    int tile = kDecTile, tc_ctas = 0, ppp = 1;
     prof_begin(s);
     st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas);
     if (st == HS_OK && tc_ctas > 0) {
         n_ctas = tc_ctas;
-        tile = 32;
+        tile = 16;
     } else if (st == HS_OK) {
         switch (view->kind) {
             case HS_KV_BF16: st = dispatch_d<HS_KV_BF16>(D, G, v, qp, seq_lens, n_seqs, n_q_heads, scale_log2, o_part, lse_part, err, n_ctas, s); break;
@@ -399,8 +441,9 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     prof_end(s);
     if (st != HS_OK) return st;
     if (int32_t e = check_launch("hs_attn_decode")) return e;
-    dim3 mgrid(n_seqs, n_q_heads);
-    decode_merge_kernel<<<mgrid, D, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, tile, v.page_tokens * v.pages_per_seq, o_part,
+    if (static_cast<int64_t>(n_ctas) * ppp > kMergeMaxParts) return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode: %d partial slots exceed the merge kernel's table", n_ctas * ppp);
+    dim3 mgrid(n_seqs, (n_q_heads + kMergeHeads - 1) / kMergeHeads);
+    decode_merge_kernel<<<mgrid, kMergeThreads, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, tile, v.page_tokens * v.pages_per_seq, ppp, o_part,
                                             lse_part, reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate),
                                             o_shard, lse_shard);
     return check_launch("hs_attn_decode (merge)");

@@ -1,14 +1,19 @@
-// Int8-KV decode attention for head_dim 128: a persistent, warp-specialised kernel.
+// Int8-KV decode attention for head_dim 128, 8 kv heads, 4 query heads per kv head: a persistent,
+// warp-specialised kernel.
 //
-//   * one CTA per SM; the tokens of ALL sequences, cut into 32-token tiles, are divided evenly over the
-//     CTAs (flat split-KV), so ragged batches balance without padding;
-//   * a producer warp streams each tile of the [tokens, kv_heads, 128] u8 cache into a 3-stage shared
-//     memory ring with bulk async copies (cp.async.bulk, one 16-byte-aligned row of all kv heads per
-//     lane, completion on an mbarrier) — the HBM reads are whole contiguous rows;
-//   * consumer warp h owns kv head h and the G query heads that share it: codes are widened to fp16 with
-//     byte permutes (exactly: 1024 + code, minus 1151), q.K^T and P.V run on the tensor cores
-//     (mma.sync m16n8k16, fp32 accumulate) with the block scales applied to the fp32 scores (K) and
-//     folded into P (V); online softmax in the exp2 domain, quad shuffles for the row maximum;
+//   * two CTAs per SM (while one winds up a sequence or starts the next, the other keeps streaming); the
+//     tokens of ALL sequences, cut into 16-token tiles, are divided evenly over the CTAs (flat split-KV),
+//     so ragged batches balance without padding;
+//   * each tile of the [tokens, kv_heads, 128] u8 cache is streamed into a 3-stage shared memory ring with
+//     four bulk async copies (cp.async.bulk: K codes, V codes, K scales, V scales; each a single contiguous
+//     run of 16 token rows, completion on an mbarrier), issued two tiles ahead by lanes 0-3 of warp 0;
+//   * 8 warps: warp h owns kv head h and the 4 query heads that share it.
+//     Codes are widened to fp16 with byte permutes only (the bytes become 1024 + code exactly); the
+//     constant 1151 = 1024 + 127 is removed algebraically: q.(1024+c) - 1151*sum(q) and
+//     p'.(1024+c) - 1151*sum(p').  q.K^T runs as mma.sync m16n8k16 with the query heads as rows, P.V with
+//     the head_dim as rows (so P's accumulator registers are reused unchanged as the B operand and the
+//     output accumulators are dense); fp32 accumulation; block scales applied to the fp32 scores (K) and
+//     folded into P (V); online softmax in the exp2 domain with quad shuffles;
 //   * each (CTA, sequence) pair writes one normalised partial + log-sum-exp; the merge kernel combines.
 //
 // Replaces, for the q_len == 1 path, cache.get() (full-history dequantise, kv_cache.rs:1499-1643) + GQA
@@ -22,9 +27,13 @@
 
 namespace hs {
 
-constexpr int kTcTile = 32;    // tokens per stage
+constexpr int kTcTile = 16;    // tokens per stage
 constexpr int kTcStages = 3;
-constexpr int kTcRowPad = 64;  // bytes of padding per token row in shared memory (bank spread)
+constexpr int kTcHkv = 8;
+constexpr int kTcG = 4;
+constexpr int kTcConsumers = kTcHkv;  // every warp consumes; warp 0 also issues the copies
+constexpr int kTcThreads = kTcConsumers * 32;
+constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory
 constexpr long long kTcWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -66,136 +75,202 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    // rows 8..15 of A are never used (a1 = a3 = 0): at most 8 query heads share a kv head
+// D += A.B, m16n8k16, fp16 operands, fp32 accumulate.  A rows 8..15 unused (a1 = a3 = 0).
+__device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
-// two u8 codes (bytes `lo_sel` of w) -> fp16x2 of (code - 127): bytes become 1024 + code exactly, then - 1151
-__device__ __forceinline__ uint32_t codes_to_h2(uint32_t w, uint32_t selector) {
-    uint32_t h = __byte_perm(w, 0x64646464u, selector);
-    uint32_t r;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(h), "r"(0x647F647Fu));
-    return r;
+__device__ __forceinline__ void mma_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// two u8 codes (the bytes `selector` picks from w) -> fp16x2 of (1024 + code), exact
+__device__ __forceinline__ uint32_t codes_biased_h2(uint32_t w, uint32_t selector) { return __byte_perm(w, 0x64646464u, selector); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
 }
+__device__ __forceinline__ float h2_sum(uint32_t w) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    return f.x + f.y;
+}
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-template <int HKV, int BPR, bool SF16>
+template <int BPR, bool SF16>
 struct TcLayout {
-    static constexpr int kRowG = HKV * 128;            // bytes of one token row in global memory
-    static constexpr int kRowS = kRowG + kTcRowPad;    // ... in shared memory
-    static constexpr int kSRow = HKV * BPR * (SF16 ? 2 : 4);  // scale bytes per token
+    static constexpr int kRow = kTcHkv * 128;                    // bytes of one token row of codes
+    static constexpr int kSRow = kTcHkv * BPR * (SF16 ? 2 : 4);  // scale bytes per token
     static constexpr int kKOff = 0;
-    static constexpr int kVOff = kTcTile * kRowS;
-    static constexpr int kKsOff = 2 * kTcTile * kRowS;
+    static constexpr int kVOff = kTcTile * kRow;
+    static constexpr int kKsOff = 2 * kTcTile * kRow;
     static constexpr int kVsOff = kKsOff + kTcTile * kSRow;
     static constexpr int kStage = (kVsOff + kTcTile * kSRow + 127) / 128 * 128;
     static constexpr int kBarOff = kTcStages * kStage;
-    static constexpr int kTotal = kBarOff + 2 * kTcStages * 8 + 16;
-    static constexpr uint32_t kTxBytes = 2u * kTcTile * kRowG + 2u * kTcTile * kSRow;
+    static constexpr int kPrefOff = kBarOff + 2 * kTcStages * 8 + 16;  // int tile-count prefix [kTcMaxSeqs + 1]
+    static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
+    static constexpr int kTotal = kLenOff + kTcMaxSeqs * 4;
+    static constexpr uint32_t kTxBytes = 2u * kTcTile * kRow + 2u * kTcTile * kSRow;
 };
 
-template <int HKV, int G, int BPR, bool SF16>
-__global__ void __launch_bounds__((HKV + 1) * 32, 1)
+#ifdef HS_TC_TIMING  // diagnostic build only: per-CTA timestamps (ns) written to a harness-owned buffer
+__constant__ unsigned long long *g_tc_timing;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define HS_TC_STAMP(slot) do { if (g_tc_timing && lane == 0 && (slot) < 16) g_tc_timing[(blockIdx.x * 20 + warp) * 16 + (slot)] = gtime(); } while (0)
+#else
+#define HS_TC_STAMP(slot) do {} while (0)
+#endif
+
+template <int BPR, bool SF16>
+__global__ void __launch_bounds__(kTcThreads, 2)
 decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_t *__restrict__ seq_lens, int n_seqs,
                       int n_q_heads, float kmul, float *__restrict__ o_part, float *__restrict__ lse_part,
                       int *__restrict__ err) {
-    using LT = TcLayout<HKV, BPR, SF16>;
+    using LT = TcLayout<BPR, SF16>;
     extern __shared__ __align__(128) unsigned char smem[];
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + LT::kBarOff + 2 * kTcStages * 8);
+    int *s_pref = reinterpret_cast<int *>(smem + LT::kPrefOff);
+    int *s_len = reinterpret_cast<int *>(smem + LT::kLenOff);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_full = smem_base + LT::kBarOff, bar_empty = bar_full + kTcStages * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cap = view.page_tokens * view.pages_per_seq;
 
+    HS_TC_STAMP(0);
+    // ---- tile counts of all sequences (one coalesced pass), exclusive prefix by warp 0 ----
+    bool over = false;
+    for (int i = threadIdx.x; i < n_seqs; i += kTcThreads) {
+        const int L = seq_lens[i];
+        over |= L > cap;
+        s_len[i] = min(max(L, 0), cap);
+        s_pref[i + 1] = (s_len[i] + kTcTile - 1) / kTcTile;
+    }
+    if (over && blockIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, HKV);
+            mbar_init(bar_empty + 8 * s, kTcConsumers);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-
-    const int cap = view.page_tokens * view.pages_per_seq;
-    const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
-    int64_t total = 0;
-    bool over = false;
-    for (int r = 0; r < n_seqs; ++r) {
-        const int L = seq_lens[r];
-        over |= L > cap;
-        total += (min(max(L, 0), cap) + kTcTile - 1) / kTcTile;
-    }
-    if (over && threadIdx.x == 0 && cta == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
-    const int64_t t_begin = part_begin(cta, total, n_ctas), t_end = part_begin(cta + 1, total, n_ctas);
-    if (t_begin >= t_end) return;
-
-    if (warp == HKV) {
-        // ================================ producer warp ================================
-        int it = 0;
-        int64_t acc = 0;
-        bool ok = true;
-        for (int r = 0; r < n_seqs && acc < t_end && ok; ++r) {
-            const int L = min(max(seq_lens[r], 0), cap);
-            const int nt = (L + kTcTile - 1) / kTcTile;
-            const int64_t lo = max(t_begin, acc), hi = min(t_end, acc + nt), base = acc;
-            acc += nt;
-            for (int64_t tile = lo - base; tile < hi - base && ok; ++tile, ++it) {
-                const int stage = it % kTcStages;
-                if (it >= kTcStages) ok = mbar_wait(bar_empty + 8 * stage, ((it / kTcStages) - 1) & 1, abort_flag);
-                if (!ok) break;
-                const int t0 = static_cast<int>(tile) * kTcTile;
-                const int page = t0 / view.page_tokens;
-                const int64_t pidx = static_cast<int64_t>(r) * view.pages_per_seq + page;
-                const int in_page = t0 - page * view.page_tokens;
-                const uint32_t full = bar_full + 8 * stage;
-                if (lane == 0) mbar_expect_tx(full, LT::kTxBytes);
-                __syncwarp();
-                const uint32_t sbase = smem_base + stage * LT::kStage;
-                const unsigned char *kp = reinterpret_cast<const unsigned char *>(view.k_pages[pidx]);
-                const unsigned char *vp = reinterpret_cast<const unsigned char *>(view.v_pages[pidx]);
-                bulk_g2s(sbase + LT::kKOff + lane * LT::kRowS, kp + static_cast<int64_t>(in_page + lane) * LT::kRowG, LT::kRowG, full);
-                bulk_g2s(sbase + LT::kVOff + lane * LT::kRowS, vp + static_cast<int64_t>(in_page + lane) * LT::kRowG, LT::kRowG, full);
-                if (lane == 0)
-                    bulk_g2s(sbase + LT::kKsOff, reinterpret_cast<const unsigned char *>(view.k_scale_pages[pidx]) + static_cast<int64_t>(in_page) * LT::kSRow,
-                             kTcTile * LT::kSRow, full);
-                if (lane == 1)
-                    bulk_g2s(sbase + LT::kVsOff, reinterpret_cast<const unsigned char *>(view.v_scale_pages[pidx]) + static_cast<int64_t>(in_page) * LT::kSRow,
-                             kTcTile * LT::kSRow, full);
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < n_seqs; base += 32) {
+            const int i = base + lane;
+            const int v = i < n_seqs ? s_pref[i + 1] : 0;
+            int inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += t;
             }
+            if (i < n_seqs) s_pref[i + 1] = carry + inc;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
         }
-        if (!ok) {
-            // give the copies already in flight a bounded chance to land before the CTA's shared memory is released
-            const long long t0c = clock64();
-            while (clock64() - t0c < 2000000LL) {}
-            if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
-        }
-        return;
+        if (lane == 0) s_pref[0] = 0;
     }
+    __syncthreads();
+    const int64_t total = s_pref[n_seqs];
+    const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
+    const int t_begin = static_cast<int>(part_begin(cta, total, n_ctas)), t_end = static_cast<int>(part_begin(cta + 1, total, n_ctas));
+    if (t_begin >= t_end) return;
+    // first sequence of this CTA: the largest r with s_pref[r] <= t_begin
+    int r_first = 0;
+    {
+        int lo = 0, hi = n_seqs;  // invariant: s_pref[lo] <= t_begin < s_pref[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_pref[mid] <= t_begin) lo = mid; else hi = mid;
+        }
+        r_first = lo;
+    }
+
+    // ---- producer state (warp 0; lanes 0..3 each own one pointer table: K, V, K scales, V scales) ----
+    // Page pointers are read one page (or one sequence) ahead so that the load latency never sits in front of a copy.
+    int p_r = r_first, p_tile = t_begin - s_pref[r_first], p_hi = min(t_end, s_pref[r_first + 1]) - s_pref[r_first], p_it = 0;
+    void *const *p_table = lane == 0 ? view.k_pages : (lane == 1 ? view.v_pages : (lane == 2 ? view.k_scale_pages : view.v_scale_pages));
+    int64_t cur_pidx = -1, nxt_pidx = -1;
+    const unsigned char *cur_ptr = nullptr, *nxt_ptr = nullptr;
+    // index of the page that follows page `page` of sequence r inside this CTA's range, or -1
+    auto following_page = [&](int r, int page) -> int64_t {
+        const int last_tile = min(t_end, s_pref[r + 1]) - s_pref[r] - 1;
+        if (page < last_tile * kTcTile / view.page_tokens) return static_cast<int64_t>(r) * view.pages_per_seq + page + 1;
+        for (int r2 = r + 1; r2 < n_seqs && s_pref[r2] < t_end; ++r2)
+            if (s_pref[r2 + 1] > s_pref[r2]) return static_cast<int64_t>(r2) * view.pages_per_seq;  // later sequences start at their tile 0
+        return -1;
+    };
+    if (warp == 0 && lane < 4) {
+        const int page = p_tile * kTcTile / view.page_tokens;
+        cur_pidx = static_cast<int64_t>(p_r) * view.pages_per_seq + page;
+        cur_ptr = reinterpret_cast<const unsigned char *>(p_table[cur_pidx]);
+        nxt_pidx = following_page(p_r, page);
+        if (nxt_pidx >= 0) nxt_ptr = reinterpret_cast<const unsigned char *>(p_table[nxt_pidx]);
+    }
+    // issue the copies of the next tile (warp 0, all lanes call); false on a timed-out wait
+    auto produce_one = [&]() -> bool {
+        const int stage = p_it % kTcStages;
+        if (p_it >= kTcStages && !mbar_wait(bar_empty + 8 * stage, ((p_it / kTcStages) - 1) & 1, abort_flag)) return false;
+        if (lane < 4) {
+            const int t0 = p_tile * kTcTile;
+            const int page = t0 / view.page_tokens;
+            const int64_t pidx = static_cast<int64_t>(p_r) * view.pages_per_seq + page;
+            if (pidx != cur_pidx) {
+                cur_ptr = pidx == nxt_pidx ? nxt_ptr : reinterpret_cast<const unsigned char *>(p_table[pidx]);
+                cur_pidx = pidx;
+                nxt_pidx = following_page(p_r, page);
+                if (nxt_pidx >= 0) nxt_ptr = reinterpret_cast<const unsigned char *>(p_table[nxt_pidx]);
+            }
+            const int in_page = t0 - page * view.page_tokens;
+            const uint32_t full = bar_full + 8 * stage;
+            const uint32_t sbase = smem_base + stage * LT::kStage;
+            if (lane == 0) mbar_expect_tx(full, LT::kTxBytes);
+            __syncwarp(0xfu);
+            if (lane < 2)
+                bulk_g2s(sbase + (lane ? LT::kVOff : LT::kKOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kRow, kTcTile * LT::kRow, full);
+            else
+                bulk_g2s(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kSRow, kTcTile * LT::kSRow, full);
+        }
+        __syncwarp();
+        ++p_it;
+        if (++p_tile >= p_hi) {  // next sequence that has tiles in this CTA's range
+            p_hi = 0;
+            for (++p_r; p_r < n_seqs && s_pref[p_r] < t_end; ++p_r)
+                if (s_pref[p_r + 1] > s_pref[p_r]) {
+                    p_tile = 0;
+                    p_hi = min(t_end, s_pref[p_r + 1]) - s_pref[p_r];
+                    break;
+                }
+        }
+        return true;
+    };
+    const int n_tiles_cta = t_end - t_begin;
+    bool ok = true;
+    if (warp == 0)  // fill the ring before anything else touches global memory
+        while (ok && p_it < n_tiles_cta && p_it < kTcStages) ok = produce_one();
 
     // ================================ consumer warps ================================
-    const int head = warp;           // kv head
+    const int head = warp;
     const int g = lane >> 2, j = lane & 3;
     const float vmul = 1.0f / 127.0f;
     int it = 0;
-    int64_t acc = 0;
-    bool ok = true;
-    for (int r = 0; r < n_seqs && acc < t_end && ok; ++r) {
-        const int L = min(max(seq_lens[r], 0), cap);
-        const int nt_seq = (L + kTcTile - 1) / kTcTile;
-        const int64_t lo = max(t_begin, acc), hi = min(t_end, acc + nt_seq), base = acc;
-        acc += nt_seq;
+    int seg_idx = 0;
+    (void)seg_idx;
+    for (int r = r_first; r < n_seqs && s_pref[r] < t_end && ok; ++r) {
+        const int base = s_pref[r];
+        const int lo = max(t_begin, base), hi = min(t_end, s_pref[r + 1]);
         if (lo >= hi) continue;
+        HS_TC_STAMP(2 + 4 * seg_idx);
+        const int L = s_len[r];
 
-        // ---- query fragments of this sequence: fp16, d permuted so that one 16-byte K load feeds 4 k-steps ----
+        // ---- query fragments: fp16, d permuted so that one 16-byte K load feeds 4 k-steps; per-block sums ----
         uint32_t qa[2][4][2];
-        if (g < G) {
-            const uint16_t *qp = q + (static_cast<int64_t>(r) * n_q_heads + head * G + g) * 128;
+        float qsum[2] = {0.0f, 0.0f};
+        if (g < kTcG) {
+            const uint16_t *qp = q + (static_cast<int64_t>(r) * n_q_heads + head * kTcG + g) * 128;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
                 const uint4 w0 = *reinterpret_cast<const uint4 *>(qp + 64 * b + 16 * j);
@@ -205,6 +280,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 for (int s = 0; s < 4; ++s) {
                     qa[b][s][0] = pack_h2(clamp_h(bf16lo(ww[2 * s])), clamp_h(bf16hi(ww[2 * s])));
                     qa[b][s][1] = pack_h2(clamp_h(bf16lo(ww[2 * s + 1])), clamp_h(bf16hi(ww[2 * s + 1])));
+                    qsum[b] += h2_sum(qa[b][s][0]) + h2_sum(qa[b][s][1]);
                 }
             }
         } else {
@@ -213,23 +289,48 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 #pragma unroll
                 for (int s = 0; s < 4; ++s) qa[b][s][0] = qa[b][s][1] = 0u;
         }
-        float m = -INFINITY, l_part = 0.0f;
-        float O[16][4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.0f;
+        for (int b = 0; b < 2; ++b) {
+            qsum[b] += __shfl_xor_sync(0xffffffffu, qsum[b], 1);
+            qsum[b] += __shfl_xor_sync(0xffffffffu, qsum[b], 2);
+            qsum[b] *= 1151.0f;
+        }
+        // pull the next sequence's query rows towards L1 now, so that the segment switch does not wait on L2
+        if (g < kTcG) {
+            for (int r2 = r + 1; r2 < n_seqs && s_pref[r2] < t_end; ++r2)
+                if (s_pref[r2 + 1] > s_pref[r2]) {
+                    const uint16_t *qn = q + (static_cast<int64_t>(r2) * n_q_heads + head * kTcG + g) * 128 + 16 * j;
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(qn));
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(qn + 64));
+                    break;
+                }
+        }
+        HS_TC_STAMP(3 + 4 * seg_idx);
+        // running softmax state of query head g (row layout of the q.K^T accumulators)
+        float m = -INFINITY, l_part = 0.0f, ps_part[2] = {0.0f, 0.0f};
+        // O^T accumulators: tile (b, mt): rows d = 64b + 8g + 4*(mt>>1) + 2*(mt&1) (+1 for regs 2,3), cols heads 2j, 2j+1
+        float O[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.0f;
 
-        for (int64_t tile = lo - base; tile < hi - base; ++tile, ++it) {
+        for (int tile = lo - base; tile < hi - base; ++tile, ++it) {
             const int stage = it % kTcStages;
+            if (warp == 0) {  // keep the ring two tiles ahead of the tile about to be consumed
+                while (ok && p_it < n_tiles_cta && p_it <= it + kTcStages - 1) ok = produce_one();
+                if (!ok) break;
+            }
             ok = mbar_wait(bar_full + 8 * stage, (it / kTcStages) & 1, abort_flag);
             if (!ok) break;
             const unsigned char *sK = smem + stage * LT::kStage + LT::kKOff;
             const unsigned char *sV = smem + stage * LT::kStage + LT::kVOff;
             const unsigned char *sKs = smem + stage * LT::kStage + LT::kKsOff;
             const unsigned char *sVs = smem + stage * LT::kStage + LT::kVsOff;
-            const int t0 = static_cast<int>(tile) * kTcTile;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                // ---- S = q . K^T for 16 tokens (two n-tiles of 8), one accumulator per 64-wide d block ----
+            constexpr int tl0 = 0;
+#ifdef HS_TC_DRAIN_ONLY  // diagnostic build only: consumers drain the ring without computing (measures the copy pipeline)
+            if (false)
+#endif
+            {
+                // ---- S = q.(1024 + K)^T for 16 tokens (two n-tiles of 8), one accumulator per 64-wide d block ----
                 float sacc[2][2][4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
@@ -237,14 +338,14 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     for (int b = 0; b < 2; ++b) sacc[nt][b][0] = sacc[nt][b][1] = sacc[nt][b][2] = sacc[nt][b][3] = 0.0f;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const unsigned char *krow = sK + (u * 16 + nt * 8 + g) * LT::kRowS + head * 128 + 16 * j;
+                    const unsigned char *krow = sK + (tl0 + nt * 8 + g) * LT::kRow + head * 128 + 16 * j;
 #pragma unroll
                     for (int b = 0; b < 2; ++b) {
                         const uint4 kv = *reinterpret_cast<const uint4 *>(krow + 64 * b);
                         const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
                         for (int s = 0; s < 4; ++s)
-                            mma_f16(sacc[nt][b], qa[b][s][0], qa[b][s][1], codes_to_h2(kw[s], 0x4140), codes_to_h2(kw[s], 0x4342));
+                            mma_rows8(sacc[nt][b], qa[b][s][0], qa[b][s][1], codes_biased_h2(kw[s], 0x4140), codes_biased_h2(kw[s], 0x4342));
                     }
                 }
                 // ---- scales of this thread's 4 tokens, scores in the exp2 domain, masking ----
@@ -254,23 +355,23 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int tl = u * 16 + nt * 8 + 2 * j + e;
-                        const bool valid = t0 + tl < L;
+                        const int tl = tl0 + nt * 8 + 2 * j + e;
+                        const bool valid = tile * kTcTile + tl < L;
                         float ks[2], vs[2];
                         if (SF16) {
-                            const __half *kp = reinterpret_cast<const __half *>(sKs) + (tl * HKV + head) * BPR;
-                            const __half *vp = reinterpret_cast<const __half *>(sVs) + (tl * HKV + head) * BPR;
+                            const __half *kp = reinterpret_cast<const __half *>(sKs) + (tl * kTcHkv + head) * BPR;
+                            const __half *vp = reinterpret_cast<const __half *>(sVs) + (tl * kTcHkv + head) * BPR;
                             ks[0] = __half2float(kp[0]); vs[0] = __half2float(vp[0]);
                             ks[1] = BPR == 2 ? __half2float(kp[BPR - 1]) : ks[0];
                             vs[1] = BPR == 2 ? __half2float(vp[BPR - 1]) : vs[0];
                         } else {
-                            const float *kp = reinterpret_cast<const float *>(sKs) + (tl * HKV + head) * BPR;
-                            const float *vp = reinterpret_cast<const float *>(sVs) + (tl * HKV + head) * BPR;
+                            const float *kp = reinterpret_cast<const float *>(sKs) + (tl * kTcHkv + head) * BPR;
+                            const float *vp = reinterpret_cast<const float *>(sVs) + (tl * kTcHkv + head) * BPR;
                             ks[0] = kp[0]; vs[0] = vp[0];
                             ks[1] = BPR == 2 ? kp[BPR - 1] : ks[0];
                             vs[1] = BPR == 2 ? vp[BPR - 1] : vs[0];
                         }
-                        const float s2 = (sacc[nt][0][e] * ks[0] + sacc[nt][1][e] * ks[1]) * kmul;
+                        const float s2 = ((sacc[nt][0][e] - qsum[0]) * ks[0] + (sacc[nt][1][e] - qsum[1]) * ks[1]) * kmul;
                         p[nt][e] = valid ? s2 : -INFINITY;
                         pv[nt][e][0] = valid ? vs[0] * vmul : 0.0f;
                         pv[nt][e][1] = valid ? vs[1] * vmul : 0.0f;
@@ -290,29 +391,35 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                         psum += p[nt][e];
                     }
                 l_part = l_part * corr + psum;
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                    // the O^T accumulators hold heads 2j, 2j+1: fetch their factors from the lanes whose row is that head
+                    const float c0 = __shfl_sync(0xffffffffu, corr, 8 * j), c1 = __shfl_sync(0xffffffffu, corr, 8 * j + 4);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) { O[i][0] *= corr; O[i][1] *= corr; }
-                // ---- O += P' . V with the V block scale folded into P' ----
+                    for (int i = 0; i < 8; ++i) { O[i][0] *= c0; O[i][1] *= c1; O[i][2] *= c0; O[i][3] *= c1; }
+                    ps_part[0] *= corr; ps_part[1] *= corr;
+                }
+                // ---- O^T += (1024 + V)^T . P'^T, the V block scale folded into P' ----
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    const uint32_t a0 = pack_h2(p[0][0] * pv[0][0][b], p[0][1] * pv[0][1][b]);
-                    const uint32_t a2 = pack_h2(p[1][0] * pv[1][0][b], p[1][1] * pv[1][1][b]);
+                    const uint32_t b0 = pack_h2(p[0][0] * pv[0][0][b], p[0][1] * pv[0][1][b]);
+                    const uint32_t b1 = pack_h2(p[1][0] * pv[1][0][b], p[1][1] * pv[1][1][b]);
+                    ps_part[b] += h2_sum(b0) + h2_sum(b1);
                     uint2 x[2][2];
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
-                            x[nt][e] = *reinterpret_cast<const uint2 *>(sV + (u * 16 + nt * 8 + 2 * j + e) * LT::kRowS + head * 128 + 64 * b + 8 * g);
+                            x[nt][e] = *reinterpret_cast<const uint2 *>(sV + (tl0 + nt * 8 + 2 * j + e) * LT::kRow + head * 128 + 64 * b + 8 * g);
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const uint32_t A0 = k ? x[0][0].y : x[0][0].x, B0 = k ? x[0][1].y : x[0][1].x;
                         const uint32_t A1 = k ? x[1][0].y : x[1][0].x, B1 = k ? x[1][1].y : x[1][1].x;
                         const uint32_t t01 = __byte_perm(A0, B0, 0x5140), t23 = __byte_perm(A0, B0, 0x7362);
                         const uint32_t u01 = __byte_perm(A1, B1, 0x5140), u23 = __byte_perm(A1, B1, 0x7362);
-                        mma_f16(O[8 * b + 4 * k + 0], a0, a2, codes_to_h2(t01, 0x4140), codes_to_h2(u01, 0x4140));
-                        mma_f16(O[8 * b + 4 * k + 1], a0, a2, codes_to_h2(t01, 0x4342), codes_to_h2(u01, 0x4342));
-                        mma_f16(O[8 * b + 4 * k + 2], a0, a2, codes_to_h2(t23, 0x4140), codes_to_h2(u23, 0x4140));
-                        mma_f16(O[8 * b + 4 * k + 3], a0, a2, codes_to_h2(t23, 0x4342), codes_to_h2(u23, 0x4342));
+                        mma_full(O[4 * b + 2 * k + 0], codes_biased_h2(t01, 0x4140), codes_biased_h2(t01, 0x4342),
+                                 codes_biased_h2(u01, 0x4140), codes_biased_h2(u01, 0x4342), b0, b1);
+                        mma_full(O[4 * b + 2 * k + 1], codes_biased_h2(t23, 0x4140), codes_biased_h2(t23, 0x4342),
+                                 codes_biased_h2(u23, 0x4140), codes_biased_h2(u23, 0x4342), b0, b1);
                     }
                 }
             }
@@ -320,61 +427,94 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
         }
         if (!ok) break;
+        HS_TC_STAMP(4 + 4 * seg_idx);
         // ---- partial of this (CTA, sequence) pair ----
         float l = l_part;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        if (g < G) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const int64_t hrow = (cta + r) * n_q_heads + head * G + g;
-            float *op = o_part + hrow * 128;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            ps_part[b] += __shfl_xor_sync(0xffffffffu, ps_part[b], 1);
+            ps_part[b] += __shfl_xor_sync(0xffffffffu, ps_part[b], 2);
+            ps_part[b] *= 1151.0f;
+        }
+        // per-head values (row layout: lane 4*head') -> the lanes that hold heads 2j, 2j+1 in their accumulators
+        const float l0 = __shfl_sync(0xffffffffu, l, 8 * j), l1 = __shfl_sync(0xffffffffu, l, 8 * j + 4);
+        float c0[2], c1[2];
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            c0[b] = __shfl_sync(0xffffffffu, ps_part[b], 8 * j);
+            c1[b] = __shfl_sync(0xffffffffu, ps_part[b], 8 * j + 4);
+        }
+        const int64_t slot = cta + r;
+        if (2 * j < kTcG) {
+            const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+            // this thread owns, for heads 2j and 2j+1 and each block b, the 8 consecutive outputs d = 64b + 8g .. +7:
+            // two 16-byte stores each (whole 32-byte sectors)
+            float *op0 = o_part + (slot * n_q_heads + head * kTcG + 2 * j) * 128 + 8 * g;
+            float *op1 = op0 + 128;
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    op[64 * b + 16 * j + i] = O[8 * b + i][0] * inv;
-                    op[64 * b + 16 * j + 8 + i] = O[8 * b + i][1] * inv;
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float *a = O[4 * b + 2 * hf], *c = O[4 * b + 2 * hf + 1];
+                    *reinterpret_cast<float4 *>(op0 + 64 * b + 4 * hf) =
+                        make_float4((a[0] - c0[b]) * inv0, (a[2] - c0[b]) * inv0, (c[0] - c0[b]) * inv0, (c[2] - c0[b]) * inv0);
+                    *reinterpret_cast<float4 *>(op1 + 64 * b + 4 * hf) =
+                        make_float4((a[1] - c1[b]) * inv1, (a[3] - c1[b]) * inv1, (c[1] - c1[b]) * inv1, (c[3] - c1[b]) * inv1);
                 }
-            if (j == 0) lse_part[hrow] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
+        if (g < kTcG && j == 0)
+            lse_part[slot * n_q_heads + head * kTcG + g] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        HS_TC_STAMP(5 + 4 * seg_idx);
+        ++seg_idx;
     }
-    if (!ok && lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+    HS_TC_STAMP(1);
+    if (!ok) {
+        // a wait ran out: give the copies already in flight a bounded chance to land before the CTA's shared
+        // memory is released, then report
+        if (warp == 0) {
+            const long long t0c = clock64();
+            while (clock64() - t0c < 2000000LL) {}
+        }
+        if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+    }
 }
 
-template <int HKV, int G, int BPR, bool SF16>
+template <int BPR, bool SF16>
 static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads, float kmul,
                          float *o_part, float *lse_part, int *err, int n_ctas, cudaStream_t s) {
-    using LT = TcLayout<HKV, BPR, SF16>;
-    auto kern = decode_int8_tc_kernel<HKV, G, BPR, SF16>;
+    using LT = TcLayout<BPR, SF16>;
+    auto kern = decode_int8_tc_kernel<BPR, SF16>;
     static bool configured = false;  // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LT::kTotal);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode: %s", cudaGetErrorString(e));
         configured = true;
     }
-    kern<<<n_ctas, (HKV + 1) * 32, LT::kTotal, s>>>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err);
+    kern<<<n_ctas, kTcThreads, LT::kTotal, s>>>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err);
     return HS_OK;
 }
 
 // Returns HS_OK and sets *n_ctas_out (> 0) when the tensor-core kernel took the launch; *n_ctas_out = 0
-// when the shape is not covered and the caller should use the generic kernel.
+// when the shape is not covered and the caller should use the generic kernel.  Each (CTA, sequence) pair
+// writes one partial (slot cta + seq).
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out) {
     *n_ctas_out = 0;
-    if (v.kind != HS_KV_INT8 || v.head_dim != 128 || v.n_kv_heads != 8) return HS_OK;
-    if (v.page_tokens % kTcTile != 0) return HS_OK;
-    const int G = n_q_heads / v.n_kv_heads;
-    if (G != 4) return HS_OK;
+    if (v.kind != HS_KV_INT8 || v.head_dim != 128 || v.n_kv_heads != kTcHkv) return HS_OK;
+    if (v.page_tokens % kTcTile != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
+    if (n_q_heads != kTcG * kTcHkv) return HS_OK;
     const int bpr = 128 / v.block;
     if (bpr != 1 && bpr != 2) return HS_OK;
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
-    const int n_ctas = sm_count();
+    const int n_ctas = 2 * sm_count();
     const float kmul = softmax_scale * 1.4426950408889634f / 127.0f;
     int32_t st;
-    if (bpr == 2 && !sf16) st = launch_tc<8, 4, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else if (bpr == 2 && sf16) st = launch_tc<8, 4, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else if (bpr == 1 && !sf16) st = launch_tc<8, 4, 1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else st = launch_tc<8, 4, 1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
+    if (bpr == 2 && !sf16) st = launch_tc<2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
+    else if (bpr == 2 && sf16) st = launch_tc<2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
+    else if (bpr == 1 && !sf16) st = launch_tc<1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
+    else st = launch_tc<1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
     if (st == HS_OK) *n_ctas_out = n_ctas;
     return st;
 }
