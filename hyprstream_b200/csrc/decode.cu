@@ -9,6 +9,8 @@
 // This file holds the shape-generic CUDA-core kernel (any supported kind, head_dim 64/128/256,
 // group 1/2/4/8) and the merge kernel.  It is HBM-bound: per cached token and kv head it moves
 // 2*head_dim code bytes plus the scales, and does 2*group*head_dim FMAs.
+#include <mutex>
+
 #include "hs_common.cuh"
 
 namespace hs {
@@ -384,6 +386,40 @@ static int32_t dispatch_d(int D, int G, const ViewDev &v, const uint16_t *q, con
     }
 }
 
+// ---- decode scratch that lives inside the library ------------------------------------------------
+// Backing store of hs_attn_decode_static(): the split-KV partials go here instead of into a workspace the
+// caller would have had to allocate.  Every GPU that loads the library holds these bytes until exit.
+constexpr int64_t kStaticScratchBytes = 24ll << 20;  // 24 MiB
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+// Device address of the array on each device.  The array's name is only a host-side handle: the address a
+// kernel can use has to be asked for, per device, with that device current.
+static void *g_static_scratch_ptr[kStaticMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+static int32_t static_scratch_for_current_device(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(HS_ERR_DEVICE, "hs_attn_decode_static: no usable CUDA device: %s", cudaGetErrorString(e));
+    }
+    if (dev < 0 || dev >= kStaticMaxDevices) return fail(HS_ERR_DEVICE, "hs_attn_decode_static: device ordinal %d is beyond the table of %d", dev, kStaticMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return fail(e != cudaSuccess ? static_cast<int32_t>(e) : HS_ERR_DEVICE, "hs_attn_decode_static: cudaGetSymbolAddress failed: %s",
+                        cudaGetErrorString(e));
+        }
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return HS_OK;
+}
+
 }  // namespace hs
 
 using namespace hs;
@@ -459,6 +495,27 @@ int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int
     merge_parts_kernel<<<static_cast<unsigned>(n_rows), head_dim, 0, as_stream(stream)>>>(
         o_parts, lse_parts, n_parts, n_rows, head_dim, reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate));
     return check_launch("hs_attn_merge_partials");
+}
+
+
+int64_t hs_attn_decode_static_max_bytes(void) { return kStaticScratchBytes; }
+
+int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                              float softmax_scale, void *out, const void *gate, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (int32_t st = validate_view(view)) return st;
+    if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode_static: bad sizes");
+    const int64_t need = hs_attn_decode_workspace_bytes(n_seqs, n_q_heads, view->head_dim);
+    if (need < 0 || need > kStaticScratchBytes)
+        return fail(HS_ERR_WORKSPACE,
+                    "hs_attn_decode_static: n_seqs %d x n_q_heads %d x head_dim %d needs %lld bytes of scratch, the built-in array holds "
+                    "%lld; use hs_attn_decode with a caller-provided workspace",
+                    n_seqs, n_q_heads, view->head_dim, (long long)need, (long long)kStaticScratchBytes);
+    void *scratch = nullptr;
+    if (int32_t st = static_scratch_for_current_device(&scratch)) return st;
+    // Nothing in the scratch has to start at zero: each launch writes every partial slot it later reads.
+    return hs_attn_decode(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, scratch, kStaticScratchBytes, nullptr,
+                          nullptr, stream);
 }
 
 }  // extern "C"

@@ -153,6 +153,25 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
                        int32_t n_q_heads, float softmax_scale, void *out, const void *gate, void *workspace,
                        int64_t workspace_bytes, float *o_shard, float *lse_shard, hs_stream_t stream);
 
+/* hs_attn_decode for callers that cannot hand over a workspace.  (No counterpart in the reference: there the
+ * caller allocates every buffer with libtorch.)  Some hosts of this library cannot allocate device memory at
+ * the point where they decode: a serving loop that is being captured into a CUDA graph (allocation is not a
+ * capturable operation), an embedder whose whole device budget is owned by another allocator, or a worker
+ * that must not synchronise the device, which cudaMalloc/cudaFree do.  For them the split-KV partials go into
+ * an array that is part of the library image itself: 24 MiB (hs_attn_decode_static_max_bytes()), resident on
+ * every GPU that loads the library for as long as the process lives.  Inputs and outputs are still the
+ * caller's; the arguments mean what they mean for hs_attn_decode, minus workspace and shard outputs.
+ *   - Shapes whose hs_attn_decode_workspace_bytes() exceeds the array are refused with HS_ERR_WORKSPACE and a
+ *     message that states both sizes (at 32 query heads and head_dim 128 that is n_seqs above 170).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture begins.  No call allocates or frees.
+ *   - All calls share the one array, and it keeps whatever the previous call left; nothing in it needs to be
+ *     zero, because a launch only reads partial slots it has just written.  Two calls whose kernels overlap on
+ *     the GPU (different streams, or different host threads on one device) race on it: serialise them. */
+int64_t hs_attn_decode_static_max_bytes(void);
+int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs,
+                              int32_t n_q_heads, float softmax_scale, void *out, const void *gate, hs_stream_t stream);
+
 /* Log-sum-exp merge of `n_parts` partial results: o_parts fp32 [n_parts, n_rows, head_dim],
  * lse_parts fp32 [n_parts, n_rows] (n_rows = n_seqs * n_q_heads) -> out bf16 [n_rows, head_dim],
  * optionally times sigmoid(gate).  A part with lse = -inf contributes nothing. */
