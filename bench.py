@@ -7,7 +7,7 @@ the int8 KV cache, then ragged decode attention of the batch's 32 query tokens o
 uniformly from 512..8192 (seed 1 + rank).  Synthetic N(0,1) data.  Inputs are larger than L2
 (about 290 MB of KV per GPU against 126 MB), so no flush is needed between steps.
 
-    python bench.py --gpus 1 --steps 50 --warmup 5
+    python bench.py --gpus 1 --steps 2000 --warmup 20
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference --steps 3 --warmup 1     # the reference's CPU op sequence
@@ -34,6 +34,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 BATCH, HQ, HKV, D = 32, 32, 8, 128
+# ncu capture of decode_int8_tc_kernel on this workload: 290.45 MB read + 4.50 MB written for 289.31 MB algorithmic
+NCU_TRAFFIC_PER_ALGO_BYTE = (290.446848 + 4.504576) / 289.309344
 LAYOUTS = {"baseline": (128, 1), "reference": (64, 0)}  # (block, scale dtype: 0 = f32, 1 = f16)
 
 
@@ -65,7 +67,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.tmp,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.tmp,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -174,8 +176,8 @@ def workload_config(layout: str, lens: list[int]) -> dict:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layout", default="baseline", choices=sorted(LAYOUTS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -322,7 +324,10 @@ def main():
         "gpu_launches": 3 * args.steps,
         "roofline": {"bound": "hbm", "kernel": "decode split-KV kernel (rank 0)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "kernel_ms": kernel_ms,
-                     "bytes_per_launch": kernel_bytes, "traffic": None},
+                     "bytes_per_launch": kernel_bytes,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch on this workload
+                     # (profiles/decode_int8_tc_config2.md), scaled by this run's algorithmic bytes
+                     "traffic": NCU_TRAFFIC_PER_ALGO_BYTE * kernel_bytes if args.layout == "baseline" else None},
         "clocks": clocks, "device_error_flags": dev_err,
     }
     if world == 1 and not args.no_cpu_baseline:
