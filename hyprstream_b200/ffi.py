@@ -58,6 +58,8 @@ _SIGS = {
     "hs_attn_decode": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "hs_attn_decode_static_max_bytes": (c_int64, []),
     "hs_attn_decode_static": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_prefill_causal": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_float, c_void_p]),
+    "hs_gdn_recurrent": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
     "hs_attn_merge_partials": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
 }
 

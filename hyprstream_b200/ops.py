@@ -136,3 +136,30 @@ def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, gate: Optiona
     out = torch.empty(n_seqs, hq, d, dtype=torch.bfloat16, device=o_parts.device)
     check(lib.hs_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), p, n_seqs * hq, d, _ptr(out), _ptr(gate), _stream()))
     return out
+
+
+def gdn_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                  state: torch.Tensor) -> torch.Tensor:
+    """Recurrent gated delta rule (qwen3_5.rs:725-751) over [B, T, heads, dim] fp32 inputs; `state`
+    [B, nv, hk, hv] fp32 is updated in place.  Returns out [B, T, nv, hv] fp32."""
+    _need_cuda(q, k, v, g, beta, state)
+    b, t, nk, hk = q.shape
+    nv, hv = v.shape[2], v.shape[3]
+    out = torch.empty(b, t, nv, hv, dtype=torch.float32, device=q.device)
+    check(lib.hs_gdn_recurrent(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(out), b, t, nk, nv, hk, hv,
+                               _stream()))
+    return out
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: Optional[float] = None,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal GQA prefill (llama.rs:1023-1119; qwen3_5.rs:1012-1059 with `gate`).
+
+    q bf16 [B, q_len, Hq, D]; k, v bf16 [B, kv_len, Hkv, D], kv_len >= q_len.  Returns bf16 [B, q_len, Hq, D]."""
+    _need_cuda(q, k, v, gate)
+    b, ql, hq, d = q.shape
+    kl, hkv = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
+    out = torch.empty_like(q)
+    check(lib.hs_attn_prefill_causal(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(gate), b, ql, kl, hq, hkv, d, scale, _stream()))
+    return out

@@ -178,6 +178,33 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
 int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows,
                                int32_t head_dim, void *out, const void *gate, hs_stream_t stream);
 
+/* ---- causal prefill attention ---------------------------------------------------------------
+ * compute_attention_masked for q_len > 1 (architectures/llama.rs:1023-1119, single shot and the 1024-row
+ * chunked loop), fused with GQA expansion (llama.rs:847-872), and Qwen3_5FullAttention's prefill branch
+ * (qwen3_5.rs:1012-1059) when `gate` is given.
+ *   q    bf16 [n_seqs, q_len, n_q_heads, head_dim]     k, v  bf16 [n_seqs, kv_len, n_kv_heads, head_dim]
+ *   out  bf16 [n_seqs, q_len, n_q_heads, head_dim]     gate  optional bf16 like out: out *= sigmoid(gate)
+ * Query row i sits at absolute position (kv_len - q_len) + i and sees keys 0 .. (kv_len - q_len) + i, the
+ * reference's tril(k_len - q_len) offset for a cached prefix (llama.rs:1074-1084); kv_len >= q_len.
+ * K/V are the post-RoPE tensors the reference hands to attention (cache.get() or the fresh k, v). */
+int32_t hs_attn_prefill_causal(const void *q, const void *k, const void *v, void *out, const void *gate, int32_t n_seqs,
+                               int32_t q_len, int32_t kv_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                               float softmax_scale, hs_stream_t stream);
+
+/* ---- gated DeltaNet ------------------------------------------------------------------------
+ * The recurrent delta rule of GatedDeltaNetLayer::forward (architectures/qwen3_5.rs:725-751) for n_tokens >= 1
+ * tokens per sequence, state updated in place:
+ *   S <- exp(g) S;  m = k^T S;  delta = beta (v - m);  S <- S + k delta^T;  o = q^T S
+ *   q, k   f32 [n_seqs, n_tokens, n_k_heads, head_k_dim]  (already L2-normalised; q already scaled, :679-682)
+ *   v      f32 [n_seqs, n_tokens, n_v_heads, head_v_dim]
+ *   g,beta f32 [n_seqs, n_tokens, n_v_heads]              (log-decay <= 0 and write strength, :687-701)
+ *   state  f32 [n_seqs, n_v_heads, head_k_dim, head_v_dim] in/out (rec_state, :697-699)
+ *   out    f32 [n_seqs, n_tokens, n_v_heads, head_v_dim]
+ * k/q head i feeds value heads [i*r, (i+1)*r), r = n_v_heads / n_k_heads (:704-720). */
+int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
+                         float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
+                         int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
