@@ -1,0 +1,68 @@
+"""KV-length sharding of one long context across the GPUs of a node (BASELINE.json configs[2]).
+
+The reference has no collectives (its multi-GPU story is replicas and a layer split); this is
+new design.  Each rank owns a contiguous, page-aligned slice of every sequence's KV cache, runs the
+ordinary decode kernel over its slice with the shard outputs (normalised fp32 o and natural-log lse per
+(sequence, head)), all-gathers the 66 KB pair over NCCL, and merges with the log-sum-exp kernel:
+m = max lse_i; w_i = exp(lse_i - m); o = sum w_i o_i / sum w_i.  q is replicated.  No other exchange exists
+on this path, so the NCCL all-gather (latency-bound at this size) is the only collective.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+PAGE_TOKENS = 256  # shard boundaries fall on the reference's page size (kv_cache.rs:477)
+
+
+def shard_bounds(length: int, n_shards: int, page: int = PAGE_TOKENS) -> List[Tuple[int, int]]:
+    """[start, end) token ranges of `n_shards` contiguous shards of a context of `length` tokens.
+
+    Boundaries are multiples of `page`; pages are dealt as evenly as possible, earlier shards take the
+    remainder, trailing shards may be empty when there are fewer pages than shards."""
+    if length < 0 or n_shards <= 0 or page <= 0:
+        raise ValueError("shard_bounds: length >= 0, n_shards > 0, page > 0 required")
+    n_pages = (length + page - 1) // page
+    base, rem = divmod(n_pages, n_shards)
+    out, start = [], 0
+    for i in range(n_shards):
+        pages = base + (1 if i < rem else 0)
+        end = min(length, start + pages * page)
+        out.append((start, end))
+        start = end
+    return out
+
+
+def pack_partial(o: torch.Tensor, lse: torch.Tensor) -> torch.Tensor:
+    """(o [B,Hq,D], lse [B,Hq]) -> one [B,Hq,D+1] fp32 message, so a step is a single all-gather."""
+    return torch.cat([o, lse.unsqueeze(-1)], dim=-1).contiguous()
+
+
+def unpack_partials(msgs: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[P,B,Hq,D+1] -> (o_parts [P,B,Hq,D], lse_parts [P,B,Hq]), contiguous."""
+    return msgs[..., :-1].contiguous(), msgs[..., -1].contiguous()
+
+
+def all_gather_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-gather every rank's (o, lse); works on any backend (NCCL on GPUs, gloo in the CPU tests)."""
+    world = dist.get_world_size(group)
+    msg = pack_partial(o, lse)
+    buf = torch.empty(world * msg.numel(), dtype=msg.dtype, device=msg.device)  # flat: the form every backend accepts
+    dist.all_gather_into_tensor(buf, msg.reshape(-1), group=group)
+    return unpack_partials(buf.reshape((world,) + tuple(msg.shape)))
+
+
+def sharded_decode(q: torch.Tensor, local_view, local_lens: torch.Tensor, softmax_scale: Optional[float] = None,
+                   gate: Optional[torch.Tensor] = None, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Decode attention over a KV-length-sharded cache: local shard -> all-gather -> LSE merge.
+
+    `local_view`/`local_lens` describe this rank's slice (lengths may be 0: such a shard contributes lse = -inf).
+    Every rank returns the same bf16 [B, Hq, D]."""
+    from . import ops
+
+    o, lse = ops.decode_attention(q, local_view, local_lens, softmax_scale=softmax_scale, shard=True)
+    o_parts, lse_parts = all_gather_partials(o, lse, group)
+    return ops.merge_partials(o_parts, lse_parts, gate=gate)
