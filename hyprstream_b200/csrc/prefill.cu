@@ -220,6 +220,10 @@ static int32_t launch_prefill(const uint16_t *q, const uint16_t *k, const uint16
     return HS_OK;
 }
 
+// prefill_tc5.cu: tcgen05 / TMEM / TMA kernel for head_dim 128
+int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int n_seqs,
+                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2, cudaStream_t s, int *taken);
+
 }  // namespace hs
 
 using namespace hs;
@@ -245,8 +249,11 @@ int32_t hs_attn_prefill_causal(const void *q, const void *k, const void *v, void
     uint16_t *op = reinterpret_cast<uint16_t *>(out);
     const uint16_t *gp = reinterpret_cast<const uint16_t *>(gate);
     int32_t st;
+    int taken = 0;
     prof_begin(s);
-    if (head_dim == 64) st = launch_prefill<64, 64>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
+    st = prefill_tc5_try(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, head_dim, sl2, s, &taken);
+    if (st != HS_OK || taken) {
+    } else if (head_dim == 64) st = launch_prefill<64, 64>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
     else if (head_dim == 128) st = launch_prefill<128, 64>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
     else st = launch_prefill<256, 32>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
     prof_end(s);

@@ -1,0 +1,384 @@
+// Causal GQA prefill attention on the 5th-generation tensor cores (head_dim 128, bf16).
+//
+// One CTA = one 128-row query block of one head.  Roles (6 warps):
+//   warp 4  loader: TMA tensor loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the Q block once
+//           and of K/V tiles of 128 keys into a 2-stage shared-memory ring; completion on mbarriers
+//   warp 5  MMA issuer: one elected thread issues tcgen05.mma
+//             S_j = Q . K_j^T      (both operands K-major in shared memory, accumulator 128 x 128 fp32 in TMEM)
+//             O  += P_j . V_j      (P_j read from TMEM as bf16, V_j MN-major in shared memory)
+//           and tcgen05.commit to the mbarriers that hand results over; S is double-buffered in TMEM so that
+//           S_{j+1} runs under the softmax of tile j
+//   warps 0-3  softmax: thread = query row (TMEM lane).  tcgen05.ld the score row, mask, online softmax in the
+//           exp2 domain, write P_j (bf16 pairs) back over the score buffer with tcgen05.st; the output
+//           accumulator in TMEM is rescaled only when a row maximum grew by more than 2^8 (the final O / l is
+//           exact either way); epilogue: O / l, optional sigmoid gate, bf16 store
+//
+// TMEM columns: [0,128) S buffer 0 / P 0, [128,256) S buffer 1 / P 1, [256,384) O.   Shared memory: Q 32 KB +
+// 2 x (K 32 KB + V 32 KB).  FLOPs per tile pair: 2 x 2 x 128^3.  Bound: tensor pipe (and MUFU exp2).
+//
+// Replaces compute_attention_masked for q_len > 1 (architectures/llama.rs:1023-1119) with GQA expansion
+// (llama.rs:847-872) and the cached-prefix offset tril(k_len - q_len) (llama.rs:1074-1084); with `gate`,
+// Qwen3_5FullAttention's prefill branch (qwen3_5.rs:1012-1059) at head_dim 128.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records HS_DEVERR_WAIT_TIMEOUT, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "hs_common.cuh"
+
+namespace hs {
+
+constexpr int kT5M = 128, kT5N = 128, kT5D = 128;
+constexpr int kT5Stages = 2;
+constexpr int kT5Threads = 192;
+constexpr int kT5TileBytes = kT5N * kT5D * 2;          // 32 KB: two 64-column halves of [128 rows][128 B]
+constexpr int kT5HalfBytes = kT5TileBytes / 2;
+constexpr int kT5SmemBytes = kT5TileBytes * (1 + 2 * kT5Stages) + 1024;  // + alignment slack
+constexpr long long kT5WaitCycles = 4000000000LL;
+constexpr float kT5RescaleThreshold = 8.0f;            // log2 units
+
+__device__ __forceinline__ uint32_t t5_s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ bool t5_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (t5_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (t5_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kT5WaitCycles) { *abort_flag = 1; return false; }
+    }
+}
+__device__ __forceinline__ void t5_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void t5_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100)
+__device__ __forceinline__ uint64_t t5_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFF) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void t5_mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5,%6,%7,%8}, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void t5_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5,%6,%7,%8}, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void t5_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void t5_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void t5_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void t5_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void t5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void t5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// one [128 rows x 64 columns] box of a 4-D tensor (d, head, token, sequence) -> swizzled shared memory
+__device__ __forceinline__ void t5_tma_load(uint32_t dst, const CUtensorMap *map, int x, int head, int token, int seq, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(head), "r"(token), "r"(seq), "r"(bar) : "memory");
+}
+
+struct T5Bars {
+    uint64_t q, kfull[kT5Stages], vfull[kT5Stages], kvempty[kT5Stages], sfull[2], pready[2], odone;
+};
+
+__global__ void __launch_bounds__(kT5Threads, 1)
+prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
+                   int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) T5Bars bars;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t sQ = t5_s32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mb = gridDim.x - 1 - blockIdx.x;  // latest (heaviest) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / (n_q_heads / n_kv_heads);
+    const int m0 = mb * kT5M, off = kv_len - q_len;
+    const int n_end = min(kv_len, off + min(m0 + kT5M, q_len));
+    const int n_tiles = (n_end + kT5N - 1) / kT5N;
+    volatile int *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        auto init = [](uint64_t *bar, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(t5_s32(bar)), "r"(count)); };
+        init(&bars.q, 1);
+        for (int s = 0; s < kT5Stages; ++s) { init(&bars.kfull[s], 1); init(&bars.vfull[s], 1); init(&bars.kvempty[s], 1); }
+        for (int i = 0; i < 2; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kT5M); }
+        init(&bars.odone, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(t5_s32(&s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    t5_fence_before();
+    __syncthreads();
+    t5_fence_after();
+    const uint32_t tm = s_tmem;
+    const uint32_t tO = tm + 256;
+    bool ok = true;
+
+    if (warp == 4) {
+        // ================================ loader ================================
+        if (lane == 0) {
+            t5_expect_tx(t5_s32(&bars.q), kT5TileBytes);
+            t5_tma_load(sQ, &map_q, 0, h, m0, b, t5_s32(&bars.q));
+            t5_tma_load(sQ + kT5HalfBytes, &map_q, 64, h, m0, b, t5_s32(&bars.q));
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                if (j >= kT5Stages) ok = t5_wait(t5_s32(&bars.kvempty[s]), ((j >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                const uint32_t sK = sQ + kT5TileBytes * (1 + 2 * s), sV = sK + kT5TileBytes;
+                t5_expect_tx(t5_s32(&bars.kfull[s]), kT5TileBytes);
+                t5_tma_load(sK, &map_k, 0, kvh, j * kT5N, b, t5_s32(&bars.kfull[s]));
+                t5_tma_load(sK + kT5HalfBytes, &map_k, 64, kvh, j * kT5N, b, t5_s32(&bars.kfull[s]));
+                t5_expect_tx(t5_s32(&bars.vfull[s]), kT5TileBytes);
+                t5_tma_load(sV, &map_v, 0, kvh, j * kT5N, b, t5_s32(&bars.vfull[s]));
+                t5_tma_load(sV + kT5HalfBytes, &map_v, 64, kvh, j * kT5N, b, t5_s32(&bars.vfull[s]));
+            }
+        }
+    } else if (warp == 5) {
+        // ================================ MMA issuer ================================
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kT5N >> 3) << 17) | ((kT5M >> 4) << 24);  // bf16 x bf16 -> f32, K-major A and B
+            const uint32_t idesc_pv = idesc_qk | (1u << 16);                                                         // B (V) is MN-major
+            auto issue_s = [&](int j) {
+                const uint32_t sK = sQ + kT5TileBytes * (1 + 2 * (j & 1));
+#pragma unroll
+                for (int ks = 0; ks < kT5D / 16; ++ks) {
+                    const uint32_t o = (ks >> 2) * kT5HalfBytes + (ks & 3) * 32;
+                    t5_mma_ss(tm + (j & 1) * kT5N, t5_desc(sQ + o, 16, 1024), t5_desc(sK + o, 16, 1024), idesc_qk, ks > 0);
+                }
+                t5_commit(t5_s32(&bars.sfull[j & 1]));
+            };
+            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag) && t5_wait(t5_s32(&bars.kfull[0]), 0, abort_flag);
+            if (ok) {
+                t5_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = t5_wait(t5_s32(&bars.kfull[(j + 1) & 1]), ((j + 1) >> 1) & 1, abort_flag);
+                    if (ok && j >= 1) ok = t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag);  // score buffer (j+1)&1 was P_{j-1}
+                    if (!ok) break;
+                    t5_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = t5_wait(t5_s32(&bars.pready[j & 1]), (j >> 1) & 1, abort_flag) &&
+                     t5_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1, abort_flag);
+                if (!ok) break;
+                t5_fence_after();
+                const uint32_t sV = sQ + kT5TileBytes * (2 + 2 * (j & 1));
+#pragma unroll
+                for (int ks = 0; ks < kT5N / 16; ++ks)
+                    t5_mma_ts(tO, tm + (j & 1) * kT5N + ks * 8, t5_desc(sV + ks * 2048, kT5HalfBytes, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                t5_commit(t5_s32(&bars.kvempty[j & 1]));
+                t5_commit(t5_s32(&bars.odone));
+            }
+        }
+    } else {
+        // ================================ softmax: thread = query row ================================
+        const int row = m0 + threadIdx.x;
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        float m_used = -INFINITY, l = 0.0f;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 1]), (j >> 1) & 1, abort_flag));  // warp-uniform: the
+            if (!ok) break;                                                                             // TMEM accesses below are warp-collective
+            t5_fence_after();
+            const uint32_t tS = tm + lane_base + (j & 1) * kT5N;
+            float s[kT5N];
+#pragma unroll
+            for (int c0 = 0; c0 < kT5N; c0 += 32) {
+                uint32_t r[32];
+                t5_ld32(tS + c0, r);
+                t5_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c0 + i] = __uint_as_float(r[i]) * scale_log2;
+            }
+            const int n0 = j * kT5N;
+            if (n0 + kT5N > min(kv_len, off + m0 + 1)) {
+                const int lim = min(kv_len - 1, off + row);  // last visible key of this row
+#pragma unroll
+                for (int i = 0; i < kT5N; ++i)
+                    if (n0 + i > lim) s[i] = -INFINITY;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kT5N; ++i) mx = fmaxf(mx, s[i]);
+            const float m_new = fmaxf(m_used, mx);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool need = m_new - m_used > kT5RescaleThreshold;  // false while both are -inf (NaN compares false)
+                if (__any_sync(0xffffffffu, need)) {
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag));
+                    if (!ok) break;
+                    t5_fence_after();
+                    const float f = need ? exp2f(m_used - m_new) : 1.0f;
+#pragma unroll
+                    for (int c0 = 0; c0 < kT5D; c0 += 32) {
+                        uint32_t r[32];
+                        t5_ld32(tO + lane_base + c0, r);
+                        t5_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+                        t5_st32(tO + lane_base + c0, r);
+                    }
+                    t5_wait_st();
+                    l *= f;
+                    if (need) m_used = m_new;
+                }
+                if (m_used == -INFINITY) m_used = m_new;
+            }
+            float psum = 0.0f;
+#pragma unroll
+            for (int c0 = 0; c0 < kT5N; c0 += 32) {
+                uint32_t r[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = s[c0 + 2 * i] == -INFINITY ? 0.0f : exp2f(s[c0 + 2 * i] - m_used);
+                    const float p1 = s[c0 + 2 * i + 1] == -INFINITY ? 0.0f : exp2f(s[c0 + 2 * i + 1] - m_used);
+                    psum += p0 + p1;
+                    r[i] = pack_bf16(p0, p1);
+                }
+                t5_st16(tS + c0 / 2, r);
+            }
+            l += psum;
+            t5_wait_st();
+            t5_fence_before();
+            t5_arrive(t5_s32(&bars.pready[j & 1]));
+        }
+        // ---- epilogue ----
+        if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (n_tiles - 1) & 1, abort_flag));
+        if (ok && n_tiles > 0) {
+            t5_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kT5D;
+#pragma unroll
+            for (int c0 = 0; c0 < kT5D; c0 += 32) {
+                uint32_t r[32];
+                t5_ld32(tO + lane_base + c0, r);
+                t5_wait_ld();
+                if (row < q_len) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float x0 = __uint_as_float(r[v4 * 8 + 2 * i]) * inv, x1 = __uint_as_float(r[v4 * 8 + 2 * i + 1]) * inv;
+                            if (gate != nullptr) {
+                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + base + c0 + v4 * 8 + 2 * i);
+                                x0 = bf16_round(x0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
+                                x1 = bf16_round(x1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
+                            }
+                            w[i] = pack_bf16(x0, x1);
+                        }
+                        *reinterpret_cast<uint4 *>(out + base + c0 + v4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: every thread arrives here, also after a timed-out wait ----
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        const long long t0c = clock64();
+        while (clock64() - t0c < 2000000LL) {}  // bounded grace period for copies and MMAs still in flight
+    }
+    t5_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(512) : "memory");
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// [n_seqs, n_tokens, n_heads, 128] bf16 -> 4-D map (d, head, token, sequence), box 64 x 1 x 128 x 1, 128-byte swizzle
+static bool make_map(CUtensorMap *map, const void *base, int n_seqs, int n_tokens, int n_heads) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kT5D), static_cast<cuuint64_t>(n_heads), static_cast<cuuint64_t>(n_tokens),
+                                static_cast<cuuint64_t>(n_seqs)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kT5D) * 2, static_cast<cuuint64_t>(n_heads) * kT5D * 2,
+                                   static_cast<cuuint64_t>(n_tokens) * n_heads * kT5D * 2};
+    const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(kT5N), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns HS_OK with *taken = 1 when this kernel took the launch, *taken = 0 when the caller should use the
+// mma.sync kernel (head_dim != 128, or no tensor-map encoder in the driver).
+int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int n_seqs,
+                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2, cudaStream_t s, int *taken) {
+    *taken = 0;
+    if (head_dim != kT5D || q_len < 2) return HS_OK;
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, q, n_seqs, q_len, n_q_heads) || !make_map(&mk, k, n_seqs, kv_len, n_kv_heads) ||
+        !make_map(&mv, v, n_seqs, kv_len, n_kv_heads))
+        return HS_OK;
+    int *err = device_error_word();
+    if (!err) return fail(HS_ERR_DEVICE, "hs_attn_prefill_causal: device error word unavailable");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5SmemBytes);
+        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((q_len + kT5M - 1) / kT5M, n_q_heads, n_seqs);
+    prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err);
+    *taken = 1;
+    return HS_OK;
+}
+
+}  // namespace hs
