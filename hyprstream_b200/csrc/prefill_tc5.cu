@@ -1,20 +1,21 @@
 // Causal GQA prefill attention on the 5th-generation tensor cores (head_dim 128, bf16).
 //
-// One CTA = one 128-row query block of one head.  Roles (6 warps):
-//   warp 4  loader: TMA tensor loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the Q block once
-//           and of K/V tiles of 128 keys into a 2-stage shared-memory ring; completion on mbarriers
-//   warp 5  MMA issuer: one elected thread issues tcgen05.mma
-//             S_j = Q . K_j^T      (both operands K-major in shared memory, accumulator 128 x 128 fp32 in TMEM)
-//             O  += P_j . V_j      (P_j read from TMEM as bf16, V_j MN-major in shared memory)
-//           and tcgen05.commit to the mbarriers that hand results over; S is double-buffered in TMEM so that
-//           S_{j+1} runs under the softmax of tile j
-//   warps 0-3  softmax: thread = query row (TMEM lane).  tcgen05.ld the score row, mask, online softmax in the
-//           exp2 domain, write P_j (bf16 pairs) back over the score buffer with tcgen05.st; the output
-//           accumulator in TMEM is rescaled only when a row maximum grew by more than 2^8 (the final O / l is
-//           exact either way); epilogue: O / l, optional sigmoid gate, bf16 store
+// One CTA = two 128-row query tiles of one head (256 rows) sharing every K/V tile.  Roles (10 warps):
+//   warp 8  loader: TMA tensor loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the two Q tiles
+//           once and of K/V tiles of 128 keys into a 2-stage shared-memory ring; completion on mbarriers
+//   warp 9  MMA issuer: one elected thread issues, per query tile x and key tile j,
+//             S_j = Q_x . K_j^T    (both operands K-major in shared memory, accumulator 128 x 128 fp32 in TMEM)
+//             O_x += P_j . V_j     (P_j read from TMEM as bf16, V_j MN-major in shared memory)
+//           and tcgen05.commit to the mbarriers that hand results over; a polling scheduler issues whichever
+//           tile's next operation is ready, so one tile's MMAs run under the other tile's softmax
+//   warps 0-3 / 4-7  softmax of tile 0 / 1: thread = query row (TMEM lane).  Two passes of tcgen05.ld over the
+//           score row (maximum, then exp2 and P as bf16 pairs written back over the scores with tcgen05.st); the
+//           output accumulator in TMEM is rescaled only when a row maximum grew by more than 2^8 (the final
+//           O / l is exact either way); epilogue: O / l, optional sigmoid gate, bf16 store
 //
-// TMEM columns: [0,128) S buffer 0 / P 0, [128,256) S buffer 1 / P 1, [256,384) O.   Shared memory: Q 32 KB +
-// 2 x (K 32 KB + V 32 KB).  FLOPs per tile pair: 2 x 2 x 128^3.  Bound: tensor pipe (and MUFU exp2).
+// TMEM columns: [0,128) S/P tile 0, [128,256) S/P tile 1, [256,384) O tile 0, [384,512) O tile 1.  Shared
+// memory: 2 x Q 32 KB + 2 x (K 32 KB + V 32 KB).  FLOPs per (query tile, key tile): 2 x 2 x 128^3.
+// Bound: tensor pipe (and MUFU exp2).
 //
 // Replaces compute_attention_masked for q_len > 1 (architectures/llama.rs:1023-1119) with GQA expansion
 // (llama.rs:847-872) and the cached-prefix offset tril(k_len - q_len) (llama.rs:1074-1084); with `gate`,
@@ -29,10 +30,11 @@ namespace hs {
 
 constexpr int kT5M = 128, kT5N = 128, kT5D = 128;
 constexpr int kT5Stages = 2;
-constexpr int kT5Threads = 192;
+constexpr int kT5BlockM = 2 * kT5M;  // two query tiles per CTA
+constexpr int kT5Threads = 320;
 constexpr int kT5TileBytes = kT5N * kT5D * 2;          // 32 KB: two 64-column halves of [128 rows][128 B]
 constexpr int kT5HalfBytes = kT5TileBytes / 2;
-constexpr int kT5SmemBytes = kT5TileBytes * (1 + 2 * kT5Stages) + 1024;  // + alignment slack
+constexpr int kT5SmemBytes = kT5TileBytes * (2 + 2 * kT5Stages) + 1024;  // two Q tiles, K/V ring, alignment slack
 constexpr long long kT5WaitCycles = 4000000000LL;
 constexpr float kT5RescaleThreshold = 8.0f;            // log2 units
 
@@ -110,9 +112,17 @@ __device__ __forceinline__ void t5_tma_load(uint32_t dst, const CUtensorMap *map
 }
 
 struct T5Bars {
-    uint64_t q, kfull[kT5Stages], vfull[kT5Stages], kvempty[kT5Stages], sfull[2], pready[2], odone;
+    uint64_t q, kfull[kT5Stages], vfull[kT5Stages], kvempty[kT5Stages], sfull[2], pready[2], odone[2];
 };
 
+__device__ __forceinline__ float t5_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Two 128-row query tiles (x = 0, 1) per CTA share every K/V tile.  Warps 0-3: softmax of tile 0, warps 4-7: softmax of
+// tile 1, warp 8: loader, warp 9: MMA issuer.  TMEM columns: S/P of tile x at 128x, O of tile x at 256 + 128x.
 __global__ void __launch_bounds__(kT5Threads, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
@@ -122,21 +132,26 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const uint32_t sQ = t5_s32(smem);
+    const uint32_t sQ = t5_s32(smem);                       // Q tile 0, Q tile 1
+    const uint32_t sKV = sQ + 2 * kT5TileBytes;             // stage s: K at sKV + 2 s tile, V one tile later
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mb = gridDim.x - 1 - blockIdx.x;  // latest (heaviest) query blocks first
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (n_q_heads / n_kv_heads);
-    const int m0 = mb * kT5M, off = kv_len - q_len;
-    const int n_end = min(kv_len, off + min(m0 + kT5M, q_len));
-    const int n_tiles = (n_end + kT5N - 1) / kT5N;
+    const int m0 = mb * kT5BlockM, off = kv_len - q_len;
+    int n_tiles[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int lo = m0 + x * kT5M;
+        n_tiles[x] = lo < q_len ? (min(kv_len, off + min(lo + kT5M, q_len)) + kT5N - 1) / kT5N : 0;
+    }
+    const int n_max = max(n_tiles[0], n_tiles[1]);
     volatile int *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         auto init = [](uint64_t *bar, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(t5_s32(bar)), "r"(count)); };
         init(&bars.q, 1);
         for (int s = 0; s < kT5Stages; ++s) { init(&bars.kfull[s], 1); init(&bars.vfull[s], 1); init(&bars.kvempty[s], 1); }
-        for (int i = 0; i < 2; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kT5M); }
-        init(&bars.odone, 1);
+        for (int i = 0; i < 2; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kT5M); init(&bars.odone[i], 1); }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -148,20 +163,22 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     t5_fence_after();
     const uint32_t tm = s_tmem;
-    const uint32_t tO = tm + 256;
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================================ loader ================================
         if (lane == 0) {
-            t5_expect_tx(t5_s32(&bars.q), kT5TileBytes);
-            t5_tma_load(sQ, &map_q, 0, h, m0, b, t5_s32(&bars.q));
-            t5_tma_load(sQ + kT5HalfBytes, &map_q, 64, h, m0, b, t5_s32(&bars.q));
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            t5_expect_tx(t5_s32(&bars.q), 2 * kT5TileBytes);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                t5_tma_load(sQ + x * kT5TileBytes, &map_q, 0, h, m0 + x * kT5M, b, t5_s32(&bars.q));
+                t5_tma_load(sQ + x * kT5TileBytes + kT5HalfBytes, &map_q, 64, h, m0 + x * kT5M, b, t5_s32(&bars.q));
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
                 const int s = j & 1;
                 if (j >= kT5Stages) ok = t5_wait(t5_s32(&bars.kvempty[s]), ((j >> 1) - 1) & 1, abort_flag);
                 if (!ok) break;
-                const uint32_t sK = sQ + kT5TileBytes * (1 + 2 * s), sV = sK + kT5TileBytes;
+                const uint32_t sK = sKV + 2 * s * kT5TileBytes, sV = sK + kT5TileBytes;
                 t5_expect_tx(t5_s32(&bars.kfull[s]), kT5TileBytes);
                 t5_tma_load(sK, &map_k, 0, kvh, j * kT5N, b, t5_s32(&bars.kfull[s]));
                 t5_tma_load(sK + kT5HalfBytes, &map_k, 64, kvh, j * kT5N, b, t5_s32(&bars.kfull[s]));
@@ -170,92 +187,110 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 t5_tma_load(sV + kT5HalfBytes, &map_v, 64, kvh, j * kT5N, b, t5_s32(&bars.vfull[s]));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================================ MMA issuer ================================
+        // A small polling scheduler: for each query tile the order is S_0, PV_0, S_1, PV_1, ...; S_j needs K_j and
+        // (for j > 0) PV_{j-1} complete (it overwrites the buffer PV_{j-1} reads P from); PV_j needs P_j and V_j.
+        // Whichever tile has its next operation ready gets issued, so one tile's MMAs run under the other's softmax.
         if (lane == 0) {
             const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kT5N >> 3) << 17) | ((kT5M >> 4) << 24);  // bf16 x bf16 -> f32, K-major A and B
             const uint32_t idesc_pv = idesc_qk | (1u << 16);                                                         // B (V) is MN-major
-            auto issue_s = [&](int j) {
-                const uint32_t sK = sQ + kT5TileBytes * (1 + 2 * (j & 1));
+            int next_s[2] = {0, 0}, next_pv[2] = {0, 0};
+            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag);
+            long long t_idle = clock64();
+            while (ok && (next_pv[0] < n_tiles[0] || next_pv[1] < n_tiles[1])) {
+                bool progress = false;
 #pragma unroll
-                for (int ks = 0; ks < kT5D / 16; ++ks) {
-                    const uint32_t o = (ks >> 2) * kT5HalfBytes + (ks & 3) * 32;
-                    t5_mma_ss(tm + (j & 1) * kT5N, t5_desc(sQ + o, 16, 1024), t5_desc(sK + o, 16, 1024), idesc_qk, ks > 0);
-                }
-                t5_commit(t5_s32(&bars.sfull[j & 1]));
-            };
-            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag) && t5_wait(t5_s32(&bars.kfull[0]), 0, abort_flag);
-            if (ok) {
-                t5_fence_after();
-                issue_s(0);
-            }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    ok = t5_wait(t5_s32(&bars.kfull[(j + 1) & 1]), ((j + 1) >> 1) & 1, abort_flag);
-                    if (ok && j >= 1) ok = t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag);  // score buffer (j+1)&1 was P_{j-1}
-                    if (!ok) break;
-                    t5_fence_after();
-                    issue_s(j + 1);
-                }
-                ok = t5_wait(t5_s32(&bars.pready[j & 1]), (j >> 1) & 1, abort_flag) &&
-                     t5_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1, abort_flag);
-                if (!ok) break;
-                t5_fence_after();
-                const uint32_t sV = sQ + kT5TileBytes * (2 + 2 * (j & 1));
+                for (int x = 0; x < 2; ++x) {
+                    int j = next_s[x];
+                    if (j < n_tiles[x] && j == next_pv[x] && t5_try_wait(t5_s32(&bars.kfull[j & 1]), (j >> 1) & 1) &&
+                        (j == 0 || t5_try_wait(t5_s32(&bars.odone[x]), (j - 1) & 1))) {
+                        t5_fence_after();
+                        const uint32_t sK = sKV + 2 * (j & 1) * kT5TileBytes, sQx = sQ + x * kT5TileBytes;
 #pragma unroll
-                for (int ks = 0; ks < kT5N / 16; ++ks)
-                    t5_mma_ts(tO, tm + (j & 1) * kT5N + ks * 8, t5_desc(sV + ks * 2048, kT5HalfBytes, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                t5_commit(t5_s32(&bars.kvempty[j & 1]));
-                t5_commit(t5_s32(&bars.odone));
+                        for (int ks = 0; ks < kT5D / 16; ++ks) {
+                            const uint32_t o = (ks >> 2) * kT5HalfBytes + (ks & 3) * 32;
+                            t5_mma_ss(tm + x * kT5N, t5_desc(sQx + o, 16, 1024), t5_desc(sK + o, 16, 1024), idesc_qk, ks > 0);
+                        }
+                        t5_commit(t5_s32(&bars.sfull[x]));
+                        next_s[x] = j + 1;
+                        progress = true;
+                    }
+                    j = next_pv[x];
+                    if (j < next_s[x] && t5_try_wait(t5_s32(&bars.pready[x]), j & 1) && t5_try_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1)) {
+                        t5_fence_after();
+                        const uint32_t sV = sKV + (2 * (j & 1) + 1) * kT5TileBytes;
+#pragma unroll
+                        for (int ks = 0; ks < kT5N / 16; ++ks)
+                            t5_mma_ts(tm + 256 + x * kT5D, tm + x * kT5N + ks * 8, t5_desc(sV + ks * 2048, kT5HalfBytes, 1024), idesc_pv,
+                                      (j > 0 || ks > 0) ? 1u : 0u);
+                        t5_commit(t5_s32(&bars.odone[x]));
+                        next_pv[x] = j + 1;
+                        const int y = x ^ 1;
+                        if (next_pv[y] > j || j >= n_tiles[y]) t5_commit(t5_s32(&bars.kvempty[j & 1]));  // both tiles are past K_j / V_j
+                        progress = true;
+                    }
+                }
+                if (progress) {
+                    t_idle = clock64();
+                } else if (*abort_flag || clock64() - t_idle > kT5WaitCycles) {
+                    *abort_flag = 1;
+                    ok = false;
+                }
             }
         }
     } else {
         // ================================ softmax: thread = query row ================================
-        const int row = m0 + threadIdx.x;
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const int x = warp >> 2;  // query tile of this warp group
+        const int row = m0 + x * kT5M + (threadIdx.x & 127);
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tm + lane_base + x * kT5N, tO = tm + lane_base + 256 + x * kT5D;
+        const int nt = n_tiles[x];
         float m_used = -INFINITY, l = 0.0f;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 1]), (j >> 1) & 1, abort_flag));  // warp-uniform: the
-            if (!ok) break;                                                                             // TMEM accesses below are warp-collective
+        for (int j = 0; j < nt && ok; ++j) {
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[x]), j & 1, abort_flag));  // warp-uniform: the TMEM
+            if (!ok) break;                                                                      // accesses below are warp-collective
             t5_fence_after();
-            const uint32_t tS = tm + lane_base + (j & 1) * kT5N;
-            float s[kT5N];
+            const int n0 = j * kT5N;
+            const bool masked = n0 + kT5N > min(kv_len, off + m0 + x * kT5M + 1);
+            const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
+            // ---- pass 1: row maximum ----
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
             for (int c0 = 0; c0 < kT5N; c0 += 32) {
                 uint32_t r[32];
                 t5_ld32(tS + c0, r);
                 t5_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c0 + i] = __uint_as_float(r[i]) * scale_log2;
+                for (int i = 0; i < 32; i += 4) {
+                    float a0 = __uint_as_float(r[i]), a1 = __uint_as_float(r[i + 1]), a2 = __uint_as_float(r[i + 2]), a3 = __uint_as_float(r[i + 3]);
+                    if (masked) {
+                        if (c0 + i > lim) a0 = -INFINITY;
+                        if (c0 + i + 1 > lim) a1 = -INFINITY;
+                        if (c0 + i + 2 > lim) a2 = -INFINITY;
+                        if (c0 + i + 3 > lim) a3 = -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, a0); mx1 = fmaxf(mx1, a1); mx2 = fmaxf(mx2, a2); mx3 = fmaxf(mx3, a3);
+                }
             }
-            const int n0 = j * kT5N;
-            if (n0 + kT5N > min(kv_len, off + m0 + 1)) {
-                const int lim = min(kv_len - 1, off + row);  // last visible key of this row
-#pragma unroll
-                for (int i = 0; i < kT5N; ++i)
-                    if (n0 + i > lim) s[i] = -INFINITY;
-            }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < kT5N; ++i) mx = fmaxf(mx, s[i]);
-            const float m_new = fmaxf(m_used, mx);
+            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
             if (j == 0) {
                 m_used = m_new;
             } else {
                 const bool need = m_new - m_used > kT5RescaleThreshold;  // false while both are -inf (NaN compares false)
                 if (__any_sync(0xffffffffu, need)) {
-                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag));
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone[x]), (j - 1) & 1, abort_flag));
                     if (!ok) break;
                     t5_fence_after();
                     const float f = need ? exp2f(m_used - m_new) : 1.0f;
 #pragma unroll
                     for (int c0 = 0; c0 < kT5D; c0 += 32) {
                         uint32_t r[32];
-                        t5_ld32(tO + lane_base + c0, r);
+                        t5_ld32(tO + c0, r);
                         t5_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-                        t5_st32(tO + lane_base + c0, r);
+                        t5_st32(tO + c0, r);
                     }
                     t5_wait_st();
                     l *= f;
@@ -263,34 +298,44 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 if (m_used == -INFINITY) m_used = m_new;
             }
-            float psum = 0.0f;
+            // ---- pass 2: P = exp2(s * scale - m) as bf16 pairs, written over the score buffer ----
+            const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
+            float ps0 = 0.0f, ps1 = 0.0f;
 #pragma unroll
             for (int c0 = 0; c0 < kT5N; c0 += 32) {
-                uint32_t r[16];
+                uint32_t r[32], w[16];
+                t5_ld32(tS + c0, r);
+                t5_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = s[c0 + 2 * i] == -INFINITY ? 0.0f : exp2f(s[c0 + 2 * i] - m_used);
-                    const float p1 = s[c0 + 2 * i + 1] == -INFINITY ? 0.0f : exp2f(s[c0 + 2 * i + 1] - m_used);
-                    psum += p0 + p1;
-                    r[i] = pack_bf16(p0, p1);
+                    float p0 = t5_ex2(fmaf(__uint_as_float(r[2 * i]), scale_log2, neg_m));
+                    float p1 = t5_ex2(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, neg_m));
+                    if (masked) {
+                        if (c0 + 2 * i > lim) p0 = 0.0f;
+                        if (c0 + 2 * i + 1 > lim) p1 = 0.0f;
+                    }
+                    ps0 += p0; ps1 += p1;
+                    w[i] = pack_bf16(p0, p1);
                 }
-                t5_st16(tS + c0 / 2, r);
+                // chunk c0 of P lands in columns [c0/2, c0/2 + 16) of the score buffer: those columns were read in
+                // an earlier (or this) chunk of this pass, so nothing unread is overwritten
+                t5_st16(tS + c0 / 2, w);
             }
-            l += psum;
+            l += ps0 + ps1;
             t5_wait_st();
             t5_fence_before();
-            t5_arrive(t5_s32(&bars.pready[j & 1]));
+            t5_arrive(t5_s32(&bars.pready[x]));
         }
         // ---- epilogue ----
-        if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (n_tiles - 1) & 1, abort_flag));
-        if (ok && n_tiles > 0) {
+        if (ok && nt > 0) ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone[x]), (nt - 1) & 1, abort_flag));
+        if (ok && nt > 0) {
             t5_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kT5D;
 #pragma unroll
             for (int c0 = 0; c0 < kT5D; c0 += 32) {
                 uint32_t r[32];
-                t5_ld32(tO + lane_base + c0, r);
+                t5_ld32(tO + c0, r);
                 t5_wait_ld();
                 if (row < q_len) {
 #pragma unroll
@@ -375,7 +420,7 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((q_len + kT5M - 1) / kT5M, n_q_heads, n_seqs);
+    dim3 grid((q_len + kT5BlockM - 1) / kT5BlockM, n_q_heads, n_seqs);
     prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err);
     *taken = 1;
     return HS_OK;
