@@ -115,6 +115,39 @@ struct T5Bars {
     uint64_t q, kfull[kT5Stages], vfull[kT5Stages], kvempty[kT5Stages], sfull[2], pready[2], odone[2];
 };
 
+__device__ __forceinline__ uint32_t t5_pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float t5_max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// packed pairs of f32 (sm_100): d = a * b + c and d = a + b on both halves
+__device__ __forceinline__ uint64_t t5_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void t5_unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t t5_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t t5_add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ bool t5_test_wait(uint32_t bar, uint32_t parity) {  // non-blocking probe
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ float t5_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -203,8 +236,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     int j = next_s[x];
-                    if (j < n_tiles[x] && j == next_pv[x] && t5_try_wait(t5_s32(&bars.kfull[j & 1]), (j >> 1) & 1) &&
-                        (j == 0 || t5_try_wait(t5_s32(&bars.odone[x]), (j - 1) & 1))) {
+                    if (j < n_tiles[x] && j == next_pv[x] && t5_test_wait(t5_s32(&bars.kfull[j & 1]), (j >> 1) & 1) &&
+                        (j == 0 || t5_test_wait(t5_s32(&bars.odone[x]), (j - 1) & 1))) {
                         t5_fence_after();
                         const uint32_t sK = sKV + 2 * (j & 1) * kT5TileBytes, sQx = sQ + x * kT5TileBytes;
 #pragma unroll
@@ -217,7 +250,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         progress = true;
                     }
                     j = next_pv[x];
-                    if (j < next_s[x] && t5_try_wait(t5_s32(&bars.pready[x]), j & 1) && t5_try_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1)) {
+                    if (j < next_s[x] && t5_test_wait(t5_s32(&bars.pready[x]), j & 1) && t5_test_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1)) {
                         t5_fence_after();
                         const uint32_t sV = sKV + (2 * (j & 1) + 1) * kT5TileBytes;
 #pragma unroll
@@ -236,6 +269,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 } else if (*abort_flag || clock64() - t_idle > kT5WaitCycles) {
                     *abort_flag = 1;
                     ok = false;
+                } else {
+                    __nanosleep(20);  // leave the issue slots to the softmax warps
                 }
             }
         }
@@ -254,23 +289,32 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int n0 = j * kT5N;
             const bool masked = n0 + kT5N > min(kv_len, off + m0 + x * kT5M + 1);
             const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
-            // ---- pass 1: row maximum ----
+            // ---- pass 1: row maximum (all four loads in flight, one wait) ----
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            {
+                uint32_t r[4][32];
 #pragma unroll
-            for (int c0 = 0; c0 < kT5N; c0 += 32) {
-                uint32_t r[32];
-                t5_ld32(tS + c0, r);
+                for (int c = 0; c < 4; ++c) t5_ld32(tS + 32 * c, r[c]);
                 t5_wait_ld();
+                if (!masked) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float a0 = __uint_as_float(r[i]), a1 = __uint_as_float(r[i + 1]), a2 = __uint_as_float(r[i + 2]), a3 = __uint_as_float(r[i + 3]);
-                    if (masked) {
-                        if (c0 + i > lim) a0 = -INFINITY;
-                        if (c0 + i + 1 > lim) a1 = -INFINITY;
-                        if (c0 + i + 2 > lim) a2 = -INFINITY;
-                        if (c0 + i + 3 > lim) a3 = -INFINITY;
-                    }
-                    mx0 = fmaxf(mx0, a0); mx1 = fmaxf(mx1, a1); mx2 = fmaxf(mx2, a2); mx3 = fmaxf(mx3, a3);
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            mx0 = t5_max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                            mx1 = t5_max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                            mx2 = t5_max3(mx2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                            mx3 = t5_max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+                        }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float a0 = 32 * c + i > lim ? -INFINITY : __uint_as_float(r[c][i]);
+                            const float a1 = 32 * c + i + 1 > lim ? -INFINITY : __uint_as_float(r[c][i + 1]);
+                            mx0 = t5_max3(mx0, a0, a1);
+                        }
                 }
             }
             const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
@@ -301,25 +345,44 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // ---- pass 2: P = exp2(s * scale - m) as bf16 pairs, written over the score buffer ----
             const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
             float ps0 = 0.0f, ps1 = 0.0f;
+            {
+                uint32_t r[4][32];
 #pragma unroll
-            for (int c0 = 0; c0 < kT5N; c0 += 32) {
-                uint32_t r[32], w[16];
-                t5_ld32(tS + c0, r);
-                t5_wait_ld();
+                for (int c = 0; c < 4; ++c) t5_ld32(tS + 32 * c, r[c]);
+                t5_wait_ld();  // the whole score row is in registers: P may now overwrite it
+                if (!masked) {
+                    const uint64_t sc2 = t5_pack2(scale_log2, scale_log2), nm2 = t5_pack2(neg_m, neg_m);
+                    uint64_t acc_a = t5_pack2(0.0f, 0.0f), acc_b = acc_a;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float p0 = t5_ex2(fmaf(__uint_as_float(r[2 * i]), scale_log2, neg_m));
-                    float p1 = t5_ex2(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, neg_m));
-                    if (masked) {
-                        if (c0 + 2 * i > lim) p0 = 0.0f;
-                        if (c0 + 2 * i + 1 > lim) p1 = 0.0f;
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float x0, x1;
+                            t5_unpack2(t5_fma2(t5_pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2), x0, x1);
+                            const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);
+                            if (i & 1) acc_b = t5_add2(acc_b, t5_pack2(p0, p1)); else acc_a = t5_add2(acc_a, t5_pack2(p0, p1));
+                            w[i] = t5_pack_bf16x2(p0, p1);
+                        }
+                        t5_st16(tS + 16 * c, w);
                     }
-                    ps0 += p0; ps1 += p1;
-                    w[i] = pack_bf16(p0, p1);
+                    float a0, a1;
+                    t5_unpack2(t5_add2(acc_a, acc_b), a0, a1);
+                    ps0 = a0; ps1 = a1;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float p0 = 32 * c + 2 * i > lim ? 0.0f : t5_ex2(fmaf(__uint_as_float(r[c][2 * i]), scale_log2, neg_m));
+                            const float p1 = 32 * c + 2 * i + 1 > lim ? 0.0f : t5_ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), scale_log2, neg_m));
+                            ps0 += p0; ps1 += p1;
+                            w[i] = t5_pack_bf16x2(p0, p1);
+                        }
+                        t5_st16(tS + 16 * c, w);
+                    }
                 }
-                // chunk c0 of P lands in columns [c0/2, c0/2 + 16) of the score buffer: those columns were read in
-                // an earlier (or this) chunk of this pass, so nothing unread is overwritten
-                t5_st16(tS + c0 / 2, w);
             }
             l += ps0 + ps1;
             t5_wait_st();
