@@ -5,8 +5,9 @@
 //     S <- exp(g) S;  m = k^T S;  delta = beta (v - m);  S <- S + k delta^T;  o = q^T S
 //   (o is evaluated as q^T(exp(g)S) + (q.k) delta, so S is read once and written once per token)
 //
-// One CTA owns one (sequence, value head) pair and keeps the whole 128 x hv state in registers
-// (64 floats per thread at 128 x 128), so a decode step moves exactly the state once in and once out:
+// One CTA owns 64 of the 128 value columns of one (sequence, value head) pair — the rule is independent per
+// value column — and keeps its 128 x 64 slice of the state in registers (32 floats per thread), several CTAs
+// per SM, so a decode step moves exactly the state once in and once out:
 // 2 * hk * hv * 4 bytes per (sequence, head) — the kernel is HBM-bound on the state.
 // k/q head i feeds value heads [i*r, (i+1)*r), r = n_v_heads / n_k_heads (qwen3_5.rs:704-720).
 #include "hs_common.cuh"
@@ -15,31 +16,33 @@ namespace hs {
 
 constexpr int kGdnThreads = 256;
 constexpr int kGdnWarps = kGdnThreads / 32;
-constexpr int kGdnHV = 128;  // value head dim handled per CTA (one float4 per lane)
+constexpr int kGdnHV = 128;    // value head dim
+constexpr int kGdnCols = 64;   // state columns per CTA: the rule is independent per value column, so a head is cut in two
 
-// HK: key head dim.  Thread (warp w, lane l) holds S[k][v] for k = w + 8*i (i < HK/8), v = 4l .. 4l+3.
+// HK: key head dim.  Thread (warp w, lane l) of column block c holds S[k][v] for k = w + 8*i (i < HK/8), v = 64c + 2l, 2l+1.
 template <int HK>
 __global__ void __launch_bounds__(kGdnThreads)
 gdn_recurrent_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                      const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state,
                      float *__restrict__ out, int n_tokens, int n_k_heads, int n_v_heads) {
     constexpr int R = HK / kGdnWarps;  // rows per thread
-    __shared__ __align__(16) float s_k[2][HK], s_q[2][HK], s_v[2][kGdnHV];
-    __shared__ __align__(16) float s_pm[2][kGdnWarps][kGdnHV], s_pr[2][kGdnWarps][kGdnHV];
+    __shared__ __align__(16) float s_k[2][HK], s_q[2][HK], s_v[2][kGdnCols];
+    __shared__ __align__(16) float s_pm[2][kGdnWarps][kGdnCols], s_pr[2][kGdnWarps][kGdnCols];
     __shared__ float s_gb[2][2];
-    const int b = blockIdx.y, h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y, h = blockIdx.x >> 1, c0 = (blockIdx.x & 1) * kGdnCols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kh = h / (n_v_heads / n_k_heads);
-    float4 S[R];
-    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * HK * kGdnHV;
+    float2 S[R];
+    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * HK * kGdnHV + c0;
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = *reinterpret_cast<const float4 *>(sp + (warp + kGdnWarps * i) * kGdnHV + 4 * lane);
+    for (int i = 0; i < R; ++i) S[i] = *reinterpret_cast<const float2 *>(sp + (warp + kGdnWarps * i) * kGdnHV + 2 * lane);
 
     auto load_token = [&](int t, int buf) {
         const int64_t tok = static_cast<int64_t>(b) * n_tokens + t;
         const float *kp = k + (tok * n_k_heads + kh) * HK, *qp = q + (tok * n_k_heads + kh) * HK;
-        const float *vp = v + (tok * n_v_heads + h) * kGdnHV;
+        const float *vp = v + (tok * n_v_heads + h) * kGdnHV + c0;
         for (int i = threadIdx.x; i < HK; i += kGdnThreads) { s_k[buf][i] = kp[i]; s_q[buf][i] = qp[i]; }
-        for (int i = threadIdx.x; i < kGdnHV; i += kGdnThreads) s_v[buf][i] = vp[i];
+        for (int i = threadIdx.x; i < kGdnCols; i += kGdnThreads) s_v[buf][i] = vp[i];
         if (threadIdx.x == 0) { s_gb[buf][0] = g[tok * n_v_heads + h]; s_gb[buf][1] = beta[tok * n_v_heads + h]; }
     };
     load_token(0, 0);
@@ -56,45 +59,41 @@ gdn_recurrent_kernel(const float *__restrict__ q, const float *__restrict__ k, c
         for (int i = lane; i < HK; i += 32) qk = fmaf(s_q[buf][i], s_k[buf][i], qk);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
-        float4 pm = make_float4(0, 0, 0, 0), pr = make_float4(0, 0, 0, 0);
+        float2 pm = make_float2(0, 0), pr = make_float2(0, 0);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            S[i].x *= decay; S[i].y *= decay; S[i].z *= decay; S[i].w *= decay;
-            pm.x = fmaf(kr[i], S[i].x, pm.x); pm.y = fmaf(kr[i], S[i].y, pm.y); pm.z = fmaf(kr[i], S[i].z, pm.z); pm.w = fmaf(kr[i], S[i].w, pm.w);
-            pr.x = fmaf(qr[i], S[i].x, pr.x); pr.y = fmaf(qr[i], S[i].y, pr.y); pr.z = fmaf(qr[i], S[i].z, pr.z); pr.w = fmaf(qr[i], S[i].w, pr.w);
+            S[i].x *= decay; S[i].y *= decay;
+            pm.x = fmaf(kr[i], S[i].x, pm.x); pm.y = fmaf(kr[i], S[i].y, pm.y);
+            pr.x = fmaf(qr[i], S[i].x, pr.x); pr.y = fmaf(qr[i], S[i].y, pr.y);
         }
-        const float4 vt = *reinterpret_cast<const float4 *>(&s_v[buf][4 * lane]);  // read before the barrier: the
+        const float2 vt = *reinterpret_cast<const float2 *>(&s_v[buf][2 * lane]);  // read before the barrier: the
         // buffer is refilled for token t + 2 by threads that are already one barrier ahead
-        *reinterpret_cast<float4 *>(&s_pm[buf][warp][4 * lane]) = pm;
-        *reinterpret_cast<float4 *>(&s_pr[buf][warp][4 * lane]) = pr;
+        *reinterpret_cast<float2 *>(&s_pm[buf][warp][2 * lane]) = pm;
+        *reinterpret_cast<float2 *>(&s_pr[buf][warp][2 * lane]) = pr;
         __syncthreads();  // partials of this token visible; next token's inputs loaded
-        float4 m = make_float4(0, 0, 0, 0), r = make_float4(0, 0, 0, 0);
+        float2 m = make_float2(0, 0), r = make_float2(0, 0);
 #pragma unroll
         for (int w = 0; w < kGdnWarps; ++w) {
-            const float4 a = *reinterpret_cast<const float4 *>(&s_pm[buf][w][4 * lane]);
-            m.x += a.x; m.y += a.y; m.z += a.z; m.w += a.w;
+            const float2 a = *reinterpret_cast<const float2 *>(&s_pm[buf][w][2 * lane]);
+            m.x += a.x; m.y += a.y;
         }
-        const float4 d = make_float4((vt.x - m.x) * bt, (vt.y - m.y) * bt, (vt.z - m.z) * bt, (vt.w - m.w) * bt);
+        const float2 d = make_float2((vt.x - m.x) * bt, (vt.y - m.y) * bt);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            S[i].x = fmaf(kr[i], d.x, S[i].x); S[i].y = fmaf(kr[i], d.y, S[i].y);
-            S[i].z = fmaf(kr[i], d.z, S[i].z); S[i].w = fmaf(kr[i], d.w, S[i].w);
-        }
+        for (int i = 0; i < R; ++i) { S[i].x = fmaf(kr[i], d.x, S[i].x); S[i].y = fmaf(kr[i], d.y, S[i].y); }
         if (warp == 0) {
 #pragma unroll
             for (int w = 0; w < kGdnWarps; ++w) {
-                const float4 a = *reinterpret_cast<const float4 *>(&s_pr[buf][w][4 * lane]);
-                r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
+                const float2 a = *reinterpret_cast<const float2 *>(&s_pr[buf][w][2 * lane]);
+                r.x += a.x; r.y += a.y;
             }
             const int64_t tok = static_cast<int64_t>(b) * n_tokens + t;
-            *reinterpret_cast<float4 *>(out + (tok * n_v_heads + h) * kGdnHV + 4 * lane) =
-                make_float4(fmaf(qk, d.x, r.x), fmaf(qk, d.y, r.y), fmaf(qk, d.z, r.z), fmaf(qk, d.w, r.w));
+            *reinterpret_cast<float2 *>(out + (tok * n_v_heads + h) * kGdnHV + c0 + 2 * lane) = make_float2(fmaf(qk, d.x, r.x), fmaf(qk, d.y, r.y));
         }
         // the buffers of token t are overwritten by load_token(t + 2) during token t + 1, i.e. after the next
         // barrier; the partial buffers alternate, so one barrier per token is enough
     }
 #pragma unroll
-    for (int i = 0; i < R; ++i) *reinterpret_cast<float4 *>(sp + (warp + kGdnWarps * i) * kGdnHV + 4 * lane) = S[i];
+    for (int i = 0; i < R; ++i) *reinterpret_cast<float2 *>(sp + (warp + kGdnWarps * i) * kGdnHV + 2 * lane) = S[i];
 }
 
 }  // namespace hs
@@ -116,7 +115,7 @@ int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const f
     if (!aligned(state, 16) || !aligned(out, 16) || !aligned(q, 4) || !aligned(k, 4) || !aligned(v, 4))
         return fail(HS_ERR_ARG, "hs_gdn_recurrent: state and out must be 16-byte aligned");
     if (n_seqs > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_gdn_recurrent: more than 65535 sequences");
-    dim3 grid(n_v_heads, n_seqs);
+    dim3 grid(2 * n_v_heads, n_seqs);
     cudaStream_t s = as_stream(stream);
     prof_begin(s);
     if (head_k_dim == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads);
