@@ -344,7 +344,8 @@ constexpr int kMaxPartsPerPair = 2;
 
 // decode_tc.cu: tensor-core kernel for the int8 / head_dim 128 / 8 kv heads / group 4 shape
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
-                           float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out);
+                           float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
+                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out);
 
 template <int KIND, int D, int G>
 static int32_t launch_generic(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
@@ -461,9 +462,10 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     cudaStream_t s = as_stream(stream);
     const uint16_t *qp = reinterpret_cast<const uint16_t *>(q);
     int32_t st;
-    int tile = kDecTile, tc_ctas = 0, ppp = 1;
+    int tile = kDecTile, tc_ctas = 0, ppp = 1, merged = 0;
     prof_begin(s);
-    st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas);
+    st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas,
+                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard, lse_shard, &merged);
     if (st == HS_OK && tc_ctas > 0) {
         n_ctas = tc_ctas;
         tile = 16;
@@ -477,6 +479,7 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     prof_end(s);
     if (st != HS_OK) return st;
     if (int32_t e = check_launch("hs_attn_decode")) return e;
+    if (merged) return HS_OK;  // the decode kernel merged its own partials behind a grid barrier
     if (static_cast<int64_t>(n_ctas) * ppp > kMergeMaxParts) return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode: %d partial slots exceed the merge kernel's table", n_ctas * ppp);
     dim3 mgrid(n_seqs, (n_q_heads + kMergeHeads - 1) / kMergeHeads);
     decode_merge_kernel<<<mgrid, kMergeThreads, 0, s>>>(seq_lens, n_seqs, n_q_heads, D, n_ctas, tile, v.page_tokens * v.pages_per_seq, ppp, o_part,

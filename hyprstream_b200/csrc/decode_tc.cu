@@ -115,6 +115,14 @@ struct TcLayout {
     static constexpr uint32_t kTxBytes = 2u * kTcTile * kRow + 2u * kTcTile * kSRow;
 };
 
+// Outputs of the merge that runs inside the kernel after a grid-wide barrier (cooperative launch only).
+struct TcMergeArgs {
+    int fused;            // 0: partials only (a separate merge kernel follows)
+    uint16_t *out;        // bf16 [n_seqs, Hq, 128] or NULL
+    const uint16_t *gate; // optional
+    float *o_shard, *lse_shard;  // optional fp32 shard outputs
+};
+
 #ifdef HS_TC_TIMING  // diagnostic build only: per-CTA timestamps (ns) written to a harness-owned buffer
 __constant__ unsigned long long *g_tc_timing;
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
@@ -127,7 +135,7 @@ template <int BPR, bool SF16>
 __global__ void __launch_bounds__(kTcThreads, 2)
 decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_t *__restrict__ seq_lens, int n_seqs,
                       int n_q_heads, float kmul, float *__restrict__ o_part, float *__restrict__ lse_part,
-                      int *__restrict__ err) {
+                      int *__restrict__ err, TcMergeArgs mg) {
     using LT = TcLayout<BPR, SF16>;
     extern __shared__ __align__(128) unsigned char smem[];
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + LT::kBarOff + 2 * kTcStages * 8);
@@ -177,10 +185,11 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     const int64_t total = s_pref[n_seqs];
     const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
     const int t_begin = static_cast<int>(part_begin(cta, total, n_ctas)), t_end = static_cast<int>(part_begin(cta + 1, total, n_ctas));
-    if (t_begin >= t_end) return;
+    const bool has_work = t_begin < t_end;
+    if (!has_work && !mg.fused) return;
     // first sequence of this CTA: the largest r with s_pref[r] <= t_begin
-    int r_first = 0;
-    {
+    int r_first = n_seqs;
+    if (has_work) {
         int lo = 0, hi = n_seqs;  // invariant: s_pref[lo] <= t_begin < s_pref[hi]
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
@@ -191,7 +200,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 
     // ---- producer state (warp 0; lanes 0..3 each own one pointer table: K, V, K scales, V scales) ----
     // Page pointers are read one page (or one sequence) ahead so that the load latency never sits in front of a copy.
-    int p_r = r_first, p_tile = t_begin - s_pref[r_first], p_hi = min(t_end, s_pref[r_first + 1]) - s_pref[r_first], p_it = 0;
+    int p_r = r_first, p_tile = 0, p_hi = 0, p_it = 0;
+    if (has_work) { p_tile = t_begin - s_pref[r_first]; p_hi = min(t_end, s_pref[r_first + 1]) - s_pref[r_first]; }
     void *const *p_table = lane == 0 ? view.k_pages : (lane == 1 ? view.v_pages : (lane == 2 ? view.k_scale_pages : view.v_scale_pages));
     int64_t cur_pidx = -1, nxt_pidx = -1;
     const unsigned char *cur_ptr = nullptr, *nxt_ptr = nullptr;
@@ -203,7 +213,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             if (s_pref[r2 + 1] > s_pref[r2]) return static_cast<int64_t>(r2) * view.pages_per_seq;  // later sequences start at their tile 0
         return -1;
     };
-    if (warp == 0 && lane < 4) {
+    if (has_work && warp == 0 && lane < 4) {
         const int page = p_tile * kTcTile / view.page_tokens;
         cur_pidx = static_cast<int64_t>(p_r) * view.pages_per_seq + page;
         cur_ptr = reinterpret_cast<const unsigned char *>(p_table[cur_pidx]);
@@ -247,7 +257,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         return true;
     };
-    const int n_tiles_cta = t_end - t_begin;
+    const int n_tiles_cta = has_work ? t_end - t_begin : 0;
     bool ok = true;
     if (warp == 0)  // fill the ring before anything else touches global memory
         while (ok && p_it < n_tiles_cta && p_it < kTcStages) ok = produce_one();
@@ -479,29 +489,159 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
     }
+    if (!mg.fused) return;
+
+    // ================================ grid barrier, then the log-sum-exp merge ================================
+    // All CTAs are co-resident (cooperative launch).  err[1] counts arrivals, err[2] is the generation; the last
+    // CTA to arrive resets the count and bumps the generation.  The wait is bounded.
+    __shared__ int s_bar_ok;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();  // this CTA's partials are visible device-wide before it is counted
+        volatile int *gen_p = err + 2;
+        const int gen = *gen_p;
+        int good = 1;
+        if (atomicAdd(err + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            atomicExch(err + 1, 0);
+            __threadfence();
+            atomicAdd(err + 2, 1);
+        } else {
+            const long long t0b = clock64();
+            while (*gen_p == gen) {
+                if (clock64() - t0b > kTcWaitCycles) { good = 0; break; }
+                __nanosleep(64);
+            }
+        }
+        __threadfence();
+        s_bar_ok = good;
+    }
+    __syncthreads();
+    if (!s_bar_ok) {
+        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        return;
+    }
+    // work item = (sequence, group of 4 query heads); the slot table and weights live in the (now idle) ring
+    int *m_slot = reinterpret_cast<int *>(smem);
+    float *m_w = reinterpret_cast<float *>(smem + 4096);            // [parts][4]
+    float *m_stat = reinterpret_cast<float *>(smem + 4096 + 32768);  // max[4], den[4]
+    const int groups = n_q_heads / 4;
+    for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
+        const int r = item / groups, h0 = (item - r * groups) * 4;
+        __syncthreads();  // previous item's readers are done with the tables
+        const int64_t before = s_pref[r], nt = s_pref[r + 1] - s_pref[r];
+        // CTAs whose tile range overlaps this sequence: [c_lo, c_hi]; every thread computes the bounds itself
+        int64_t c_lo = 0, c_hi = -1;
+        if (nt > 0) {
+            c_lo = before * n_ctas / total;
+            while (c_lo > 0 && part_begin(c_lo, total, n_ctas) > before) --c_lo;
+            while (part_begin(c_lo + 1, total, n_ctas) <= before) ++c_lo;
+            c_hi = (before + nt - 1) * n_ctas / total;
+            while (c_hi > 0 && part_begin(c_hi, total, n_ctas) > before + nt - 1) --c_hi;
+            while (part_begin(c_hi + 1, total, n_ctas) <= before + nt - 1) ++c_hi;
+        }
+        const int np = c_hi - c_lo + 1 > 1024 ? 1024 : static_cast<int>(c_hi - c_lo + 1);
+        // one thread per (candidate CTA, head): a CTA with an empty range wrote nothing and gets weight 0
+        for (int i = threadIdx.x; i < np * 4; i += kTcThreads) {
+            const int64_t c = c_lo + (i >> 2);
+            const bool wrote = part_begin(c, total, n_ctas) < part_begin(c + 1, total, n_ctas);
+            if ((i & 3) == 0) m_slot[i >> 2] = static_cast<int>(c) + r;
+            m_w[i] = wrote ? __ldcg(lse_part + (c + r) * n_q_heads + h0 + (i & 3)) : -INFINITY;
+        }
+        __syncthreads();
+        if (threadIdx.x < 4) {
+            float M = -INFINITY;
+            for (int pi = 0; pi < np; ++pi) M = fmaxf(M, m_w[pi * 4 + threadIdx.x]);
+            float den = 0.0f;
+            for (int pi = 0; pi < np; ++pi) {
+                const float ls = m_w[pi * 4 + threadIdx.x];
+                const float w = ls == -INFINITY ? 0.0f : __expf(ls - M);
+                m_w[pi * 4 + threadIdx.x] = w;
+                den += w;
+            }
+            m_stat[threadIdx.x] = M;
+            m_stat[4 + threadIdx.x] = den;
+        }
+        __syncthreads();
+        {
+            // thread = (head hh, column pair d2): all loads of a batch of 8 partials are issued before they are used
+            const int hh = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;
+            const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
+            float2 num = make_float2(0.0f, 0.0f);
+            for (int p0 = 0; p0 < np; p0 += 8) {
+                float2 vals[8];
+                float w[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int pi = p0 + u;
+                    w[u] = pi < np ? m_w[pi * 4 + hh] : 0.0f;
+                    vals[u] = w[u] != 0.0f ? __ldcg(reinterpret_cast<const float2 *>(o_part + (static_cast<int64_t>(m_slot[pi]) * n_q_heads + h0 + hh) * 128 + d))
+                                           : make_float2(0.0f, 0.0f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { num.x = fmaf(w[u], vals[u].x, num.x); num.y = fmaf(w[u], vals[u].y, num.y); }
+            }
+            const float den = m_stat[4 + hh];
+            const float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
+            if (mg.o_shard != nullptr) {
+                *reinterpret_cast<float2 *>(mg.o_shard + row * 128 + d) = make_float2(o0, o1);
+                if (d == 0) mg.lse_shard[row] = den > 0.0f ? m_stat[hh] + __logf(den) : -INFINITY;
+            } else {
+                float r0 = o0, r1 = o1;
+                if (mg.gate != nullptr) {  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
+                    const uint32_t gw = *reinterpret_cast<const uint32_t *>(mg.gate + row * 128 + d);
+                    r0 = bf16_round(o0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
+                    r1 = bf16_round(o1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
+                }
+                *reinterpret_cast<uint32_t *>(mg.out + row * 128 + d) = pack_bf16(r0, r1);
+            }
+        }
+    }
 }
 
 template <int BPR, bool SF16>
 static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads, float kmul,
-                         float *o_part, float *lse_part, int *err, int n_ctas, cudaStream_t s) {
+                         float *o_part, float *lse_part, int *err, int n_ctas, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
     using LT = TcLayout<BPR, SF16>;
     auto kern = decode_int8_tc_kernel<BPR, SF16>;
     static bool configured = false;  // per instantiation
+    static bool coop_ok = true;      // cleared when a cooperative launch is refused
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LT::kTotal);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode: %s", cudaGetErrorString(e));
+        int dev = 0, coop = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kTcThreads, LT::kTotal);
+        coop_ok = coop != 0 && per_sm * sm_count() >= n_ctas;
         configured = true;
     }
-    kern<<<n_ctas, kTcThreads, LT::kTotal, s>>>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err);
+    *fused_out = 0;
+    if (coop_ok) {
+        mg.fused = 1;
+        ViewDev vv = v;
+        void *args[] = {&vv, &q, &seq_lens, &n_seqs, &n_q_heads, &kmul, &o_part, &lse_part, &err, &mg};
+        cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
+        if (e == cudaSuccess) {
+            *fused_out = 1;
+            return HS_OK;
+        }
+        cudaGetLastError();  // refused (e.g. the device is shared and cannot hold the whole grid): fall back for good
+        coop_ok = false;
+    }
+    mg.fused = 0;
+    kern<<<n_ctas, kTcThreads, LT::kTotal, s>>>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, mg);
     return HS_OK;
 }
 
 // Returns HS_OK and sets *n_ctas_out (> 0) when the tensor-core kernel took the launch; *n_ctas_out = 0
 // when the shape is not covered and the caller should use the generic kernel.  Each (CTA, sequence) pair
-// writes one partial (slot cta + seq).
+// writes one partial (slot cta + seq).  *merged_out = 1 when the kernel also merged the partials into the
+// outputs (cooperative launch); otherwise the caller runs the merge kernel.
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
-                           float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out) {
+                           float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
+                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out) {
     *n_ctas_out = 0;
+    *merged_out = 0;
     if (v.kind != HS_KV_INT8 || v.head_dim != 128 || v.n_kv_heads != kTcHkv) return HS_OK;
     if (v.page_tokens % kTcTile != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
     if (n_q_heads != kTcG * kTcHkv) return HS_OK;
@@ -510,11 +650,12 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     const int n_ctas = 2 * sm_count();
     const float kmul = softmax_scale * 1.4426950408889634f / 127.0f;
+    TcMergeArgs mg{0, out, gate, o_shard, lse_shard};
     int32_t st;
-    if (bpr == 2 && !sf16) st = launch_tc<2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else if (bpr == 2 && sf16) st = launch_tc<2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else if (bpr == 1 && !sf16) st = launch_tc<1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
-    else st = launch_tc<1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, s);
+    if (bpr == 2 && !sf16) st = launch_tc<2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (bpr == 2 && sf16) st = launch_tc<2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (bpr == 1 && !sf16) st = launch_tc<1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else st = launch_tc<1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
     if (st == HS_OK) *n_ctas_out = n_ctas;
     return st;
 }

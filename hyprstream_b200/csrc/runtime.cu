@@ -6,7 +6,8 @@
 namespace hs {
 
 static thread_local char g_err[512] = "";
-static __device__ int g_device_error;
+// word 0: error flags; words 1, 2: arrival count and generation of the grid barrier used by fused kernels
+static __device__ int g_device_error[4];
 
 int *device_error_word() {
     int *p = nullptr;
@@ -144,7 +145,10 @@ int32_t hs_attn_take_device_error(int32_t *flags) {
     if (int32_t st = hs::check_device()) return st;
     int v = 0, zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, hs::g_device_error, sizeof v);
-    if (e == cudaSuccess && v != 0) e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero);
+    if (e == cudaSuccess && v != 0) {
+        e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero);                   // clear the flags
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero, sizeof(int));  // and a barrier count a timed-out kernel may have left
+    }
     if (e != cudaSuccess) return hs::fail(static_cast<int32_t>(e), "hs_attn_take_device_error: %s", cudaGetErrorString(e));
     *flags = v;
     return HS_OK;
