@@ -1,5 +1,6 @@
-// Int8-KV decode attention for head_dim 128, 8 kv heads, 4 query heads per kv head: a persistent,
-// warp-specialised kernel.
+// Quantised-KV (int8, NF4, FP4) decode attention for head_dim 128, 8 kv heads, 4 query heads per kv head: a
+// persistent, warp-specialised kernel.  (The int8 form is described; the 4-bit form differs only in how codes
+// become fp16: one lookup per byte in a 256-entry fp16x2 table replicated per lane in shared memory.)
 //
 //   * two CTAs per SM (while one winds up a sequence or starts the next, the other keeps streaming); the
 //     tokens of ALL sequences, cut into 16-token tiles, are divided evenly over the CTAs (flat split-KV),
@@ -28,7 +29,6 @@
 namespace hs {
 
 constexpr int kTcTile = 16;    // tokens per stage
-constexpr int kTcStages = 3;
 constexpr int kTcHkv = 8;
 constexpr int kTcG = 4;
 constexpr int kTcConsumers = kTcHkv;  // every warp consumes; warp 0 also issues the copies
@@ -99,19 +99,24 @@ __device__ __forceinline__ float h2_sum(uint32_t w) {
 }
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-template <int BPR, bool SF16>
+// FOURBIT = false: u8 codes (128 B per head row).  FOURBIT = true: NF4 / FP4 codes (64 B per head row), widened through a
+// 256-entry byte -> fp16x2 table replicated per lane (bank-conflict-free lookups).
+template <bool FOURBIT, int BPR, bool SF16>
 struct TcLayout {
-    static constexpr int kRow = kTcHkv * 128;                    // bytes of one token row of codes
+    static constexpr int kStages = FOURBIT ? 4 : 3;
+    static constexpr int kHeadRow = FOURBIT ? 64 : 128;          // code bytes of one (token, head) row
+    static constexpr int kRow = kTcHkv * kHeadRow;               // bytes of one token row of codes
     static constexpr int kSRow = kTcHkv * BPR * (SF16 ? 2 : 4);  // scale bytes per token
     static constexpr int kKOff = 0;
     static constexpr int kVOff = kTcTile * kRow;
     static constexpr int kKsOff = 2 * kTcTile * kRow;
     static constexpr int kVsOff = kKsOff + kTcTile * kSRow;
     static constexpr int kStage = (kVsOff + kTcTile * kSRow + 127) / 128 * 128;
-    static constexpr int kBarOff = kTcStages * kStage;
-    static constexpr int kPrefOff = kBarOff + 2 * kTcStages * 8 + 16;  // int tile-count prefix [kTcMaxSeqs + 1]
+    static constexpr int kBarOff = kStages * kStage;
+    static constexpr int kPrefOff = kBarOff + 2 * kStages * 8 + 16;    // int tile-count prefix [kTcMaxSeqs + 1]
     static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
-    static constexpr int kTotal = kLenOff + kTcMaxSeqs * 4;
+    static constexpr int kLutOff = (kLenOff + kTcMaxSeqs * 4 + 127) / 128 * 128;  // uint32 [256][32] (4-bit kinds only)
+    static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
     static constexpr uint32_t kTxBytes = 2u * kTcTile * kRow + 2u * kTcTile * kSRow;
 };
 
@@ -131,12 +136,13 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define HS_TC_STAMP(slot) do {} while (0)
 #endif
 
-template <int BPR, bool SF16>
+template <bool FOURBIT, int BPR, bool SF16>
 __global__ void __launch_bounds__(kTcThreads, 2)
 decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_t *__restrict__ seq_lens, int n_seqs,
                       int n_q_heads, float kmul, float *__restrict__ o_part, float *__restrict__ lse_part,
                       int *__restrict__ err, TcMergeArgs mg) {
-    using LT = TcLayout<BPR, SF16>;
+    using LT = TcLayout<FOURBIT, BPR, SF16>;
+    constexpr int kTcStages = LT::kStages;
     extern __shared__ __align__(128) unsigned char smem[];
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + LT::kBarOff + 2 * kTcStages * 8);
     int *s_pref = reinterpret_cast<int *>(smem + LT::kPrefOff);
@@ -156,6 +162,13 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         s_pref[i + 1] = (s_len[i] + kTcTile - 1) / kTcTile;
     }
     if (over && blockIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
+    const uint32_t *s_lut = reinterpret_cast<const uint32_t *>(smem + LT::kLutOff) + lane;  // entry of byte x: s_lut[32 x]
+    if constexpr (FOURBIT) {
+        // byte -> (table[high nibble], table[low nibble]) as fp16x2, low half = the even (first) element
+        const float *tab = view.kind == HS_KV_NF4 ? c_nf4 : c_fp4;
+        uint32_t *lut = reinterpret_cast<uint32_t *>(smem + LT::kLutOff);
+        for (int i = threadIdx.x; i < 256 * 32; i += kTcThreads) lut[i] = pack_h2(tab[(i >> 5) >> 4], tab[(i >> 5) & 15]);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -265,7 +278,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     // ================================ consumer warps ================================
     const int head = warp;
     const int g = lane >> 2, j = lane & 3;
-    const float vmul = 1.0f / 127.0f;
+    const float vmul = FOURBIT ? 1.0f : 1.0f / 127.0f;  // u8 codes are (code - 127): the 1/127 of the codebook goes here
     int it = 0;
     int seg_idx = 0;
     (void)seg_idx;
@@ -303,7 +316,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         for (int b = 0; b < 2; ++b) {
             qsum[b] += __shfl_xor_sync(0xffffffffu, qsum[b], 1);
             qsum[b] += __shfl_xor_sync(0xffffffffu, qsum[b], 2);
-            qsum[b] *= 1151.0f;
+            qsum[b] *= FOURBIT ? 0.0f : 1151.0f;  // the 4-bit table values carry no bias
         }
         // pull the next sequence's query rows towards L1 now, so that the segment switch does not wait on L2
         if (g < kTcG) {
@@ -348,14 +361,29 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     for (int b = 0; b < 2; ++b) sacc[nt][b][0] = sacc[nt][b][1] = sacc[nt][b][2] = sacc[nt][b][3] = 0.0f;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const unsigned char *krow = sK + (tl0 + nt * 8 + g) * LT::kRow + head * 128 + 16 * j;
+                    if constexpr (!FOURBIT) {
+                        const unsigned char *krow = sK + (tl0 + nt * 8 + g) * LT::kRow + head * 128 + 16 * j;
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint4 kv = *reinterpret_cast<const uint4 *>(krow + 64 * b);
-                        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+                        for (int b = 0; b < 2; ++b) {
+                            const uint4 kv = *reinterpret_cast<const uint4 *>(krow + 64 * b);
+                            const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-                        for (int s = 0; s < 4; ++s)
-                            mma_rows8(sacc[nt][b], qa[b][s][0], qa[b][s][1], codes_biased_h2(kw[s], 0x4140), codes_biased_h2(kw[s], 0x4342));
+                            for (int s = 0; s < 4; ++s)
+                                mma_rows8(sacc[nt][b], qa[b][s][0], qa[b][s][1], codes_biased_h2(kw[s], 0x4140), codes_biased_h2(kw[s], 0x4342));
+                        }
+                    } else {
+                        // 16 codes = 8 bytes per (block, lane); byte 2s holds d = 4s, 4s+1 and byte 2s+1 holds d = 4s+2, 4s+3
+                        const unsigned char *krow = sK + (tl0 + nt * 8 + g) * LT::kRow + head * 64 + 8 * j;
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            const uint2 kv = *reinterpret_cast<const uint2 *>(krow + 32 * b);
+#pragma unroll
+                            for (int s = 0; s < 4; ++s) {
+                                const uint32_t w = s < 2 ? kv.x : kv.y;
+                                const uint32_t b0 = s_lut[((w >> (16 * (s & 1))) & 0xffu) << 5], b1 = s_lut[((w >> (16 * (s & 1) + 8)) & 0xffu) << 5];
+                                mma_rows8(sacc[nt][b], qa[b][s][0], qa[b][s][1], b0, b1);
+                            }
+                        }
                     }
                 }
                 // ---- scales of this thread's 4 tokens, scores in the exp2 domain, masking ----
@@ -414,22 +442,40 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     const uint32_t b0 = pack_h2(p[0][0] * pv[0][0][b], p[0][1] * pv[0][1][b]);
                     const uint32_t b1 = pack_h2(p[1][0] * pv[1][0][b], p[1][1] * pv[1][1][b]);
                     ps_part[b] += h2_sum(b0) + h2_sum(b1);
-                    uint2 x[2][2];
+                    if constexpr (!FOURBIT) {
+                        uint2 x[2][2];
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
+                        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                        for (int e = 0; e < 2; ++e)
-                            x[nt][e] = *reinterpret_cast<const uint2 *>(sV + (tl0 + nt * 8 + 2 * j + e) * LT::kRow + head * 128 + 64 * b + 8 * g);
+                            for (int e = 0; e < 2; ++e)
+                                x[nt][e] = *reinterpret_cast<const uint2 *>(sV + (tl0 + nt * 8 + 2 * j + e) * LT::kRow + head * 128 + 64 * b + 8 * g);
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const uint32_t A0 = k ? x[0][0].y : x[0][0].x, B0 = k ? x[0][1].y : x[0][1].x;
-                        const uint32_t A1 = k ? x[1][0].y : x[1][0].x, B1 = k ? x[1][1].y : x[1][1].x;
-                        const uint32_t t01 = __byte_perm(A0, B0, 0x5140), t23 = __byte_perm(A0, B0, 0x7362);
-                        const uint32_t u01 = __byte_perm(A1, B1, 0x5140), u23 = __byte_perm(A1, B1, 0x7362);
-                        mma_full(O[4 * b + 2 * k + 0], codes_biased_h2(t01, 0x4140), codes_biased_h2(t01, 0x4342),
-                                 codes_biased_h2(u01, 0x4140), codes_biased_h2(u01, 0x4342), b0, b1);
-                        mma_full(O[4 * b + 2 * k + 1], codes_biased_h2(t23, 0x4140), codes_biased_h2(t23, 0x4342),
-                                 codes_biased_h2(u23, 0x4140), codes_biased_h2(u23, 0x4342), b0, b1);
+                        for (int k = 0; k < 2; ++k) {
+                            const uint32_t A0 = k ? x[0][0].y : x[0][0].x, B0 = k ? x[0][1].y : x[0][1].x;
+                            const uint32_t A1 = k ? x[1][0].y : x[1][0].x, B1 = k ? x[1][1].y : x[1][1].x;
+                            const uint32_t t01 = __byte_perm(A0, B0, 0x5140), t23 = __byte_perm(A0, B0, 0x7362);
+                            const uint32_t u01 = __byte_perm(A1, B1, 0x5140), u23 = __byte_perm(A1, B1, 0x7362);
+                            mma_full(O[4 * b + 2 * k + 0], codes_biased_h2(t01, 0x4140), codes_biased_h2(t01, 0x4342),
+                                     codes_biased_h2(u01, 0x4140), codes_biased_h2(u01, 0x4342), b0, b1);
+                            mma_full(O[4 * b + 2 * k + 1], codes_biased_h2(t23, 0x4140), codes_biased_h2(t23, 0x4342),
+                                     codes_biased_h2(u23, 0x4140), codes_biased_h2(u23, 0x4342), b0, b1);
+                        }
+                    } else {
+                        // this lane's 8 values d = 64b + 8g .. +7 of a token are 4 bytes; byte k holds d = 8g + 2k (row g of
+                        // m-tile k) and 8g + 2k + 1 (row g + 8)
+                        uint32_t x[2][2];
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                x[nt][e] = *reinterpret_cast<const uint32_t *>(sV + (tl0 + nt * 8 + 2 * j + e) * LT::kRow + head * 64 + 32 * b + 4 * g);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t la = s_lut[((x[0][0] >> (8 * k)) & 0xffu) << 5], lb = s_lut[((x[0][1] >> (8 * k)) & 0xffu) << 5];
+                            const uint32_t lc = s_lut[((x[1][0] >> (8 * k)) & 0xffu) << 5], ld = s_lut[((x[1][1] >> (8 * k)) & 0xffu) << 5];
+                            mma_full(O[4 * b + k], __byte_perm(la, lb, 0x5410), __byte_perm(la, lb, 0x7632), __byte_perm(lc, ld, 0x5410),
+                                     __byte_perm(lc, ld, 0x7632), b0, b1);
+                        }
                     }
                 }
             }
@@ -446,7 +492,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         for (int b = 0; b < 2; ++b) {
             ps_part[b] += __shfl_xor_sync(0xffffffffu, ps_part[b], 1);
             ps_part[b] += __shfl_xor_sync(0xffffffffu, ps_part[b], 2);
-            ps_part[b] *= 1151.0f;
+            ps_part[b] *= FOURBIT ? 0.0f : 1151.0f;
         }
         // per-head values (row layout: lane 4*head') -> the lanes that hold heads 2j, 2j+1 in their accumulators
         const float l0 = __shfl_sync(0xffffffffu, l, 8 * j), l1 = __shfl_sync(0xffffffffu, l, 8 * j + 4);
@@ -598,11 +644,11 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     }
 }
 
-template <int BPR, bool SF16>
+template <bool FOURBIT, int BPR, bool SF16>
 static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads, float kmul,
                          float *o_part, float *lse_part, int *err, int n_ctas, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
-    using LT = TcLayout<BPR, SF16>;
-    auto kern = decode_int8_tc_kernel<BPR, SF16>;
+    using LT = TcLayout<FOURBIT, BPR, SF16>;
+    auto kern = decode_int8_tc_kernel<FOURBIT, BPR, SF16>;
     static bool configured = false;  // per instantiation
     static bool coop_ok = true;      // cleared when a cooperative launch is refused
     if (!configured) {
@@ -642,20 +688,24 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
                            uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out) {
     *n_ctas_out = 0;
     *merged_out = 0;
-    if (v.kind != HS_KV_INT8 || v.head_dim != 128 || v.n_kv_heads != kTcHkv) return HS_OK;
+    if (v.kind == HS_KV_BF16 || v.head_dim != 128 || v.n_kv_heads != kTcHkv) return HS_OK;
     if (v.page_tokens % kTcTile != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
     if (n_q_heads != kTcG * kTcHkv) return HS_OK;
+    const bool four = v.kind != HS_KV_INT8;
     const int bpr = 128 / v.block;
     if (bpr != 1 && bpr != 2) return HS_OK;
+    if (four && bpr != 2) return HS_OK;  // 4-bit caches use the reference's block of 64
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     const int n_ctas = 2 * sm_count();
-    const float kmul = softmax_scale * 1.4426950408889634f / 127.0f;
+    const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
     TcMergeArgs mg{0, out, gate, o_shard, lse_shard};
     int32_t st;
-    if (bpr == 2 && !sf16) st = launch_tc<2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (bpr == 2 && sf16) st = launch_tc<2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (bpr == 1 && !sf16) st = launch_tc<1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else st = launch_tc<1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    if (four && !sf16) st = launch_tc<true, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (four) st = launch_tc<true, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (bpr == 2 && !sf16) st = launch_tc<false, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (bpr == 2 && sf16) st = launch_tc<false, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else if (bpr == 1 && !sf16) st = launch_tc<false, 1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+    else st = launch_tc<false, 1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
     if (st == HS_OK) *n_ctas_out = n_ctas;
     return st;
 }
