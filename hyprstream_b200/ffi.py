@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libhs_attn.so")
 
 HS_OK = 0
 HS_ERR_ARG, HS_ERR_UNSUPPORTED, HS_ERR_DEVICE, HS_ERR_WORKSPACE = -1, -2, -3, -4
+HS_ERR_POOL_EXHAUSTED, HS_ERR_CACHE_OVERFLOW, HS_ERR_CACHE_EMPTY = -5, -6, -7
 KV_BF16, KV_INT8, KV_NF4, KV_FP4 = 0, 1, 2, 3
 SCALE_F32, SCALE_F16 = 0, 1
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
@@ -60,6 +61,26 @@ _SIGS = {
     "hs_attn_decode_static": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p]),
     "hs_attn_prefill_causal": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_float, c_void_p]),
     "hs_gdn_recurrent": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
+    "hs_host_set_allocator": (c_int32, [c_void_p, c_void_p]),
+    "hs_pool_create": (c_int32, [c_int32] * 7 + [POINTER(c_void_p)]),
+    "hs_pool_destroy": (None, [c_void_p]),
+    "hs_pool_num_free": (c_int32, [c_void_p]),
+    "hs_cache_create": (c_int32, [c_int32] * 6 + [POINTER(c_void_p)]),
+    "hs_cache_create_paged": (c_int32, [c_int32, c_void_p, c_int64, POINTER(c_void_p)]),
+    "hs_cache_destroy": (None, [c_void_p]),
+    "hs_cache_update": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    "hs_cache_get": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hs_cache_reserve": (c_int32, [c_void_p, c_int32]),
+    "hs_cache_clear": (c_int32, [c_void_p]),
+    "hs_cache_truncate_to": (c_int32, [c_void_p, c_int32]),
+    "hs_cache_seq_pos": (c_int32, [c_void_p]),
+    "hs_cache_set_seq_pos": (c_int32, [c_void_p, c_int32]),
+    "hs_cache_capacity": (c_int32, [c_void_p]),
+    "hs_cache_num_pages": (c_int32, [c_void_p]),
+    "hs_cache_memory_usage": (c_int64, [c_void_p]),
+    "hs_view_create": (c_int32, [POINTER(c_void_p), c_int32, POINTER(c_void_p)]),
+    "hs_view_get": (c_void_p, [c_void_p]),
+    "hs_view_destroy": (None, [c_void_p]),
     "hs_attn_merge_partials": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
 }
 

@@ -39,6 +39,9 @@ typedef void *hs_stream_t; /* a cudaStream_t; NULL = default stream (cf. bnb_str
 #define HS_ERR_UNSUPPORTED (-2) /* head_dim / group / block combination with no kernel */
 #define HS_ERR_DEVICE (-3)    /* current device is not sm_100 */
 #define HS_ERR_WORKSPACE (-4) /* workspace too small */
+#define HS_ERR_POOL_EXHAUSTED (-5) /* block pool has no free page (typed, fail-soft: kv_cache.rs:482-505) */
+#define HS_ERR_CACHE_OVERFLOW (-6) /* update past max_seq_len (kv_cache.rs:1288-1294) */
+#define HS_ERR_CACHE_EMPTY (-7)    /* get() on an empty cache (kv_cache.rs:1500-1503) */
 
 /* storage kinds: mirrors KVQuantType {None, Int8, Nf4, Fp4}
  * (crates/hyprstream-rpc-std/schema/model.capnp:252-257; kv_cache.rs:741-788) */
@@ -204,6 +207,49 @@ int32_t hs_attn_prefill_causal(const void *q, const void *k, const void *v, void
 int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
                          float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
                          int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
+
+/* ---- host-side cache objects ------------------------------------------------------------------
+ * C++ mirror of the reference's per-layer cache (crates/hyprstream/src/runtime/kv_cache.rs): LayerKVCache
+ * (:1029-1900: new / new_paged / update / get / clear / truncate_to / seq_pos / memory_usage) and BlockPool
+ * (:477-680: fixed 256-token pages, LIFO free list, owner tags, typed exhaustion with roll-back).  Storage is
+ * device-resident and token-granular for every kind (quantised + paged allowed).  These objects own device
+ * memory (cudaMalloc on the device current at creation, or the allocator installed with
+ * hs_host_set_allocator, e.g. libtorch's caching allocator); the kernels above never allocate.
+ * Handles are opaque; all calls on one cache must come from one thread at a time, like the reference's
+ * (inference/local.rs:84-85).  */
+typedef struct hs_pool hs_pool;
+typedef struct hs_cache hs_cache;
+typedef struct hs_view hs_view;
+typedef void *(*hs_alloc_fn)(size_t bytes);  /* returns device memory or NULL */
+typedef void (*hs_free_fn)(void *ptr);
+int32_t hs_host_set_allocator(hs_alloc_fn alloc_fn, hs_free_fn free_fn); /* NULL, NULL restores cudaMalloc / cudaFree */
+
+int32_t hs_pool_create(int32_t n_blocks, int32_t page_tokens, int32_t kind, int32_t block, int32_t scale_dtype,
+                       int32_t n_kv_heads, int32_t head_dim, hs_pool **out);
+void hs_pool_destroy(hs_pool *pool);
+int32_t hs_pool_num_free(const hs_pool *pool);
+
+int32_t hs_cache_create(int32_t max_seq_len, int32_t kind, int32_t block, int32_t scale_dtype, int32_t n_kv_heads,
+                        int32_t head_dim, hs_cache **out);                                  /* LayerKVCache::new */
+int32_t hs_cache_create_paged(int32_t max_seq_len, hs_pool *pool, int64_t owner, hs_cache **out); /* ::new_paged */
+void hs_cache_destroy(hs_cache *cache); /* returns pages to the pool (Drop, kv_cache.rs:1889-1898) */
+/* k_new, v_new: bf16 [1, n_tokens, n_kv_heads, head_dim] on the device; sin/cos optional (fused K RoPE). */
+int32_t hs_cache_update(hs_cache *cache, const void *k_new, const void *v_new, int32_t n_tokens, int32_t start_pos,
+                        const void *sin, const void *cos, int32_t rotary_dim, int32_t n_positions, hs_stream_t stream);
+/* k_out, v_out: bf16 [1, seq_pos, n_kv_heads, head_dim] device buffers of the caller. */
+int32_t hs_cache_get(hs_cache *cache, void *k_out, void *v_out, hs_stream_t stream);
+int32_t hs_cache_reserve(hs_cache *cache, int32_t n_tokens); /* grow capacity (1024-token chunks / pages) */
+int32_t hs_cache_clear(hs_cache *cache);
+int32_t hs_cache_truncate_to(hs_cache *cache, int32_t n_tokens);
+int32_t hs_cache_seq_pos(const hs_cache *cache);
+int32_t hs_cache_set_seq_pos(hs_cache *cache, int32_t n_tokens); /* after writing through a view directly */
+int32_t hs_cache_capacity(const hs_cache *cache);
+int32_t hs_cache_num_pages(const hs_cache *cache);
+int64_t hs_cache_memory_usage(const hs_cache *cache);
+/* One hs_kv_view over the caches of a batch (one sequence each); the handle owns the device pointer tables. */
+int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out);
+const hs_kv_view *hs_view_get(const hs_view *view);
+void hs_view_destroy(hs_view *view);
 
 #ifdef __cplusplus
 }
