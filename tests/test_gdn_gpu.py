@@ -86,7 +86,9 @@ def test_decode_steps_equal_one_multi_token_call(cuda):
     s_b = s0.clone().to(cuda)
     outs = [ops.gdn_recurrent(*(x[:, i:i + 1].contiguous() for x in dev), s_b) for i in range(256)]
     torch.cuda.synchronize()
-    assert torch.equal(torch.cat(outs, 1), out_a) and torch.equal(s_a, s_b)
+    # the single-token and the multi-token kernels sum in different orders: equal to fp32 round-off, not bit for bit
+    assert (torch.cat(outs, 1) - out_a).abs().max().item() <= 1e-5
+    assert (s_a - s_b).abs().max().item() <= 1e-5 * max(1.0, s_a.abs().max().item())
 
 
 def test_rejects_unsupported_geometry(cuda):
