@@ -80,7 +80,7 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     __syncthreads();
 
     const int kvh = blockIdx.y, H = view.n_kv_heads;
-    const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
+    const int64_t cta = blockIdx.x;
     const int cap = view.page_tokens * view.pages_per_seq;  // lengths beyond the view's pages are cut (and recorded)
     int64_t total = 0;
     bool over = false;
@@ -89,6 +89,9 @@ decode_generic_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         total += ceil_div_i(min(max(seq_lens[r], 0), cap), kDecTile);
     }
     if (over && threadIdx.x == 0 && cta == 0 && kvh == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
+    // never more working CTAs than tiles (the merge uses the same rule)
+    const int64_t n_ctas = total < static_cast<int64_t>(gridDim.x) ? (total > 0 ? total : 1) : static_cast<int64_t>(gridDim.x);
+    if (cta >= n_ctas) return;
     const int64_t t_begin = part_begin(cta, total, n_ctas), t_end = part_begin(cta + 1, total, n_ctas);
     if (t_begin >= t_end) return;
 
@@ -256,6 +259,7 @@ decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_he
         before += __shfl_xor_sync(0xffffffffu, before, off);
     }
     const long long nt = ceil_div_i(min(max(seq_lens[r], 0), cap), tile);
+    if (total < n_ctas) n_ctas = total > 0 ? static_cast<int>(total) : 1;  // the decode kernels never use more CTAs than tiles
     if (threadIdx.x == 0) {
         // CTAs whose tile range overlaps [before, before + nt); a CTA with an empty range wrote nothing
         int n = 0;

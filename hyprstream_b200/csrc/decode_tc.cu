@@ -75,6 +75,18 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// The cache is read once per step: its copies carry an evict-first L2 policy so that they do not push the partials
+// (written early, read back by the merge) out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+                 : "memory");
+}
 // D += A.B, m16n8k16, fp16 operands, fp32 accumulate.  A rows 8..15 unused (a1 = a3 = 0).
 __device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -174,6 +186,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, kTcConsumers);
         }
+        mbar_init(bar_full + 2 * kTcStages * 8 + 8, 1);  // the merge's staging barrier
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -196,9 +209,11 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     }
     __syncthreads();
     const int64_t total = s_pref[n_seqs];
-    const int64_t cta = blockIdx.x, n_ctas = gridDim.x;
+    // never more working CTAs than tiles: every CTA below n_ctas owns at least one tile and writes its partials
+    const int64_t cta = blockIdx.x;
+    const int64_t n_ctas = total < static_cast<int64_t>(gridDim.x) ? (total > 0 ? total : 1) : static_cast<int64_t>(gridDim.x);
     const int t_begin = static_cast<int>(part_begin(cta, total, n_ctas)), t_end = static_cast<int>(part_begin(cta + 1, total, n_ctas));
-    const bool has_work = t_begin < t_end;
+    const bool has_work = cta < n_ctas && t_begin < t_end;
     if (!has_work && !mg.fused) return;
     // first sequence of this CTA: the largest r with s_pref[r] <= t_begin
     int r_first = n_seqs;
@@ -216,6 +231,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     int p_r = r_first, p_tile = 0, p_hi = 0, p_it = 0;
     if (has_work) { p_tile = t_begin - s_pref[r_first]; p_hi = min(t_end, s_pref[r_first + 1]) - s_pref[r_first]; }
     void *const *p_table = lane == 0 ? view.k_pages : (lane == 1 ? view.v_pages : (lane == 2 ? view.k_scale_pages : view.v_scale_pages));
+    const uint64_t stream_policy = l2_evict_first_policy();
     int64_t cur_pidx = -1, nxt_pidx = -1;
     const unsigned char *cur_ptr = nullptr, *nxt_ptr = nullptr;
     // index of the page that follows page `page` of sequence r inside this CTA's range, or -1
@@ -253,9 +269,9 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             if (lane == 0) mbar_expect_tx(full, LT::kTxBytes);
             __syncwarp(0xfu);
             if (lane < 2)
-                bulk_g2s(sbase + (lane ? LT::kVOff : LT::kKOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kRow, kTcTile * LT::kRow, full);
+                bulk_g2s_hint(sbase + (lane ? LT::kVOff : LT::kKOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kRow, kTcTile * LT::kRow, full, stream_policy);
             else
-                bulk_g2s(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kSRow, kTcTile * LT::kSRow, full);
+                bulk_g2s_hint(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kSRow, kTcTile * LT::kSRow, full, stream_policy);
         }
         __syncwarp();
         ++p_it;
@@ -566,80 +582,84 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
         return;
     }
-    // work item = (sequence, group of 4 query heads); the slot table and weights live in the (now idle) ring
-    int *m_slot = reinterpret_cast<int *>(smem);
-    float *m_w = reinterpret_cast<float *>(smem + 4096);            // [parts][4]
-    float *m_stat = reinterpret_cast<float *>(smem + 4096 + 32768);  // max[4], den[4]
+    // Work item = (sequence, group of 4 query heads).  The ring is idle now: the item's partials (2 KB of outputs and 16
+    // bytes of log-sum-exps per contributing CTA) are brought into it with bulk copies that are all in flight at once, up
+    // to kChunk partials per round, so the merge costs one trip to L2 instead of one per batch of loads.
+    constexpr int kChunk = 32;
+    static_assert(kChunk * 2064 <= LT::kBarOff, "merge staging must fit in the ring");
+    float *m_val = reinterpret_cast<float *>(smem);                  // [kChunk][4][128]
+    float *m_lse = reinterpret_cast<float *>(smem + kChunk * 2048);  // [kChunk][4]
+    const uint32_t bar_merge = bar_full + 2 * kTcStages * 8 + 8;
+    uint32_t mphase = 0;
+    asm volatile("fence.proxy.async;" ::: "memory");  // partials were written with ordinary stores, the copies read them through the async proxy
     const int groups = n_q_heads / 4;
+    const bool small = total * n_ctas < (1LL << 31);  // 32-bit divisions when they are exact
+    auto pbegin = [&](int64_t c) -> int64_t {
+        return small ? static_cast<int64_t>(static_cast<uint32_t>(c) * static_cast<uint32_t>(total) / static_cast<uint32_t>(n_ctas)) : part_begin(c, total, n_ctas);
+    };
+    auto owner = [&](int64_t t) -> int64_t {  // the CTA whose range holds tile t
+        int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(t) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(total)) : t * n_ctas / total;
+        while (c > 0 && pbegin(c) > t) --c;
+        while (pbegin(c + 1) <= t) ++c;
+        return c;
+    };
     for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
         const int r = item / groups, h0 = (item - r * groups) * 4;
-        __syncthreads();  // previous item's readers are done with the tables
         const int64_t before = s_pref[r], nt = s_pref[r + 1] - s_pref[r];
-        // CTAs whose tile range overlaps this sequence: [c_lo, c_hi]; every thread computes the bounds itself
-        int64_t c_lo = 0, c_hi = -1;
+        int64_t c_lo = 0;
+        int np = 0;
         if (nt > 0) {
-            c_lo = before * n_ctas / total;
-            while (c_lo > 0 && part_begin(c_lo, total, n_ctas) > before) --c_lo;
-            while (part_begin(c_lo + 1, total, n_ctas) <= before) ++c_lo;
-            c_hi = (before + nt - 1) * n_ctas / total;
-            while (c_hi > 0 && part_begin(c_hi, total, n_ctas) > before + nt - 1) --c_hi;
-            while (part_begin(c_hi + 1, total, n_ctas) <= before + nt - 1) ++c_hi;
+            c_lo = owner(before);
+            np = static_cast<int>(owner(before + nt - 1) - c_lo + 1);
         }
-        const int np = c_hi - c_lo + 1 > 1024 ? 1024 : static_cast<int>(c_hi - c_lo + 1);
-        // one thread per (candidate CTA, head): a CTA with an empty range wrote nothing and gets weight 0
-        for (int i = threadIdx.x; i < np * 4; i += kTcThreads) {
-            const int64_t c = c_lo + (i >> 2);
-            const bool wrote = part_begin(c, total, n_ctas) < part_begin(c + 1, total, n_ctas);
-            if ((i & 3) == 0) m_slot[i >> 2] = static_cast<int>(c) + r;
-            m_w[i] = wrote ? __ldcg(lse_part + (c + r) * n_q_heads + h0 + (i & 3)) : -INFINITY;
-        }
-        __syncthreads();
-        if (threadIdx.x < 4) {
-            float M = -INFINITY;
-            for (int pi = 0; pi < np; ++pi) M = fmaxf(M, m_w[pi * 4 + threadIdx.x]);
-            float den = 0.0f;
-            for (int pi = 0; pi < np; ++pi) {
-                const float ls = m_w[pi * 4 + threadIdx.x];
-                const float w = ls == -INFINITY ? 0.0f : __expf(ls - M);
-                m_w[pi * 4 + threadIdx.x] = w;
-                den += w;
+        const int hh = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;  // thread = (head, column pair)
+        float M = -INFINITY, den = 0.0f;
+        float2 num = make_float2(0.0f, 0.0f);
+        for (int p0 = 0; p0 < np; p0 += kChunk) {
+            const int n = min(kChunk, np - p0);
+            __syncthreads();  // the previous round's readers are done with the staging area
+            if (threadIdx.x == 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(n) * 2064u);
+            __syncthreads();
+            if (threadIdx.x < n) {
+                const int64_t slot = c_lo + p0 + threadIdx.x + r;
+                bulk_g2s(smem_u32(m_val + threadIdx.x * 512), o_part + (slot * n_q_heads + h0) * 128, 2048u, bar_merge);
+                bulk_g2s(smem_u32(m_lse + threadIdx.x * 4), lse_part + slot * n_q_heads + h0, 16u, bar_merge);
             }
-            m_stat[threadIdx.x] = M;
-            m_stat[4 + threadIdx.x] = den;
-        }
-        __syncthreads();
-        {
-            // thread = (head hh, column pair d2): all loads of a batch of 8 partials are issued before they are used
-            const int hh = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;
-            const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
-            float2 num = make_float2(0.0f, 0.0f);
-            for (int p0 = 0; p0 < np; p0 += 8) {
-                float2 vals[8];
-                float w[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int pi = p0 + u;
-                    w[u] = pi < np ? m_w[pi * 4 + hh] : 0.0f;
-                    vals[u] = w[u] != 0.0f ? __ldcg(reinterpret_cast<const float2 *>(o_part + (static_cast<int64_t>(m_slot[pi]) * n_q_heads + h0 + hh) * 128 + d))
-                                           : make_float2(0.0f, 0.0f);
+            if (!mbar_wait(bar_merge, mphase, abort_flag)) {
+                if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+                return;
+            }
+            mphase ^= 1u;
+            float Mc = M;
+            for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hh]);
+            if (Mc != -INFINITY) {
+                const float resc = M == -INFINITY ? 0.0f : __expf(M - Mc);
+                num.x *= resc; num.y *= resc; den *= resc;
+                M = Mc;
+#pragma unroll 4
+                for (int pi = 0; pi < n; ++pi) {
+                    const float ls = m_lse[pi * 4 + hh];
+                    const float w = ls == -INFINITY ? 0.0f : __expf(ls - M);
+                    const float2 v = *reinterpret_cast<const float2 *>(m_val + pi * 512 + hh * 128 + d);
+                    den += w;
+                    num.x = fmaf(w, v.x, num.x);
+                    num.y = fmaf(w, v.y, num.y);
                 }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) { num.x = fmaf(w[u], vals[u].x, num.x); num.y = fmaf(w[u], vals[u].y, num.y); }
             }
-            const float den = m_stat[4 + hh];
-            const float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
-            if (mg.o_shard != nullptr) {
-                *reinterpret_cast<float2 *>(mg.o_shard + row * 128 + d) = make_float2(o0, o1);
-                if (d == 0) mg.lse_shard[row] = den > 0.0f ? m_stat[hh] + __logf(den) : -INFINITY;
-            } else {
-                float r0 = o0, r1 = o1;
-                if (mg.gate != nullptr) {  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
-                    const uint32_t gw = *reinterpret_cast<const uint32_t *>(mg.gate + row * 128 + d);
-                    r0 = bf16_round(o0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
-                    r1 = bf16_round(o1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
-                }
-                *reinterpret_cast<uint32_t *>(mg.out + row * 128 + d) = pack_bf16(r0, r1);
+        }
+        const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
+        const float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
+        if (mg.o_shard != nullptr) {
+            *reinterpret_cast<float2 *>(mg.o_shard + row * 128 + d) = make_float2(o0, o1);
+            if (d == 0) mg.lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
+        } else {
+            float r0 = o0, r1 = o1;
+            if (mg.gate != nullptr) {  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
+                const uint32_t gw = *reinterpret_cast<const uint32_t *>(mg.gate + row * 128 + d);
+                r0 = bf16_round(o0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
+                r1 = bf16_round(o1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
             }
+            *reinterpret_cast<uint32_t *>(mg.out + row * 128 + d) = pack_bf16(r0, r1);
         }
     }
 }
