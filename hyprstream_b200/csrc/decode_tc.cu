@@ -33,6 +33,7 @@ constexpr int kTcHkv = 8;
 constexpr int kTcG = 4;
 constexpr int kTcConsumers = kTcHkv;  // every warp consumes; warp 0 also issues the copies
 constexpr int kTcThreads = kTcConsumers * 32;
+constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence, in eighths of a tile (measured: 10-20 are alike)
 constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory
 constexpr long long kTcWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -134,15 +135,16 @@ struct TcLayout {
 
 // Outputs of the merge that runs inside the kernel after a grid-wide barrier (cooperative launch only).
 struct TcMergeArgs {
-    int fused;            // 0: partials only (a separate merge kernel follows)
     uint16_t *out;        // bf16 [n_seqs, Hq, 128] or NULL
     const uint16_t *gate; // optional
     float *o_shard, *lse_shard;  // optional fp32 shard outputs
 };
 
+__device__ unsigned long long g_tc_barrier;  // arrivals of all launches so far (see the grid barrier in the kernel)
+
 #ifdef HS_TC_TIMING  // diagnostic build only: per-CTA timestamps (ns) written to a harness-owned buffer
 __constant__ unsigned long long *g_tc_timing;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) :: "memory"); return t; }
 #define HS_TC_STAMP(slot) do { if (g_tc_timing && lane == 0 && (slot) < 16) g_tc_timing[(blockIdx.x * 20 + warp) * 16 + (slot)] = gtime(); } while (0)
 #else
 #define HS_TC_STAMP(slot) do {} while (0)
@@ -209,12 +211,33 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     }
     __syncthreads();
     const int64_t total = s_pref[n_seqs];
-    // never more working CTAs than tiles: every CTA below n_ctas owns at least one tile and writes its partials
+    // ---- weighted flat partition ----
+    // Tiles are laid out on a virtual axis, 8 units per tile, with kTcPadUnits empty units in front of every sequence:
+    // a CTA whose range crosses into another sequence pays for a second partial, a second set of query fragments and a
+    // cold restart, and the empty units give it that much less streaming to do.  The axis is cut evenly.  Never more
+    // working CTAs than tiles, so that every CTA has at least 8 units and no CTA inside a sequence's span comes out empty.
     const int64_t cta = blockIdx.x;
     const int64_t n_ctas = total < static_cast<int64_t>(gridDim.x) ? (total > 0 ? total : 1) : static_cast<int64_t>(gridDim.x);
-    const int t_begin = static_cast<int>(part_begin(cta, total, n_ctas)), t_end = static_cast<int>(part_begin(cta + 1, total, n_ctas));
-    const bool has_work = cta < n_ctas && t_begin < t_end;
-    if (!has_work && !mg.fused) return;
+    const int64_t vtotal = 8 * total + static_cast<int64_t>(kTcPadUnits) * n_seqs;
+    const bool small = vtotal * n_ctas < (1LL << 32);  // 32-bit divisions when they are exact
+    auto vbegin = [&](int64_t c) -> int64_t {  // first virtual unit of CTA c
+        return small ? static_cast<int64_t>(static_cast<uint32_t>(vtotal) * static_cast<uint32_t>(c) / static_cast<uint32_t>(n_ctas)) : vtotal * c / n_ctas;
+    };
+    auto tiles_before = [&](int64_t v) -> int {  // tiles whose first unit lies before virtual unit v
+        if (v >= vtotal) return static_cast<int>(total);
+        int lo = 0, hi = n_seqs;  // invariant: start(lo) <= v < start(hi), start(r) = 8 s_pref[r] + pad r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (8LL * s_pref[mid] + static_cast<int64_t>(kTcPadUnits) * mid <= v) lo = mid; else hi = mid;
+        }
+        const int64_t off = v - (8LL * s_pref[lo] + static_cast<int64_t>(kTcPadUnits) * lo) - kTcPadUnits;
+        int64_t k = off <= 0 ? 0 : (off + 7) >> 3;
+        const int64_t nt = s_pref[lo + 1] - s_pref[lo];
+        if (k > nt) k = nt;
+        return s_pref[lo] + static_cast<int>(k);
+    };
+    const int t_begin = cta < n_ctas ? tiles_before(vbegin(cta)) : 0, t_end = cta < n_ctas ? tiles_before(vbegin(cta + 1)) : 0;
+    const bool has_work = t_begin < t_end;
     // first sequence of this CTA: the largest r with s_pref[r] <= t_begin
     int r_first = n_seqs;
     if (has_work) {
@@ -302,7 +325,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         const int base = s_pref[r];
         const int lo = max(t_begin, base), hi = min(t_end, s_pref[r + 1]);
         if (lo >= hi) continue;
-        HS_TC_STAMP(2 + 4 * seg_idx);
+        HS_TC_STAMP(seg_idx < 2 ? 2 + 4 * seg_idx : 16);
         const int L = s_len[r];
 
         // ---- query fragments: fp16, d permuted so that one 16-byte K load feeds 4 k-steps; per-block sums ----
@@ -344,7 +367,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     break;
                 }
         }
-        HS_TC_STAMP(3 + 4 * seg_idx);
+        HS_TC_STAMP(seg_idx < 2 ? 3 + 4 * seg_idx : 16);
         // running softmax state of query head g (row layout of the q.K^T accumulators)
         float m = -INFINITY, l_part = 0.0f, ps_part[2] = {0.0f, 0.0f};
         // O^T accumulators: tile (b, mt): rows d = 64b + 8g + 4*(mt>>1) + 2*(mt&1) (+1 for regs 2,3), cols heads 2j, 2j+1
@@ -499,7 +522,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
         }
         if (!ok) break;
-        HS_TC_STAMP(4 + 4 * seg_idx);
+        HS_TC_STAMP(seg_idx < 2 ? 4 + 4 * seg_idx : 16);
         // ---- partial of this (CTA, sequence) pair ----
         float l = l_part;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -538,7 +561,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         if (g < kTcG && j == 0)
             lse_part[slot * n_q_heads + head * kTcG + g] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        HS_TC_STAMP(5 + 4 * seg_idx);
+        HS_TC_STAMP(seg_idx < 2 ? 5 + 4 * seg_idx : 16);
         ++seg_idx;
     }
     HS_TC_STAMP(1);
@@ -551,75 +574,91 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
     }
-    if (!mg.fused) return;
 
     // ================================ grid barrier, then the log-sum-exp merge ================================
-    // All CTAs are co-resident (cooperative launch).  err[1] counts arrivals, err[2] is the generation; the last
-    // CTA to arrive resets the count and bumps the generation.  The wait is bounded.
-    __shared__ int s_bar_ok;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();  // this CTA's partials are visible device-wide before it is counted
-        volatile int *gen_p = err + 2;
-        const int gen = *gen_p;
-        int good = 1;
-        if (atomicAdd(err + 1, 1) == static_cast<int>(gridDim.x) - 1) {
-            atomicExch(err + 1, 0);
-            __threadfence();
-            atomicAdd(err + 2, 1);
-        } else {
-            const long long t0b = clock64();
-            while (*gen_p == gen) {
-                if (clock64() - t0b > kTcWaitCycles) { good = 0; break; }
-                __nanosleep(64);
-            }
-        }
-        __threadfence();
-        s_bar_ok = good;
-    }
-    __syncthreads();
-    if (!s_bar_ok) {
-        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
-        return;
-    }
-    // Work item = (sequence, group of 4 query heads).  The ring is idle now: the item's partials (2 KB of outputs and 16
-    // bytes of log-sum-exps per contributing CTA) are brought into it with bulk copies that are all in flight at once, up
-    // to kChunk partials per round, so the merge costs one trip to L2 instead of one per batch of loads.
+    // Work item = (sequence, group of 4 query heads).  The ring is idle after the barrier: the item's partials (2 KB of
+    // outputs and 16 bytes of log-sum-exps per contributing CTA) are brought into it with bulk copies that are all in
+    // flight at once, up to kChunk partials per round, so the merge costs one trip to L2 instead of one per batch of loads.
+    // Everything that does not depend on other CTAs (which partials the first item needs) is worked out before the wait.
     constexpr int kChunk = 32;
     static_assert(kChunk * 2064 <= LT::kBarOff, "merge staging must fit in the ring");
     float *m_val = reinterpret_cast<float *>(smem);                  // [kChunk][4][128]
     float *m_lse = reinterpret_cast<float *>(smem + kChunk * 2048);  // [kChunk][4]
     const uint32_t bar_merge = bar_full + 2 * kTcStages * 8 + 8;
     uint32_t mphase = 0;
-    asm volatile("fence.proxy.async;" ::: "memory");  // partials were written with ordinary stores, the copies read them through the async proxy
     const int groups = n_q_heads / 4;
-    const bool small = total * n_ctas < (1LL << 31);  // 32-bit divisions when they are exact
-    auto pbegin = [&](int64_t c) -> int64_t {
-        return small ? static_cast<int64_t>(static_cast<uint32_t>(c) * static_cast<uint32_t>(total) / static_cast<uint32_t>(n_ctas)) : part_begin(c, total, n_ctas);
-    };
-    auto owner = [&](int64_t t) -> int64_t {  // the CTA whose range holds tile t
-        int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(t) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(total)) : t * n_ctas / total;
-        while (c > 0 && pbegin(c) > t) --c;
-        while (pbegin(c + 1) <= t) ++c;
+    auto owner = [&](int64_t t, int r) -> int64_t {  // the CTA whose range holds tile t of sequence r
+        const int64_t v = 8 * t + static_cast<int64_t>(kTcPadUnits) * (r + 1);  // the tile's first virtual unit
+        int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(v) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(vtotal)) : v * n_ctas / vtotal;
+        if (c > n_ctas - 1) c = n_ctas - 1;
+        while (c > 0 && vbegin(c) > v) --c;
+        while (c < n_ctas - 1 && vbegin(c + 1) <= v) ++c;
         return c;
     };
-    for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
-        const int r = item / groups, h0 = (item - r * groups) * 4;
+    auto item_parts = [&](int item, int &r, int &h0, int64_t &c_lo, int &np) {
+        r = item / groups;
+        h0 = (item - r * groups) * 4;
         const int64_t before = s_pref[r], nt = s_pref[r + 1] - s_pref[r];
-        int64_t c_lo = 0;
-        int np = 0;
+        c_lo = 0;
+        np = 0;
         if (nt > 0) {
-            c_lo = owner(before);
-            np = static_cast<int>(owner(before + nt - 1) - c_lo + 1);
+            c_lo = owner(before, r);
+            np = static_cast<int>(owner(before + nt - 1, r) - c_lo + 1);
         }
+    };
+    int r = 0, h0 = 0, np = 0;
+    int64_t c_lo = 0;
+    const bool has_item = static_cast<int>(blockIdx.x) < n_seqs * groups;
+    if (has_item) item_parts(blockIdx.x, r, h0, c_lo, np);
+
+    // All CTAs are co-resident (cooperative launch).  g_tc_barrier only ever counts up: a CTA's ticket tells it which
+    // multiple of the grid size completes its launch (every launch of this kernel family uses the same grid size and every
+    // CTA, even one whose waits ran out, takes exactly one ticket).  The wait is bounded.
+    __shared__ int s_bar_ok;
+    __syncthreads();
+    HS_TC_STAMP(10);
+    if (threadIdx.x == 0) {
+        if (has_item && np > 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(min(kChunk, np)) * 2064u);
+        const unsigned long long n = gridDim.x;
+        unsigned long long ticket;
+        // release: this CTA's partials are visible device-wide before it is counted; acquire: the CTA that arrives last sees
+        // everyone else's
+        asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(&g_tc_barrier) : "memory");
+        const unsigned long long target = (ticket / n + 1ULL) * n;
+        int good = 1;
+        if (ticket + 1ULL != target) {
+            const long long t0b = clock64();
+            while (true) {
+                unsigned long long seen;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(&g_tc_barrier) : "memory");
+                if (seen >= target) break;
+                if (clock64() - t0b > kTcWaitCycles) { good = 0; break; }
+                __nanosleep(32);
+            }
+        }
+        s_bar_ok = good;
+    }
+    __syncthreads();
+    HS_TC_STAMP(11);
+    if (!s_bar_ok) {
+        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        return;
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");  // partials were written with ordinary stores, the copies read them through the async proxy
+    for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
+        const bool first_item = item == static_cast<int>(blockIdx.x);
+        if (!first_item) item_parts(item, r, h0, c_lo, np);
         const int hh = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;  // thread = (head, column pair)
+        HS_TC_STAMP(12);
         float M = -INFINITY, den = 0.0f;
         float2 num = make_float2(0.0f, 0.0f);
         for (int p0 = 0; p0 < np; p0 += kChunk) {
             const int n = min(kChunk, np - p0);
-            __syncthreads();  // the previous round's readers are done with the staging area
-            if (threadIdx.x == 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(n) * 2064u);
-            __syncthreads();
+            if (!(first_item && p0 == 0)) {  // (the first round's byte count was posted before the grid barrier)
+                __syncthreads();  // the previous round's readers are done with the staging area
+                if (threadIdx.x == 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(n) * 2064u);
+                __syncthreads();
+            }
             if (threadIdx.x < n) {
                 const int64_t slot = c_lo + p0 + threadIdx.x + r;
                 bulk_g2s(smem_u32(m_val + threadIdx.x * 512), o_part + (slot * n_q_heads + h0) * 128, 2048u, bar_merge);
@@ -630,6 +669,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 return;
             }
             mphase ^= 1u;
+            HS_TC_STAMP(13);
             float Mc = M;
             for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hh]);
             if (Mc != -INFINITY) {
@@ -661,7 +701,9 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             }
             *reinterpret_cast<uint32_t *>(mg.out + row * 128 + d) = pack_bf16(r0, r1);
         }
+        HS_TC_STAMP(14);
     }
+    HS_TC_STAMP(15);
 }
 
 template <bool FOURBIT, int BPR, bool SF16>
@@ -682,27 +724,22 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
         configured = true;
     }
     *fused_out = 0;
-    if (coop_ok) {
-        mg.fused = 1;
-        ViewDev vv = v;
-        void *args[] = {&vv, &q, &seq_lens, &n_seqs, &n_q_heads, &kmul, &o_part, &lse_part, &err, &mg};
-        cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
-        if (e == cudaSuccess) {
-            *fused_out = 1;
-            return HS_OK;
-        }
-        cudaGetLastError();  // refused (e.g. the device is shared and cannot hold the whole grid): fall back for good
-        coop_ok = false;
+    if (!coop_ok) return HS_OK;
+    ViewDev vv = v;
+    void *args[] = {&vv, &q, &seq_lens, &n_seqs, &n_q_heads, &kmul, &o_part, &lse_part, &err, &mg};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
+    if (e == cudaSuccess) {
+        *fused_out = 1;
+        return HS_OK;
     }
-    mg.fused = 0;
-    kern<<<n_ctas, kTcThreads, LT::kTotal, s>>>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, mg);
+    cudaGetLastError();  // refused (e.g. the device is shared and cannot hold the whole grid): the generic kernel takes over for good
+    coop_ok = false;
     return HS_OK;
 }
 
-// Returns HS_OK and sets *n_ctas_out (> 0) when the tensor-core kernel took the launch; *n_ctas_out = 0
-// when the shape is not covered and the caller should use the generic kernel.  Each (CTA, sequence) pair
-// writes one partial (slot cta + seq).  *merged_out = 1 when the kernel also merged the partials into the
-// outputs (cooperative launch); otherwise the caller runs the merge kernel.
+// Returns HS_OK and sets *n_ctas_out (> 0) and *merged_out = 1 when the tensor-core kernel took the launch (it
+// merges its own partials, which needs a cooperative launch); *n_ctas_out = 0 when the shape is not covered or
+// the device refuses cooperative launches, and the caller should use the generic kernel.
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
                            uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out) {
@@ -718,7 +755,7 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     const int n_ctas = 2 * sm_count();
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
-    TcMergeArgs mg{0, out, gate, o_shard, lse_shard};
+    TcMergeArgs mg{out, gate, o_shard, lse_shard};
     int32_t st;
     if (four && !sf16) st = launch_tc<true, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
     else if (four) st = launch_tc<true, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
@@ -726,7 +763,7 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     else if (bpr == 2 && sf16) st = launch_tc<false, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
     else if (bpr == 1 && !sf16) st = launch_tc<false, 1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
     else st = launch_tc<false, 1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    if (st == HS_OK) *n_ctas_out = n_ctas;
+    if (st == HS_OK && *merged_out) *n_ctas_out = n_ctas;
     return st;
 }
 
