@@ -28,10 +28,7 @@
 
 namespace hs {
 
-constexpr int kTcTile = 16;    // tokens per stage
-constexpr int kTcHkv = 8;
-constexpr int kTcG = 4;
-constexpr int kTcConsumers = kTcHkv;  // every warp consumes; warp 0 also issues the copies
+constexpr int kTcConsumers = 8;       // every warp consumes; warp 0 also issues the copies
 constexpr int kTcThreads = kTcConsumers * 32;
 constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence, in eighths of a tile (measured: 10-20 are alike)
 constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory
@@ -114,23 +111,38 @@ __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504
 
 // FOURBIT = false: u8 codes (128 B per head row).  FOURBIT = true: NF4 / FP4 codes (64 B per head row), widened through a
 // 256-entry byte -> fp16x2 table replicated per lane (bank-conflict-free lookups).
-template <bool FOURBIT, int BPR, bool SF16>
+//
+// Two shapes share the kernel.  A token row of codes is cut into "lanes of 128": WIDE = false is 8 kv heads of
+// head_dim 128 with 4 query heads each (one warp per kv head, 16-token tiles); WIDE = true is 2 kv heads of head_dim 256
+// with 8 query heads each: a kv head is two 128-wide halves, a warp owns one half of one head for 16 of the tile's 32
+// tokens, and the two warps of a head add their halves of q.k through shared memory before the softmax.  BPR counts the
+// scale blocks of one 128-wide half.
+template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
 struct TcLayout {
+    static constexpr int kVH = WIDE ? 4 : 8;                     // 128-wide halves ("virtual heads") per token row
+    static constexpr int kSplit = WIDE ? 2 : 1;                  // halves per kv head
+    static constexpr int kG = WIDE ? 8 : 4;                      // query heads per kv head
+    static constexpr int kTH = kTcConsumers / kVH;               // 16-token groups per tile, one warp each per half
+    static constexpr int kTile = 16 * kTH;                       // tokens per stage
+    static constexpr int kD = 128 * kSplit;                      // head_dim
+    static constexpr int kHq = kVH / kSplit * kG;                // query heads
     static constexpr int kStages = FOURBIT ? 4 : 3;
-    static constexpr int kHeadRow = FOURBIT ? 64 : 128;          // code bytes of one (token, head) row
-    static constexpr int kRow = kTcHkv * kHeadRow;               // bytes of one token row of codes
-    static constexpr int kSRow = kTcHkv * BPR * (SF16 ? 2 : 4);  // scale bytes per token
+    static constexpr int kHeadRow = FOURBIT ? 64 : 128;          // code bytes of one (token, half) row
+    static constexpr int kRow = kVH * kHeadRow;                  // bytes of one token row of codes
+    static constexpr int kSRow = kVH * BPR * (SF16 ? 2 : 4);     // scale bytes per token
     static constexpr int kKOff = 0;
-    static constexpr int kVOff = kTcTile * kRow;
-    static constexpr int kKsOff = 2 * kTcTile * kRow;
-    static constexpr int kVsOff = kKsOff + kTcTile * kSRow;
-    static constexpr int kStage = (kVsOff + kTcTile * kSRow + 127) / 128 * 128;
+    static constexpr int kVOff = kTile * kRow;
+    static constexpr int kKsOff = 2 * kTile * kRow;
+    static constexpr int kVsOff = kKsOff + kTile * kSRow;
+    static constexpr int kStage = (kVsOff + kTile * kSRow + 127) / 128 * 128;
     static constexpr int kBarOff = kStages * kStage;
-    static constexpr int kPrefOff = kBarOff + 2 * kStages * 8 + 16;    // int tile-count prefix [kTcMaxSeqs + 1]
+    static constexpr int kXBarOff = kBarOff + 2 * kStages * 8 + 16;    // 4 mbarriers: score exchange of a warp pair (WIDE)
+    static constexpr int kPrefOff = kXBarOff + 32;                     // int tile-count prefix [kTcMaxSeqs + 1]
     static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
-    static constexpr int kLutOff = (kLenOff + kTcMaxSeqs * 4 + 127) / 128 * 128;  // uint32 [256][32] (4-bit kinds only)
+    static constexpr int kXOff = (kLenOff + kTcMaxSeqs * 4 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
+    static constexpr int kLutOff = kXOff + (WIDE ? 4 * 2 * 2 * 512 : 0);        // uint32 [256][32] (4-bit kinds only)
     static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
-    static constexpr uint32_t kTxBytes = 2u * kTcTile * kRow + 2u * kTcTile * kSRow;
+    static constexpr uint32_t kTxBytes = 2u * kTile * kRow + 2u * kTile * kSRow;
 };
 
 // Outputs of the merge that runs inside the kernel after a grid-wide barrier (cooperative launch only).
@@ -150,13 +162,14 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define HS_TC_STAMP(slot) do {} while (0)
 #endif
 
-template <bool FOURBIT, int BPR, bool SF16>
+template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
 __global__ void __launch_bounds__(kTcThreads, 2)
 decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_t *__restrict__ seq_lens, int n_seqs,
                       int n_q_heads, float kmul, float *__restrict__ o_part, float *__restrict__ lse_part,
                       int *__restrict__ err, TcMergeArgs mg) {
-    using LT = TcLayout<FOURBIT, BPR, SF16>;
+    using LT = TcLayout<FOURBIT, BPR, SF16, WIDE>;
     constexpr int kTcStages = LT::kStages;
+    constexpr int kTcTile = LT::kTile, kTcG = LT::kG, kD = LT::kD;
     extern __shared__ __align__(128) unsigned char smem[];
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + LT::kBarOff + 2 * kTcStages * 8);
     int *s_pref = reinterpret_cast<int *>(smem + LT::kPrefOff);
@@ -189,6 +202,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             mbar_init(bar_empty + 8 * s, kTcConsumers);
         }
         mbar_init(bar_full + 2 * kTcStages * 8 + 8, 1);  // the merge's staging barrier
+        if constexpr (WIDE)
+            for (int i = 0; i < 4; ++i) mbar_init(smem_base + LT::kXBarOff + 8 * i, 2);  // one arrival per warp of the pair
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -315,10 +330,25 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         while (ok && p_it < n_tiles_cta && p_it < kTcStages) ok = produce_one();
 
     // ================================ consumer warps ================================
-    const int head = warp;
+    // warp -> (128-wide half `head` of the token row, 16-token group `th` of the tile); `kvh`, `half`: the kv head and
+    // which half of its head_dim this warp owns
+    const int head = warp % LT::kVH, th = warp / LT::kVH;
+    const int kvh = head / LT::kSplit, half = head % LT::kSplit;
     const int g = lane >> 2, j = lane & 3;
+    float *x_mine = nullptr;
+    const float *x_peer = nullptr;
+    uint32_t x_bar = 0;
+    if constexpr (WIDE) {  // exchange buffers of the pair (this warp, the warp owning the other half of the head)
+        const int pair = th * (LT::kVH / 2) + kvh;
+        float *xb = reinterpret_cast<float *>(smem + LT::kXOff) + pair * 2 * 2 * 128;  // [parity][warp of pair][lane][4]
+        x_mine = xb + half * 128 + lane * 4;
+        x_peer = xb + (half ^ 1) * 128 + lane * 4;
+        x_bar = smem_base + LT::kXBarOff + 8 * pair;
+    }
     const float vmul = FOURBIT ? 1.0f : 1.0f / 127.0f;  // u8 codes are (code - 127): the 1/127 of the codebook goes here
     int it = 0;
+    int pair_it = 0;  // tiles this warp pair has exchanged scores for (WIDE)
+    (void)pair_it;
     int seg_idx = 0;
     (void)seg_idx;
     for (int r = r_first; r < n_seqs && s_pref[r] < t_end && ok; ++r) {
@@ -332,7 +362,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         uint32_t qa[2][4][2];
         float qsum[2] = {0.0f, 0.0f};
         if (g < kTcG) {
-            const uint16_t *qp = q + (static_cast<int64_t>(r) * n_q_heads + head * kTcG + g) * 128;
+            const uint16_t *qp = q + (static_cast<int64_t>(r) * n_q_heads + kvh * kTcG + g) * kD + half * 128;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
                 const uint4 w0 = *reinterpret_cast<const uint4 *>(qp + 64 * b + 16 * j);
@@ -361,7 +391,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         if (g < kTcG) {
             for (int r2 = r + 1; r2 < n_seqs && s_pref[r2] < t_end; ++r2)
                 if (s_pref[r2 + 1] > s_pref[r2]) {
-                    const uint16_t *qn = q + (static_cast<int64_t>(r2) * n_q_heads + head * kTcG + g) * 128 + 16 * j;
+                    const uint16_t *qn = q + (static_cast<int64_t>(r2) * n_q_heads + kvh * kTcG + g) * kD + half * 128 + 16 * j;
                     asm volatile("prefetch.global.L1 [%0];" ::"l"(qn));
                     asm volatile("prefetch.global.L1 [%0];" ::"l"(qn + 64));
                     break;
@@ -387,7 +417,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             const unsigned char *sV = smem + stage * LT::kStage + LT::kVOff;
             const unsigned char *sKs = smem + stage * LT::kStage + LT::kKsOff;
             const unsigned char *sVs = smem + stage * LT::kStage + LT::kVsOff;
-            constexpr int tl0 = 0;
+            const int tl0 = 16 * th;
 #ifdef HS_TC_DRAIN_ONLY  // diagnostic build only: consumers drain the ring without computing (measures the copy pipeline)
             if (false)
 #endif
@@ -427,6 +457,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 }
                 // ---- scales of this thread's 4 tokens, scores in the exp2 domain, masking ----
                 float p[2][2], pv[2][2][2];
+                bool vld[2][2];
                 float mx = -INFINITY;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
@@ -434,26 +465,44 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     for (int e = 0; e < 2; ++e) {
                         const int tl = tl0 + nt * 8 + 2 * j + e;
                         const bool valid = tile * kTcTile + tl < L;
+                        vld[nt][e] = valid;
                         float ks[2], vs[2];
                         if (SF16) {
-                            const __half *kp = reinterpret_cast<const __half *>(sKs) + (tl * kTcHkv + head) * BPR;
-                            const __half *vp = reinterpret_cast<const __half *>(sVs) + (tl * kTcHkv + head) * BPR;
+                            const __half *kp = reinterpret_cast<const __half *>(sKs) + (tl * LT::kVH + head) * BPR;
+                            const __half *vp = reinterpret_cast<const __half *>(sVs) + (tl * LT::kVH + head) * BPR;
                             ks[0] = __half2float(kp[0]); vs[0] = __half2float(vp[0]);
                             ks[1] = BPR == 2 ? __half2float(kp[BPR - 1]) : ks[0];
                             vs[1] = BPR == 2 ? __half2float(vp[BPR - 1]) : vs[0];
                         } else {
-                            const float *kp = reinterpret_cast<const float *>(sKs) + (tl * kTcHkv + head) * BPR;
-                            const float *vp = reinterpret_cast<const float *>(sVs) + (tl * kTcHkv + head) * BPR;
+                            const float *kp = reinterpret_cast<const float *>(sKs) + (tl * LT::kVH + head) * BPR;
+                            const float *vp = reinterpret_cast<const float *>(sVs) + (tl * LT::kVH + head) * BPR;
                             ks[0] = kp[0]; vs[0] = vp[0];
                             ks[1] = BPR == 2 ? kp[BPR - 1] : ks[0];
                             vs[1] = BPR == 2 ? vp[BPR - 1] : vs[0];
                         }
                         const float s2 = ((sacc[nt][0][e] - qsum[0]) * ks[0] + (sacc[nt][1][e] - qsum[1]) * ks[1]) * kmul;
-                        p[nt][e] = valid ? s2 : -INFINITY;
+                        p[nt][e] = (valid || WIDE) ? s2 : -INFINITY;  // (WIDE: masked after the halves are added)
                         pv[nt][e][0] = valid ? vs[0] * vmul : 0.0f;
                         pv[nt][e][1] = valid ? vs[1] * vmul : 0.0f;
-                        mx = fmaxf(mx, p[nt][e]);
+                        if constexpr (!WIDE) mx = fmaxf(mx, p[nt][e]);
                     }
+                if constexpr (WIDE) {
+                    // q.k over head_dim 256 = this warp's half + the peer's: swap through shared memory (two buffers by
+                    // tile parity; the pair's mbarrier flips once per tile, one arrival per warp)
+                    const int par = pair_it & 1;
+                    *reinterpret_cast<float4 *>(x_mine + par * 256) = make_float4(p[0][0], p[0][1], p[1][0], p[1][1]);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(x_bar);
+                    ok = mbar_wait(x_bar, par, abort_flag);
+                    if (!ok) break;
+                    const float4 o4 = *reinterpret_cast<const float4 *>(x_peer + par * 256);
+                    ++pair_it;
+                    p[0][0] = vld[0][0] ? p[0][0] + o4.x : -INFINITY;
+                    p[0][1] = vld[0][1] ? p[0][1] + o4.y : -INFINITY;
+                    p[1][0] = vld[1][0] ? p[1][0] + o4.z : -INFINITY;
+                    p[1][1] = vld[1][1] ? p[1][1] + o4.w : -INFINITY;
+                    mx = fmaxf(fmaxf(p[0][0], p[0][1]), fmaxf(p[1][0], p[1][1]));
+                }
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m, mx);
@@ -541,13 +590,13 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             c0[b] = __shfl_sync(0xffffffffu, ps_part[b], 8 * j);
             c1[b] = __shfl_sync(0xffffffffu, ps_part[b], 8 * j + 4);
         }
-        const int64_t slot = cta + r;
+        const int64_t slot = (cta + r) * LT::kTH + th;
         if (2 * j < kTcG) {
             const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
             // this thread owns, for heads 2j and 2j+1 and each block b, the 8 consecutive outputs d = 64b + 8g .. +7:
             // two 16-byte stores each (whole 32-byte sectors)
-            float *op0 = o_part + (slot * n_q_heads + head * kTcG + 2 * j) * 128 + 8 * g;
-            float *op1 = op0 + 128;
+            float *op0 = o_part + (slot * n_q_heads + kvh * kTcG + 2 * j) * kD + half * 128 + 8 * g;
+            float *op1 = op0 + kD;
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
@@ -559,8 +608,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                         make_float4((a[1] - c1[b]) * inv1, (a[3] - c1[b]) * inv1, (c[1] - c1[b]) * inv1, (c[3] - c1[b]) * inv1);
                 }
         }
-        if (g < kTcG && j == 0)
-            lse_part[slot * n_q_heads + head * kTcG + g] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        if (g < kTcG && j == 0 && half == 0)
+            lse_part[slot * n_q_heads + kvh * kTcG + g] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         HS_TC_STAMP(seg_idx < 2 ? 5 + 4 * seg_idx : 16);
         ++seg_idx;
     }
@@ -586,7 +635,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     float *m_lse = reinterpret_cast<float *>(smem + kChunk * 2048);  // [kChunk][4]
     const uint32_t bar_merge = bar_full + 2 * kTcStages * 8 + 8;
     uint32_t mphase = 0;
-    const int groups = n_q_heads / 4;
+    constexpr int kHpi = 512 / kD;  // query heads per work item: 2 KB of partial outputs either way
+    const int groups = n_q_heads / kHpi;
     auto owner = [&](int64_t t, int r) -> int64_t {  // the CTA whose range holds tile t of sequence r
         const int64_t v = 8 * t + static_cast<int64_t>(kTcPadUnits) * (r + 1);  // the tile's first virtual unit
         int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(v) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(vtotal)) : v * n_ctas / vtotal;
@@ -597,13 +647,13 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     };
     auto item_parts = [&](int item, int &r, int &h0, int64_t &c_lo, int &np) {
         r = item / groups;
-        h0 = (item - r * groups) * 4;
+        h0 = (item - r * groups) * kHpi;
         const int64_t before = s_pref[r], nt = s_pref[r + 1] - s_pref[r];
         c_lo = 0;
         np = 0;
         if (nt > 0) {
             c_lo = owner(before, r);
-            np = static_cast<int>(owner(before + nt - 1, r) - c_lo + 1);
+            np = static_cast<int>(owner(before + nt - 1, r) - c_lo + 1) * LT::kTH;
         }
     };
     int r = 0, h0 = 0, np = 0;
@@ -648,7 +698,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
         const bool first_item = item == static_cast<int>(blockIdx.x);
         if (!first_item) item_parts(item, r, h0, c_lo, np);
-        const int hh = threadIdx.x >> 6, d = (threadIdx.x & 63) * 2;  // thread = (head, column pair)
+        const int hh = threadIdx.x / (kD / 2), d = (threadIdx.x % (kD / 2)) * 2;  // thread = (head, column pair)
+        const int h0a = h0 & ~3, hl = h0 - h0a + hh;                            // log-sum-exps travel in aligned groups of 4 heads
         HS_TC_STAMP(12);
         float M = -INFINITY, den = 0.0f;
         float2 num = make_float2(0.0f, 0.0f);
@@ -660,9 +711,9 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 __syncthreads();
             }
             if (threadIdx.x < n) {
-                const int64_t slot = c_lo + p0 + threadIdx.x + r;
-                bulk_g2s(smem_u32(m_val + threadIdx.x * 512), o_part + (slot * n_q_heads + h0) * 128, 2048u, bar_merge);
-                bulk_g2s(smem_u32(m_lse + threadIdx.x * 4), lse_part + slot * n_q_heads + h0, 16u, bar_merge);
+                const int64_t slot = (c_lo + r) * LT::kTH + p0 + threadIdx.x;
+                bulk_g2s(smem_u32(m_val + threadIdx.x * 512), o_part + (slot * n_q_heads + h0) * kD, 2048u, bar_merge);
+                bulk_g2s(smem_u32(m_lse + threadIdx.x * 4), lse_part + slot * n_q_heads + h0a, 16u, bar_merge);
             }
             if (!mbar_wait(bar_merge, mphase, abort_flag)) {
                 if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
@@ -671,16 +722,16 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             mphase ^= 1u;
             HS_TC_STAMP(13);
             float Mc = M;
-            for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hh]);
+            for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hl]);
             if (Mc != -INFINITY) {
                 const float resc = M == -INFINITY ? 0.0f : __expf(M - Mc);
                 num.x *= resc; num.y *= resc; den *= resc;
                 M = Mc;
 #pragma unroll 4
                 for (int pi = 0; pi < n; ++pi) {
-                    const float ls = m_lse[pi * 4 + hh];
+                    const float ls = m_lse[pi * 4 + hl];
                     const float w = ls == -INFINITY ? 0.0f : __expf(ls - M);
-                    const float2 v = *reinterpret_cast<const float2 *>(m_val + pi * 512 + hh * 128 + d);
+                    const float2 v = *reinterpret_cast<const float2 *>(m_val + pi * 512 + hh * kD + d);
                     den += w;
                     num.x = fmaf(w, v.x, num.x);
                     num.y = fmaf(w, v.y, num.y);
@@ -690,27 +741,27 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
         const float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
         if (mg.o_shard != nullptr) {
-            *reinterpret_cast<float2 *>(mg.o_shard + row * 128 + d) = make_float2(o0, o1);
+            *reinterpret_cast<float2 *>(mg.o_shard + row * kD + d) = make_float2(o0, o1);
             if (d == 0) mg.lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
         } else {
             float r0 = o0, r1 = o1;
             if (mg.gate != nullptr) {  // ctx * sigmoid(gate) in bf16 (qwen3_5.rs:1056-1059)
-                const uint32_t gw = *reinterpret_cast<const uint32_t *>(mg.gate + row * 128 + d);
+                const uint32_t gw = *reinterpret_cast<const uint32_t *>(mg.gate + row * kD + d);
                 r0 = bf16_round(o0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
                 r1 = bf16_round(o1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
             }
-            *reinterpret_cast<uint32_t *>(mg.out + row * 128 + d) = pack_bf16(r0, r1);
+            *reinterpret_cast<uint32_t *>(mg.out + row * kD + d) = pack_bf16(r0, r1);
         }
         HS_TC_STAMP(14);
     }
     HS_TC_STAMP(15);
 }
 
-template <bool FOURBIT, int BPR, bool SF16>
+template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
 static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads, float kmul,
                          float *o_part, float *lse_part, int *err, int n_ctas, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
-    using LT = TcLayout<FOURBIT, BPR, SF16>;
-    auto kern = decode_int8_tc_kernel<FOURBIT, BPR, SF16>;
+    using LT = TcLayout<FOURBIT, BPR, SF16, WIDE>;
+    auto kern = decode_int8_tc_kernel<FOURBIT, BPR, SF16, WIDE>;
     static bool configured = false;  // per instantiation
     static bool coop_ok = true;      // cleared when a cooperative launch is refused
     if (!configured) {
@@ -745,24 +796,34 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
                            uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out) {
     *n_ctas_out = 0;
     *merged_out = 0;
-    if (v.kind == HS_KV_BF16 || v.head_dim != 128 || v.n_kv_heads != kTcHkv) return HS_OK;
-    if (v.page_tokens % kTcTile != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
-    if (n_q_heads != kTcG * kTcHkv) return HS_OK;
+    // covered shapes: 8 kv heads x 128 with 4 query heads each, and 2 kv heads x 256 with 8 query heads each
+    const bool wide = v.head_dim == 256 && v.n_kv_heads == 2 && n_q_heads == 16;
+    if (v.kind == HS_KV_BF16 || !(wide || (v.head_dim == 128 && v.n_kv_heads == 8 && n_q_heads == 32))) return HS_OK;
+    if (v.page_tokens % 32 != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
+    // the merge writes 4-byte pairs
+    if ((out && !aligned(out, 4)) || (gate && !aligned(gate, 4)) || (o_shard && !aligned(o_shard, 8))) return HS_OK;
     const bool four = v.kind != HS_KV_INT8;
-    const int bpr = 128 / v.block;
+    const int bpr = 128 / v.block;  // scale blocks per 128-wide half of a head row
     if (bpr != 1 && bpr != 2) return HS_OK;
-    if (four && bpr != 2) return HS_OK;  // 4-bit caches use the reference's block of 64
+    if (four && (bpr != 2 || wide)) return HS_OK;  // 4-bit caches: the reference's block of 64, Llama shape
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     const int n_ctas = 2 * sm_count();
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
     TcMergeArgs mg{out, gate, o_shard, lse_shard};
     int32_t st;
-    if (four && !sf16) st = launch_tc<true, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (four) st = launch_tc<true, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (bpr == 2 && !sf16) st = launch_tc<false, 2, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (bpr == 2 && sf16) st = launch_tc<false, 2, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else if (bpr == 1 && !sf16) st = launch_tc<false, 1, false>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
-    else st = launch_tc<false, 1, true>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out);
+#define HS_TC_LAUNCH(F, B, S, W) launch_tc<F, B, S, W>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out)
+    if (wide) {
+        if (bpr == 2 && !sf16) st = HS_TC_LAUNCH(false, 2, false, true);
+        else if (bpr == 2) st = HS_TC_LAUNCH(false, 2, true, true);
+        else if (!sf16) st = HS_TC_LAUNCH(false, 1, false, true);
+        else st = HS_TC_LAUNCH(false, 1, true, true);
+    } else if (four && !sf16) st = HS_TC_LAUNCH(true, 2, false, false);
+    else if (four) st = HS_TC_LAUNCH(true, 2, true, false);
+    else if (bpr == 2 && !sf16) st = HS_TC_LAUNCH(false, 2, false, false);
+    else if (bpr == 2 && sf16) st = HS_TC_LAUNCH(false, 2, true, false);
+    else if (bpr == 1 && !sf16) st = HS_TC_LAUNCH(false, 1, false, false);
+    else st = HS_TC_LAUNCH(false, 1, true, false);
+#undef HS_TC_LAUNCH
     if (st == HS_OK && *merged_out) *n_ctas_out = n_ctas;
     return st;
 }

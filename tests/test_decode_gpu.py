@@ -132,6 +132,28 @@ def test_ragged_batch_equals_serial_and_oracle(cuda, kind, block, sdt):
     no_device_error()
 
 
+@pytest.mark.parametrize("block,sdt,paged", [(128, 1, False), (128, 1, True), (64, 1, False), (128, 0, False)])
+def test_qwen_shape_ragged_gated_decode(cuda, block, sdt, paged):
+    """Qwen3.5 full-attention decode shape (16 q / 2 kv heads, head_dim 256, int8 cache, output gate,
+    qwen3_5.rs:992-1059) on a ragged batch: the oracle's gated core and the fp32 recomputation, row by row, and one
+    long row cut across many CTAs."""
+    rng = np.random.default_rng(3)
+    lens = [int(x) for x in rng.integers(1, 900, size=12)] + [1, 31, 32, 33, 5000]
+    hq, hkv, d = 16, 2, 256
+    caches, ks, vs = build_caches(cuda, 1, lens, hkv, d, seed=21, block=block, scale_dtype=sdt, paged=paged)
+    torch.manual_seed(8)
+    q = torch.randn(len(lens), hq, d).bfloat16()
+    gate = torch.randn(len(lens), hq, d).bfloat16()
+    out = run_decode(cuda, caches, q, lens, gate=gate)
+    plain = run_decode(cuda, caches, q, lens)
+    for r, l in enumerate(lens):
+        oracle = ar.qwen_gated_attention_core(q[r].reshape(1, 1, hq, d), gate[r].reshape(1, 1, hq, d), ks[r], vs[r], hq).reshape(hq, d)
+        assert_close_attn(out[r], oracle.float(), f"L={l} gated vs oracle")
+        fp32 = ar.attention_fp32(q[r].reshape(1, 1, hq, d), ks[r], vs[r]).reshape(hq, d)
+        assert_close_attn(plain[r], fp32, f"L={l} vs fp32")
+    no_device_error()
+
+
 @pytest.mark.parametrize("kind", [0, 1, 2])
 def test_paged_equals_contiguous(cuda, kind):
     lens = [5, 300, 1000, 257]
