@@ -1,4 +1,4 @@
-// Causal GQA prefill attention on the 5th-generation tensor cores (head_dim 128, bf16).
+// Causal GQA prefill attention on the 5th-generation tensor cores (bf16; head_dim 128 first, head_dim 256 further down).
 //
 // One CTA = two 128-row query tiles of one head (256 rows) sharing every K/V tile.  Roles (10 warps):
 //   warp 8  loader: TMA tensor loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the two Q tiles
@@ -431,6 +431,291 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(512) : "memory");
 }
 
+// ================================================================================================================
+// head_dim 256 (Qwen3.5 full attention, qwen3_5.rs:1012-1059): one 128-row query tile per CTA, key tiles of 64.
+//   TMEM columns: four score/probability buffers of 64 columns ([0,256): tile j uses buffer j & 3, so q.k^T runs up to
+//   three key tiles ahead of the softmax), the output accumulator 128 x 256 fp32 in [256,512).
+//   Shared memory: Q 64 KB (four 64-column boxes of 128 rows), K ring 3 x 32 KB, V ring 2 x 32 KB (boxes of 64 rows).
+//   Warps 0-3: softmax (thread = query row), warp 4: loader, warp 5: MMA issuer.
+//   Per key tile: S = Q.K^T is 16 MMAs 128x64x16 (operands in shared memory), O += P.V is 4 MMAs 128x256x16 (P from TMEM,
+//   V MN-major: its four 64-column boxes are 8 KB apart).
+constexpr int kW5D = 256, kW5M = 128, kW5N = 64;
+constexpr int kW5KStages = 3, kW5VStages = 2, kW5SBufs = 4;
+constexpr int kW5Threads = 192;
+constexpr int kW5QBytes = kW5M * kW5D * 2;    // 64 KB
+constexpr int kW5QBox = kW5M * 128;           // one 64-column box of Q
+constexpr int kW5KVBytes = kW5N * kW5D * 2;   // 32 KB
+constexpr int kW5KVBox = kW5N * 128;          // one 64-column box of K or V
+constexpr int kW5SmemBytes = kW5QBytes + (kW5KStages + kW5VStages) * kW5KVBytes + 1024;
+
+struct W5Bars {
+    uint64_t q, kfull[kW5KStages], kempty[kW5KStages], vfull[kW5VStages], vempty[kW5VStages], sfull[kW5SBufs], pready[kW5SBufs],
+        pvdone[kW5SBufs], odone;
+};
+
+__global__ void __launch_bounds__(kW5Threads, 1)
+prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
+                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) W5Bars bars;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t sQ = t5_s32(smem), sK = sQ + kW5QBytes, sV = sK + kW5KStages * kW5KVBytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mb = gridDim.x - 1 - blockIdx.x;  // latest (heaviest) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / (n_q_heads / n_kv_heads);
+    const int m0 = mb * kW5M, off = kv_len - q_len;
+    const int n_tiles = (min(kv_len, off + min(m0 + kW5M, q_len)) + kW5N - 1) / kW5N;
+    volatile int *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        auto init = [](uint64_t *bar, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(t5_s32(bar)), "r"(count)); };
+        init(&bars.q, 1);
+        init(&bars.odone, 1);
+        for (int s = 0; s < kW5KStages; ++s) { init(&bars.kfull[s], 1); init(&bars.kempty[s], 1); }
+        for (int s = 0; s < kW5VStages; ++s) { init(&bars.vfull[s], 1); init(&bars.vempty[s], 1); }
+        for (int i = 0; i < kW5SBufs; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kW5M); init(&bars.pvdone[i], 1); }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(t5_s32(&s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    t5_fence_before();
+    __syncthreads();
+    t5_fence_after();
+    const uint32_t tm = s_tmem;
+    bool ok = true;
+
+    if (warp == 4) {
+        // ================================ loader ================================
+        if (lane == 0) {
+            t5_expect_tx(t5_s32(&bars.q), kW5QBytes);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) t5_tma_load(sQ + c * kW5QBox, &map_q, 64 * c, h, m0, b, t5_s32(&bars.q));
+            // K tiles run ahead of V tiles by the difference of the ring depths
+            int jk = 0, jv = 0;
+            while (ok && (jk < n_tiles || jv < n_tiles)) {
+                if (jk < n_tiles && (jv >= n_tiles || jk - jv < kW5KStages)) {
+                    const int s = jk % kW5KStages;
+                    if (jk >= kW5KStages) ok = t5_wait(t5_s32(&bars.kempty[s]), (jk / kW5KStages - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    t5_expect_tx(t5_s32(&bars.kfull[s]), kW5KVBytes);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        t5_tma_load(sK + s * kW5KVBytes + c * kW5KVBox, &map_k, 64 * c, kvh, jk * kW5N, b, t5_s32(&bars.kfull[s]));
+                    ++jk;
+                } else {
+                    const int s = jv % kW5VStages;
+                    if (jv >= kW5VStages) ok = t5_wait(t5_s32(&bars.vempty[s]), (jv / kW5VStages - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    t5_expect_tx(t5_s32(&bars.vfull[s]), kW5KVBytes);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        t5_tma_load(sV + s * kW5KVBytes + c * kW5KVBox, &map_v, 64 * c, kvh, jv * kW5N, b, t5_s32(&bars.vfull[s]));
+                    ++jv;
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ================================ MMA issuer ================================
+        // S_j needs K_j and a free score buffer (P.V of tile j - 4 complete); P.V_j needs P_j and V_j.  Whichever is ready is
+        // issued; q.k^T runs ahead so that the tensor pipe works under the softmax.
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kW5N >> 3) << 17) | ((kW5M >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kW5D >> 3) << 17) | ((kW5M >> 4) << 24);
+            int next_s = 0, next_pv = 0;
+            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag);
+            long long t_idle = clock64();
+            while (ok && next_pv < n_tiles) {
+                bool progress = false;
+                int j = next_pv;
+                if (j < next_s && t5_test_wait(t5_s32(&bars.pready[j & 3]), (j >> 2) & 1) &&
+                    t5_test_wait(t5_s32(&bars.vfull[j % kW5VStages]), (j / kW5VStages) & 1)) {
+                    t5_fence_after();
+                    const uint32_t sVj = sV + (j % kW5VStages) * kW5KVBytes;
+#pragma unroll
+                    for (int ks = 0; ks < kW5N / 16; ++ks)
+                        t5_mma_ts(tm + 256, tm + (j & 3) * kW5N + ks * 8, t5_desc(sVj + ks * 2048, kW5KVBox, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    t5_commit(t5_s32(&bars.odone));
+                    t5_commit(t5_s32(&bars.pvdone[j & 3]));
+                    t5_commit(t5_s32(&bars.vempty[j % kW5VStages]));
+                    next_pv = j + 1;
+                    progress = true;
+                }
+                j = next_s;
+                if (j < n_tiles && j < next_pv + kW5SBufs && t5_test_wait(t5_s32(&bars.kfull[j % kW5KStages]), (j / kW5KStages) & 1) &&
+                    (j < kW5SBufs || t5_test_wait(t5_s32(&bars.pvdone[j & 3]), ((j >> 2) - 1) & 1))) {
+                    t5_fence_after();
+                    const uint32_t sKj = sK + (j % kW5KStages) * kW5KVBytes;
+#pragma unroll
+                    for (int ks = 0; ks < kW5D / 16; ++ks)
+                        t5_mma_ss(tm + (j & 3) * kW5N, t5_desc(sQ + (ks >> 2) * kW5QBox + (ks & 3) * 32, 16, 1024),
+                                  t5_desc(sKj + (ks >> 2) * kW5KVBox + (ks & 3) * 32, 16, 1024), idesc_qk, ks > 0);
+                    t5_commit(t5_s32(&bars.sfull[j & 3]));
+                    t5_commit(t5_s32(&bars.kempty[j % kW5KStages]));
+                    next_s = j + 1;
+                    progress = true;
+                }
+                if (progress) {
+                    t_idle = clock64();
+                } else if (*abort_flag || clock64() - t_idle > kT5WaitCycles) {
+                    *abort_flag = 1;
+                    ok = false;
+                } else {
+                    __nanosleep(20);
+                }
+            }
+        }
+    } else {
+        // ================================ softmax: thread = query row ================================
+        const int row = m0 + threadIdx.x;
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t tO = tm + lane_base + 256;
+        float m_used = -INFINITY, l = 0.0f;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t tS = tm + lane_base + (j & 3) * kW5N;
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 3]), (j >> 2) & 1, abort_flag));
+            if (!ok) break;
+            t5_fence_after();
+            const int n0 = j * kW5N;
+            const bool masked = n0 + kW5N > min(kv_len, off + m0 + 1);
+            const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
+            uint32_t r[2][32];
+            t5_ld32(tS, r[0]);
+            t5_ld32(tS + 32, r[1]);
+            t5_wait_ld();
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            if (!masked) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = t5_max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                        mx1 = t5_max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                        mx2 = t5_max3(mx2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                        mx3 = t5_max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+                    }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a0 = 32 * c + i > lim ? -INFINITY : __uint_as_float(r[c][i]);
+                        const float a1 = 32 * c + i + 1 > lim ? -INFINITY : __uint_as_float(r[c][i + 1]);
+                        mx0 = t5_max3(mx0, a0, a1);
+                    }
+            }
+            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool need = m_new - m_used > kT5RescaleThreshold;  // false while both are -inf (NaN compares false)
+                if (__any_sync(0xffffffffu, need)) {
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag));
+                    if (!ok) break;
+                    t5_fence_after();
+                    const float f = need ? exp2f(m_used - m_new) : 1.0f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kW5D; c0 += 32) {
+                        uint32_t o[32];
+                        t5_ld32(tO + c0, o);
+                        t5_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        t5_st32(tO + c0, o);
+                    }
+                    t5_wait_st();
+                    l *= f;
+                    if (need) m_used = m_new;
+                }
+                if (m_used == -INFINITY) m_used = m_new;
+            }
+            const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
+            float ps0 = 0.0f, ps1 = 0.0f;
+            if (!masked) {
+                const uint64_t sc2 = t5_pack2(scale_log2, scale_log2), nm2 = t5_pack2(neg_m, neg_m);
+                uint64_t acc_a = t5_pack2(0.0f, 0.0f), acc_b = acc_a;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float x0, x1;
+                        t5_unpack2(t5_fma2(t5_pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2), x0, x1);
+                        const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);
+                        if (i & 1) acc_b = t5_add2(acc_b, t5_pack2(p0, p1)); else acc_a = t5_add2(acc_a, t5_pack2(p0, p1));
+                        w[i] = t5_pack_bf16x2(p0, p1);
+                    }
+                    t5_st16(tS + 16 * c, w);
+                }
+                float a0, a1;
+                t5_unpack2(t5_add2(acc_a, acc_b), a0, a1);
+                ps0 = a0; ps1 = a1;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float p0 = 32 * c + 2 * i > lim ? 0.0f : t5_ex2(fmaf(__uint_as_float(r[c][2 * i]), scale_log2, neg_m));
+                        const float p1 = 32 * c + 2 * i + 1 > lim ? 0.0f : t5_ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), scale_log2, neg_m));
+                        ps0 += p0; ps1 += p1;
+                        w[i] = t5_pack_bf16x2(p0, p1);
+                    }
+                    t5_st16(tS + 16 * c, w);
+                }
+            }
+            l += ps0 + ps1;
+            t5_wait_st();
+            t5_fence_before();
+            t5_arrive(t5_s32(&bars.pready[j & 3]));
+        }
+        // ---- epilogue ----
+        if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (n_tiles - 1) & 1, abort_flag));
+        if (ok && n_tiles > 0) {
+            t5_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kW5D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kW5D; c0 += 32) {
+                uint32_t o[32];
+                t5_ld32(tO + c0, o);
+                t5_wait_ld();
+                if (row < q_len) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float x0 = __uint_as_float(o[v4 * 8 + 2 * i]) * inv, x1 = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                            if (gate != nullptr) {
+                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + base + c0 + v4 * 8 + 2 * i);
+                                x0 = bf16_round(x0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
+                                x1 = bf16_round(x1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
+                            }
+                            w[i] = pack_bf16(x0, x1);
+                        }
+                        *reinterpret_cast<uint4 *>(out + base + c0 + v4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: every thread arrives here, also after a timed-out wait ----
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        const long long t0c = clock64();
+        while (clock64() - t0c < 2000000LL) {}  // bounded grace period for copies and MMAs still in flight
+    }
+    t5_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(512) : "memory");
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -451,15 +736,15 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// [n_seqs, n_tokens, n_heads, 128] bf16 -> 4-D map (d, head, token, sequence), box 64 x 1 x 128 x 1, 128-byte swizzle
-static bool make_map(CUtensorMap *map, const void *base, int n_seqs, int n_tokens, int n_heads) {
+// [n_seqs, n_tokens, n_heads, head_dim] bf16 -> 4-D map (d, head, token, sequence), box 64 x 1 x box_rows x 1, 128-byte swizzle
+static bool make_map(CUtensorMap *map, const void *base, int n_seqs, int n_tokens, int n_heads, int head_dim = kT5D, int box_rows = kT5N) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kT5D), static_cast<cuuint64_t>(n_heads), static_cast<cuuint64_t>(n_tokens),
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(n_heads), static_cast<cuuint64_t>(n_tokens),
                                 static_cast<cuuint64_t>(n_seqs)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kT5D) * 2, static_cast<cuuint64_t>(n_heads) * kT5D * 2,
-                                   static_cast<cuuint64_t>(n_tokens) * n_heads * kT5D * 2};
-    const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(kT5N), 1};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(n_heads) * head_dim * 2,
+                                   static_cast<cuuint64_t>(n_tokens) * n_heads * head_dim * 2};
+    const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -470,7 +755,26 @@ static bool make_map(CUtensorMap *map, const void *base, int n_seqs, int n_token
 int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int n_seqs,
                         int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2, cudaStream_t s, int *taken) {
     *taken = 0;
-    if (head_dim != kT5D || q_len < 2) return HS_OK;
+    if (q_len < 2) return HS_OK;
+    if (head_dim == kW5D) {
+        CUtensorMap mq, mk, mv;
+        if (!make_map(&mq, q, n_seqs, q_len, n_q_heads, kW5D, kW5M) || !make_map(&mk, k, n_seqs, kv_len, n_kv_heads, kW5D, kW5N) ||
+            !make_map(&mv, v, n_seqs, kv_len, n_kv_heads, kW5D, kW5N))
+            return HS_OK;
+        int *errw = device_error_word();
+        if (!errw) return fail(HS_ERR_DEVICE, "hs_attn_prefill_causal: device error word unavailable");
+        static bool configured_w = false;
+        if (!configured_w) {
+            cudaError_t e = cudaFuncSetAttribute(prefill_tc5_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kW5SmemBytes);
+            if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
+            configured_w = true;
+        }
+        dim3 gridw((q_len + kW5M - 1) / kW5M, n_q_heads, n_seqs);
+        prefill_tc5_wide_kernel<<<gridw, kW5Threads, kW5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, errw);
+        *taken = 1;
+        return HS_OK;
+    }
+    if (head_dim != kT5D) return HS_OK;
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, q, n_seqs, q_len, n_q_heads) || !make_map(&mk, k, n_seqs, kv_len, n_kv_heads) ||
         !make_map(&mv, v, n_seqs, kv_len, n_kv_heads))

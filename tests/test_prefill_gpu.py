@@ -82,6 +82,21 @@ def test_qwen_gated_prefill(cuda):
     assert_close_attn(out, oracle.float(), "gated prefill vs oracle")
 
 
+@pytest.mark.parametrize("ql,kl", [(130, 700), (1024, 1024), (1, 64)])
+def test_qwen_shape_prefix_and_long_rows(cuda, ql, kl):
+    """head_dim 256 with a cached prefix (kv_len > q_len), more key tiles than score buffers and ring stages, two
+    sequences, gate on: against the oracle's gated core and the fp32 recomputation of the ungated attention."""
+    from hyprstream_b200 import ops
+
+    q, k, v = _rand(2, ql, kl, 16, 2, 256, seed=ql)
+    gate = torch.randn(2, ql, 16, 256, generator=torch.Generator().manual_seed(ql + 1)).bfloat16()
+    out = ops.prefill_attention(q.to(cuda), k.to(cuda), v.to(cuda), gate=gate.to(cuda))
+    plain = ops.prefill_attention(q.to(cuda), k.to(cuda), v.to(cuda))
+    torch.cuda.synchronize()
+    assert_close_attn(out, ar.qwen_gated_attention_core(q, gate, k, v, 16).reshape(2, ql, 16, 256).float(), "gated vs oracle")
+    assert_close_attn(plain, ar.attention_fp32(q, k, v), "vs fp32")
+
+
 def test_prefill_then_quantise_on_write_then_decode(cuda):
     """Config-4 flow at reduced size: RoPE -> prefill attention -> K/V written to the int8 cache (codes bit-exact to the
     oracle) -> the next decode step over that cache agrees with the oracle over the dequantised cache."""
