@@ -96,42 +96,83 @@ gdn_recurrent_kernel(const float *__restrict__ q, const float *__restrict__ k, c
     for (int i = 0; i < R; ++i) *reinterpret_cast<float2 *>(sp + (warp + kGdnWarps * i) * kGdnHV + 2 * lane) = S[i];
 }
 
-// ---- column-owner form for runs of tokens --------------------------------------------------------------------
-// The rule is independent per value column: m[v], delta[v], S[:,v] and o[v] never mix columns.  Here a pair of lanes owns
-// one column of the state (HK/2 floats each in registers), so a token needs one shuffle for m and one for o and no barrier: S <- decay S; m = k.S; delta = beta (v - m); S <- S + k delta; o = q.S, all in-lane.  The
-// four warps of a CTA are the four column groups of one (sequence, value head) and share k, q, v, g, beta of a batch
-// of 8 tokens staged in shared memory (double buffered with cp.async; one barrier per 8 tokens).
+// ---- register-tile form for runs of tokens ---------------------------------------------------------------------
+// The rule is independent per value column: m[v], delta[v], S[:,v] and o[v] never mix columns.  One CTA of 8 warps owns a
+// whole (sequence, value head) state; warp w owns value columns [16w, 16w+16) and a thread an (HK/RG rows) x (CPT columns)
+// tile of the state in registers (head_k_dim 128: 32 x 2), row pairs packed for the two-wide fp32 FMA (which saves issue
+// slots; the fp32 rate itself, ~125 FMA per clock per SM measured, is the same packed or not).  Per token a thread reads
+// its rows of k and q (shared memory, rows of a group padded so that the groups of a warp hit distinct banks) and its
+// values of v, and the RG row groups of a column add their partial k.S and q.S with log2(RG) shuffle rounds; no barrier.
+// k, q, v, g, beta of 8 tokens are staged per barrier (cp.async, double buffered).
+//
+// The decay is carried as a scalar: with G the product of the decays since the last renormalisation and S^ = S / G,
+//   m = G (k.S^);  delta = beta (v - m);  S^ <- S^ + k (delta / G);  o = G (q.S^)
+// which is the reference's S <- exp(g) S; m = k.S; S <- S + k delta; o = q.S with one multiply-add per state element
+// less.  S^ is multiplied back (S = G S^, G = 1) every 8 tokens and whenever G would drop below 2^-60; a single
+// decay below that is applied to the state directly.
 constexpr int kGdnColTokens = 8;
 
-// A column is shared by two adjacent lanes (rows [0, HK/2) and [HK/2, HK)): 256 threads per CTA, HK/2 state floats per
-// thread, one shuffle each for m and o per token.
-template <int HK>
-__global__ void __launch_bounds__(256)
-gdn_column_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-                  const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state,
-                  float *__restrict__ out, int n_tokens, int n_k_heads, int n_v_heads) {
-    constexpr int R = HK / 2;
-    __shared__ __align__(16) float s_k[2][kGdnColTokens][HK], s_q[2][kGdnColTokens][HK], s_v[2][kGdnColTokens][kGdnHV];
+__device__ __forceinline__ uint64_t gdn_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void gdn_unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t gdn_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t gdn_mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// RG: row groups (lanes of a warp that share a column), CPT: columns per thread; a warp covers (32 / RG) * CPT columns and
+// the CTA has as many warps as cover the 128 columns.
+template <int HK, int RG, int CPT>
+__global__ void __launch_bounds__(32 * 128 / ((32 / RG) * CPT))
+gdn_tile_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state,
+                float *__restrict__ out, int n_tokens, int n_k_heads, int n_v_heads) {
+    static_assert(CPT == 2 || CPT == 4, "columns are moved in pairs");
+    constexpr int WC = (32 / RG) * CPT;        // columns per warp
+    constexpr int NT = 32 * kGdnHV / WC;       // threads per CTA
+    constexpr int R = HK / RG;       // rows per thread
+    constexpr int RP = R / 2;        // row pairs per thread
+    constexpr int GS = R + 4;        // padded stride of a row group in shared memory (floats): the groups hit distinct banks
+    __shared__ __align__(16) float s_k[2][kGdnColTokens][RG * GS], s_q[2][kGdnColTokens][RG * GS], s_v[2][kGdnColTokens][kGdnHV];
     __shared__ float s_g[2][kGdnColTokens], s_b[2][kGdnColTokens];
     const int b = blockIdx.y, h = blockIdx.x, kh = h / (n_v_heads / n_k_heads);
-    const int col = threadIdx.x >> 1, r0 = (threadIdx.x & 1) * R;
-    float S[R];
-    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * HK * kGdnHV + static_cast<int64_t>(r0) * kGdnHV + col;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rg = lane / (32 / RG), cg = lane % (32 / RG);
+    const int r0 = rg * R, c0 = warp * WC + cg * CPT;
+    // S2[p][c] = (S[r0 + 2p][c0 + c], S[r0 + 2p + 1][c0 + c])
+    uint64_t S2[RP][CPT];
+    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * HK * kGdnHV + static_cast<int64_t>(r0) * kGdnHV + c0;
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = sp[i * kGdnHV];
+    for (int p = 0; p < RP; ++p)
+#pragma unroll
+        for (int c = 0; c < CPT; c += 2) {
+            const float2 a = *reinterpret_cast<const float2 *>(sp + (2 * p) * kGdnHV + c), e = *reinterpret_cast<const float2 *>(sp + (2 * p + 1) * kGdnHV + c);
+            S2[p][c] = gdn_pack2(a.x, e.x);
+            S2[p][c + 1] = gdn_pack2(a.y, e.y);
+        }
 
     auto stage = [&](int t0, int buf) {
         const int nt = min(kGdnColTokens, n_tokens - t0);
-        // HK/4 16-byte chunks of k and of q per token, 32 chunks of v per token
-        for (int i = threadIdx.x; i < nt * (HK / 4); i += 256) {
+        // HK/4 16-byte chunks of k and of q per token (chunk c lands in row group c / (R/4)), 32 chunks of v per token
+        for (int i = threadIdx.x; i < nt * (HK / 4); i += NT) {
             const int t = i / (HK / 4), c = i - t * (HK / 4);
+            const int dst = (c / (R / 4)) * GS + (c % (R / 4)) * 4;
             const int64_t tok = static_cast<int64_t>(b) * n_tokens + t0 + t;
-            const uint32_t dk = static_cast<uint32_t>(__cvta_generic_to_shared(&s_k[buf][t][4 * c]));
-            const uint32_t dq = static_cast<uint32_t>(__cvta_generic_to_shared(&s_q[buf][t][4 * c]));
+            const uint32_t dk = static_cast<uint32_t>(__cvta_generic_to_shared(&s_k[buf][t][dst]));
+            const uint32_t dq = static_cast<uint32_t>(__cvta_generic_to_shared(&s_q[buf][t][dst]));
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(k + (tok * n_k_heads + kh) * HK + 4 * c) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dq), "l"(q + (tok * n_k_heads + kh) * HK + 4 * c) : "memory");
         }
-        for (int i = threadIdx.x; i < nt * (kGdnHV / 4); i += 256) {
+        for (int i = threadIdx.x; i < nt * (kGdnHV / 4); i += NT) {
             const int t = i / (kGdnHV / 4), c = i - t * (kGdnHV / 4);
             const int64_t tok = static_cast<int64_t>(b) * n_tokens + t0 + t;
             const uint32_t dv = static_cast<uint32_t>(__cvta_generic_to_shared(&s_v[buf][t][4 * c]));
@@ -144,6 +185,15 @@ gdn_column_kernel(const float *__restrict__ q, const float *__restrict__ k, cons
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    auto renormalise = [&](float f) {
+        const uint64_t f2 = gdn_pack2(f, f);
+#pragma unroll
+        for (int p = 0; p < RP; ++p)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) S2[p][c] = gdn_mul2(S2[p][c], f2);
+    };
+    constexpr float kTiny = 8.673617379884035e-19f;  // 2^-60
+    float G = 1.0f;  // product of the decays since the state was last multiplied back
     stage(0, 0);
     for (int t0 = 0, it = 0; t0 < n_tokens; t0 += kGdnColTokens, ++it) {
         const int buf = it & 1;
@@ -153,35 +203,97 @@ gdn_column_kernel(const float *__restrict__ q, const float *__restrict__ k, cons
         const int nt = min(kGdnColTokens, n_tokens - t0);
         for (int t = 0; t < nt; ++t) {
             const float decay = __expf(s_g[buf][t]), bt = s_b[buf][t];
-            const float *kt = &s_k[buf][t][r0], *qt = &s_q[buf][t][r0];
-            float m0 = 0.0f, m1 = 0.0f, m2 = 0.0f, m3 = 0.0f;
-#pragma unroll
-            for (int i = 0; i < R; i += 4) {
-                const float4 kk = *reinterpret_cast<const float4 *>(kt + i);  // two addresses per warp: broadcast
-                S[i] *= decay; S[i + 1] *= decay; S[i + 2] *= decay; S[i + 3] *= decay;
-                m0 = fmaf(kk.x, S[i], m0); m1 = fmaf(kk.y, S[i + 1], m1); m2 = fmaf(kk.z, S[i + 2], m2); m3 = fmaf(kk.w, S[i + 3], m3);
+            if (G * decay < kTiny) {  // (uniform over the CTA)
+                renormalise(G);
+                G = 1.0f;
+                if (decay < kTiny) renormalise(decay); else G = decay;
+            } else {
+                G *= decay;
             }
-            float m = (m0 + m1) + (m2 + m3);
-            m += __shfl_xor_sync(0xffffffffu, m, 1);
-            const float d = (s_v[buf][t][col] - m) * bt;
-            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            const float *kt = &s_k[buf][t][rg * GS], *qt = &s_q[buf][t][rg * GS];
+            uint64_t k2[RP], m2[2][CPT];
 #pragma unroll
-            for (int i = 0; i < R; i += 4) {
-                const float4 kk = *reinterpret_cast<const float4 *>(kt + i);
-                const float4 qq = *reinterpret_cast<const float4 *>(qt + i);
-                S[i] = fmaf(kk.x, d, S[i]); S[i + 1] = fmaf(kk.y, d, S[i + 1]); S[i + 2] = fmaf(kk.z, d, S[i + 2]); S[i + 3] = fmaf(kk.w, d, S[i + 3]);
-                o0 = fmaf(qq.x, S[i], o0); o1 = fmaf(qq.y, S[i + 1], o1); o2 = fmaf(qq.z, S[i + 2], o2); o3 = fmaf(qq.w, S[i + 3], o3);
+            for (int c = 0; c < CPT; ++c) m2[0][c] = m2[1][c] = 0ull;
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const ulonglong2 kk = *reinterpret_cast<const ulonglong2 *>(kt + 4 * i);  // rows 4i, 4i+1 | 4i+2, 4i+3
+                k2[2 * i] = kk.x;
+                k2[2 * i + 1] = kk.y;
             }
-            float o = (o0 + o1) + (o2 + o3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            if ((threadIdx.x & 1) == 0) {
+#pragma unroll
+            for (int p = 0; p < RP; ++p)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) m2[p & 1][c] = gdn_fma2(k2[p], S2[p][c], m2[p & 1][c]);
+            float m[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float a0, a1, b0, b1;
+                gdn_unpack2(m2[0][c], a0, a1);
+                gdn_unpack2(m2[1][c], b0, b1);
+                m[c] = (a0 + a1) + (b0 + b1);
+            }
+#pragma unroll
+            for (int off = 32 / RG; off < 32; off <<= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) m[c] += __shfl_xor_sync(0xffffffffu, m[c], off);
+            float vin[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; c += 2) {
+                const float2 vv = *reinterpret_cast<const float2 *>(&s_v[buf][t][c0 + c]);
+                vin[c] = vv.x;
+                vin[c + 1] = vv.y;
+            }
+            const float invG = 1.0f / G;
+            uint64_t d2[CPT], o2[2][CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const float d = (vin[c] - G * m[c]) * bt * invG;  // delta / G
+                d2[c] = gdn_pack2(d, d);
+                o2[0][c] = o2[1][c] = 0ull;
+            }
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const ulonglong2 qq = *reinterpret_cast<const ulonglong2 *>(qt + 4 * i);
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    S2[2 * i][c] = gdn_fma2(k2[2 * i], d2[c], S2[2 * i][c]);
+                    o2[0][c] = gdn_fma2(qq.x, S2[2 * i][c], o2[0][c]);
+                    S2[2 * i + 1][c] = gdn_fma2(k2[2 * i + 1], d2[c], S2[2 * i + 1][c]);
+                    o2[1][c] = gdn_fma2(qq.y, S2[2 * i + 1][c], o2[1][c]);
+                }
+            }
+            float o[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float a0, a1, b0, b1;
+                gdn_unpack2(o2[0][c], a0, a1);
+                gdn_unpack2(o2[1][c], b0, b1);
+                o[c] = (a0 + a1) + (b0 + b1);
+            }
+#pragma unroll
+            for (int off = 32 / RG; off < 32; off <<= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
+            if (rg == 0) {
                 const int64_t tok = static_cast<int64_t>(b) * n_tokens + t0 + t;
-                out[(tok * n_v_heads + h) * kGdnHV + col] = o;
+                float *op = out + (tok * n_v_heads + h) * kGdnHV + c0;
+#pragma unroll
+                for (int c = 0; c < CPT; c += 2) *reinterpret_cast<float2 *>(op + c) = make_float2(o[c] * G, o[c + 1] * G);
             }
         }
+        renormalise(G);  // back to the true state at the end of every batch
+        G = 1.0f;
     }
 #pragma unroll
-    for (int i = 0; i < R; ++i) sp[i * kGdnHV] = S[i];
+    for (int p = 0; p < RP; ++p)
+#pragma unroll
+        for (int c = 0; c < CPT; c += 2) {
+            float a0, e0, a1, e1;
+            gdn_unpack2(S2[p][c], a0, e0);
+            gdn_unpack2(S2[p][c + 1], a1, e1);
+            *reinterpret_cast<float2 *>(sp + (2 * p) * kGdnHV + c) = make_float2(a0, a1);
+            *reinterpret_cast<float2 *>(sp + (2 * p + 1) * kGdnHV + c) = make_float2(e0, e1);
+        }
 }
 
 }  // namespace hs
@@ -205,11 +317,11 @@ int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const f
     if (n_seqs > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_gdn_recurrent: more than 65535 sequences");
     cudaStream_t s = as_stream(stream);
     if (n_tokens >= 4 && aligned(q, 16) && aligned(k, 16) && aligned(v, 16)) {
-        // runs of tokens: one lane per state column, no per-token synchronisation
+        // runs of tokens: the whole state of a (sequence, head) in one CTA's registers, no per-token barrier
         dim3 cgrid(n_v_heads, n_seqs);
         prof_begin(s);
-        if (head_k_dim == 128) gdn_column_kernel<128><<<cgrid, 256, 0, s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads);
-        else gdn_column_kernel<64><<<cgrid, 256, 0, s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads);
+        if (head_k_dim == 128) gdn_tile_kernel<128, 4, 2><<<cgrid, 256, 0, s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads);
+        else gdn_tile_kernel<64, 8, 4><<<cgrid, 256, 0, s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads);
         prof_end(s);
         return check_launch("hs_gdn_recurrent");
     }
