@@ -322,17 +322,19 @@ decode_merge_kernel(const int32_t *__restrict__ seq_lens, int n_seqs, int n_q_he
 }
 
 // Merge of externally produced partials (KV-length shards from several GPUs, or a caller's own split).
+// Part p's outputs start at o_parts + p * stride_o floats ([n_rows, D] dense), its log-sum-exps at lse_parts + p * stride_l.
 __global__ void merge_parts_kernel(const float *__restrict__ o_parts, const float *__restrict__ lse_parts, int n_parts,
-                                   int64_t n_rows, int D, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate) {
+                                   int64_t stride_o, int64_t stride_l, int D, uint16_t *__restrict__ out,
+                                   const uint16_t *__restrict__ gate) {
     const int64_t row = blockIdx.x;
     const int d = threadIdx.x;
     float M = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, lse_parts[p * n_rows + row]);
+    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, lse_parts[p * stride_l + row]);
     float num = 0.0f, den = 0.0f;
     for (int p = 0; p < n_parts; ++p) {
-        const float ls = lse_parts[p * n_rows + row];
+        const float ls = lse_parts[p * stride_l + row];
         const float wgt = ls == -INFINITY ? 0.0f : __expf(ls - M);
-        num = fmaf(wgt, o_parts[(p * n_rows + row) * D + d], num);
+        num = fmaf(wgt, o_parts[p * stride_o + row * D + d], num);
         den += wgt;
     }
     float res = den > 0.0f ? num / den : 0.0f;
@@ -492,16 +494,24 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     return check_launch("hs_attn_decode (merge)");
 }
 
-int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows, int32_t head_dim,
-                               void *out, const void *gate, hs_stream_t stream) {
+int32_t hs_attn_merge_partials_strided(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t part_stride_o,
+                                       int64_t part_stride_lse, int64_t n_rows, int32_t head_dim, void *out, const void *gate,
+                                       hs_stream_t stream) {
     if (int32_t st = check_device()) return st;
     if (n_parts <= 0 || n_rows < 0 || head_dim <= 0 || head_dim > 1024) return fail(HS_ERR_ARG, "hs_attn_merge_partials: bad sizes");
+    if (part_stride_o < n_rows * head_dim || part_stride_lse < n_rows) return fail(HS_ERR_ARG, "hs_attn_merge_partials: part strides overlap");
     if (n_rows == 0) return HS_OK;
     if (!o_parts || !lse_parts || !out) return fail(HS_ERR_ARG, "hs_attn_merge_partials: NULL pointer");
     if (n_rows > 0x7fffffffLL) return fail(HS_ERR_ARG, "hs_attn_merge_partials: too many rows");
     merge_parts_kernel<<<static_cast<unsigned>(n_rows), head_dim, 0, as_stream(stream)>>>(
-        o_parts, lse_parts, n_parts, n_rows, head_dim, reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate));
+        o_parts, lse_parts, n_parts, part_stride_o, part_stride_lse, head_dim, reinterpret_cast<uint16_t *>(out),
+        reinterpret_cast<const uint16_t *>(gate));
     return check_launch("hs_attn_merge_partials");
+}
+
+int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows, int32_t head_dim,
+                               void *out, const void *gate, hs_stream_t stream) {
+    return hs_attn_merge_partials_strided(o_parts, lse_parts, n_parts, n_rows * head_dim, n_rows, n_rows, head_dim, out, gate, stream);
 }
 
 

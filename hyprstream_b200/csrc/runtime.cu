@@ -1,6 +1,8 @@
 // Status plumbing shared by every entry point: thread-local error text, device check, view validation.
 #include <cstring>
 
+#include <atomic>
+
 #include "hs_common.cuh"
 
 namespace hs {
@@ -64,7 +66,10 @@ int sm_count() {
     return n > 0 ? n : 148;
 }
 
-int32_t check_launch(const char *what) {
+static std::atomic<long long> g_launches{0};
+
+int32_t check_launch(const char *what) {  // called once after every kernel launch of the library
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "%s: %s", what, cudaGetErrorString(e));
     return HS_OK;
@@ -117,6 +122,8 @@ int32_t hs_attn_device_check(int32_t device) {
 }
 
 const char *hs_attn_last_error(void) { return hs::g_err; }
+
+int64_t hs_attn_launch_count(void) { return hs::g_launches.load(std::memory_order_relaxed); }
 
 int32_t hs_attn_set_profiling(int32_t on) {
     if (int32_t st = hs::check_device()) return st;

@@ -50,6 +50,7 @@ _SIGS = {
     "hs_attn_take_device_error": (c_int32, [POINTER(c_int32)]),
     "hs_attn_set_profiling": (c_int32, [c_int32]),
     "hs_attn_last_kernel_ms": (c_int32, [POINTER(c_float)]),
+    "hs_attn_launch_count": (c_int64, []),
     "hs_quantize_blockwise": (c_int32, [c_int32, c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "hs_dequantize_blockwise": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32, c_void_p]),
     "hs_rope_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
@@ -82,6 +83,7 @@ _SIGS = {
     "hs_view_get": (c_void_p, [c_void_p]),
     "hs_view_destroy": (None, [c_void_p]),
     "hs_attn_merge_partials": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_merge_partials_strided": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
 }
 
 
@@ -114,6 +116,11 @@ def take_device_error() -> int:
 
 def set_profiling(on: bool) -> None:
     check(lib.hs_attn_set_profiling(1 if on else 0))
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib.hs_attn_launch_count())
 
 
 def last_kernel_ms() -> float:

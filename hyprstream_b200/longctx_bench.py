@@ -61,10 +61,14 @@ def main():
     lens = torch.full((B,), n_local, dtype=torch.int32, device=dev)
     q = torch.randn(B, HQ, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).bfloat16()
 
-    def step():
+    dec = sharded.ShardedDecoder(B, HQ, D, dev) if world > 1 else None
+
+    def eager_step():
         if world == 1:
             return ops.decode_attention(q, view, lens)
-        return sharded.sharded_decode(q, view, lens)
+        return dec.step(q, view, lens)
+
+    step = eager_step
 
     def barrier():
         torch.cuda.synchronize()

@@ -107,18 +107,25 @@ def decode_workspace(n_seqs: int, n_q_heads: int, head_dim: int, device: torch.d
 
 def decode_attention(q: torch.Tensor, view: KVView, seq_lens: torch.Tensor, softmax_scale: Optional[float] = None,
                      gate: Optional[torch.Tensor] = None, shard: bool = False, out: Optional[torch.Tensor] = None,
-                     workspace: Optional[torch.Tensor] = None):
+                     workspace: Optional[torch.Tensor] = None, shard_out=None):
     """Fused decode attention (llama.rs:605-640,710-844,1023-1119; qwen3_5.rs:992-1059).
 
     q bf16 [n_seqs, Hq, D], seq_lens int32 [n_seqs].  Returns bf16 [n_seqs, Hq, D], or with
-    ``shard=True`` the fp32 pair (o [n_seqs, Hq, D], lse [n_seqs, Hq]) of a KV-length shard."""
+    ``shard=True`` the fp32 pair (o [n_seqs, Hq, D], lse [n_seqs, Hq]) of a KV-length shard (written into the
+    pair ``shard_out`` when given)."""
     _need_cuda(q, seq_lens, gate)
     n_seqs, hq, d = q.shape
     scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
     ws = decode_workspace(n_seqs, hq, d, q.device) if workspace is None else workspace
     if shard:
-        o = torch.empty(n_seqs, hq, d, dtype=torch.float32, device=q.device)
-        lse = torch.empty(n_seqs, hq, dtype=torch.float32, device=q.device)
+        if shard_out is not None:
+            o, lse = shard_out
+            _need_cuda(o, lse)
+            if o.dtype != torch.float32 or lse.dtype != torch.float32 or o.numel() != n_seqs * hq * d or lse.numel() != n_seqs * hq:
+                raise ValueError("decode_attention: shard_out must be fp32 (o [n_seqs, Hq, D], lse [n_seqs, Hq])")
+        else:
+            o = torch.empty(n_seqs, hq, d, dtype=torch.float32, device=q.device)
+            lse = torch.empty(n_seqs, hq, dtype=torch.float32, device=q.device)
         check(lib.hs_attn_decode(_ptr(q), ctypes.byref(view), _ptr(seq_lens), n_seqs, hq, scale, None, None, _ptr(ws),
                                  ws.numel(), _ptr(o), _ptr(lse), _stream()))
         return o, lse
@@ -135,6 +142,22 @@ def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, gate: Optiona
     p, n_seqs, hq, d = o_parts.shape
     out = torch.empty(n_seqs, hq, d, dtype=torch.bfloat16, device=o_parts.device)
     check(lib.hs_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), p, n_seqs * hq, d, _ptr(out), _ptr(gate), _stream()))
+    return out
+
+
+def merge_gathered(msgs: torch.Tensor, n_parts: int, n_seqs: int, hq: int, d: int, out: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LSE merge of `n_parts` all-gathered shard messages, in place: msgs is flat fp32, part p = [o (n_seqs*Hq*D) | lse
+    (n_seqs*Hq)] at offset p * n_seqs*Hq*(D+1).  Returns bf16 [n_seqs, Hq, D]."""
+    _need_cuda(msgs, gate, out)
+    rows = n_seqs * hq
+    stride = rows * (d + 1)
+    if msgs.dtype != torch.float32 or msgs.numel() < n_parts * stride:
+        raise ValueError("merge_gathered: msgs must hold n_parts fp32 messages of n_seqs*Hq*(D+1) floats")
+    if out is None:
+        out = torch.empty(n_seqs, hq, d, dtype=torch.bfloat16, device=msgs.device)
+    base = msgs.data_ptr()
+    check(lib.hs_attn_merge_partials_strided(base, base + rows * d * 4, n_parts, stride, stride, rows, d, _ptr(out), _ptr(gate), _stream()))
     return out
 
 

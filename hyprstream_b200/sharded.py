@@ -55,6 +55,40 @@ def all_gather_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional[dist
     return unpack_partials(buf.reshape((world,) + tuple(msg.shape)))
 
 
+class ShardedDecoder:
+    """Decode over a KV-length-sharded cache with nothing allocated or repacked per step.
+
+    The local decode writes its shard result straight into one flat fp32 message [o (B*Hq*D) | lse (B*Hq)]; one
+    all-gather brings every rank's message into `gathered`; the merge kernel reads the parts where they landed
+    (hs_attn_merge_partials_strided).  Per step: one decode launch, one collective, one merge launch."""
+
+    def __init__(self, n_seqs: int, n_q_heads: int, head_dim: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        from . import ops
+
+        self.n_seqs, self.hq, self.d, self.group = n_seqs, n_q_heads, head_dim, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rows = n_seqs * n_q_heads
+        self.msg = torch.empty(rows * (head_dim + 1), dtype=torch.float32, device=device)
+        self.o = self.msg[:rows * head_dim].view(n_seqs, n_q_heads, head_dim)
+        self.lse = self.msg[rows * head_dim:].view(n_seqs, n_q_heads)
+        self.gathered = torch.empty(self.world * self.msg.numel(), dtype=torch.float32, device=device)
+        self.out = torch.empty(n_seqs, n_q_heads, head_dim, dtype=torch.bfloat16, device=device)
+        self.ws = ops.decode_workspace(n_seqs, n_q_heads, head_dim, device)
+
+    def step(self, q: torch.Tensor, local_view, local_lens: torch.Tensor, softmax_scale: Optional[float] = None,
+             gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from . import ops
+
+        ops.decode_attention(q, local_view, local_lens, softmax_scale=softmax_scale, shard=True, shard_out=(self.o, self.lse),
+                             workspace=self.ws)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.msg, group=self.group)
+            src = self.gathered
+        else:
+            src = self.msg
+        return ops.merge_gathered(src, self.world, self.n_seqs, self.hq, self.d, out=self.out, gate=gate)
+
+
 def sharded_decode(q: torch.Tensor, local_view, local_lens: torch.Tensor, softmax_scale: Optional[float] = None,
                    gate: Optional[torch.Tensor] = None, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Decode attention over a KV-length-sharded cache: local shard -> all-gather -> LSE merge.

@@ -101,6 +101,8 @@ int32_t hs_attn_take_device_error(int32_t *flags);
  * elapsed device time.  Off by default; one set of events per process, so profile one stream at a time. */
 int32_t hs_attn_set_profiling(int32_t on);
 int32_t hs_attn_last_kernel_ms(float *ms);
+/* Kernels this library has launched in this process so far (all entry points, all streams). */
+int64_t hs_attn_launch_count(void);
 
 /* ---- blockwise quantiser (flat tensors) --------------------------------------------------
  * Replaces cquantize_blockwise_{bf16,fp16,fp32}[_nf4,_fp4] and cdequantize_blockwise_*
@@ -180,6 +182,11 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
  * optionally times sigmoid(gate).  A part with lse = -inf contributes nothing. */
 int32_t hs_attn_merge_partials(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t n_rows,
                                int32_t head_dim, void *out, const void *gate, hs_stream_t stream);
+/* The same with the parts `part_stride_o` / `part_stride_lse` floats apart (>= n_rows * head_dim / n_rows), so that
+ * each GPU's (o, lse) message of an all-gather can be merged where it landed, without repacking. */
+int32_t hs_attn_merge_partials_strided(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t part_stride_o,
+                                       int64_t part_stride_lse, int64_t n_rows, int32_t head_dim, void *out, const void *gate,
+                                       hs_stream_t stream);
 
 /* ---- causal prefill attention ---------------------------------------------------------------
  * compute_attention_masked for q_len > 1 (architectures/llama.rs:1023-1119, single shot and the 1024-row

@@ -189,6 +189,10 @@ def test_shards_merge_to_unsplit(cuda):
         o, lse = run_decode(cuda, [c], q, [b - a], shard=True)
         os_.append(o); ls_.append(lse)
     merged = ops.merge_partials(torch.stack(os_), torch.stack(ls_))
+    # the same parts laid out as all-gathered messages [o | lse] per part, merged where they lie
+    msgs = torch.cat([torch.cat([o.reshape(-1), l.reshape(-1)]) for o, l in zip(os_, ls_)])
+    in_place = ops.merge_gathered(msgs, len(os_), q.shape[0], q.shape[1], q.shape[2])
+    assert torch.equal(in_place, merged)
     assert (merged.float() - ref.float()).abs().max().item() <= 1e-3 + 8e-3  # bf16 output rounding
     # an empty shard (lse = -inf) contributes nothing
     os_.append(torch.zeros_like(os_[0])); ls_.append(torch.full_like(ls_[0], float("-inf")))
