@@ -174,6 +174,38 @@ def gdn_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
     return out
 
 
+def gdn_prologue(mixed_qkv: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor, has_state: bool, a_in: torch.Tensor,
+                 b_in: torch.Tensor, neg_a_exp: torch.Tensor, dt_bias: torch.Tensor, n_k_heads: int, n_v_heads: int,
+                 head_k_dim: int = 128, head_v_dim: int = 128):
+    """conv1d + SiLU + split + L2 norm + gates of GatedDeltaNetLayer::forward (qwen3_5.rs:627-701).
+
+    mixed_qkv bf16 [B, T, conv_dim]; conv_weight bf16 [conv_dim, 1, ks] or [conv_dim, ks]; conv_state bf16
+    [B, conv_dim, ks-1], read when ``has_state`` and always replaced; a_in, b_in bf16 [B, T, nv]; neg_a_exp, dt_bias
+    fp32 [nv].  Returns fp32 (q [B,T,nk,hk], k, v [B,T,nv,hv], g [B,T,nv], beta [B,T,nv])."""
+    _need_cuda(mixed_qkv, conv_weight, conv_state, a_in, b_in, neg_a_exp, dt_bias)
+    b, t, _ = mixed_qkv.shape
+    ks = conv_weight.shape[-1]
+    dev = mixed_qkv.device
+    q = torch.empty(b, t, n_k_heads, head_k_dim, dtype=torch.float32, device=dev)
+    k = torch.empty_like(q)
+    v = torch.empty(b, t, n_v_heads, head_v_dim, dtype=torch.float32, device=dev)
+    g = torch.empty(b, t, n_v_heads, dtype=torch.float32, device=dev)
+    beta = torch.empty_like(g)
+    check(lib.hs_gdn_prologue(_ptr(mixed_qkv), _ptr(conv_weight), _ptr(conv_state), 1 if has_state else 0, _ptr(a_in), _ptr(b_in),
+                              _ptr(neg_a_exp), _ptr(dt_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), b, t, n_k_heads,
+                              n_v_heads, head_k_dim, head_v_dim, ks, _stream()))
+    return q, k, v, g, beta
+
+
+def gdn_epilogue(o: torch.Tensor, z: torch.Tensor, norm_weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNormGated (qwen3_5.rs:305-313): o fp32 [..., hv], z bf16 same shape, norm_weight fp32 [hv] -> bf16 [..., hv]."""
+    _need_cuda(o, z, norm_weight)
+    hv = o.shape[-1]
+    y = torch.empty(o.shape, dtype=torch.bfloat16, device=o.device)
+    check(lib.hs_gdn_epilogue(_ptr(o), _ptr(z), _ptr(norm_weight), float(eps), _ptr(y), o.numel() // hv, hv, _stream()))
+    return y
+
+
 def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: Optional[float] = None,
                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal GQA prefill (llama.rs:1023-1119; qwen3_5.rs:1012-1059 with `gate`).

@@ -215,6 +215,29 @@ int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const f
                          float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
                          int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
 
+/* The elementwise steps either side of the rule in GatedDeltaNetLayer::forward, one pass over HBM each.
+ *
+ * hs_gdn_prologue (architectures/qwen3_5.rs:627-701, after the fused input projection): depthwise causal conv1d over
+ * time with `kernel_size` taps (left context: conv_state, or zeros when has_state == 0) in bf16, SiLU, split into
+ * q | k | v, q and k to fp32 and divided by max(||.||_2, 1e-3) per head, q times 1/sqrt(head_k_dim), v to fp32,
+ * g = neg_a_exp * softplus(a_in + dt_bias), beta = sigmoid(b_in); conv_state is replaced by the last kernel_size-1 frames.
+ *   mixed_qkv   bf16 [n_seqs, n_tokens, 2*n_k_heads*head_k_dim + n_v_heads*head_v_dim]     (qwen3_5.rs:622)
+ *   conv_weight bf16 [conv_dim, kernel_size]  (the reference's [conv_dim, 1, kernel_size])  (qwen3_5.rs:655-662)
+ *   conv_state  bf16 [n_seqs, conv_dim, kernel_size-1] in/out, always kernel_size-1 frames   (qwen3_5.rs:633-653)
+ *   a_in, b_in  bf16 [n_seqs, n_tokens, n_v_heads];  neg_a_exp = -exp(A_log), dt_bias  f32 [n_v_heads]  (:687-689,701)
+ *   q, k  f32 [n_seqs, n_tokens, n_k_heads, head_k_dim];  v f32 [n_seqs, n_tokens, n_v_heads, head_v_dim]
+ *   g, beta  f32 [n_seqs, n_tokens, n_v_heads]                 -> the inputs of hs_gdn_recurrent
+ *
+ * hs_gdn_epilogue (RMSNormGated, qwen3_5.rs:305-313 as called at :771-784): per (token, value head) row of head_v_dim:
+ *   y = bf16( o * rsqrt(mean(o^2) + eps) * norm_weight * silu(z) )
+ *   o f32 [n_rows, head_v_dim] (the rule's output), z bf16 [n_rows, head_v_dim], norm_weight f32 [head_v_dim]. */
+int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in,
+                        const void *b_in, const float *neg_a_exp, const float *dt_bias, float *q, float *k, float *v, float *g,
+                        float *beta, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
+                        int32_t head_k_dim, int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream);
+int32_t hs_gdn_epilogue(const float *o, const void *z, const float *norm_weight, float eps, void *y, int64_t n_rows,
+                        int32_t head_v_dim, hs_stream_t stream);
+
 /* ---- host-side cache objects ------------------------------------------------------------------
  * C++ mirror of the reference's per-layer cache (crates/hyprstream/src/runtime/kv_cache.rs): LayerKVCache
  * (:1029-1900: new / new_paged / update / get / clear / truncate_to / seq_pos / memory_usage) and BlockPool

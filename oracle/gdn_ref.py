@@ -42,6 +42,39 @@ def rmsnorm_gated(x: torch.Tensor, gate: torch.Tensor, weight_f32: torch.Tensor,
     return (normed * weight_f32 * g).to(orig)
 
 
+def gdn_prologue(mixed_qkv: torch.Tensor, conv_weight: torch.Tensor, conv_state: Optional[torch.Tensor], a_in: torch.Tensor,
+                 b_in: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, n_k_heads: int, head_k_dim: int,
+                 n_v_heads: int, head_v_dim: int):
+    """GatedDeltaNetLayer::forward between the input projection and the delta rule (qwen3_5.rs:627-701), same ATen
+    operators in the same order and dtypes: depthwise causal conv1d (kernel ks, left context = conv_state or zeros) in
+    the model dtype, SiLU, split into q | k | v, q and k to fp32 and L2-normalised, q * 1/sqrt(head_k_dim), v to fp32,
+    g and beta in fp32.
+
+    mixed_qkv [B,T,conv_dim] and conv_weight [conv_dim,1,ks] in the model dtype; conv_state [B,conv_dim,ks-1] or None.
+    Returns (q [B,T,nk,hk], k, v [B,T,nv,hv], g [B,T,nv], beta [B,T,nv], new_conv_state [B,conv_dim,ks-1]).
+
+    The reference keeps fewer than ks-1 frames after a first call shorter than ks-1 tokens (:650-651) and then cannot
+    run the next call; here the state always has ks-1 frames (zeros in front), which is the same wherever the
+    reference runs."""
+    bsz, seq, conv_dim = mixed_qkv.shape
+    ks = conv_weight.shape[-1]
+    x_t = mixed_qkv.permute(0, 2, 1)
+    if conv_state is None:
+        conv_state = torch.zeros(bsz, conv_dim, ks - 1, dtype=mixed_qkv.dtype)
+    padded = torch.cat([conv_state, x_t], dim=2)
+    new_state = padded.narrow(2, padded.shape[2] - (ks - 1), ks - 1).contiguous()
+    conv_out = torch.nn.functional.conv1d(padded, conv_weight, None, stride=1, padding=0, dilation=1, groups=conv_dim)
+    conv_out = torch.nn.functional.silu(conv_out).permute(0, 2, 1)
+    key_dim, val_dim = n_k_heads * head_k_dim, n_v_heads * head_v_dim
+    q = conv_out.narrow(2, 0, key_dim).reshape(bsz, seq, n_k_heads, head_k_dim)
+    k = conv_out.narrow(2, key_dim, key_dim).reshape(bsz, seq, n_k_heads, head_k_dim)
+    v = conv_out.narrow(2, 2 * key_dim, val_dim).reshape(bsz, seq, n_v_heads, head_v_dim)
+    q = l2_normalize(q.float()) * (1.0 / float(head_k_dim) ** 0.5)
+    k = l2_normalize(k.float())
+    g, beta = gdn_gates(a_in, b_in, a_log, dt_bias)
+    return q, k, v.float(), g, beta, new_state
+
+
 def recurrent_step(q_t, k_t, v_t, g_t, b_t, state) -> Tuple[torch.Tensor, torch.Tensor]:
     """One decode step (qwen3_5.rs:725-751).
 
