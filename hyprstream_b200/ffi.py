@@ -54,6 +54,8 @@ _SIGS = {
     "hs_quantize_blockwise": (c_int32, [c_int32, c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "hs_dequantize_blockwise": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32, c_void_p]),
     "hs_rope_apply": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "hs_qk_norm_rope": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p,
+                                  c_int32, c_int32, c_int64, c_int32, c_int32, c_void_p]),
     "hs_kv_quantize_write": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "hs_kv_gather_dequantize": (c_int32, [POINTER(KVView), c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "hs_attn_decode_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),

@@ -71,6 +71,27 @@ def rope_apply(x: torch.Tensor, sin: torch.Tensor, cos: torch.Tensor, positions:
     return out
 
 
+def qk_norm_rope(x: torch.Tensor, n_heads: int, head_dim: int, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                 weight_plus_one: bool = True, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                 positions: Optional[torch.Tensor] = None, rotary_dim: int = 0, with_gate: bool = False):
+    """Per-head RMS norm + partial RoPE (+ gate split) of a projection output (qwen3_5.rs:963-990,1077-1091).
+
+    x bf16 [n_tokens, n_heads * head_dim] (or [n_tokens, n_heads * 2 * head_dim] with ``with_gate``: per head the query
+    half then the gate half).  Returns bf16 [n_tokens, n_heads, head_dim], and the gate of the same shape with
+    ``with_gate``."""
+    _need_cuda(x, norm_weight, sin, cos, positions)
+    n_tokens = x.shape[0]
+    per_head = head_dim * (2 if with_gate else 1)
+    if x.dim() != 2 or x.shape[1] != n_heads * per_head or not x.is_contiguous():
+        raise ValueError("qk_norm_rope: x must be contiguous [n_tokens, n_heads * head_dim (* 2 with the gate)]")
+    out = torch.empty(n_tokens, n_heads, head_dim, dtype=torch.bfloat16, device=x.device)
+    gate = torch.empty_like(out) if with_gate else None
+    check(lib.hs_qk_norm_rope(_ptr(x), n_heads * per_head, per_head, _ptr(out), _ptr(gate), _ptr(norm_weight), float(eps),
+                              1 if weight_plus_one else 0, _ptr(sin), _ptr(cos), _ptr(positions),
+                              0 if sin is None else sin.shape[0], rotary_dim, n_tokens, n_heads, head_dim, _stream()))
+    return (out, gate) if with_gate else out
+
+
 def kv_quantize_write(view: KVView, k_new: torch.Tensor, v_new: torch.Tensor, dst_pos: Optional[torch.Tensor],
                       sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
                       rotary_dim: int = 0) -> None:

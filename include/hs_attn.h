@@ -123,6 +123,21 @@ int32_t hs_rope_apply(const void *x, void *out, const void *sin, const void *cos
                       int64_t n_rows, int32_t n_heads, int32_t head_dim, int32_t rotary_dim, int32_t n_positions,
                       hs_stream_t stream);
 
+/* Per-head RMS norm + (partial) RoPE + gate split in one pass: the steps between the q/k/v projections and the
+ * cache / attention call of Qwen3_5FullAttention::forward (architectures/qwen3_5.rs:963-990; apply_qknorm :1077-1091)
+ * and LlamaAttention's optional QK-norm (architectures/llama.rs:929-992).
+ *   x         bf16, row (t, h) at x + t*token_stride + h*head_stride (elements): e.g. the doubled q projection
+ *             [n_tokens, n_heads, 2*head_dim] with head_stride = 2*head_dim, or a dense k
+ *   out       bf16 [n_tokens, n_heads, head_dim] = rope(bf16(x * rsqrt(mean(x^2) + eps) * (w or 1 + w)))
+ *   gate_out  optional bf16 [n_tokens, n_heads, head_dim] = x[.., head_dim : 2*head_dim] (qwen3_5.rs:965-967)
+ *   norm_weight f32 [head_dim] or NULL (no norm); weight_plus_one != 0 for Qwen3.5's (1 + w)
+ *   sin, cos  bf16 [n_positions, rotary_dim/2] or NULL (no rotation); positions int32 [n_tokens]; a position outside
+ *             the table leaves the row unrotated and records HS_DEVERR_ROPE_RANGE */
+int32_t hs_qk_norm_rope(const void *x, int64_t token_stride, int64_t head_stride, void *out, void *gate_out,
+                        const float *norm_weight, float eps, int32_t weight_plus_one, const void *sin, const void *cos,
+                        const int32_t *positions, int32_t n_positions, int32_t rotary_dim, int64_t n_tokens,
+                        int32_t n_heads, int32_t head_dim, hs_stream_t stream);
+
 /* ---- KV quantise-on-write -----------------------------------------------------------------
  * LayerKVCache::update (kv_cache.rs:1275-1496) for device-resident storage: appends
  * k_new/v_new [n_seqs, n_tokens, n_kv_heads, head_dim] bf16 to the caches in `view`, sequence s at
