@@ -1,0 +1,380 @@
+// Gated DeltaNet prefill in chunked (WY / UT-transform) form on the tensor cores: chunked_delta_rule
+// (architectures/qwen3_5.rs:342-498) re-cut for one CTA per (sequence, value head) with the state in registers.
+//
+// For a chunk of C tokens with G = cumsum(g), Gamma = exp(G), the rule  S <- e^g S; u = beta (v - S^T k); S <- S + k u^T;
+// o = S^T q  is equivalent to (qwen3_5.rs:394-485, same algebra):
+//   A'[t][s] = beta_t (k_t.k_s) exp(G_t - G_s), s < t;   T = (I + A')^-1;   U = T (beta V - beta Gamma K S0)
+//   o_t = Gamma_t q_t^T S0 + sum_{s<=t} exp(G_t - G_s)(q_t.k_s) u_s;   S = Gamma_C S0 + sum_s exp(G_C - G_s) k_s u_s^T
+// (the reference forms W = T (beta Gamma K) and V' = T (beta V) first and U = V' - W S0; applying T last is the same
+// product and leaves no per-chunk matrix products outside the tensor cores)
+// The reference uses C = 64; the result does not depend on C, and C = 16 keeps the triangular solve (a 16 x 16 forward
+// substitution) and the other per-chunk set-up short enough to sit in front of every chunk.
+//
+// Layout: warp w of 8 owns value columns [16w, 16w+16) and keeps S^T[v][k] (16 x 128 fp32) in its mma accumulator
+// registers; every S-dependent product of the chunk is warp-local, with the state or U^T as the A operand straight from
+// those accumulators (fp32 -> bf16 pairs), mma.sync.m16n8k16 bf16 x bf16 -> fp32:
+//   [K S0 | Qg S0]^T = S^T . [K | Qg]^T   (32 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (2 MMAs)
+//   O^T = (Qg S0)^T + U^T . P^T           (2 MMAs)       S^T = Gamma_C S^T + U^T . Kd           (16 MMAs)
+// The per-chunk set-up that does not depend on S: the k.k and q.k products also run on the tensor cores (bf16 k, q); decay,
+// Qg = Gamma q and Kd = exp(G_C - G) k are elementwise; a ninth warp stages the next chunk's fp32 inputs (bulk async copies),
+// scans the decay and solves for T while the eight state warps already run the first product.  Only MMA operands are
+// rounded to bf16; the state and all accumulation stay fp32.
+// Bound: latency of the per-chunk dependency chain (4 block barriers); FLOPs are far below the tensor peak.
+//
+// Accuracy: bf16 operand rounding (2^-9 relative) enters every S-dependent product, so outputs agree with the fp32 rule
+// to ~1e-3, inside the path's stated tolerance (max-abs 2e-2, mean-abs 2e-3); hs_gdn_recurrent remains the fp32-exact form.
+#include <cuda_bf16.h>
+
+#include "hs_common.cuh"
+
+namespace hs {
+
+constexpr int kGcC = 16;          // tokens per chunk
+constexpr int kGcD = 128;         // head_k_dim = head_v_dim
+constexpr int kGcThreads = 288;   // warps 0-7: one 16-column slice of the state each; warp 8: staging, decay scan, solve
+constexpr int kGcRS = kGcD + 4;   // fp32 row stride of the staged inputs (floats)
+constexpr int kGcBS = kGcD + 8;   // bf16 row stride of the [16][128] operand tiles
+constexpr int kGcPS = kGcC + 8;   // bf16 row stride of P, T and of Kd^T
+
+struct GcSmem {
+    float raw[2][3][kGcC][kGcRS];       // k, q, v of a chunk (fp32), double buffered
+    float g[2][kGcC], b[2][kGcC];
+    float G[kGcC], gam[kGcC], dec[kGcC];  // cumulative log-decay, exp(G), exp(G_C - G)
+    __align__(16) float A[kGcC][kGcC];  // A' (strictly lower, the rest zero)
+    __nv_bfloat16 Tb[kGcC][kGcPS];      // (I + A')^-1 (lower)
+    __nv_bfloat16 Kb[kGcC][kGcBS], Qb[kGcC][kGcBS];    // k, q
+    __nv_bfloat16 Qg[kGcC][kGcBS];      // Gamma q
+    __nv_bfloat16 KdT[kGcD][kGcPS];     // (exp(G_C - G) k)^T
+    __nv_bfloat16 P[kGcC][kGcPS];       // (q.k) exp(G_t - G_s), s <= t
+    __align__(8) uint64_t full[2];      // mbarriers: the bulk copies of a raw buffer have landed
+};
+
+constexpr long long kGcWaitCycles = 4000000000LL;  // ~2 s: bound of the wait on the copies
+
+__device__ __forceinline__ uint32_t gc_s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ bool gc_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity) {  // bounded
+    if (gc_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!gc_try_wait(bar, parity))
+        if (clock64() - t0 > kGcWaitCycles) return false;
+    return true;
+}
+__device__ __forceinline__ void gc_bulk_row(uint32_t dst, const float *src, uint32_t bar) {  // one 512-byte row
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(512u), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t gc_pack(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void gc_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t gc_ld32(const __nv_bfloat16 *p) { return *reinterpret_cast<const uint32_t *>(p); }
+
+#ifdef HS_GC_TIMING  // diagnostic build only: cycle stamps of CTA 0, warp 1, first chunks
+__device__ long long g_gc_stamps[64 * 8];
+__device__ long long g_gc_stamps2[64 * 8];
+#define HS_GC_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32 && c < 64) g_gc_stamps[c * 8 + (i)] = clock64(); } while (0)
+__device__ long long g_gc_stamps3[32 * 6 * 9];
+__device__ __forceinline__ long long gc_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
+#define HS_GC_WSTAMP(ph) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && c < 32) g_gc_stamps3[(c * 6 + (ph)) * 9 + warp] = gc_clock(); } while (0)
+#define HS_GC_STAMP8(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 256 && c < 64) g_gc_stamps[c * 8 + (i)] = clock64(); } while (0)
+#else
+#define HS_GC_STAMP(i) do {} while (0)
+__device__ long long g_gc_stamps3[32 * 6 * 9];
+__device__ __forceinline__ long long gc_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
+#define HS_GC_WSTAMP(ph) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && c < 32) g_gc_stamps3[(c * 6 + (ph)) * 9 + warp] = gc_clock(); } while (0)
+#define HS_GC_STAMP8(i) do {} while (0)
+#endif
+
+__global__ void __launch_bounds__(kGcThreads, 1)
+gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v, const float *__restrict__ g,
+                 const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
+                 int n_v_heads, int *__restrict__ err) {
+    extern __shared__ __align__(16) unsigned char gc_smem_raw[];
+    GcSmem &sm = *reinterpret_cast<GcSmem *>(gc_smem_raw);
+    const int b = blockIdx.y, h = blockIdx.x, kh = h / (n_v_heads / n_k_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, jq = lane & 3;
+    const bool chain_warp = warp < 8;
+    const int v0 = (warp & 7) * 16;  // a chain warp's value columns
+
+    // S^T accumulators: tile i covers k columns [8i, 8i+8): St[i] = {S^T[v0+gq][8i+2jq], [..+1], S^T[v0+gq+8][8i+2jq], [..+1]}
+    float St[16][4];
+    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * kGcD * kGcD;  // [k][v]
+    if (chain_warp) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            St[i][0] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq];
+            St[i][1] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq];
+            St[i][2] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8];
+            St[i][3] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8];
+        }
+    }
+
+    // Staging (warp 8): lane t < 16 issues the three 512-byte bulk copies (k, q, v rows) of token t of the chunk; they
+    // complete on the buffer's mbarrier and never touch the load/store pipe the other warps' shared-memory traffic uses.
+    // Tokens past the end are zero-filled (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).
+    const float *src_k = k + (static_cast<int64_t>(b) * n_tokens * n_k_heads + kh) * kGcD;
+    const float *src_q = q + (static_cast<int64_t>(b) * n_tokens * n_k_heads + kh) * kGcD;
+    const float *src_v = v + (static_cast<int64_t>(b) * n_tokens * n_v_heads + h) * kGcD;
+    const int64_t kq_tok = static_cast<int64_t>(n_k_heads) * kGcD, v_tok = static_cast<int64_t>(n_v_heads) * kGcD;
+    auto stage = [&](int c, int buf) {  // called by warp 8 only
+        const int t0 = c * kGcC;
+        const uint32_t bar = gc_s32(&sm.full[buf]);
+        const int n_in = min(kGcC, n_tokens - t0);
+        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(static_cast<uint32_t>(n_in) * 1536u) : "memory");
+        __syncwarp();
+        if (lane < kGcC) {
+            if (lane < n_in) {
+                gc_bulk_row(gc_s32(&sm.raw[buf][0][lane][0]), src_k + (t0 + lane) * kq_tok, bar);
+                gc_bulk_row(gc_s32(&sm.raw[buf][1][lane][0]), src_q + (t0 + lane) * kq_tok, bar);
+                gc_bulk_row(gc_s32(&sm.raw[buf][2][lane][0]), src_v + (t0 + lane) * v_tok, bar);
+            } else {
+                for (int i = 0; i < kGcD; i += 4) {
+                    *reinterpret_cast<float4 *>(&sm.raw[buf][0][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    *reinterpret_cast<float4 *>(&sm.raw[buf][1][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    *reinterpret_cast<float4 *>(&sm.raw[buf][2][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+            const bool in = lane < n_in;
+            const int64_t tok = static_cast<int64_t>(b) * n_tokens + t0 + lane;
+            sm.g[buf][lane] = in ? g[tok * n_v_heads + h] : 0.0f;
+            sm.b[buf][lane] = in ? beta[tok * n_v_heads + h] : 0.0f;
+        }
+    };
+
+    const int n_chunks = (n_tokens + kGcC - 1) / kGcC;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.full[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.full[1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!chain_warp) stage(0, 0);
+    bool failed = false;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int buf = c & 1;
+        const bool landed = gc_wait(gc_s32(&sm.full[buf]), (c >> 1) & 1);
+        // chunk c has landed (and its zero-fill / g / beta stores are visible); every warp is done with the previous chunk's
+        // set-up buffers.  A wait that ran out ends the loop for the whole CTA.
+        if (!__syncthreads_and(landed)) { failed = true; break; }
+        HS_GC_STAMP(0);
+        HS_GC_WSTAMP(0);
+
+        // ---- Pa: k, q -> bf16 (warps 0-7) | cumulative decay, then the next chunk's copies (warp 8) ----
+        if (chain_warp) {
+            const int t = threadIdx.x >> 4, c8 = (threadIdx.x & 15) * 8;
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                const float4 x0 = *reinterpret_cast<const float4 *>(&sm.raw[buf][which][t][c8]);
+                const float4 x1 = *reinterpret_cast<const float4 *>(&sm.raw[buf][which][t][c8 + 4]);
+                *reinterpret_cast<uint4 *>(which ? &sm.Qb[t][c8] : &sm.Kb[t][c8]) =
+                    make_uint4(gc_pack(x0.x, x0.y), gc_pack(x0.z, x0.w), gc_pack(x1.x, x1.y), gc_pack(x1.z, x1.w));
+            }
+        } else {
+            float x = lane < kGcC ? sm.g[buf][lane] : 0.0f;
+#pragma unroll
+            for (int off = 1; off < kGcC; off <<= 1) {
+                const float y = __shfl_up_sync(0xffffffffu, x, off);
+                if (lane >= off) x += y;
+            }
+            const float G_last = __shfl_sync(0xffffffffu, x, kGcC - 1);
+            if (lane < kGcC) { sm.G[lane] = x; sm.gam[lane] = __expf(x); sm.dec[lane] = __expf(G_last - x); }
+        }
+        HS_GC_WSTAMP(1);
+        __syncthreads();
+        HS_GC_STAMP(1);
+        // ---- Pb: k.k and q.k on the tensor cores (warps 0-3) | Qg, Kd^T (warps 4-7) |
+        //          the next chunk's copies (warp 8) ----
+        if (warp < 4) {
+            const int mt = warp >> 1, nt = warp & 1;  // mt 0: rows k (-> A'), 1: rows q (-> P); nt: tokens s in [8nt, 8nt+8)
+            const __nv_bfloat16(*Am)[kGcBS] = mt ? sm.Qb : sm.Kb;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two chains
+#pragma unroll
+            for (int kk8 = 0; kk8 < 8; ++kk8) {
+                const int col = 16 * kk8 + 2 * jq;
+                gc_mma(kk8 & 1 ? acc2 : acc, gc_ld32(&Am[gq][col]), gc_ld32(&Am[gq + 8][col]), gc_ld32(&Am[gq][col + 8]), gc_ld32(&Am[gq + 8][col + 8]),
+                       gc_ld32(&sm.Kb[8 * nt + gq][col]), gc_ld32(&sm.Kb[8 * nt + gq][col + 8]));
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] += acc2[e];
+            // acc[0], acc[1]: (t = gq, s = 8nt + 2jq, +1); acc[2], acc[3]: (t = gq + 8, same s)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = gq + 8 * (e >> 1), s2 = 8 * nt + 2 * jq + (e & 1);
+                const float dg = s2 <= t ? __expf(sm.G[t] - sm.G[s2]) : 0.0f;
+                if (mt == 0) sm.A[t][s2] = s2 < t ? sm.b[buf][t] * acc[e] * dg : 0.0f;
+                else sm.P[t][s2] = __float2bfloat16_rn(acc[e] * dg);
+            }
+        } else if (chain_warp) {
+            const int d = threadIdx.x - 128;
+#pragma unroll
+            for (int t = 0; t < kGcC; ++t) sm.Qg[t][d] = __float2bfloat16_rn(sm.gam[t] * sm.raw[buf][1][t][d]);
+#pragma unroll
+            for (int s2 = 0; s2 < kGcC; s2 += 2)
+                *reinterpret_cast<uint32_t *>(&sm.KdT[d][s2]) = gc_pack(sm.dec[s2] * sm.raw[buf][0][s2][d], sm.dec[s2 + 1] * sm.raw[buf][0][s2 + 1][d]);
+        } else if (c + 1 < n_chunks) {
+            stage(c + 1, buf ^ 1);
+        }
+        HS_GC_WSTAMP(2);
+        __syncthreads();
+        HS_GC_STAMP(2);
+
+        // ---- C: T = (I + A')^-1 by forward substitution (warp 8, one column per lane) | [K S0 | Qg S0]^T and R^T (warps 0-7) ----
+        float X[4][4];
+        uint32_t r[4];
+        if (!chain_warp) {
+#ifdef HS_GC_NOSOLVE  // diagnostic build only
+            if (lane < kGcC) for (int i = 0; i < kGcC; ++i) sm.Tb[i][lane] = __float2bfloat16_rn(i == lane ? 1.0f : 0.0f);
+#else
+            if (lane < kGcC) {
+                float col[kGcC];
+#pragma unroll
+                for (int i = 0; i < kGcC; ++i) {
+                    // row i of A' in four broadcast loads (they do not depend on the columns solved so far)
+                    float ar[kGcC];
+#pragma unroll
+                    for (int m4 = 0; m4 < kGcC; m4 += 4) {
+                        const float4 a4 = *reinterpret_cast<const float4 *>(&sm.A[i][m4]);
+                        ar[m4] = a4.x; ar[m4 + 1] = a4.y; ar[m4 + 2] = a4.z; ar[m4 + 3] = a4.w;
+                    }
+                    float a0 = i == lane ? 1.0f : 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // four chains
+#pragma unroll
+                    for (int m = 0; m < i; m += 4) {
+                        a0 = fmaf(-ar[m], col[m], a0);
+                        if (m + 1 < i) a1 = fmaf(-ar[m + 1], col[m + 1], a1);
+                        if (m + 2 < i) a2 = fmaf(-ar[m + 2], col[m + 2], a2);
+                        if (m + 3 < i) a3 = fmaf(-ar[m + 3], col[m + 3], a3);
+                    }
+                    col[i] = i >= lane ? (a0 + a1) + (a2 + a3) : 0.0f;
+                    sm.Tb[i][lane] = __float2bfloat16_rn(col[i]);
+                }
+            }
+#endif
+        } else {
+            // rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of Qg
+#pragma unroll
+            for (int n = 0; n < 4; ++n) X[n][0] = X[n][1] = X[n][2] = X[n][3] = 0.0f;
+#pragma unroll
+            for (int kk8 = 0; kk8 < 8; ++kk8) {
+                const uint32_t a0 = gc_pack(St[2 * kk8][0], St[2 * kk8][1]), a1 = gc_pack(St[2 * kk8][2], St[2 * kk8][3]);
+                const uint32_t a2 = gc_pack(St[2 * kk8 + 1][0], St[2 * kk8 + 1][1]), a3 = gc_pack(St[2 * kk8 + 1][2], St[2 * kk8 + 1][3]);
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const __nv_bfloat16 *row = n < 2 ? &sm.Kb[8 * n + gq][0] : &sm.Qg[8 * (n - 2) + gq][0];
+                    gc_mma(X[n], a0, a1, a2, a3, gc_ld32(row + 16 * kk8 + 2 * jq), gc_ld32(row + 16 * kk8 + 2 * jq + 8));
+                }
+            }
+            // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int s0 = 8 * n + 2 * jq;
+                const float b0 = sm.b[buf][s0], b1 = sm.b[buf][s0 + 1], g0 = sm.gam[s0], g1 = sm.gam[s0 + 1];
+                const float r00 = b0 * (sm.raw[buf][2][s0][v0 + gq] - g0 * X[n][0]), r01 = b1 * (sm.raw[buf][2][s0 + 1][v0 + gq] - g1 * X[n][1]);
+                const float r10 = b0 * (sm.raw[buf][2][s0][v0 + gq + 8] - g0 * X[n][2]), r11 = b1 * (sm.raw[buf][2][s0 + 1][v0 + gq + 8] - g1 * X[n][3]);
+                r[2 * n] = gc_pack(r00, r01);
+                r[2 * n + 1] = gc_pack(r10, r11);
+            }
+            HS_GC_STAMP(4);
+        }
+        HS_GC_WSTAMP(3);
+        __syncthreads();  // T is ready
+        HS_GC_STAMP(3);
+        if (chain_warp) {
+            // ---- D: U^T = R^T . T^T; O^T = (Qg S0)^T + U^T . P^T; S^T = Gamma_C S^T + U^T . Kd ----
+            float U[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                U[n][0] = U[n][1] = U[n][2] = U[n][3] = 0.0f;
+                gc_mma(U[n], r[0], r[1], r[2], r[3], gc_ld32(&sm.Tb[8 * n + gq][2 * jq]), gc_ld32(&sm.Tb[8 * n + gq][2 * jq + 8]));
+            }
+            const uint32_t u0 = gc_pack(U[0][0], U[0][1]), u1 = gc_pack(U[0][2], U[0][3]), u2 = gc_pack(U[1][0], U[1][1]), u3 = gc_pack(U[1][2], U[1][3]);
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+                gc_mma(X[2 + n], u0, u1, u2, u3, gc_ld32(&sm.P[8 * n + gq][2 * jq]), gc_ld32(&sm.P[8 * n + gq][2 * jq + 8]));
+            const float gC = sm.gam[kGcC - 1];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                St[i][0] *= gC; St[i][1] *= gC; St[i][2] *= gC; St[i][3] *= gC;
+                gc_mma(St[i], u0, u1, u2, u3, gc_ld32(&sm.KdT[8 * i + gq][2 * jq]), gc_ld32(&sm.KdT[8 * i + gq][2 * jq + 8]));
+            }
+            // outputs: X[2 + n] = O^T rows v0+gq (+8), tokens 8n + 2jq (+1)
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int t = c * kGcC + 8 * n + 2 * jq + e;
+#ifdef HS_GC_NOSTORE  // diagnostic build only
+                    if (t < 0) {
+#else
+                    if (t < n_tokens) {
+#endif
+                        float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
+                        op[0] = X[2 + n][e];
+                        op[8] = X[2 + n][2 + e];
+                    }
+                }
+            HS_GC_STAMP(5);
+        }
+        HS_GC_WSTAMP(4);
+    }
+    if (failed) {
+        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        return;  // the state is left as it was
+    }
+    if (chain_warp) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            sp[(8 * i + 2 * jq) * kGcD + v0 + gq] = St[i][0];
+            sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq] = St[i][1];
+            sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8] = St[i][2];
+            sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8] = St[i][3];
+        }
+    }
+}
+
+}  // namespace hs
+
+using namespace hs;
+
+extern "C" {
+
+int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
+                             float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
+                             int32_t head_v_dim, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (n_seqs < 0 || n_tokens < 0 || n_k_heads <= 0 || n_v_heads <= 0) return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: bad sizes");
+    if (n_v_heads % n_k_heads != 0) return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: n_v_heads %d not a multiple of n_k_heads %d", n_v_heads, n_k_heads);
+    if (head_k_dim != kGcD || head_v_dim != kGcD)
+        return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: head dims %d x %d (supported: 128 x 128; use hs_gdn_recurrent)", head_k_dim, head_v_dim);
+    if (n_seqs == 0 || n_tokens == 0) return HS_OK;
+    if (!q || !k || !v || !g || !beta || !state || !out) return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: NULL pointer");
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(state, 4) || !aligned(out, 4))
+        return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: q, k, v must be 16-byte aligned");
+    if (n_seqs > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: more than 65535 sequences");
+    int *err = device_error_word();
+    if (!err) return fail(HS_ERR_DEVICE, "hs_gdn_chunk_prefill: device error word unavailable");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(GcSmem)));
+        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaStream_t s = as_stream(stream);
+    dim3 grid(n_v_heads, n_seqs);
+    prof_begin(s);
+    gdn_chunk_kernel<<<grid, kGcThreads, sizeof(GcSmem), s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
+    prof_end(s);
+    return check_launch("hs_gdn_chunk_prefill");
+}
+
+}  // extern "C"

@@ -64,6 +64,7 @@ _SIGS = {
     "hs_attn_decode_static": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p]),
     "hs_attn_prefill_causal": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_float, c_void_p]),
     "hs_gdn_recurrent": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
+    "hs_gdn_chunk_prefill": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
     "hs_gdn_prologue": (c_int32, [c_void_p] * 3 + [c_int32] + [c_void_p] * 9 + [c_int32] * 7 + [c_void_p]),
     "hs_gdn_epilogue": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_void_p]),
     "hs_host_set_allocator": (c_int32, [c_void_p, c_void_p]),

@@ -54,11 +54,14 @@ def main():
     q, k, v, g, beta = _inputs(4, a.tokens, dev, 2)
     st = torch.zeros(4, 32, 128, 128, device=dev)
     pre_ms = _time(lambda: ops.gdn_recurrent(q, k, v, g, beta, st), max(2, a.iters // 10), warmup=1)
+    st2 = torch.zeros(4, 32, 128, 128, device=dev)
+    chunk_ms = _time(lambda: ops.gdn_chunk_prefill(q, k, v, g, beta, st2), max(2, a.iters // 5), warmup=1)
     flops_chunked = 11.7e6 * (a.tokens / 64) * 32 * 4  # the chunked algorithm's count (qwen3_5.rs:342-498), for reference
     print(json.dumps({"workload": "configs[4] gated DeltaNet", "decode_batch": 64, "decode_ms": dec_ms,
                       "decode_state_gbps": dec_bytes / dec_ms / 1e6, "prefill_tokens": a.tokens, "prefill_batch": 4,
-                      "prefill_ms": pre_ms, "prefill_tokens_per_s": 4 * a.tokens / pre_ms * 1e3,
-                      "prefill_equiv_chunked_tflops": flops_chunked / pre_ms / 1e9, "device_error_flags": ffi.take_device_error()}))
+                      "prefill_fp32_rule_ms": pre_ms, "prefill_fp32_rule_tokens_per_s": 4 * a.tokens / pre_ms * 1e3,
+                      "prefill_chunked_ms": chunk_ms, "prefill_chunked_tokens_per_s": 4 * a.tokens / chunk_ms * 1e3,
+                      "prefill_chunked_tflops_at_c64_count": flops_chunked / chunk_ms / 1e9, "device_error_flags": ffi.take_device_error()}))
 
 
 if __name__ == "__main__":

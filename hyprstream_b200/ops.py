@@ -195,6 +195,19 @@ def gdn_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
     return out
 
 
+def gdn_chunk_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                      state: torch.Tensor) -> torch.Tensor:
+    """chunked_delta_rule (qwen3_5.rs:342-498) on the tensor cores: same arguments as gdn_recurrent, bf16 operand
+    rounding inside (results within ~1e-3 of the fp32 rule); `state` is updated in place."""
+    _need_cuda(q, k, v, g, beta, state)
+    b, t, nk, hk = q.shape
+    nv, hv = v.shape[2], v.shape[3]
+    out = torch.empty(b, t, nv, hv, dtype=torch.float32, device=q.device)
+    check(lib.hs_gdn_chunk_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(out), b, t, nk, nv, hk, hv,
+                                   _stream()))
+    return out
+
+
 def gdn_prologue(mixed_qkv: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor, has_state: bool, a_in: torch.Tensor,
                  b_in: torch.Tensor, neg_a_exp: torch.Tensor, dt_bias: torch.Tensor, n_k_heads: int, n_v_heads: int,
                  head_k_dim: int = 128, head_v_dim: int = 128):

@@ -230,6 +230,16 @@ int32_t hs_gdn_recurrent(const float *q, const float *k, const float *v, const f
                          float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
                          int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
 
+/* The prefill branch of the same layer: chunked_delta_rule (architectures/qwen3_5.rs:342-498, called at :753-769) on
+ * the tensor cores.  Same arguments, layouts and in-place state update as hs_gdn_recurrent, same mathematics (the chunked
+ * form is an exact re-association of the rule; the chunk length is internal), but the operands of the S-dependent
+ * products are rounded to bf16 (state, accumulation and the per-chunk triangular solve stay fp32): results agree with
+ * hs_gdn_recurrent / the fp32 reference to ~1e-3, inside the path's tolerance (max-abs 2e-2, mean-abs 2e-3).  Head dims
+ * 128 x 128.  Use hs_gdn_recurrent where fp32-exact results are wanted or for single decode tokens. */
+int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
+                             float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads,
+                             int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
+
 /* The elementwise steps either side of the rule in GatedDeltaNetLayer::forward, one pass over HBM each.
  *
  * hs_gdn_prologue (architectures/qwen3_5.rs:627-701, after the fused input projection): depthwise causal conv1d over

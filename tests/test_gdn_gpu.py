@@ -99,3 +99,60 @@ def test_rejects_unsupported_geometry(cuda):
     assert ffi.lib.hs_gdn_recurrent(p, p, p, p, p, p, p, 1, 1, 2, 4, 96, 128, None) == ffi.HS_ERR_UNSUPPORTED
     assert ffi.lib.hs_gdn_recurrent(p, p, p, p, p, p, p, 1, 1, 3, 4, 128, 128, None) == ffi.HS_ERR_ARG
     assert ffi.lib.hs_gdn_recurrent(None, p, p, p, p, p, p, 1, 1, 2, 4, 128, 128, None) == ffi.HS_ERR_ARG
+
+
+CHUNK_MAX_TOL, CHUNK_MEAN_TOL = 2e-2, 2e-3   # the path's stated tolerance against an fp32 recomputation
+
+
+@pytest.mark.parametrize("t", [1, 15, 16, 17, 64, 200, 1000])
+def test_chunk_prefill_matches_oracle_and_fp32_kernel(cuda, t):
+    """hs_gdn_chunk_prefill (tensor cores, bf16 operands) against the oracle's chunked_delta_rule (fp32, chunk 64) and
+    the fp32 recurrent kernel: outputs and final state, from a non-zero initial state."""
+    from hyprstream_b200 import ops
+
+    q, k, v, g, beta, s0 = _inputs(2, t, 2, 4, 128, 128, seed=100 + t)
+    state = s0.clone().to(cuda)
+    out = ops.gdn_chunk_prefill(*(x.to(cuda) for x in (q, k, v, g, beta)), state)
+    state32 = s0.clone().to(cuda)
+    out32 = ops.gdn_recurrent(*(x.to(cuda) for x in (q, k, v, g, beta)), state32)
+    torch.cuda.synchronize()
+    o_ref, s_ref = _oracle(q, k, v, g, beta, s0, chunked=t > 1)
+    for ref_o, ref_s, what in ((o_ref, s_ref, "oracle"), (out32.cpu(), state32.cpu(), "fp32 kernel")):
+        d = (out.cpu() - ref_o).abs()
+        assert d.max().item() <= CHUNK_MAX_TOL and d.mean().item() <= CHUNK_MEAN_TOL, f"T={t} vs {what}: max {d.max().item():.3g} mean {d.mean().item():.3g}"
+        sd = (state.cpu() - ref_s).abs().max().item() / max(ref_s.abs().max().item(), 1e-6)
+        assert sd <= 1e-2, f"T={t} state vs {what}: rel {sd:.3g}"
+
+
+def test_chunk_prefill_long_run_stays_close(cuda):
+    """8192 tokens: the bf16 operand rounding does not accumulate in the fp32 state."""
+    from hyprstream_b200 import ops
+
+    q, k, v, g, beta, s0 = _inputs(1, 8192, 2, 2, 128, 128, seed=77)
+    dev = [x.to(cuda) for x in (q, k, v, g, beta)]
+    state, state32 = s0.clone().to(cuda), s0.clone().to(cuda)
+    out = ops.gdn_chunk_prefill(*dev, state)
+    out32 = ops.gdn_recurrent(*dev, state32)
+    torch.cuda.synchronize()
+    d = (out - out32).abs()
+    assert d.max().item() <= CHUNK_MAX_TOL and d.mean().item() <= CHUNK_MEAN_TOL, f"max {d.max().item():.3g} mean {d.mean().item():.3g}"
+    tail = d[:, -256:]
+    assert tail.mean().item() <= 2 * d[:, :256].mean().item() + 1e-4, "error grows along the sequence"
+    assert (state - state32).abs().max().item() <= 1e-2 * state32.abs().max().item()
+
+
+def test_chunk_prefill_extreme_decay(cuda):
+    """Decays down to e^-30 per token and beta at its ends: nothing overflows, results match the fp32 kernel."""
+    from hyprstream_b200 import ops
+
+    q, k, v, g, beta, s0 = _inputs(1, 100, 2, 2, 128, 128, seed=5)
+    g = g * 0.0 - torch.tensor([0.0, 30.0]).repeat(50).reshape(1, 100, 1)
+    beta = torch.where(torch.arange(100).reshape(1, 100, 1) % 3 == 0, torch.ones_like(beta), beta * 0.0)
+    dev = [x.to(cuda) for x in (q, k, v, g.expand_as(beta).contiguous(), beta)]
+    state, state32 = s0.clone().to(cuda), s0.clone().to(cuda)
+    out = ops.gdn_chunk_prefill(*dev, state)
+    out32 = ops.gdn_recurrent(*dev, state32)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and torch.isfinite(state).all()
+    d = (out - out32).abs()
+    assert d.max().item() <= CHUNK_MAX_TOL and d.mean().item() <= CHUNK_MEAN_TOL
