@@ -7,8 +7,9 @@
 //   o_t = Gamma_t q_t^T S0 + sum_{s<=t} exp(G_t - G_s)(q_t.k_s) u_s;   S = Gamma_C S0 + sum_s exp(G_C - G_s) k_s u_s^T
 // (the reference forms W = T (beta Gamma K) and V' = T (beta V) first and U = V' - W S0; applying T last is the same
 // product and leaves no per-chunk matrix products outside the tensor cores)
-// The reference uses C = 64; the result does not depend on C, and C = 16 keeps the triangular solve (a 16 x 16 forward
-// substitution) and the other per-chunk set-up short enough to sit in front of every chunk.
+// The reference uses C = 64; the result does not depend on C, and C = 16 keeps the triangular inverse (16 x 16: the
+// product (I + M)(I + M^2)(I + M^4)(I + M^8), M = -A', six small MMAs) and the other per-chunk set-up short enough to sit
+// in front of every chunk.
 //
 // Layout: warp w of 8 owns value columns [16w, 16w+16) and keeps S^T[v][k] (16 x 128 fp32) in its mma accumulator
 // registers; every S-dependent product of the chunk is warp-local, with the state or U^T as the A operand straight from
@@ -23,6 +24,7 @@
 //
 // Accuracy: bf16 operand rounding (2^-9 relative) enters every S-dependent product, so outputs agree with the fp32 rule
 // to ~1e-3, inside the path's stated tolerance (max-abs 2e-2, mean-abs 2e-3); hs_gdn_recurrent remains the fp32-exact form.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "hs_common.cuh"
@@ -32,12 +34,12 @@ namespace hs {
 constexpr int kGcC = 16;          // tokens per chunk
 constexpr int kGcD = 128;         // head_k_dim = head_v_dim
 constexpr int kGcThreads = 288;   // warps 0-7: one 16-column slice of the state each; warp 8: staging, decay scan, solve
-constexpr int kGcRS = kGcD + 4;   // fp32 row stride of the staged inputs (floats)
+constexpr int kGcRS = kGcD;       // fp32 row stride of the staged inputs (floats): dense, as the tensor copies write them
 constexpr int kGcBS = kGcD + 8;   // bf16 row stride of the [16][128] operand tiles
 constexpr int kGcPS = kGcC + 8;   // bf16 row stride of P, T and of Kd^T
 
 struct GcSmem {
-    float raw[2][3][kGcC][kGcRS];       // k, q, v of a chunk (fp32), double buffered
+    __align__(128) float raw[2][3][kGcC][kGcRS];  // k, q, v of a chunk (fp32), double buffered
     float g[2][kGcC], b[2][kGcC];
     float G[kGcC], gam[kGcC], dec[kGcC];  // cumulative log-decay, exp(G), exp(G_C - G)
     __align__(16) float A[kGcC][kGcC];  // A' (strictly lower, the rest zero)
@@ -65,8 +67,10 @@ __device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity) {  // bou
         if (clock64() - t0 > kGcWaitCycles) return false;
     return true;
 }
-__device__ __forceinline__ void gc_bulk_row(uint32_t dst, const float *src, uint32_t bar) {  // one 512-byte row
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(512u), "r"(bar) : "memory");
+// one [16 tokens][128] fp32 box of a 4-D tensor (d, head, token, sequence); tokens past the tensor's end arrive as zeros
+__device__ __forceinline__ void gc_tma_box(uint32_t dst, const CUtensorMap *map, int head, int token, int seq, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(map), "r"(0), "r"(head), "r"(token), "r"(seq), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ uint32_t gc_pack(float lo, float hi) {
@@ -97,11 +101,11 @@ __device__ __forceinline__ long long gc_clock() { long long t; asm volatile("mov
 #endif
 
 __global__ void __launch_bounds__(kGcThreads, 1)
-gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v, const float *__restrict__ g,
-                 const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
+gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
                  int n_v_heads, int *__restrict__ err) {
-    extern __shared__ __align__(16) unsigned char gc_smem_raw[];
-    GcSmem &sm = *reinterpret_cast<GcSmem *>(gc_smem_raw);
+    extern __shared__ unsigned char gc_smem_raw[];
+    GcSmem &sm = *reinterpret_cast<GcSmem *>((reinterpret_cast<uintptr_t>(gc_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
     const int b = blockIdx.y, h = blockIdx.x, kh = h / (n_v_heads / n_k_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, jq = lane & 3;
     const bool chain_warp = warp < 8;
@@ -120,36 +124,33 @@ gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const
         }
     }
 
-    // Staging (warp 8): lane t < 16 issues the three 512-byte bulk copies (k, q, v rows) of token t of the chunk; they
-    // complete on the buffer's mbarrier and never touch the load/store pipe the other warps' shared-memory traffic uses.
-    // Tokens past the end are zero-filled (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).
-    const float *src_k = k + (static_cast<int64_t>(b) * n_tokens * n_k_heads + kh) * kGcD;
-    const float *src_q = q + (static_cast<int64_t>(b) * n_tokens * n_k_heads + kh) * kGcD;
-    const float *src_v = v + (static_cast<int64_t>(b) * n_tokens * n_v_heads + h) * kGcD;
-    const int64_t kq_tok = static_cast<int64_t>(n_k_heads) * kGcD, v_tok = static_cast<int64_t>(n_v_heads) * kGcD;
+    // Staging (warp 8): one lane issues three TMA tensor copies per chunk (the [16 tokens][128] boxes of k, q and v; rows
+    // of a head are 512 bytes, strided by the number of heads); they complete on the buffer's mbarrier.  Tokens past the
+    // end of the sequence arrive as zeros (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).
+    // g and beta of a chunk are loaded one stage call ahead (registers gb_g, gb_b), so their global-memory latency is never
+    // waited for: stage(c) stores the values fetched during stage(c - 1) and fetches those of chunk c + 1.
+    float gb_g = 0.0f, gb_b = 0.0f;
+    auto fetch_gates = [&](int c) {
+        const int t = c * kGcC + lane;
+        const bool in = lane < kGcC && t < n_tokens;
+        const int64_t tok = static_cast<int64_t>(b) * n_tokens + t;
+        gb_g = in ? g[tok * n_v_heads + h] : 0.0f;
+        gb_b = in ? beta[tok * n_v_heads + h] : 0.0f;
+    };
     auto stage = [&](int c, int buf) {  // called by warp 8 only
         const int t0 = c * kGcC;
         const uint32_t bar = gc_s32(&sm.full[buf]);
-        const int n_in = min(kGcC, n_tokens - t0);
-        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(static_cast<uint32_t>(n_in) * 1536u) : "memory");
-        __syncwarp();
-        if (lane < kGcC) {
-            if (lane < n_in) {
-                gc_bulk_row(gc_s32(&sm.raw[buf][0][lane][0]), src_k + (t0 + lane) * kq_tok, bar);
-                gc_bulk_row(gc_s32(&sm.raw[buf][1][lane][0]), src_q + (t0 + lane) * kq_tok, bar);
-                gc_bulk_row(gc_s32(&sm.raw[buf][2][lane][0]), src_v + (t0 + lane) * v_tok, bar);
-            } else {
-                for (int i = 0; i < kGcD; i += 4) {
-                    *reinterpret_cast<float4 *>(&sm.raw[buf][0][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    *reinterpret_cast<float4 *>(&sm.raw[buf][1][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    *reinterpret_cast<float4 *>(&sm.raw[buf][2][lane][i]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                }
-            }
-            const bool in = lane < n_in;
-            const int64_t tok = static_cast<int64_t>(b) * n_tokens + t0 + lane;
-            sm.g[buf][lane] = in ? g[tok * n_v_heads + h] : 0.0f;
-            sm.b[buf][lane] = in ? beta[tok * n_v_heads + h] : 0.0f;
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(3u * kGcC * kGcD * 4u) : "memory");
+            gc_tma_box(gc_s32(&sm.raw[buf][0][0][0]), &map_k, kh, t0, b, bar);
+            gc_tma_box(gc_s32(&sm.raw[buf][1][0][0]), &map_q, kh, t0, b, bar);
+            gc_tma_box(gc_s32(&sm.raw[buf][2][0][0]), &map_v, h, t0, b, bar);
         }
+        if (lane < kGcC) {
+            sm.g[buf][lane] = gb_g;
+            sm.b[buf][lane] = gb_b;
+        }
+        fetch_gates(c + 1);
     };
 
     const int n_chunks = (n_tokens + kGcC - 1) / kGcC;
@@ -159,7 +160,10 @@ gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (!chain_warp) stage(0, 0);
+    if (!chain_warp) {
+        fetch_gates(0);
+        stage(0, 0);
+    }
     bool failed = false;
     for (int c = 0; c < n_chunks; ++c) {
         const int buf = c & 1;
@@ -229,37 +233,59 @@ gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const
         __syncthreads();
         HS_GC_STAMP(2);
 
-        // ---- C: T = (I + A')^-1 by forward substitution (warp 8, one column per lane) | [K S0 | Qg S0]^T and R^T (warps 0-7) ----
+        // ---- C: T = (I + A')^-1 (warp 8) | [K S0 | Qg S0]^T and R^T (warps 0-7) ----
         float X[4][4];
         uint32_t r[4];
         if (!chain_warp) {
-#ifdef HS_GC_NOSOLVE  // diagnostic build only
-            if (lane < kGcC) for (int i = 0; i < kGcC; ++i) sm.Tb[i][lane] = __float2bfloat16_rn(i == lane ? 1.0f : 0.0f);
-#else
-            if (lane < kGcC) {
-                float col[kGcC];
+            // (I + A')^-1 = (I + M)(I + M^2)(I + M^4)(I + M^8) with M = -A' (strictly lower 16 x 16, so M^16 = 0): three
+            // squarings and three products on the tensor cores, all in this warp's fragments.  m, p: accumulator layout,
+            // tile nt = columns [8nt, 8nt+8): {(row gq, cols 2jq, 2jq+1), (row gq+8, same cols)}.
+            float m[2][4], pm[2][4];
 #pragma unroll
-                for (int i = 0; i < kGcC; ++i) {
-                    // row i of A' in four broadcast loads (they do not depend on the columns solved so far)
-                    float ar[kGcC];
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                    for (int m4 = 0; m4 < kGcC; m4 += 4) {
-                        const float4 a4 = *reinterpret_cast<const float4 *>(&sm.A[i][m4]);
-                        ar[m4] = a4.x; ar[m4 + 1] = a4.y; ar[m4 + 2] = a4.z; ar[m4 + 3] = a4.w;
-                    }
-                    float a0 = i == lane ? 1.0f : 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // four chains
-#pragma unroll
-                    for (int m = 0; m < i; m += 4) {
-                        a0 = fmaf(-ar[m], col[m], a0);
-                        if (m + 1 < i) a1 = fmaf(-ar[m + 1], col[m + 1], a1);
-                        if (m + 2 < i) a2 = fmaf(-ar[m + 2], col[m + 2], a2);
-                        if (m + 3 < i) a3 = fmaf(-ar[m + 3], col[m + 3], a3);
-                    }
-                    col[i] = i >= lane ? (a0 + a1) + (a2 + a3) : 0.0f;
-                    sm.Tb[i][lane] = __float2bfloat16_rn(col[i]);
+                for (int e = 0; e < 4; ++e) {
+                    const int row = gq + 8 * (e >> 1), col = 8 * nt + 2 * jq + (e & 1);
+                    m[nt][e] = -sm.A[row][col];
+                    pm[nt][e] = m[nt][e] + (row == col ? 1.0f : 0.0f);
                 }
+            // A-form of a 16 x 16 matrix held in accumulator layout: its four 8 x 8 blocks as bf16 pairs; the B-form of the
+            // same matrix is each block transposed across the warp
+            auto a_form = [&](const float (&x)[2][4], uint32_t (&a)[4]) {
+                a[0] = gc_pack(x[0][0], x[0][1]); a[1] = gc_pack(x[0][2], x[0][3]); a[2] = gc_pack(x[1][0], x[1][1]); a[3] = gc_pack(x[1][2], x[1][3]);
+            };
+            auto b_form = [&](const uint32_t (&a)[4], uint32_t (&bf)[4]) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(bf[i]) : "r"(a[i]));
+            };
+            uint32_t ma[4], mb[4], pa[4];
+            a_form(m, ma);
+            b_form(ma, mb);
+#pragma unroll
+            for (int step = 0; step < 3; ++step) {
+                // m <- m . m : B operand of column tile nt = blocks (rows 0-7, nt) and (rows 8-15, nt) transposed = mb[2nt], mb[2nt+1]...
+                float m2[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    m2[nt][0] = m2[nt][1] = m2[nt][2] = m2[nt][3] = 0.0f;
+                    gc_mma(m2[nt], ma[0], ma[1], ma[2], ma[3], mb[2 * nt], mb[2 * nt + 1]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) m[nt][e] = m2[nt][e];
+                a_form(m, ma);
+                b_form(ma, mb);
+                // p <- p + p . m
+                a_form(pm, pa);
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) gc_mma(pm[nt], pa[0], pa[1], pa[2], pa[3], mb[2 * nt], mb[2 * nt + 1]);
             }
-#endif
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                *reinterpret_cast<uint32_t *>(&sm.Tb[gq][8 * nt + 2 * jq]) = gc_pack(pm[nt][0], pm[nt][1]);
+                *reinterpret_cast<uint32_t *>(&sm.Tb[gq + 8][8 * nt + 2 * jq]) = gc_pack(pm[nt][2], pm[nt][3]);
+            }
         } else {
             // rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of Qg
 #pragma unroll
@@ -344,6 +370,42 @@ gdn_chunk_kernel(const float *__restrict__ q, const float *__restrict__ k, const
 
 }  // namespace hs
 
+namespace hs {
+
+typedef CUresult (*GcEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static GcEncodeTiledFn gc_encode_fn() {
+    static GcEncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<GcEncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// [n_seqs, n_tokens, n_heads, 128] fp32 -> 4-D map (d, head, token, sequence), box 128 x 1 x 16 x 1, no swizzle
+static bool gc_make_map(CUtensorMap *map, const float *base, int n_seqs, int n_tokens, int n_heads) {
+    GcEncodeTiledFn fn = gc_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {kGcD, static_cast<cuuint64_t>(n_heads), static_cast<cuuint64_t>(n_tokens), static_cast<cuuint64_t>(n_seqs)};
+    const cuuint64_t strides[3] = {kGcD * 4ull, static_cast<cuuint64_t>(n_heads) * kGcD * 4ull,
+                                   static_cast<cuuint64_t>(n_tokens) * n_heads * kGcD * 4ull};
+    const cuuint32_t box[4] = {kGcD, 1, kGcC, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace hs
+
 using namespace hs;
 
 extern "C" {
@@ -363,16 +425,20 @@ int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, con
     if (n_seqs > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: more than 65535 sequences");
     int *err = device_error_word();
     if (!err) return fail(HS_ERR_DEVICE, "hs_gdn_chunk_prefill: device error word unavailable");
+    CUtensorMap mq, mk, mv;
+    if (!gc_make_map(&mq, q, n_seqs, n_tokens, n_k_heads) || !gc_make_map(&mk, k, n_seqs, n_tokens, n_k_heads) ||
+        !gc_make_map(&mv, v, n_seqs, n_tokens, n_v_heads))
+        return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: the driver refused the tensor maps (use hs_gdn_recurrent)");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(GcSmem)));
+        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(GcSmem) + 128));
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
         configured = true;
     }
     cudaStream_t s = as_stream(stream);
     dim3 grid(n_v_heads, n_seqs);
     prof_begin(s);
-    gdn_chunk_kernel<<<grid, kGcThreads, sizeof(GcSmem), s>>>(q, k, v, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
+    gdn_chunk_kernel<<<grid, kGcThreads, sizeof(GcSmem) + 128, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
     prof_end(s);
     return check_launch("hs_gdn_chunk_prefill");
 }
