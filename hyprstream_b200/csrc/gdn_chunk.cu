@@ -14,13 +14,14 @@
 // Layout: warp w of 8 owns value columns [16w, 16w+16) and keeps S^T[v][k] (16 x 128 fp32) in its mma accumulator
 // registers; every S-dependent product of the chunk is warp-local, with the state or U^T as the A operand straight from
 // those accumulators (fp32 -> bf16 pairs), mma.sync.m16n8k16 bf16 x bf16 -> fp32:
-//   [K S0 | Qg S0]^T = S^T . [K | Qg]^T   (32 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (2 MMAs)
-//   O^T = (Qg S0)^T + U^T . P^T           (2 MMAs)       S^T = Gamma_C S^T + U^T . Kd           (16 MMAs)
-// The per-chunk set-up that does not depend on S: the k.k and q.k products also run on the tensor cores (bf16 k, q); decay,
-// Qg = Gamma q and Kd = exp(G_C - G) k are elementwise; a ninth warp stages the next chunk's fp32 inputs (bulk async copies),
-// scans the decay and solves for T while the eight state warps already run the first product.  Only MMA operands are
-// rounded to bf16; the state and all accumulation stay fp32.
-// Bound: latency of the per-chunk dependency chain (4 block barriers); FLOPs are far below the tensor peak.
+//   [K S0 | Q S0]^T = S^T . [K | Q]^T     (32 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (2 MMAs)
+//   O^T = Gamma (Q S0)^T + U^T . P^T      (2 MMAs)       S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K   (16 MMAs)
+// The per-chunk set-up that does not depend on S belongs to three more warps: one scans the decay, forms k.k on the tensor
+// cores (bf16 k), applies the decay and computes T in its own fragments, one forms q.k and P, one stages the next chunk's
+// fp32 inputs (three TMA tensor copies), all while the eight state warps already run the first product.  Gamma and exp(G_C - G) are folded
+// into accumulator columns, so the only operand tiles in shared memory are k and q as bf16.  Only MMA operands are rounded
+// to bf16; the state and all accumulation stay fp32.
+// Bound: latency of the per-chunk dependency chain (3 block barriers); FLOPs are far below the tensor peak.
 //
 // Accuracy: bf16 operand rounding (2^-9 relative) enters every S-dependent product, so outputs agree with the fp32 rule
 // to ~1e-3, inside the path's stated tolerance (max-abs 2e-2, mean-abs 2e-3); hs_gdn_recurrent remains the fp32-exact form.
@@ -33,7 +34,7 @@ namespace hs {
 
 constexpr int kGcC = 16;          // tokens per chunk
 constexpr int kGcD = 128;         // head_k_dim = head_v_dim
-constexpr int kGcThreads = 288;   // warps 0-7: one 16-column slice of the state each; warp 8: staging, decay scan, solve
+constexpr int kGcThreads = 352;   // warps 0-7: one 16-column slice of the state each; 8: decay scan, k.k, T; 9: q.k, P; 10: staging
 constexpr int kGcRS = kGcD;       // fp32 row stride of the staged inputs (floats): dense, as the tensor copies write them
 constexpr int kGcBS = kGcD + 8;   // bf16 row stride of the [16][128] operand tiles
 constexpr int kGcPS = kGcC + 8;   // bf16 row stride of P, T and of Kd^T
@@ -42,11 +43,8 @@ struct GcSmem {
     __align__(128) float raw[2][3][kGcC][kGcRS];  // k, q, v of a chunk (fp32), double buffered
     float g[2][kGcC], b[2][kGcC];
     float G[kGcC], gam[kGcC], dec[kGcC];  // cumulative log-decay, exp(G), exp(G_C - G)
-    __align__(16) float A[kGcC][kGcC];  // A' (strictly lower, the rest zero)
     __nv_bfloat16 Tb[kGcC][kGcPS];      // (I + A')^-1 (lower)
     __nv_bfloat16 Kb[kGcC][kGcBS], Qb[kGcC][kGcBS];    // k, q
-    __nv_bfloat16 Qg[kGcC][kGcBS];      // Gamma q
-    __nv_bfloat16 KdT[kGcD][kGcPS];     // (exp(G_C - G) k)^T
     __nv_bfloat16 P[kGcC][kGcPS];       // (q.k) exp(G_t - G_s), s <= t
     __align__(8) uint64_t full[2];      // mbarriers: the bulk copies of a raw buffer have landed
 };
@@ -84,21 +82,6 @@ __device__ __forceinline__ void gc_mma(float (&d)[4], uint32_t a0, uint32_t a1, 
 }
 __device__ __forceinline__ uint32_t gc_ld32(const __nv_bfloat16 *p) { return *reinterpret_cast<const uint32_t *>(p); }
 
-#ifdef HS_GC_TIMING  // diagnostic build only: cycle stamps of CTA 0, warp 1, first chunks
-__device__ long long g_gc_stamps[64 * 8];
-__device__ long long g_gc_stamps2[64 * 8];
-#define HS_GC_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32 && c < 64) g_gc_stamps[c * 8 + (i)] = clock64(); } while (0)
-__device__ long long g_gc_stamps3[32 * 6 * 9];
-__device__ __forceinline__ long long gc_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
-#define HS_GC_WSTAMP(ph) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && c < 32) g_gc_stamps3[(c * 6 + (ph)) * 9 + warp] = gc_clock(); } while (0)
-#define HS_GC_STAMP8(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 256 && c < 64) g_gc_stamps[c * 8 + (i)] = clock64(); } while (0)
-#else
-#define HS_GC_STAMP(i) do {} while (0)
-__device__ long long g_gc_stamps3[32 * 6 * 9];
-__device__ __forceinline__ long long gc_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
-#define HS_GC_WSTAMP(ph) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && c < 32) g_gc_stamps3[(c * 6 + (ph)) * 9 + warp] = gc_clock(); } while (0)
-#define HS_GC_STAMP8(i) do {} while (0)
-#endif
 
 __global__ void __launch_bounds__(kGcThreads, 1)
 gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -124,7 +107,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     }
 
-    // Staging (warp 8): one lane issues three TMA tensor copies per chunk (the [16 tokens][128] boxes of k, q and v; rows
+    // Staging (warp 10): one lane issues three TMA tensor copies per chunk (the [16 tokens][128] boxes of k, q and v; rows
     // of a head are 512 bytes, strided by the number of heads); they complete on the buffer's mbarrier.  Tokens past the
     // end of the sequence arrive as zeros (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).
     // g and beta of a chunk are loaded one stage call ahead (registers gb_g, gb_b), so their global-memory latency is never
@@ -137,7 +120,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         gb_g = in ? g[tok * n_v_heads + h] : 0.0f;
         gb_b = in ? beta[tok * n_v_heads + h] : 0.0f;
     };
-    auto stage = [&](int c, int buf) {  // called by warp 8 only
+    auto stage = [&](int c, int buf) {  // called by warp 10 only
         const int t0 = c * kGcC;
         const uint32_t bar = gc_s32(&sm.full[buf]);
         if (lane == 0) {
@@ -160,7 +143,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (!chain_warp) {
+    if (warp == 10) {
         fetch_gates(0);
         stage(0, 0);
     }
@@ -171,10 +154,8 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // chunk c has landed (and its zero-fill / g / beta stores are visible); every warp is done with the previous chunk's
         // set-up buffers.  A wait that ran out ends the loop for the whole CTA.
         if (!__syncthreads_and(landed)) { failed = true; break; }
-        HS_GC_STAMP(0);
-        HS_GC_WSTAMP(0);
 
-        // ---- Pa: k, q -> bf16 (warps 0-7) | cumulative decay, then the next chunk's copies (warp 8) ----
+        // ---- Pa: k, q -> bf16 (warps 0-7) | cumulative decay (warp 8) ----
         if (chain_warp) {
             const int t = threadIdx.x >> 4, c8 = (threadIdx.x & 15) * 8;
 #pragma unroll
@@ -184,7 +165,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 *reinterpret_cast<uint4 *>(which ? &sm.Qb[t][c8] : &sm.Kb[t][c8]) =
                     make_uint4(gc_pack(x0.x, x0.y), gc_pack(x0.z, x0.w), gc_pack(x1.x, x1.y), gc_pack(x1.z, x1.w));
             }
-        } else {
+        } else if (warp == 8) {
             float x = lane < kGcC ? sm.g[buf][lane] : 0.0f;
 #pragma unroll
             for (int off = 1; off < kGcC; off <<= 1) {
@@ -194,51 +175,51 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float G_last = __shfl_sync(0xffffffffu, x, kGcC - 1);
             if (lane < kGcC) { sm.G[lane] = x; sm.gam[lane] = __expf(x); sm.dec[lane] = __expf(G_last - x); }
         }
-        HS_GC_WSTAMP(1);
         __syncthreads();
-        HS_GC_STAMP(1);
-        // ---- Pb: k.k and q.k on the tensor cores (warps 0-3) | Qg, Kd^T (warps 4-7) |
-        //          the next chunk's copies (warp 8) ----
-        if (warp < 4) {
-            const int mt = warp >> 1, nt = warp & 1;  // mt 0: rows k (-> A'), 1: rows q (-> P); nt: tokens s in [8nt, 8nt+8)
-            const __nv_bfloat16(*Am)[kGcBS] = mt ? sm.Qb : sm.Kb;
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two chains
+        // ---- C: k.k, decay, T = (I + A')^-1, all in its registers (warp 8) | q.k, decay, P (warp 9) | the next chunk's copies
+        //          (warp 10) | [K S0 | Q S0]^T and R^T (warps 0-7) ----
+        float X[4][4];
+        uint32_t r[4];
+        if (warp == 9) {
+            // P[t][s] = (q_t . k_s) exp(G_t - G_s), s <= t: tiles nt = columns s in [8nt, 8nt+8), two accumulators each
+            float acc[2][2][4];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i >> 3][(i >> 2) & 1][i & 3] = 0.0f;
 #pragma unroll
             for (int kk8 = 0; kk8 < 8; ++kk8) {
                 const int col = 16 * kk8 + 2 * jq;
-                gc_mma(kk8 & 1 ? acc2 : acc, gc_ld32(&Am[gq][col]), gc_ld32(&Am[gq + 8][col]), gc_ld32(&Am[gq][col + 8]), gc_ld32(&Am[gq + 8][col + 8]),
-                       gc_ld32(&sm.Kb[8 * nt + gq][col]), gc_ld32(&sm.Kb[8 * nt + gq][col + 8]));
+                const uint32_t k0 = gc_ld32(&sm.Kb[gq][col]), k1 = gc_ld32(&sm.Kb[gq + 8][col]), k2 = gc_ld32(&sm.Kb[gq][col + 8]), k3 = gc_ld32(&sm.Kb[gq + 8][col + 8]);
+                const uint32_t q0 = gc_ld32(&sm.Qb[gq][col]), q1 = gc_ld32(&sm.Qb[gq + 8][col]), q2 = gc_ld32(&sm.Qb[gq][col + 8]), q3 = gc_ld32(&sm.Qb[gq + 8][col + 8]);
+                gc_mma(acc[kk8 & 1][0], q0, q1, q2, q3, k0, k2);
+                gc_mma(acc[kk8 & 1][1], q0, q1, q2, q3, k1, k3);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[e] += acc2[e];
-            // acc[0], acc[1]: (t = gq, s = 8nt + 2jq, +1); acc[2], acc[3]: (t = gq + 8, same s)
+            for (int nt = 0; nt < 2; ++nt) {
+                float pv[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int t = gq + 8 * (e >> 1), s2 = 8 * nt + 2 * jq + (e & 1);
-                const float dg = s2 <= t ? __expf(sm.G[t] - sm.G[s2]) : 0.0f;
-                if (mt == 0) sm.A[t][s2] = s2 < t ? sm.b[buf][t] * acc[e] * dg : 0.0f;
-                else sm.P[t][s2] = __float2bfloat16_rn(acc[e] * dg);
+                for (int e = 0; e < 4; ++e) {
+                    const int row = gq + 8 * (e >> 1), col = 8 * nt + 2 * jq + (e & 1);
+                    pv[e] = col <= row ? (acc[0][nt][e] + acc[1][nt][e]) * __expf(sm.G[row] - sm.G[col]) : 0.0f;
+                }
+                *reinterpret_cast<uint32_t *>(&sm.P[gq][8 * nt + 2 * jq]) = gc_pack(pv[0], pv[1]);
+                *reinterpret_cast<uint32_t *>(&sm.P[gq + 8][8 * nt + 2 * jq]) = gc_pack(pv[2], pv[3]);
             }
-        } else if (chain_warp) {
-            const int d = threadIdx.x - 128;
+        } else if (warp == 10) {
+            if (c + 1 < n_chunks) stage(c + 1, buf ^ 1);
+        } else if (!chain_warp) {
+            // k_t . k_s: tiles nt = columns s in [8nt, 8nt+8); the A fragments of the k rows are the B fragments of the two tiles
+            float acc[2][2][4];
 #pragma unroll
-            for (int t = 0; t < kGcC; ++t) sm.Qg[t][d] = __float2bfloat16_rn(sm.gam[t] * sm.raw[buf][1][t][d]);
+            for (int i = 0; i < 16; ++i) acc[i >> 3][(i >> 2) & 1][i & 3] = 0.0f;
 #pragma unroll
-            for (int s2 = 0; s2 < kGcC; s2 += 2)
-                *reinterpret_cast<uint32_t *>(&sm.KdT[d][s2]) = gc_pack(sm.dec[s2] * sm.raw[buf][0][s2][d], sm.dec[s2 + 1] * sm.raw[buf][0][s2 + 1][d]);
-        } else if (c + 1 < n_chunks) {
-            stage(c + 1, buf ^ 1);
-        }
-        HS_GC_WSTAMP(2);
-        __syncthreads();
-        HS_GC_STAMP(2);
-
-        // ---- C: T = (I + A')^-1 (warp 8) | [K S0 | Qg S0]^T and R^T (warps 0-7) ----
-        float X[4][4];
-        uint32_t r[4];
-        if (!chain_warp) {
+            for (int kk8 = 0; kk8 < 8; ++kk8) {
+                const int col = 16 * kk8 + 2 * jq;
+                const uint32_t k0 = gc_ld32(&sm.Kb[gq][col]), k1 = gc_ld32(&sm.Kb[gq + 8][col]), k2 = gc_ld32(&sm.Kb[gq][col + 8]), k3 = gc_ld32(&sm.Kb[gq + 8][col + 8]);
+                gc_mma(acc[kk8 & 1][0], k0, k1, k2, k3, k0, k2);
+                gc_mma(acc[kk8 & 1][1], k0, k1, k2, k3, k1, k3);
+            }
             // (I + A')^-1 = (I + M)(I + M^2)(I + M^4)(I + M^8) with M = -A' (strictly lower 16 x 16, so M^16 = 0): three
-            // squarings and three products on the tensor cores, all in this warp's fragments.  m, p: accumulator layout,
+            // squarings and three products on the tensor cores, all in this warp's fragments.  m, pm: accumulator layout,
             // tile nt = columns [8nt, 8nt+8): {(row gq, cols 2jq, 2jq+1), (row gq+8, same cols)}.
             float m[2][4], pm[2][4];
 #pragma unroll
@@ -246,7 +227,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int row = gq + 8 * (e >> 1), col = 8 * nt + 2 * jq + (e & 1);
-                    m[nt][e] = -sm.A[row][col];
+                    m[nt][e] = col < row ? -sm.b[buf][row] * (acc[0][nt][e] + acc[1][nt][e]) * __expf(sm.G[row] - sm.G[col]) : 0.0f;  // -A'
                     pm[nt][e] = m[nt][e] + (row == col ? 1.0f : 0.0f);
                 }
             // A-form of a 16 x 16 matrix held in accumulator layout: its four 8 x 8 blocks as bf16 pairs; the B-form of the
@@ -263,7 +244,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             b_form(ma, mb);
 #pragma unroll
             for (int step = 0; step < 3; ++step) {
-                // m <- m . m : B operand of column tile nt = blocks (rows 0-7, nt) and (rows 8-15, nt) transposed = mb[2nt], mb[2nt+1]...
+                // m <- m . m: the B operand of column tile nt is the blocks (rows 0-7, nt), (rows 8-15, nt) transposed
                 float m2[2][4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
@@ -276,7 +257,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int e = 0; e < 4; ++e) m[nt][e] = m2[nt][e];
                 a_form(m, ma);
                 b_form(ma, mb);
-                // p <- p + p . m
+                // pm <- pm + pm . m
                 a_form(pm, pa);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) gc_mma(pm[nt], pa[0], pa[1], pa[2], pa[3], mb[2 * nt], mb[2 * nt + 1]);
@@ -287,7 +268,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 *reinterpret_cast<uint32_t *>(&sm.Tb[gq + 8][8 * nt + 2 * jq]) = gc_pack(pm[nt][2], pm[nt][3]);
             }
         } else {
-            // rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of Qg
+            // rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of q
 #pragma unroll
             for (int n = 0; n < 4; ++n) X[n][0] = X[n][1] = X[n][2] = X[n][3] = 0.0f;
 #pragma unroll
@@ -296,11 +277,12 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const uint32_t a2 = gc_pack(St[2 * kk8 + 1][0], St[2 * kk8 + 1][1]), a3 = gc_pack(St[2 * kk8 + 1][2], St[2 * kk8 + 1][3]);
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
-                    const __nv_bfloat16 *row = n < 2 ? &sm.Kb[8 * n + gq][0] : &sm.Qg[8 * (n - 2) + gq][0];
+                    const __nv_bfloat16 *row = n < 2 ? &sm.Kb[8 * n + gq][0] : &sm.Qb[8 * (n - 2) + gq][0];
                     gc_mma(X[n], a0, a1, a2, a3, gc_ld32(row + 16 * kk8 + 2 * jq), gc_ld32(row + 16 * kk8 + 2 * jq + 8));
                 }
             }
-            // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T
+            // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T;
+            // (Gamma Q S0)^T = (Q S0)^T scaled per token column
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int s0 = 8 * n + 2 * jq;
@@ -309,14 +291,12 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const float r10 = b0 * (sm.raw[buf][2][s0][v0 + gq + 8] - g0 * X[n][2]), r11 = b1 * (sm.raw[buf][2][s0 + 1][v0 + gq + 8] - g1 * X[n][3]);
                 r[2 * n] = gc_pack(r00, r01);
                 r[2 * n + 1] = gc_pack(r10, r11);
+                X[2 + n][0] *= g0; X[2 + n][1] *= g1; X[2 + n][2] *= g0; X[2 + n][3] *= g1;
             }
-            HS_GC_STAMP(4);
         }
-        HS_GC_WSTAMP(3);
-        __syncthreads();  // T is ready
-        HS_GC_STAMP(3);
+        __syncthreads();  // T and P are ready
         if (chain_warp) {
-            // ---- D: U^T = R^T . T^T; O^T = (Qg S0)^T + U^T . P^T; S^T = Gamma_C S^T + U^T . Kd ----
+            // ---- D: U^T = R^T . T^T; O^T = (Gamma Q S0)^T + U^T . P^T; S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K ----
             float U[2][4];
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
@@ -327,11 +307,22 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int n = 0; n < 2; ++n)
                 gc_mma(X[2 + n], u0, u1, u2, u3, gc_ld32(&sm.P[8 * n + gq][2 * jq]), gc_ld32(&sm.P[8 * n + gq][2 * jq + 8]));
+            // token columns of U scaled by exp(G_C - G_s); k itself is the B operand, its 8 x 8 blocks transposed on load
+            const float d00 = sm.dec[2 * jq], d01 = sm.dec[2 * jq + 1], d10 = sm.dec[8 + 2 * jq], d11 = sm.dec[8 + 2 * jq + 1];
+            const uint32_t w0 = gc_pack(U[0][0] * d00, U[0][1] * d01), w1 = gc_pack(U[0][2] * d00, U[0][3] * d01);
+            const uint32_t w2 = gc_pack(U[1][0] * d10, U[1][1] * d11), w3 = gc_pack(U[1][2] * d10, U[1][3] * d11);
             const float gC = sm.gam[kGcC - 1];
+            // lane -> row address of ldmatrix.x4.trans: matrix (lane >> 3): rows s = (lane & 7) + 8 (matrix & 1), column block + (matrix >> 1)
+            const uint32_t kb_lane = gc_s32(&sm.Kb[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 16; i += 2) {
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(kb_lane + 16u * i));
                 St[i][0] *= gC; St[i][1] *= gC; St[i][2] *= gC; St[i][3] *= gC;
-                gc_mma(St[i], u0, u1, u2, u3, gc_ld32(&sm.KdT[8 * i + gq][2 * jq]), gc_ld32(&sm.KdT[8 * i + gq][2 * jq + 8]));
+                gc_mma(St[i], w0, w1, w2, w3, b0, b1);
+                St[i + 1][0] *= gC; St[i + 1][1] *= gC; St[i + 1][2] *= gC; St[i + 1][3] *= gC;
+                gc_mma(St[i + 1], w0, w1, w2, w3, b2, b3);
             }
             // outputs: X[2 + n] = O^T rows v0+gq (+8), tokens 8n + 2jq (+1)
 #pragma unroll
@@ -339,19 +330,13 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int t = c * kGcC + 8 * n + 2 * jq + e;
-#ifdef HS_GC_NOSTORE  // diagnostic build only
-                    if (t < 0) {
-#else
                     if (t < n_tokens) {
-#endif
                         float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
                         op[0] = X[2 + n][e];
                         op[8] = X[2 + n][2 + e];
                     }
                 }
-            HS_GC_STAMP(5);
         }
-        HS_GC_WSTAMP(4);
     }
     if (failed) {
         if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
