@@ -44,6 +44,17 @@ def draw_lens(rank: int) -> list[int]:
     return [int(x) for x in rng.integers(512, 8193, size=BATCH)]
 
 
+def rank_lens(rank: int, world: int) -> list[int]:
+    """Context lengths of this rank's 32 sequences: the world's 32 * N sequences (the N = 1 draw first) are dealt
+    length-balanced, 32 per GPU; at N = 1 this is the plain draw."""
+    if world == 1:
+        return draw_lens(0)
+    from hyprstream_b200.sharded import balance_sequences
+
+    pool = [l for r in range(world) for l in draw_lens(r)]
+    return [pool[i] for i in balance_sequences(pool, world)[rank]]
+
+
 def token_bytes(block: int, scale_f16: int) -> int:
     """Algorithmic bytes of one cached token, K + V: codes plus one scale per block."""
     return 2 * HKV * (D + (D // block) * (2 if scale_f16 else 4))
@@ -168,7 +179,7 @@ def workload_config(layout: str, lens: list[int]) -> dict:
     return {"workload": "configs[1]: batched ragged decode attention over an int8 KV cache with quantise-on-write",
             "batch_per_gpu": BATCH, "q_heads": HQ, "kv_heads": HKV, "head_dim": D, "context_lens": "U{512..8192}",
             "sum_context": sum(lens), "kv_layout": f"{layout}: block {block}, {'f16' if sf16 else 'f32'} absmax",
-            "partition": "sequences across GPUs, no collective",
+            "partition": "sequences across GPUs (32 per GPU, dealt longest-first so the cached-token sums match), no collective",
             "l2": "inputs larger than L2 (KV bytes per GPU exceed 126 MB); no flush"}
 
 
@@ -202,7 +213,7 @@ def main():
     from hyprstream_b200 import ffi, kv_cache as kc, ops
 
     block, sf16 = LAYOUTS[args.layout]
-    lens = draw_lens(rank)
+    lens = rank_lens(rank, world)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     caches = []
     for l in lens:

@@ -35,6 +35,26 @@ def shard_bounds(length: int, n_shards: int, page: int = PAGE_TOKENS) -> List[Tu
     return out
 
 
+def balance_sequences(lengths: Sequence[int], n_ranks: int) -> List[List[int]]:
+    """Deal sequences (by index) to `n_ranks` GPUs for batched decode: the same number of sequences per rank (the batch
+    per GPU is fixed) and cached-token sums as equal as a longest-first greedy makes them, since a decode step costs its
+    rank the sum of its context lengths.  Deterministic; returns the index lists, rank by rank.
+
+    Sequences are independent on this path (each has its own cache, architectures/llama.rs:776-781), so the
+    assignment is free and needs no collective."""
+    n = len(lengths)
+    if n_ranks <= 0 or n % n_ranks != 0:
+        raise ValueError("balance_sequences: the number of sequences must be a positive multiple of n_ranks")
+    per_rank = n // n_ranks
+    order = sorted(range(n), key=lambda i: (-lengths[i], i))
+    sums, out = [0] * n_ranks, [[] for _ in range(n_ranks)]
+    for i in order:
+        r = min((r for r in range(n_ranks) if len(out[r]) < per_rank), key=lambda r: (sums[r], r))
+        out[r].append(i)
+        sums[r] += lengths[i]
+    return [sorted(ix) for ix in out]
+
+
 def pack_partial(o: torch.Tensor, lse: torch.Tensor) -> torch.Tensor:
     """(o [B,Hq,D], lse [B,Hq]) -> one [B,Hq,D+1] fp32 message, so a step is a single all-gather."""
     return torch.cat([o, lse.unsqueeze(-1)], dim=-1).contiguous()

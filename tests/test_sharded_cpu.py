@@ -79,3 +79,24 @@ def test_two_rank_gloo_sharded_decode_equals_unsharded(length):
     full, _ = _partial(q, k, v)
     assert torch.allclose(ret[0], full, rtol=1e-5, atol=1e-5)
     assert torch.equal(ret[0], ret[1])  # every rank ends with the same result
+
+
+def test_balance_sequences_equalises_token_sums():
+    """The batched-decode partition: equal counts per rank, near-equal cached-token sums, deterministic, a permutation."""
+    import numpy as np
+
+    from hyprstream_b200.sharded import balance_sequences
+
+    rng = np.random.default_rng(7)
+    for n_ranks in (1, 2, 4, 8):
+        lens = [int(x) for x in rng.integers(512, 8193, size=32 * n_ranks)]
+        parts = balance_sequences(lens, n_ranks)
+        assert parts == balance_sequences(lens, n_ranks)
+        assert sorted(i for p in parts for i in p) == list(range(len(lens)))
+        assert all(len(p) == 32 for p in parts)
+        sums = [sum(lens[i] for i in p) for p in parts]
+        assert max(sums) - min(sums) <= 0.01 * max(sums)
+    import pytest
+
+    with pytest.raises(ValueError):
+        balance_sequences([1, 2, 3], 2)
