@@ -157,7 +157,10 @@ struct hs_cache {
             return HS_OK;
         }
         if (end_pos <= capacity) return HS_OK;
-        const int new_cap = std::min(max_seq_len, (end_pos + kDefaultChunk - 1) / kDefaultChunk * kDefaultChunk);
+        // whole growth chunks, capped at max_seq_len rounded up to 32 tokens: the storage may hold a few tokens more than
+        // the cache may use (update() still refuses positions past max_seq_len), so that every view cuts into pages of a
+        // multiple of 32 tokens, which the tensor-core decode kernel's tiles need
+        const int new_cap = std::min((max_seq_len + 31) / 32 * 32, (end_pos + kDefaultChunk - 1) / kDefaultChunk * kDefaultChunk);
         Slab grown;
         if (int32_t st = grown.allocate(geo, new_cap)) return st;
         for (int i = 0; i < 4; ++i) {

@@ -97,12 +97,13 @@ def main():
     # ------------------------------------------------------------------ decode
     b, L = a.decode_batch, a.context
     caches = []
+    cap = (L + a.decode_steps + 8 + 1023) // 1024 * 1024  # whole 1024-token growth chunks (kv_cache.rs:700)
     for s in range(b):
-        c = kc.LayerKVCache(L + a.decode_steps + 8, kc.KVQuantType.INT8, HKV, D, dev, block=128, scale_dtype=ffi.SCALE_F16)
+        c = kc.LayerKVCache(cap, kc.KVQuantType.INT8, HKV, D, dev, block=128, scale_dtype=ffi.SCALE_F16)
         for t0 in range(0, L, 8192):
             n = min(8192, L - t0)
             c.update(rnd(1, n, HKV, D).bfloat16(), rnd(1, n, HKV, D).bfloat16(), t0)
-        c._ensure_capacity(L + a.decode_steps + 8)
+        c._ensure_capacity(cap)
         caches.append(c)
     view, keep = kc.make_view(caches)
     x = rnd(b, 1, CONV_DIM).bfloat16()
