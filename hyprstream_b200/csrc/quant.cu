@@ -17,20 +17,22 @@
 namespace hs {
 
 constexpr int kQThreads = 256;
+constexpr int kWriteUnroll = 8;  // 8-element chunks per thread of the quantise-on-write kernel
 
 __device__ __forceinline__ float code8(int i) { return __fdiv_rn(static_cast<float>(i) - 127.0f, 127.0f); }
 __device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(code8(j), code8(j + 1))); }
 
 // Index of y in the 8-bit linear codebook.  The candidate round(y*127)+127 is exact unless y*127 sits
-// within 1e-3 of a half-integer; only then are the true f32 midpoints consulted.
-__device__ __forceinline__ int index_int8(float y) {
+// within 1e-3 of a half-integer; only then are the true f32 midpoints consulted (smid: the 255 midpoints in shared
+// memory, so the rare path costs two loads and not four divisions for every lane of the warp).
+__device__ __forceinline__ int index_int8(float y, const float *smid) {
     float t = __fmul_rn(y, 127.0f);
     int c = __float2int_rn(t) + 127;
     c = max(0, min(255, c));
     float fr = t - floorf(t);
     if (fabsf(fr - 0.5f) < 1e-3f) {
-        if (c > 0 && !(y > mid8(c - 1))) c--;
-        else if (c < 255 && y > mid8(c)) c++;
+        if (c > 0 && !(y > smid[c - 1])) c--;
+        else if (c < 255 && y > smid[c]) c++;
     }
     return c;
 }
@@ -43,8 +45,11 @@ __device__ __forceinline__ int index_4bit(float y, const float *smid) {
     return c;
 }
 
+// smid: 256 floats; the block has at least 255 threads
 __device__ __forceinline__ void fill_midpoints(int kind, float *smid) {
-    if (kind != HS_KV_INT8 && threadIdx.x < 15) {
+    if (kind == HS_KV_INT8) {
+        if (threadIdx.x < 255) smid[threadIdx.x] = mid8(threadIdx.x);
+    } else if (threadIdx.x < 15) {
         const float *t = kind == HS_KV_NF4 ? c_nf4 : c_fp4;
         smid[threadIdx.x] = __fmul_rn(0.5f, __fadd_rn(t[threadIdx.x], t[threadIdx.x + 1]));
     }
@@ -75,7 +80,7 @@ __device__ __forceinline__ float quantize8(const float (&x)[8], int tpb, int sca
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         float y = __fmul_rn(x[i], inv);
-        codes[i] = KIND == HS_KV_INT8 ? index_int8(y) : index_4bit(y, smid);
+        codes[i] = KIND == HS_KV_INT8 ? index_int8(y, smid) : index_4bit(y, smid);
     }
     return a;
 }
@@ -126,7 +131,7 @@ template <int KIND>
 __global__ void __launch_bounds__(kQThreads) quantize_flat_kernel(const void *__restrict__ src, int dtype, int64_t n,
                                                                   int block, int scale_dtype, uint8_t *__restrict__ codes,
                                                                   void *__restrict__ absmax, int vec_ok) {
-    __shared__ float smid[16];
+    __shared__ float smid[256];
     fill_midpoints(KIND, smid);
     __syncthreads();
     const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
@@ -228,52 +233,63 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
                                                              const int32_t *__restrict__ dst_pos,
                                                              const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
                                                              int rotary_dim, int n_positions, int *__restrict__ err) {
-    __shared__ float smid[16];
+    __shared__ float smid[256];
     fill_midpoints(KIND, smid);
     __syncthreads();
-    const bool is_v = blockIdx.y == 1;
+    // grid: x = groups of kWriteUnroll * 256 8-element chunks of one sequence's new rows, y = 2 * sequence + (0: K, 1: V).
+    // The sequence and K/V come from the block index and the chunk index inside a sequence fits 32 bits, so the (token,
+    // head, chunk) split costs four 32-bit divisions per chunk; a thread handles kWriteUnroll chunks, which spreads the
+    // block's fixed costs (launch, midpoint table, barrier).
+    const bool is_v = (blockIdx.y & 1) != 0;
+    const int s = static_cast<int>(blockIdx.y >> 1);
     const int D = view.head_dim, H = view.n_kv_heads;
-    const int cpr = D / 8;
-    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kQThreads + threadIdx.x;
-    const int64_t total = static_cast<int64_t>(n_seqs) * n_tokens * H * cpr;
-    const bool live = chunk < total;
-    const int64_t cc = live ? chunk : 0;  // dead lanes still take part in the shuffles
-    const int d0 = static_cast<int>(cc % cpr) * 8;
-    const int64_t row = cc / cpr;  // (seq, token, head)
-    const int h = static_cast<int>(row % H);
-    const int64_t st = row / H;
-    const int t = static_cast<int>(st % n_tokens);
-    const int s = static_cast<int>(st / n_tokens);
-    const int pos = dst_pos ? dst_pos[s] + t : t;
-    const int page = pos / view.page_tokens;
-    bool ok = live && pos >= 0 && page < view.pages_per_seq;
-    if (!is_v && sin != nullptr && (pos < 0 || pos >= n_positions)) ok = false;
-    if (live && !ok) atomicExch(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
-    const uint16_t *src = (is_v ? v_new : k_new) + row * D;
-    float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (ok) load_row8_rope(src, d0, is_v ? nullptr : sin, cos, pos, rotary_dim, x);
-    const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + h;  // (token, head) row inside the page
-    const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
-    if (KIND == HS_KV_BF16) {
-        if (ok) {
-            uint16_t *dst = reinterpret_cast<uint16_t *>((is_v ? view.v_pages : view.k_pages)[pidx]) + in_page * D + d0;
-            uint4 w;
-            w.x = pack_bf16(x[0], x[1]); w.y = pack_bf16(x[2], x[3]); w.z = pack_bf16(x[4], x[5]); w.w = pack_bf16(x[6], x[7]);
-            *reinterpret_cast<uint4 *>(dst) = w;
-        }
-        return;
-    }
-    constexpr int QK = KIND == HS_KV_BF16 ? HS_KV_INT8 : KIND;
-    int c[8];
+    const uint32_t cpr = static_cast<uint32_t>(D) / 8u;
+    const uint32_t total = static_cast<uint32_t>(n_tokens) * static_cast<uint32_t>(H) * cpr;
+    const int base_pos = dst_pos ? dst_pos[s] : 0;
+    void *const *data_pages = is_v ? view.v_pages : view.k_pages;
+    void *const *scale_pages = is_v ? view.v_scale_pages : view.k_scale_pages;
     const int tpb = view.block / 8;
-    float a = quantize8<QK>(x, tpb, view.scale_dtype, smid, c);
-    if (!ok) return;
-    uint8_t *codes = reinterpret_cast<uint8_t *>((is_v ? view.v_pages : view.k_pages)[pidx]);
-    void *scales = (is_v ? view.v_scale_pages : view.k_scale_pages)[pidx];
     const int bpr = D / view.block;  // blocks per (token, head) row
-    if ((d0 % view.block) == 0) store_scale(scales, in_page * bpr + d0 / view.block, view.scale_dtype, a);
-    const int64_t e0 = in_page * D + d0;
-    store_codes8<QK>(codes, e0, e0 + 8, c, true);
+#pragma unroll 2
+    for (int u = 0; u < kWriteUnroll; ++u) {
+        const uint32_t chunk = (blockIdx.x * static_cast<uint32_t>(kWriteUnroll) + u) * static_cast<uint32_t>(kQThreads) + threadIdx.x;
+        if (chunk - threadIdx.x >= total) break;  // (uniform over the block)
+        const bool live = chunk < total;
+        const uint32_t cc = live ? chunk : 0u;  // dead lanes still take part in the shuffles
+        const uint32_t row_in_seq = cc / cpr;   // (token, head)
+        const int d0 = static_cast<int>(cc - row_in_seq * cpr) * 8;
+        const int t = static_cast<int>(row_in_seq / static_cast<uint32_t>(H));
+        const int h = static_cast<int>(row_in_seq - static_cast<uint32_t>(t) * static_cast<uint32_t>(H));
+        const int64_t row = static_cast<int64_t>(s) * n_tokens * H + row_in_seq;  // (seq, token, head)
+        const int pos = base_pos + t;
+        const int page = pos / view.page_tokens;
+        bool ok = live && pos >= 0 && page < view.pages_per_seq;
+        if (!is_v && sin != nullptr && (pos < 0 || pos >= n_positions)) ok = false;
+        if (live && !ok) atomicExch(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
+        const uint16_t *src = (is_v ? v_new : k_new) + row * D;
+        float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (ok) load_row8_rope(src, d0, is_v ? nullptr : sin, cos, pos, rotary_dim, x);
+        const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + h;  // (token, head) row inside the page
+        const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
+        if (KIND == HS_KV_BF16) {
+            if (ok) {
+                uint16_t *dst = reinterpret_cast<uint16_t *>(data_pages[pidx]) + in_page * D + d0;
+                uint4 w;
+                w.x = pack_bf16(x[0], x[1]); w.y = pack_bf16(x[2], x[3]); w.z = pack_bf16(x[4], x[5]); w.w = pack_bf16(x[6], x[7]);
+                *reinterpret_cast<uint4 *>(dst) = w;
+            }
+            continue;
+        }
+        constexpr int QK = KIND == HS_KV_BF16 ? HS_KV_INT8 : KIND;
+        int c[8];
+        float a = quantize8<QK>(x, tpb, view.scale_dtype, smid, c);
+        if (!ok) continue;
+        uint8_t *codes = reinterpret_cast<uint8_t *>(data_pages[pidx]);
+        void *scales = scale_pages[pidx];
+        if ((d0 % view.block) == 0) store_scale(scales, in_page * bpr + d0 / view.block, view.scale_dtype, a);
+        const int64_t e0 = in_page * D + d0;
+        store_codes8<QK>(codes, e0, e0 + 8, c, true);
+    }
 }
 
 // ---- gather-dequantise (LayerKVCache::get compatibility read) ------------------------------------------------
@@ -412,8 +428,9 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
             return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: rotary_dim must be a positive multiple of 16 <= head_dim");
     }
     ViewDev d = to_dev(view);
-    const int64_t chunks = static_cast<int64_t>(n_seqs) * n_tokens * d.n_kv_heads * (d.head_dim / 8);
-    dim3 grid(static_cast<unsigned>((chunks + kQThreads - 1) / kQThreads), 2);
+    const int64_t chunks = static_cast<int64_t>(n_tokens) * d.n_kv_heads * (d.head_dim / 8);  // per sequence and per K / V
+    if (chunks > 0x7fffffffLL || n_seqs > 32767) return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: more than 2^31 chunks per sequence or 32767 sequences in one call");
+    dim3 grid(static_cast<unsigned>((chunks + kQThreads * kWriteUnroll - 1) / (kQThreads * kWriteUnroll)), 2u * static_cast<unsigned>(n_seqs));
     cudaStream_t s = as_stream(stream);
     int *err = device_error_word();
     if (!err) return fail(HS_ERR_DEVICE, "hs_kv_quantize_write: device error word unavailable");

@@ -50,10 +50,19 @@ def main():
     ops.prefill_attention(q, k, v)
     kms = ffi.last_kernel_ms()
     ffi.set_profiling(False)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.iters):
+        ops.kv_quantize_write(view, k, v, zeros)
+    e1.record()
+    torch.cuda.synchronize()
+    wms = e0.elapsed_time(e1) / a.iters
+    wbytes = 2 * a.batch * a.tokens * hkv * (d * 2 + d + (d // 128) * 2)  # bf16 in, int8 codes + f16 scale per 128 out, K and V
     flops = 4.0 * a.batch * hq * d * a.tokens * (a.tokens + 1) / 2
     print(json.dumps({"workload": "configs[3] causal prefill + int8 quantise-on-write", "batch": a.batch, "tokens": a.tokens,
                       "ms_per_step": ms, "attn_kernel_ms": kms, "useful_tflops_step": flops / ms / 1e9,
-                      "useful_tflops_kernel": flops / kms / 1e9, "device_error_flags": ffi.take_device_error()}))
+                      "useful_tflops_kernel": flops / kms / 1e9,
+                      "kv_write_ms": wms, "kv_write_gbps": wbytes / wms / 1e6, "device_error_flags": ffi.take_device_error()}))
 
 
 if __name__ == "__main__":
