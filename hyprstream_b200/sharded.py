@@ -1,6 +1,6 @@
 """KV-length sharding of one long context across the GPUs of a node (BASELINE.json configs[2]).
 
-The reference has no collectives (its multi-GPU story is replicas and a layer split, SURVEY 2.4); this is
+The reference has no collectives (its multi-GPU story is replicas and a layer split); this is
 new design.  Each rank owns a contiguous, page-aligned slice of every sequence's KV cache, runs the
 ordinary decode kernel over its slice with the shard outputs (normalised fp32 o and natural-log lse per
 (sequence, head)), all-gathers the 66 KB pair over NCCL, and merges with the log-sum-exp kernel:
