@@ -436,12 +436,17 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 //   TMEM columns: four score/probability buffers of 64 columns ([0,256): tile j uses buffer j & 3, so q.k^T runs up to
 //   three key tiles ahead of the softmax), the output accumulator 128 x 256 fp32 in [256,512).
 //   Shared memory: Q 64 KB (four 64-column boxes of 128 rows), K ring 3 x 32 KB, V ring 2 x 32 KB (boxes of 64 rows).
-//   Warps 0-3: softmax (thread = query row), warp 4: loader, warp 5: MMA issuer.
+//   Warps 0-3 and 4-7: softmax of the even and of the odd key tiles (thread = query row in both groups; the special-
+//   function unit's 16 exp2 per clock bound a tile at 512 cycles, the same as its MMAs, so two groups alternate and one
+//   group's loads, maximum and stores run under the other's exponentials); warp 8: loader, warp 9: MMA issuer.
+//   The two groups share a row's reference maximum through shared memory: a group publishes it (and rescales O if it
+//   grew by more than 2^8) right after its maximum pass, the other group's next tile starts from there; each group keeps
+//   its own partial row sum with the reference it was last brought to, and the two are combined at the end.
 //   Per key tile: S = Q.K^T is 16 MMAs 128x64x16 (operands in shared memory), O += P.V is 4 MMAs 128x256x16 (P from TMEM,
 //   V MN-major: its four 64-column boxes are 8 KB apart).
 constexpr int kW5D = 256, kW5M = 128, kW5N = 64;
 constexpr int kW5KStages = 3, kW5VStages = 2, kW5SBufs = 4;
-constexpr int kW5Threads = 192;
+constexpr int kW5Threads = 320;  // warps 0-3 / 4-7: softmax of even / odd key tiles, warp 8: loader, warp 9: MMA issuer
 constexpr int kW5QBytes = kW5M * kW5D * 2;    // 64 KB
 constexpr int kW5QBox = kW5M * 128;           // one 64-column box of Q
 constexpr int kW5KVBytes = kW5N * kW5D * 2;   // 32 KB
@@ -450,7 +455,7 @@ constexpr int kW5SmemBytes = kW5QBytes + (kW5KStages + kW5VStages) * kW5KVBytes 
 
 struct W5Bars {
     uint64_t q, kfull[kW5KStages], kempty[kW5KStages], vfull[kW5VStages], vempty[kW5VStages], sfull[kW5SBufs], pready[kW5SBufs],
-        pvdone[kW5SBufs], odone;
+        pvdone[kW5SBufs];
 };
 
 __global__ void __launch_bounds__(kW5Threads, 1)
@@ -461,8 +466,17 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __shared__ __align__(8) W5Bars bars;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
+    __shared__ float s_mpub[kW5M];
+    __shared__ int s_seq[kW5M];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const uint32_t sQ = t5_s32(smem), sK = sQ + kW5QBytes, sV = sK + kW5KStages * kW5KVBytes;
+    // the two softmax groups exchange their partial sums through the first K stage once every q.k^T has completed
+    float(*s_lpart)[kW5M] = reinterpret_cast<float(*)[kW5M]>(smem + kW5QBytes);
+    float(*s_mpart)[kW5M] = reinterpret_cast<float(*)[kW5M]>(smem + kW5QBytes + 2 * kW5M * sizeof(float));
+    if (threadIdx.x < kW5M) {
+        s_seq[threadIdx.x] = 0;
+        s_mpub[threadIdx.x] = -INFINITY;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mb = gridDim.x - 1 - blockIdx.x;  // latest (heaviest) query blocks first
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (n_q_heads / n_kv_heads);
@@ -473,7 +487,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (threadIdx.x == 0) {
         auto init = [](uint64_t *bar, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(t5_s32(bar)), "r"(count)); };
         init(&bars.q, 1);
-        init(&bars.odone, 1);
         for (int s = 0; s < kW5KStages; ++s) { init(&bars.kfull[s], 1); init(&bars.kempty[s], 1); }
         for (int s = 0; s < kW5VStages; ++s) { init(&bars.vfull[s], 1); init(&bars.vempty[s], 1); }
         for (int i = 0; i < kW5SBufs; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kW5M); init(&bars.pvdone[i], 1); }
@@ -490,7 +503,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t tm = s_tmem;
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================================ loader ================================
         if (lane == 0) {
             t5_expect_tx(t5_s32(&bars.q), kW5QBytes);
@@ -520,7 +533,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================================ MMA issuer ================================
         // S_j needs K_j and a free score buffer (P.V of tile j - 4 complete); P.V_j needs P_j and V_j.  Whichever is ready is
         // issued; q.k^T runs ahead so that the tensor pipe works under the softmax.
@@ -540,7 +553,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                     for (int ks = 0; ks < kW5N / 16; ++ks)
                         t5_mma_ts(tm + 256, tm + (j & 3) * kW5N + ks * 8, t5_desc(sVj + ks * 2048, kW5KVBox, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    t5_commit(t5_s32(&bars.odone));
                     t5_commit(t5_s32(&bars.pvdone[j & 3]));
                     t5_commit(t5_s32(&bars.vempty[j % kW5VStages]));
                     next_pv = j + 1;
@@ -571,12 +583,15 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
         }
     } else {
-        // ================================ softmax: thread = query row ================================
-        const int row = m0 + threadIdx.x;
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        // ================================ softmax: thread = query row, group = parity of the key tile ================================
+        const int grp = warp >> 2, r_local = threadIdx.x & 127;
+        const int row = m0 + r_local;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tO = tm + lane_base + 256;
-        float m_used = -INFINITY, l = 0.0f;
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        volatile float *m_pub = s_mpub + r_local;   // the row's reference maximum after the latest published tile
+        volatile int *seq = s_seq + r_local;        // number of tiles whose reference has been published
+        float l = 0.0f, m_ref = -INFINITY;          // this group's partial row sum, relative to m_ref
+        for (int j = grp; j < n_tiles && ok; j += 2) {
             const uint32_t tS = tm + lane_base + (j & 3) * kW5N;
             ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 3]), (j >> 2) & 1, abort_flag));
             if (!ok) break;
@@ -609,13 +624,31 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         mx0 = t5_max3(mx0, a0, a1);
                     }
             }
-            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
+            const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+            // the reference the previous tile (other group) left behind
+            float m_used = -INFINITY;
+            if (j > 0) {
+                bool seen = *seq >= j;
+                if (!seen) {
+                    const long long t0w = clock64();
+                    while (!(seen = *seq >= j)) {
+                        if (*abort_flag) break;
+                        if (clock64() - t0w > kT5WaitCycles) { *abort_flag = 1; break; }
+                    }
+                }
+                ok = __all_sync(0xffffffffu, seen);
+                if (!ok) break;
+                m_used = *m_pub;
+            }
+            const float m_new = fmaxf(m_used, tile_max);
             if (j == 0) {
                 m_used = m_new;
             } else {
                 const bool need = m_new - m_used > kT5RescaleThreshold;  // false while both are -inf (NaN compares false)
                 if (__any_sync(0xffffffffu, need)) {
-                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (j - 1) & 1, abort_flag));
+                    // O holds P.V of tiles 0 .. j-1: wait for tile j-1's on its score buffer's barrier (one phase per four
+                    // tiles there, so the parity cannot be mistaken for an older phase; MMAs complete in order)
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pvdone[(j - 1) & 3]), ((j - 1) >> 2) & 1, abort_flag));
                     if (!ok) break;
                     t5_fence_after();
                     const float f = need ? exp2f(m_used - m_new) : 1.0f;
@@ -629,10 +662,19 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         t5_st32(tO + c0, o);
                     }
                     t5_wait_st();
-                    l *= f;
                     if (need) m_used = m_new;
                 }
                 if (m_used == -INFINITY) m_used = m_new;
+            }
+            // publish: the other group's next tile may start its exponentials (and a rescale of O it needs is ordered after
+            // this one by the same chain)
+            *m_pub = m_used;
+            __threadfence_block();
+            *seq = j + 1;
+            // bring this group's partial sum to the new reference
+            if (m_ref != m_used) {
+                l = m_ref == -INFINITY ? 0.0f : l * exp2f(m_ref - m_used);
+                m_ref = m_used;
             }
             const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
             float ps0 = 0.0f, ps1 = 0.0f;
@@ -674,14 +716,29 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             t5_fence_before();
             t5_arrive(t5_s32(&bars.pready[j & 3]));
         }
-        // ---- epilogue ----
-        if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.odone), (n_tiles - 1) & 1, abort_flag));
-        if (ok && n_tiles > 0) {
+        // ---- every MMA has completed (the last P.V, hence all before it): the K ring is idle and carries the two groups'
+        //      partial sums; every softmax warp reaches the barrier below, also after a timed-out wait ----
+        if (ok && n_tiles > 0)
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pvdone[(n_tiles - 1) & 3]), ((n_tiles - 1) >> 2) & 1, abort_flag));
+        if (ok) {
             t5_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            s_lpart[grp][r_local] = l;
+            s_mpart[grp][r_local] = m_ref;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        // ---- epilogue: group 0 writes output columns [0, 128), group 1 [128, 256) ----
+        if (ok && n_tiles > 0 && !*abort_flag) {
+            const float m_fin = *m_pub;  // the reference O is relative to
+            float lsum = 0.0f;
+#pragma unroll
+            for (int gi = 0; gi < 2; ++gi) {
+                const float lg = s_lpart[gi][r_local], mg = s_mpart[gi][r_local];
+                if (mg != -INFINITY) lsum += lg * exp2f(mg - m_fin);
+            }
+            const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
             const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kW5D;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kW5D; c0 += 32) {
+            for (int c0 = grp * (kW5D / 2); c0 < (grp + 1) * (kW5D / 2); c0 += 32) {
                 uint32_t o[32];
                 t5_ld32(tO + c0, o);
                 t5_wait_ld();
