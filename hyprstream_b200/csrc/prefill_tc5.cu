@@ -54,6 +54,12 @@ __device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile 
         if (clock64() - t0 > kT5WaitCycles) { *abort_flag = 1; return false; }
     }
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool t5_elect() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred)::"memory");
+    return pred != 0;
+}
 __device__ __forceinline__ void t5_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 __device__ __forceinline__ void t5_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -516,6 +522,9 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     const int s = jk % kW5KStages;
                     if (jk >= kW5KStages) ok = t5_wait(t5_s32(&bars.kempty[s]), (jk / kW5KStages - 1) & 1, abort_flag);
                     if (!ok) break;
+#ifdef HS_W5_NOLOAD
+                    if (jk >= kW5KStages) { t5_arrive(t5_s32(&bars.kfull[s])); ++jk; continue; }
+#endif
                     t5_expect_tx(t5_s32(&bars.kfull[s]), kW5KVBytes);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -525,6 +534,9 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     const int s = jv % kW5VStages;
                     if (jv >= kW5VStages) ok = t5_wait(t5_s32(&bars.vempty[s]), (jv / kW5VStages - 1) & 1, abort_flag);
                     if (!ok) break;
+#ifdef HS_W5_NOLOAD
+                    if (jv >= kW5VStages) { t5_arrive(t5_s32(&bars.vfull[s])); ++jv; continue; }
+#endif
                     t5_expect_tx(t5_s32(&bars.vfull[s]), kW5KVBytes);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -535,50 +547,73 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ================================
-        // S_j needs K_j and a free score buffer (P.V of tile j - 4 complete); P.V_j needs P_j and V_j.  Whichever is ready is
-        // issued; q.k^T runs ahead so that the tensor pipe works under the softmax.
-        if (lane == 0) {
-            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kW5N >> 3) << 17) | ((kW5M >> 4) << 24);
-            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kW5D >> 3) << 17) | ((kW5M >> 4) << 24);
-            int next_s = 0, next_pv = 0;
-            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag);
-            long long t_idle = clock64();
-            while (ok && next_pv < n_tiles) {
-                bool progress = false;
-                int j = next_pv;
-                if (j < next_s && t5_test_wait(t5_s32(&bars.pready[j & 3]), (j >> 2) & 1) &&
-                    t5_test_wait(t5_s32(&bars.vfull[j % kW5VStages]), (j / kW5VStages) & 1)) {
-                    t5_fence_after();
-                    const uint32_t sVj = sV + (j % kW5VStages) * kW5KVBytes;
+        // The whole warp walks a fixed schedule -- S_0 S_1 S_2, then per key tile j: P.V_j, S_{j+3} -- with blocking waits, and one
+        // elected lane issues.  Stage and buffer indices advance unconditionally, so every descriptor is a per-tile base plus a
+        // compile-time offset.  S_{j+3} overwrites the score buffer of tile j-1, whose P.V was issued one tile earlier: waiting
+        // for its completion still leaves S_{j+2} and P.V_j queued in the tensor pipe.
+        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kW5N >> 3) << 17) | ((kW5M >> 4) << 24);
+        const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kW5D >> 3) << 17) | ((kW5M >> 4) << 24);
+        const uint64_t dq = t5_desc(sQ, 16, 1024);
+        int kst = 0, kph = 0, vst = 0, vph = 0;  // ring stage and phase of the next K / V tile to consume
+        ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.q), 0, abort_flag));
+        auto issue_s = [&](int buf) {  // S(buf) = Q K^T with the K tile in stage kst
+            const uint64_t dk = t5_desc(sK + kst * kW5KVBytes, 16, 1024);
+            if (t5_elect()) {
+#ifdef HS_W5_NOQK
+                for (int ks = 0; ks < 1; ++ks)
+#else
 #pragma unroll
-                    for (int ks = 0; ks < kW5N / 16; ++ks)
-                        t5_mma_ts(tm + 256, tm + (j & 3) * kW5N + ks * 8, t5_desc(sVj + ks * 2048, kW5KVBox, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    t5_commit(t5_s32(&bars.pvdone[j & 3]));
-                    t5_commit(t5_s32(&bars.vempty[j % kW5VStages]));
-                    next_pv = j + 1;
-                    progress = true;
-                }
-                j = next_s;
-                if (j < n_tiles && j < next_pv + kW5SBufs && t5_test_wait(t5_s32(&bars.kfull[j % kW5KStages]), (j / kW5KStages) & 1) &&
-                    (j < kW5SBufs || t5_test_wait(t5_s32(&bars.pvdone[j & 3]), ((j >> 2) - 1) & 1))) {
-                    t5_fence_after();
-                    const uint32_t sKj = sK + (j % kW5KStages) * kW5KVBytes;
+                for (int ks = 0; ks < kW5D / 16; ++ks)
+#endif
+                    t5_mma_ss(tm + buf * kW5N, dq + (((ks >> 2) * kW5QBox + (ks & 3) * 32) >> 4),
+                              dk + (((ks >> 2) * kW5KVBox + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
+                t5_commit(t5_s32(&bars.sfull[buf]));
+                t5_commit(t5_s32(&bars.kempty[kst]));
+            }
+            __syncwarp();
+            if (++kst == kW5KStages) { kst = 0; kph ^= 1; }
+        };
+        for (int j = 0; j < 3 && j < n_tiles && ok; ++j) {
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.kfull[kst]), kph, abort_flag));
+            if (!ok) break;
+            t5_fence_after();
+            issue_s(j);
+        }
+        for (int j0 = 0; j0 < n_tiles && ok; j0 += kW5SBufs) {
 #pragma unroll
-                    for (int ks = 0; ks < kW5D / 16; ++ks)
-                        t5_mma_ss(tm + (j & 3) * kW5N, t5_desc(sQ + (ks >> 2) * kW5QBox + (ks & 3) * 32, 16, 1024),
-                                  t5_desc(sKj + (ks >> 2) * kW5KVBox + (ks & 3) * 32, 16, 1024), idesc_qk, ks > 0);
-                    t5_commit(t5_s32(&bars.sfull[j & 3]));
-                    t5_commit(t5_s32(&bars.kempty[j % kW5KStages]));
-                    next_s = j + 1;
-                    progress = true;
+            for (int u = 0; u < kW5SBufs; ++u) {
+                const int j = j0 + u;
+                if (j >= n_tiles || !ok) break;
+                // ---- P.V_j ----
+                ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pready[u]), (j >> 2) & 1, abort_flag) &&
+                                                 t5_wait(t5_s32(&bars.vfull[vst]), vph, abort_flag));
+                if (!ok) break;
+                t5_fence_after();
+                {
+                    const uint64_t dv = t5_desc(sV + vst * kW5KVBytes, kW5KVBox, 1024);
+                    if (t5_elect()) {
+#ifdef HS_W5_NOPV
+                        for (int ks = 0; ks < 1; ++ks)
+#else
+#pragma unroll
+                        for (int ks = 0; ks < kW5N / 16; ++ks)
+#endif
+                            t5_mma_ts(tm + 256, tm + u * kW5N + ks * 8, dv + ((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                        t5_commit(t5_s32(&bars.pvdone[u]));
+                        t5_commit(t5_s32(&bars.vempty[vst]));
+                    }
+                    __syncwarp();
+                    if (++vst == kW5VStages) { vst = 0; vph ^= 1; }
                 }
-                if (progress) {
-                    t_idle = clock64();
-                } else if (*abort_flag || clock64() - t_idle > kT5WaitCycles) {
-                    *abort_flag = 1;
-                    ok = false;
-                } else {
-                    __nanosleep(20);
+                // ---- S_{j+3} into the buffer tile j-1 used ----
+                if (j + 3 < n_tiles) {
+                    const int nb = (u + 3) & 3;
+                    bool w = t5_wait(t5_s32(&bars.kfull[kst]), kph, abort_flag);
+                    if (j >= 1) w = w && t5_wait(t5_s32(&bars.pvdone[nb]), ((j - 1) >> 2) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, w);
+                    if (!ok) break;
+                    t5_fence_after();
+                    issue_s(nb);
                 }
             }
         }
@@ -596,6 +631,11 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 3]), (j >> 2) & 1, abort_flag));
             if (!ok) break;
             t5_fence_after();
+#ifdef HS_W5_NOSOFTMAX
+            t5_fence_before();
+            t5_arrive(t5_s32(&bars.pready[j & 3]));
+            continue;
+#endif
             const int n0 = j * kW5N;
             const bool masked = n0 + kW5N > min(kv_len, off + m0 + 1);
             const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
@@ -688,7 +728,11 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     for (int i = 0; i < 16; ++i) {
                         float x0, x1;
                         t5_unpack2(t5_fma2(t5_pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2), x0, x1);
+#ifdef HS_W5_NOEXP
+                        const float p0 = x0, p1 = x1;
+#else
                         const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);
+#endif
                         if (i & 1) acc_b = t5_add2(acc_b, t5_pack2(p0, p1)); else acc_a = t5_add2(acc_a, t5_pack2(p0, p1));
                         w[i] = t5_pack_bf16x2(p0, p1);
                     }
