@@ -21,7 +21,8 @@
 // (llama.rs:847-872) and the cached-prefix offset tril(k_len - q_len) (llama.rs:1074-1084); with `gate`,
 // Qwen3_5FullAttention's prefill branch (qwen3_5.rs:1012-1059) at head_dim 128.
 //
-// Every mbarrier wait is bounded; on expiry the CTA records HS_DEVERR_WAIT_TIMEOUT, frees its TMEM and returns.
+// Every mbarrier wait is bounded; on expiry the CTA records HS_DEVERR_WAIT_TIMEOUT, frees its TMEM and returns, and CTAs that start
+// while that flag is set (until the host takes it) return at once, so a failed launch ends in a fraction of a second.
 #include <cuda.h>
 
 #include "hs_common.cuh"
@@ -35,7 +36,7 @@ constexpr int kT5Threads = 320;
 constexpr int kT5TileBytes = kT5N * kT5D * 2;          // 32 KB: two 64-column halves of [128 rows][128 B]
 constexpr int kT5HalfBytes = kT5TileBytes / 2;
 constexpr int kT5SmemBytes = kT5TileBytes * (2 + 2 * kT5Stages) + 1024;  // two Q tiles, K/V ring, alignment slack
-constexpr long long kT5WaitCycles = 4000000000LL;
+constexpr long long kT5WaitCycles = 400000000LL;  // ~0.2 s: any legitimate wait is far below a millisecond
 constexpr float kT5RescaleThreshold = 8.0f;            // log2 units
 
 __device__ __forceinline__ uint32_t t5_s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -191,7 +192,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         init(&bars.q, 1);
         for (int s = 0; s < kT5Stages; ++s) { init(&bars.kfull[s], 1); init(&bars.vfull[s], 1); init(&bars.kvempty[s], 1); }
         for (int i = 0; i < 2; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kT5M); init(&bars.odone[i], 1); }
-        s_abort = 0;
+        s_abort = (*reinterpret_cast<volatile int *>(err) & HS_DEVERR_WAIT_TIMEOUT) ? 1 : 0;  // a recorded time-out ends every later CTA at once
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -292,6 +293,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[x]), j & 1, abort_flag));  // warp-uniform: the TMEM
             if (!ok) break;                                                                      // accesses below are warp-collective
             t5_fence_after();
+#ifdef HS_T5_NOSOFTMAX
+            t5_fence_before();
+            t5_arrive(t5_s32(&bars.pready[x]));
+            continue;
+#endif
             const int n0 = j * kT5N;
             const bool masked = n0 + kT5N > min(kv_len, off + m0 + x * kT5M + 1);
             const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
@@ -450,6 +456,14 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 //   its own partial row sum with the reference it was last brought to, and the two are combined at the end.
 //   Per key tile: S = Q.K^T is 16 MMAs 128x64x16 (operands in shared memory), O += P.V is 4 MMAs 128x256x16 (P from TMEM,
 //   V MN-major: its four 64-column boxes are 8 KB apart).
+#ifdef HS_W5_PROF
+__device__ unsigned long long g_w5_prof[8];
+#define W5_T(var) const long long var = clock64()
+#define W5_ACC(i, t0, t1) prof[i] += (t1) - (t0)
+#else
+#define W5_T(var)
+#define W5_ACC(i, t0, t1)
+#endif
 constexpr int kW5D = 256, kW5M = 128, kW5N = 64;
 constexpr int kW5KStages = 3, kW5VStages = 2, kW5SBufs = 4;
 constexpr int kW5Threads = 320;  // warps 0-3 / 4-7: softmax of even / odd key tiles, warp 8: loader, warp 9: MMA issuer
@@ -460,7 +474,7 @@ constexpr int kW5KVBox = kW5N * 128;          // one 64-column box of K or V
 constexpr int kW5SmemBytes = kW5QBytes + (kW5KStages + kW5VStages) * kW5KVBytes + 1024;
 
 struct W5Bars {
-    uint64_t q, kfull[kW5KStages], kempty[kW5KStages], vfull[kW5VStages], vempty[kW5VStages], sfull[kW5SBufs], pready[kW5SBufs],
+    uint64_t q, kfull[kW5KStages], kempty[kW5KStages], vfull[kW5VStages], vempty[kW5VStages], sfull[2], pready[kW5SBufs],
         pvdone[kW5SBufs];
 };
 
@@ -487,7 +501,10 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int mb = gridDim.x - 1 - blockIdx.x;  // latest (heaviest) query blocks first
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (n_q_heads / n_kv_heads);
     const int m0 = mb * kW5M, off = kv_len - q_len;
-    const int n_tiles = (min(kv_len, off + min(m0 + kW5M, q_len)) + kW5N - 1) / kW5N;
+    // 64-key tiles, rounded up to whole pairs: q.k^T is issued per pair of tiles; keys past the causal limit or past kv_len
+    // (which the tensor maps fill with zeros) are masked in the softmax
+    const int n_tiles = ((min(kv_len, off + min(m0 + kW5M, q_len)) + 2 * kW5N - 1) / (2 * kW5N)) * 2;
+    const int n_pairs = n_tiles / 2;
     volatile int *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
@@ -495,8 +512,9 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         init(&bars.q, 1);
         for (int s = 0; s < kW5KStages; ++s) { init(&bars.kfull[s], 1); init(&bars.kempty[s], 1); }
         for (int s = 0; s < kW5VStages; ++s) { init(&bars.vfull[s], 1); init(&bars.vempty[s], 1); }
-        for (int i = 0; i < kW5SBufs; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kW5M); init(&bars.pvdone[i], 1); }
-        s_abort = 0;
+        for (int i = 0; i < 2; ++i) init(&bars.sfull[i], 1);
+        for (int i = 0; i < kW5SBufs; ++i) { init(&bars.pready[i], kW5M); init(&bars.pvdone[i], 1); }
+        s_abort = (*reinterpret_cast<volatile int *>(err) & HS_DEVERR_WAIT_TIMEOUT) ? 1 : 0;  // a recorded time-out ends every later CTA at once
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -515,82 +533,98 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             t5_expect_tx(t5_s32(&bars.q), kW5QBytes);
 #pragma unroll
             for (int c = 0; c < 4; ++c) t5_tma_load(sQ + c * kW5QBox, &map_q, 64 * c, h, m0, b, t5_s32(&bars.q));
-            // K tiles run ahead of V tiles by the difference of the ring depths
-            int jk = 0, jv = 0;
-            while (ok && (jk < n_tiles || jv < n_tiles)) {
-                if (jk < n_tiles && (jv >= n_tiles || jk - jv < kW5KStages)) {
-                    const int s = jk % kW5KStages;
-                    if (jk >= kW5KStages) ok = t5_wait(t5_s32(&bars.kempty[s]), (jk / kW5KStages - 1) & 1, abort_flag);
-                    if (!ok) break;
+            // Loads go out in the order the issuer consumes them: the K halves of pairs 0 and 1, then per pair t the V tiles 2t and
+            // 2t+1 and the K halves of pair t+2.  A K half-stage holds [128 keys][128 columns of d] as two 64-column boxes.
+            auto load_k = [&](int n) -> bool {  // half n: pair n >> 1, columns 128 (n & 1) ..
+                const int s = n % kW5KStages;
+                if (n >= kW5KStages && !t5_wait(t5_s32(&bars.kempty[s]), (n / kW5KStages - 1) & 1, abort_flag)) return false;
 #ifdef HS_W5_NOLOAD
-                    if (jk >= kW5KStages) { t5_arrive(t5_s32(&bars.kfull[s])); ++jk; continue; }
+                if (n >= kW5KStages) { t5_arrive(t5_s32(&bars.kfull[s])); return true; }
 #endif
-                    t5_expect_tx(t5_s32(&bars.kfull[s]), kW5KVBytes);
+                t5_expect_tx(t5_s32(&bars.kfull[s]), kW5KVBytes);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        t5_tma_load(sK + s * kW5KVBytes + c * kW5KVBox, &map_k, 64 * c, kvh, jk * kW5N, b, t5_s32(&bars.kfull[s]));
-                    ++jk;
-                } else {
-                    const int s = jv % kW5VStages;
-                    if (jv >= kW5VStages) ok = t5_wait(t5_s32(&bars.vempty[s]), (jv / kW5VStages - 1) & 1, abort_flag);
-                    if (!ok) break;
+                for (int c = 0; c < 2; ++c)
+                    t5_tma_load(sK + s * kW5KVBytes + c * kW5QBox, &map_k, 64 * (2 * (n & 1) + c), kvh, (n >> 1) * 2 * kW5N, b, t5_s32(&bars.kfull[s]));
+                return true;
+            };
+            auto load_v = [&](int j) -> bool {
+                const int s = j % kW5VStages;
+                if (j >= kW5VStages && !t5_wait(t5_s32(&bars.vempty[s]), (j / kW5VStages - 1) & 1, abort_flag)) return false;
 #ifdef HS_W5_NOLOAD
-                    if (jv >= kW5VStages) { t5_arrive(t5_s32(&bars.vfull[s])); ++jv; continue; }
+                if (j >= kW5VStages) { t5_arrive(t5_s32(&bars.vfull[s])); return true; }
 #endif
-                    t5_expect_tx(t5_s32(&bars.vfull[s]), kW5KVBytes);
+                t5_expect_tx(t5_s32(&bars.vfull[s]), kW5KVBytes);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        t5_tma_load(sV + s * kW5KVBytes + c * kW5KVBox, &map_v, 64 * c, kvh, jv * kW5N, b, t5_s32(&bars.vfull[s]));
-                    ++jv;
-                }
+                for (int c = 0; c < 4; ++c)
+                    t5_tma_load(sV + s * kW5KVBytes + c * kW5KVBox, &map_v, 64 * c, kvh, j * kW5N, b, t5_s32(&bars.vfull[s]));
+                return true;
+            };
+            for (int n = 0; n < 4 && n < 2 * n_pairs && ok; ++n) ok = load_k(n);
+            for (int t = 0; t < n_pairs && ok; ++t) {
+                ok = load_v(2 * t) && load_v(2 * t + 1);
+                if (ok && t + 2 < n_pairs) ok = load_k(2 * t + 4) && load_k(2 * t + 5);
             }
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ================================
-        // The whole warp walks a fixed schedule -- S_0 S_1 S_2, then per key tile j: P.V_j, S_{j+3} -- with blocking waits, and one
-        // elected lane issues.  Stage and buffer indices advance unconditionally, so every descriptor is a per-tile base plus a
-        // compile-time offset.  S_{j+3} overwrites the score buffer of tile j-1, whose P.V was issued one tile earlier: waiting
-        // for its completion still leaves S_{j+2} and P.V_j queued in the tensor pipe.
-        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kW5N >> 3) << 17) | ((kW5M >> 4) << 24);
+        // The whole warp walks a fixed schedule with blocking waits, and one elected lane issues:
+        //     S(pair 0), S(pair 1), then per pair t of key tiles:  P.V_2t,  P.V_2t+1,  S(pair t+2).
+        // S(pair) = Q K^T for 128 keys at once (16 MMAs 128x128x16: the Q slice is read from shared memory once per 128 keys, which
+        // is what keeps this MMA at the tensor pipe's rate) into two adjacent 64-column score buffers; P.V stays per 64-key tile
+        // (4 MMAs 128x256x16).  S(pair t+2) overwrites the buffers whose P tiles P.V_2t and P.V_2t+1 read: the MMAs of one thread
+        // execute in issue order, so no wait lies between them and the tensor pipe never drains.
+        // The loop is unrolled over 6 pairs (the common period of the 3 K half-stages and the 2 pairs of score buffers), so ring
+        // indices, most barrier parities and every descriptor offset are compile-time constants.
+        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (((2 * kW5N) >> 3) << 17) | ((kW5M >> 4) << 24);
         const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kW5D >> 3) << 17) | ((kW5M >> 4) << 24);
-        const uint64_t dq = t5_desc(sQ, 16, 1024);
-        int kst = 0, kph = 0, vst = 0, vph = 0;  // ring stage and phase of the next K / V tile to consume
-        ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.q), 0, abort_flag));
-        auto issue_s = [&](int buf) {  // S(buf) = Q K^T with the K tile in stage kst
-            const uint64_t dk = t5_desc(sK + kst * kW5KVBytes, 16, 1024);
-            if (t5_elect()) {
+        const uint64_t dq = t5_desc(sQ, 16, 1024), dk0 = t5_desc(sK, 16, 1024), dv0 = t5_desc(sV, kW5KVBox, 1024);
+#ifdef HS_W5_PROF
+        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+        // S(pair) into score buffers 2 pb, 2 pb + 1; its K halves are n0 and n0 + 1 (n0 = 2 * pair; ring stage n % 3, phase n / 3)
+        auto issue_s = [&](int pb, int st0, uint32_t ph0, int st1, uint32_t ph1) -> bool {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int st = hf ? st1 : st0;
+                if (!__all_sync(0xffffffffu, t5_wait(t5_s32(&bars.kfull[st]), hf ? ph1 : ph0, abort_flag))) return false;
+                t5_fence_after();
+                if (t5_elect()) {
 #ifdef HS_W5_NOQK
-                for (int ks = 0; ks < 1; ++ks)
+                    for (int ks = 0; ks < 1; ++ks)
 #else
 #pragma unroll
-                for (int ks = 0; ks < kW5D / 16; ++ks)
+                    for (int ks = 0; ks < 8; ++ks)
 #endif
-                    t5_mma_ss(tm + buf * kW5N, dq + (((ks >> 2) * kW5QBox + (ks & 3) * 32) >> 4),
-                              dk + (((ks >> 2) * kW5KVBox + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
-                t5_commit(t5_s32(&bars.sfull[buf]));
-                t5_commit(t5_s32(&bars.kempty[kst]));
+                        t5_mma_ss(tm + pb * 2 * kW5N, dq + (((2 * hf + (ks >> 2)) * kW5QBox + (ks & 3) * 32) >> 4),
+                                  dk0 + ((st * kW5KVBytes + (ks >> 2) * kW5QBox + (ks & 3) * 32) >> 4), idesc_qk, (hf > 0 || ks > 0) ? 1u : 0u);
+                    t5_commit(t5_s32(&bars.kempty[st]));
+                    if (hf) t5_commit(t5_s32(&bars.sfull[pb]));
+                }
+                __syncwarp();
             }
-            __syncwarp();
-            if (++kst == kW5KStages) { kst = 0; kph ^= 1; }
+            return true;
         };
-        for (int j = 0; j < 3 && j < n_tiles && ok; ++j) {
-            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.kfull[kst]), kph, abort_flag));
-            if (!ok) break;
-            t5_fence_after();
-            issue_s(j);
-        }
-        for (int j0 = 0; j0 < n_tiles && ok; j0 += kW5SBufs) {
+        ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.q), 0, abort_flag));
+        if (ok) ok = issue_s(0, 0, 0, 1, 0);                 // halves 0, 1
+        if (ok && n_pairs > 1) ok = issue_s(1, 2, 0, 0, 1);  // halves 2, 3
+        for (int t0 = 0; t0 < n_pairs && ok; t0 += 6) {
+            const uint32_t p6 = (t0 / 6) & 1;  // parity of the 6-pair period
 #pragma unroll
-            for (int u = 0; u < kW5SBufs; ++u) {
-                const int j = j0 + u;
-                if (j >= n_tiles || !ok) break;
-                // ---- P.V_j ----
-                ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pready[u]), (j >> 2) & 1, abort_flag) &&
-                                                 t5_wait(t5_s32(&bars.vfull[vst]), vph, abort_flag));
-                if (!ok) break;
-                t5_fence_after();
-                {
-                    const uint64_t dv = t5_desc(sV + vst * kW5KVBytes, kW5KVBox, 1024);
+            for (int i = 0; i < 6; ++i) {
+                const int t = t0 + i;
+                if (t >= n_pairs || !ok) break;
+                // ---- P.V of tiles j = 2t + e = 12 q + 2i + e: buffer j & 3, barrier phase j >> 2 = 3q + ((2i + e) >> 2); V stage e,
+                //      phase t = 6q + i ----
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int u = (2 * i + e) & 3;
+                    W5_T(ta);
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pready[u]), p6 ^ (((2 * i + e) >> 2) & 1), abort_flag) &&
+                                                     t5_wait(t5_s32(&bars.vfull[e]), i & 1, abort_flag));
+                    W5_T(tc);
+                    W5_ACC(0, ta, tc);
+                    if (!ok) break;
+                    t5_fence_after();
                     if (t5_elect()) {
 #ifdef HS_W5_NOPV
                         for (int ks = 0; ks < 1; ++ks)
@@ -598,25 +632,32 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                         for (int ks = 0; ks < kW5N / 16; ++ks)
 #endif
-                            t5_mma_ts(tm + 256, tm + u * kW5N + ks * 8, dv + ((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                        t5_commit(t5_s32(&bars.pvdone[u]));
-                        t5_commit(t5_s32(&bars.vempty[vst]));
+                            t5_mma_ts(tm + 256, tm + u * kW5N + ks * 8, dv0 + ((e * kW5KVBytes + ks * 2048) >> 4), idesc_pv,
+                                      (t > 0 || e > 0 || ks > 0) ? 1u : 0u);
+                        t5_commit(t5_s32(&bars.pvdone[u]));  // one phase per four tiles: what the softmax warps wait on
+                        t5_commit(t5_s32(&bars.vempty[e]));
                     }
                     __syncwarp();
-                    if (++vst == kW5VStages) { vst = 0; vph ^= 1; }
+                    W5_T(td);
+                    W5_ACC(2, tc, td);
                 }
-                // ---- S_{j+3} into the buffer tile j-1 used ----
-                if (j + 3 < n_tiles) {
-                    const int nb = (u + 3) & 3;
-                    bool w = t5_wait(t5_s32(&bars.kfull[kst]), kph, abort_flag);
-                    if (j >= 1) w = w && t5_wait(t5_s32(&bars.pvdone[nb]), ((j - 1) >> 2) & 1, abort_flag);
-                    ok = __all_sync(0xffffffffu, w);
-                    if (!ok) break;
-                    t5_fence_after();
-                    issue_s(nb);
+                if (!ok) break;
+                // ---- S(pair t+2): halves n = 2(t+2) + hf = 12 q + 2i + 4 + hf, stage n % 3, phase n / 3 = 4q + (2i + 4 + hf) / 3 ----
+                if (t + 2 < n_pairs) {
+                    W5_T(tf);
+                    ok = issue_s(i & 1, (2 * i + 4) % 3, ((2 * i + 4) / 3) & 1, (2 * i + 5) % 3, ((2 * i + 5) / 3) & 1);
+                    W5_T(tg);
+                    W5_ACC(5, tf, tg);
+#ifdef HS_W5_PROF
+                    prof[6] += 2;
+#endif
                 }
             }
         }
+#ifdef HS_W5_PROF
+        if (lane == 0)
+            for (int i = 0; i < 8; ++i) atomicAdd(&g_w5_prof[i], static_cast<unsigned long long>(prof[i]));
+#endif
     } else {
         // ================================ softmax: thread = query row, group = parity of the key tile ================================
         const int grp = warp >> 2, r_local = threadIdx.x & 127;
@@ -628,7 +669,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         float l = 0.0f, m_ref = -INFINITY;          // this group's partial row sum, relative to m_ref
         for (int j = grp; j < n_tiles && ok; j += 2) {
             const uint32_t tS = tm + lane_base + (j & 3) * kW5N;
-            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[j & 3]), (j >> 2) & 1, abort_flag));
+            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[(j >> 1) & 1]), (j >> 2) & 1, abort_flag));
             if (!ok) break;
             t5_fence_after();
 #ifdef HS_W5_NOSOFTMAX
@@ -859,7 +900,7 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
     if (q_len < 2) return HS_OK;
     if (head_dim == kW5D) {
         CUtensorMap mq, mk, mv;
-        if (!make_map(&mq, q, n_seqs, q_len, n_q_heads, kW5D, kW5M) || !make_map(&mk, k, n_seqs, kv_len, n_kv_heads, kW5D, kW5N) ||
+        if (!make_map(&mq, q, n_seqs, q_len, n_q_heads, kW5D, kW5M) || !make_map(&mk, k, n_seqs, kv_len, n_kv_heads, kW5D, 2 * kW5N) ||
             !make_map(&mv, v, n_seqs, kv_len, n_kv_heads, kW5D, kW5N))
             return HS_OK;
         int *errw = device_error_word();
@@ -895,3 +936,14 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
 }
 
 }  // namespace hs
+
+#ifdef HS_W5_PROF
+extern "C" int hs_w5_prof_read(unsigned long long *out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, hs::g_w5_prof, sizeof(unsigned long long) * 8);
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        e = cudaMemcpyToSymbol(hs::g_w5_prof, z, sizeof(z));
+    }
+    return static_cast<int>(e);
+}
+#endif
