@@ -229,55 +229,66 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ================================
-        // A small polling scheduler: for each query tile the order is S_0, PV_0, S_1, PV_1, ...; S_j needs K_j and
-        // (for j > 0) PV_{j-1} complete (it overwrites the buffer PV_{j-1} reads P from); PV_j needs P_j and V_j.
-        // Whichever tile has its next operation ready gets issued, so one tile's MMAs run under the other's softmax.
-        if (lane == 0) {
-            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kT5N >> 3) << 17) | ((kT5M >> 4) << 24);  // bf16 x bf16 -> f32, K-major A and B
-            const uint32_t idesc_pv = idesc_qk | (1u << 16);                                                         // B (V) is MN-major
-            int next_s[2] = {0, 0}, next_pv[2] = {0, 0};
-            ok = t5_wait(t5_s32(&bars.q), 0, abort_flag);
-            long long t_idle = clock64();
-            while (ok && (next_pv[0] < n_tiles[0] || next_pv[1] < n_tiles[1])) {
-                bool progress = false;
+        // The whole warp walks a fixed schedule with blocking waits, and one elected lane issues:
+        //     S^0_0, S^1_0, then per key tile j:  P.V^0_j, S^0_{j+1}, P.V^1_j, S^1_{j+1}
+        // (S^x_j = Q_x K_j^T, 8 MMAs 128x128x16 from shared memory; P.V^x_j: 8 MMAs 128x128x16 with P from tensor memory).  S^x_{j+1}
+        // overwrites the buffer P.V^x_j reads P from: the MMAs of one thread execute in issue order, so nothing waits in between,
+        // and one tile's softmax runs under the other tile's two operations.  The loop is unrolled over the two ring stages, so
+        // stage indices, most parities and all descriptor offsets are compile-time constants.
+        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((kT5N >> 3) << 17) | ((kT5M >> 4) << 24);  // bf16 x bf16 -> f32, K-major A and B
+        const uint32_t idesc_pv = idesc_qk | (1u << 16);                                                         // B (V) is MN-major
+        const uint64_t dq0 = t5_desc(sQ, 16, 1024), dk0 = t5_desc(sKV, 16, 1024), dv0 = t5_desc(sKV + kT5TileBytes, kT5HalfBytes, 1024);
+        auto issue_s = [&](int x, int st) {  // S^x = Q_x K^T with the K tile of ring stage st
+            if (t5_elect()) {
+#pragma unroll
+                for (int ks = 0; ks < kT5D / 16; ++ks) {
+                    const uint32_t o = (ks >> 2) * kT5HalfBytes + (ks & 3) * 32;
+                    t5_mma_ss(tm + x * kT5N, dq0 + ((x * kT5TileBytes + o) >> 4), dk0 + ((2 * st * kT5TileBytes + o) >> 4), idesc_qk, ks > 0);
+                }
+                t5_commit(t5_s32(&bars.sfull[x]));
+            }
+            __syncwarp();
+        };
+        ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.q), 0, abort_flag) && (n_max == 0 || t5_wait(t5_s32(&bars.kfull[0]), 0, abort_flag)));
+        if (ok) {
+            t5_fence_after();
+            if (n_tiles[0] > 0) issue_s(0, 0);
+            if (n_tiles[1] > 0) issue_s(1, 0);
+        }
+        for (int j0 = 0; j0 < n_max && ok; j0 += 2) {
+            const uint32_t p2 = (j0 >> 1) & 1;  // phase parity of the ring stages for tiles j0 and j0 + 1
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int j = j0 + i;
+                if (j >= n_max || !ok) break;
+                // tile j sits in stage i in phase j >> 1 (parity p2); tile j + 1 in stage i ^ 1, in phase (j + 1) >> 1 = parity p2 ^ i
+                bool k_next_ready = false;
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
-                    int j = next_s[x];
-                    if (j < n_tiles[x] && j == next_pv[x] && t5_test_wait(t5_s32(&bars.kfull[j & 1]), (j >> 1) & 1) &&
-                        (j == 0 || t5_test_wait(t5_s32(&bars.odone[x]), (j - 1) & 1))) {
-                        t5_fence_after();
-                        const uint32_t sK = sKV + 2 * (j & 1) * kT5TileBytes, sQx = sQ + x * kT5TileBytes;
-#pragma unroll
-                        for (int ks = 0; ks < kT5D / 16; ++ks) {
-                            const uint32_t o = (ks >> 2) * kT5HalfBytes + (ks & 3) * 32;
-                            t5_mma_ss(tm + x * kT5N, t5_desc(sQx + o, 16, 1024), t5_desc(sK + o, 16, 1024), idesc_qk, ks > 0);
-                        }
-                        t5_commit(t5_s32(&bars.sfull[x]));
-                        next_s[x] = j + 1;
-                        progress = true;
-                    }
-                    j = next_pv[x];
-                    if (j < next_s[x] && t5_test_wait(t5_s32(&bars.pready[x]), j & 1) && t5_test_wait(t5_s32(&bars.vfull[j & 1]), (j >> 1) & 1)) {
-                        t5_fence_after();
-                        const uint32_t sV = sKV + (2 * (j & 1) + 1) * kT5TileBytes;
+                    if (j >= n_tiles[x]) continue;
+                    ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pready[x]), i, abort_flag) &&
+                                                     t5_wait(t5_s32(&bars.vfull[i]), p2, abort_flag));
+                    if (!ok) break;
+                    t5_fence_after();
+                    const bool last_user = x == 1 || j >= n_tiles[1];  // the stage of tile j is free once this P.V has completed
+                    if (t5_elect()) {
 #pragma unroll
                         for (int ks = 0; ks < kT5N / 16; ++ks)
-                            t5_mma_ts(tm + 256 + x * kT5D, tm + x * kT5N + ks * 8, t5_desc(sV + ks * 2048, kT5HalfBytes, 1024), idesc_pv,
+                            t5_mma_ts(tm + 256 + x * kT5D, tm + x * kT5N + ks * 8, dv0 + ((2 * i * kT5TileBytes + ks * 2048) >> 4), idesc_pv,
                                       (j > 0 || ks > 0) ? 1u : 0u);
                         t5_commit(t5_s32(&bars.odone[x]));
-                        next_pv[x] = j + 1;
-                        const int y = x ^ 1;
-                        if (next_pv[y] > j || j >= n_tiles[y]) t5_commit(t5_s32(&bars.kvempty[j & 1]));  // both tiles are past K_j / V_j
-                        progress = true;
+                        if (last_user) t5_commit(t5_s32(&bars.kvempty[i]));
                     }
-                }
-                if (progress) {
-                    t_idle = clock64();
-                } else if (*abort_flag || clock64() - t_idle > kT5WaitCycles) {
-                    *abort_flag = 1;
-                    ok = false;
-                } else {
-                    __nanosleep(20);  // leave the issue slots to the softmax warps
+                    __syncwarp();
+                    if (j + 1 < n_tiles[x]) {
+                        if (!k_next_ready) {
+                            ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.kfull[i ^ 1]), p2 ^ i, abort_flag));
+                            if (!ok) break;
+                            t5_fence_after();
+                            k_next_ready = true;
+                        }
+                        issue_s(x, i ^ 1);
+                    }
                 }
             }
         }
