@@ -139,10 +139,13 @@ struct TcLayout {
     static constexpr int kXBarOff = kBarOff + 2 * kStages * 8 + 16;    // 4 mbarriers: score exchange of a warp pair (WIDE)
     static constexpr int kPrefOff = kXBarOff + 32;                     // int tile-count prefix [kTcMaxSeqs + 1]
     static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
-    static constexpr int kXOff = (kLenOff + kTcMaxSeqs * 4 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
+    static constexpr int kDescOff = kLenOff + kTcMaxSeqs * 4;          // uint64 [32 tiles][4 tables]: source addresses of the next tiles
+    static constexpr int kXOff = (kDescOff + 32 * 4 * 8 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
     static constexpr int kLutOff = kXOff + (WIDE ? 4 * 2 * 2 * 512 : 0);        // uint32 [256][32] (4-bit kinds only)
     static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
     static constexpr uint32_t kTxBytes = 2u * kTile * kRow + 2u * kTile * kSRow;
+    static_assert(kDescOff % 16 == 0, "tile addresses are stored 16 bytes at a time");
+    static_assert(WIDE || 2 * (kTotal + 1024) <= 228 * 1024, "two CTAs per SM");
 };
 
 // Outputs of the merge that runs inside the kernel after a grid-wide barrier (cooperative launch only).
@@ -264,70 +267,63 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         r_first = lo;
     }
 
-    // ---- producer state (warp 0; lanes 0..3 each own one pointer table: K, V, K scales, V scales) ----
-    // Page pointers are read one page (or one sequence) ahead so that the load latency never sits in front of a copy.
-    int p_r = r_first, p_tile = 0, p_hi = 0, p_it = 0;
-    if (has_work) { p_tile = t_begin - s_pref[r_first]; p_hi = min(t_end, s_pref[r_first + 1]) - s_pref[r_first]; }
-    void *const *p_table = lane == 0 ? view.k_pages : (lane == 1 ? view.v_pages : (lane == 2 ? view.k_scale_pages : view.v_scale_pages));
+    // ---- producer (warp 0) ----
+    // Where a tile's rows lie (sequence, page, offset in the page -> four source addresses: K codes, V codes, K scales,
+    // V scales) is worked out for 32 tiles at a time, one tile per lane, and parked in shared memory; issuing a tile's
+    // copies is then one 8-byte shared load per issuing lane.  The warp that issues also consumes, so every instruction
+    // it spends here delays the whole ring.
+    const int n_tiles_cta = has_work ? t_end - t_begin : 0;
+    unsigned long long *s_desc = reinterpret_cast<unsigned long long *>(smem + LT::kDescOff);
     const uint64_t stream_policy = l2_evict_first_policy();
-    int64_t cur_pidx = -1, nxt_pidx = -1;
-    const unsigned char *cur_ptr = nullptr, *nxt_ptr = nullptr;
-    // index of the page that follows page `page` of sequence r inside this CTA's range, or -1
-    auto following_page = [&](int r, int page) -> int64_t {
-        const int last_tile = min(t_end, s_pref[r + 1]) - s_pref[r] - 1;
-        if (page < last_tile * kTcTile / view.page_tokens) return static_cast<int64_t>(r) * view.pages_per_seq + page + 1;
-        for (int r2 = r + 1; r2 < n_seqs && s_pref[r2] < t_end; ++r2)
-            if (s_pref[r2 + 1] > s_pref[r2]) return static_cast<int64_t>(r2) * view.pages_per_seq;  // later sequences start at their tile 0
-        return -1;
+    auto fill_desc = [&](int p_base) {  // all lanes of warp 0: the addresses of tiles p_base .. p_base + 31 of this CTA
+        const int p = p_base + lane;
+        if (p < n_tiles_cta) {
+            const int T = t_begin + p;
+            int lo = r_first, hi = n_seqs;  // invariant: s_pref[lo] <= T < s_pref[hi]; ends at the sequence that owns tile T
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_pref[mid] <= T) lo = mid; else hi = mid;
+            }
+            const int t0 = (T - s_pref[lo]) * kTcTile;
+            const int page = t0 / view.page_tokens;
+            const int64_t in_page = t0 - page * view.page_tokens;
+            const int64_t pidx = static_cast<int64_t>(lo) * view.pages_per_seq + page;
+            const unsigned char *pk = reinterpret_cast<const unsigned char *>(view.k_pages[pidx]);
+            const unsigned char *pv = reinterpret_cast<const unsigned char *>(view.v_pages[pidx]);
+            const unsigned char *pks = reinterpret_cast<const unsigned char *>(view.k_scale_pages[pidx]);
+            const unsigned char *pvs = reinterpret_cast<const unsigned char *>(view.v_scale_pages[pidx]);
+            ulonglong2 *d = reinterpret_cast<ulonglong2 *>(s_desc + 4 * lane);
+            d[0] = make_ulonglong2(reinterpret_cast<unsigned long long>(pk + in_page * LT::kRow), reinterpret_cast<unsigned long long>(pv + in_page * LT::kRow));
+            d[1] = make_ulonglong2(reinterpret_cast<unsigned long long>(pks + in_page * LT::kSRow), reinterpret_cast<unsigned long long>(pvs + in_page * LT::kSRow));
+        }
+        __syncwarp();
     };
-    if (has_work && warp == 0 && lane < 4) {
-        const int page = p_tile * kTcTile / view.page_tokens;
-        cur_pidx = static_cast<int64_t>(p_r) * view.pages_per_seq + page;
-        cur_ptr = reinterpret_cast<const unsigned char *>(p_table[cur_pidx]);
-        nxt_pidx = following_page(p_r, page);
-        if (nxt_pidx >= 0) nxt_ptr = reinterpret_cast<const unsigned char *>(p_table[nxt_pidx]);
-    }
+    int p_it = 0, p_stage = 0, p_round = 0;  // tiles issued; ring stage and trip of the next one
     // issue the copies of the next tile (warp 0, all lanes call); false on a timed-out wait
     auto produce_one = [&]() -> bool {
-        const int stage = p_it % kTcStages;
-        if (p_it >= kTcStages && !mbar_wait(bar_empty + 8 * stage, ((p_it / kTcStages) - 1) & 1, abort_flag)) return false;
+        if ((p_it & 31) == 0 && p_it > 0) fill_desc(p_it);  // (every earlier tile's copies have been issued)
+        if (p_round > 0 && !mbar_wait(bar_empty + 8 * p_stage, (p_round - 1) & 1, abort_flag)) return false;
         if (lane < 4) {
-            const int t0 = p_tile * kTcTile;
-            const int page = t0 / view.page_tokens;
-            const int64_t pidx = static_cast<int64_t>(p_r) * view.pages_per_seq + page;
-            if (pidx != cur_pidx) {
-                cur_ptr = pidx == nxt_pidx ? nxt_ptr : reinterpret_cast<const unsigned char *>(p_table[pidx]);
-                cur_pidx = pidx;
-                nxt_pidx = following_page(p_r, page);
-                if (nxt_pidx >= 0) nxt_ptr = reinterpret_cast<const unsigned char *>(p_table[nxt_pidx]);
-            }
-            const int in_page = t0 - page * view.page_tokens;
-            const uint32_t full = bar_full + 8 * stage;
-            const uint32_t sbase = smem_base + stage * LT::kStage;
+            const unsigned char *src = reinterpret_cast<const unsigned char *>(s_desc[4 * (p_it & 31) + lane]);
+            const uint32_t full = bar_full + 8 * p_stage;
+            const uint32_t sbase = smem_base + p_stage * LT::kStage;
             if (lane == 0) mbar_expect_tx(full, LT::kTxBytes);
             __syncwarp(0xfu);
             if (lane < 2)
-                bulk_g2s_hint(sbase + (lane ? LT::kVOff : LT::kKOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kRow, kTcTile * LT::kRow, full, stream_policy);
+                bulk_g2s_hint(sbase + (lane ? LT::kVOff : LT::kKOff), src, kTcTile * LT::kRow, full, stream_policy);
             else
-                bulk_g2s_hint(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), cur_ptr + static_cast<int64_t>(in_page) * LT::kSRow, kTcTile * LT::kSRow, full, stream_policy);
+                bulk_g2s_hint(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), src, kTcTile * LT::kSRow, full, stream_policy);
         }
         __syncwarp();
         ++p_it;
-        if (++p_tile >= p_hi) {  // next sequence that has tiles in this CTA's range
-            p_hi = 0;
-            for (++p_r; p_r < n_seqs && s_pref[p_r] < t_end; ++p_r)
-                if (s_pref[p_r + 1] > s_pref[p_r]) {
-                    p_tile = 0;
-                    p_hi = min(t_end, s_pref[p_r + 1]) - s_pref[p_r];
-                    break;
-                }
-        }
+        if (++p_stage == kTcStages) { p_stage = 0; ++p_round; }
         return true;
     };
-    const int n_tiles_cta = has_work ? t_end - t_begin : 0;
     bool ok = true;
-    if (warp == 0)  // fill the ring before anything else touches global memory
+    if (warp == 0 && has_work) {  // fill the ring before anything else touches global memory
+        fill_desc(0);
         while (ok && p_it < n_tiles_cta && p_it < kTcStages) ok = produce_one();
+    }
 
     // ================================ consumer warps ================================
     // warp -> (128-wide half `head` of the token row, 16-token group `th` of the tile); `kvh`, `half`: the kv head and
@@ -346,7 +342,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         x_bar = smem_base + LT::kXBarOff + 8 * pair;
     }
     const float vmul = FOURBIT ? 1.0f : 1.0f / 127.0f;  // u8 codes are (code - 127): the 1/127 of the codebook goes here
-    int it = 0;
+    int it = 0, c_stage = 0;
+    uint32_t c_par = 0;  // ring stage and barrier parity of tile `it`
     int pair_it = 0;  // tiles this warp pair has exchanged scores for (WIDE)
     (void)pair_it;
     int seg_idx = 0;
@@ -406,13 +403,14 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.0f;
 
         for (int tile = lo - base; tile < hi - base; ++tile, ++it) {
-            const int stage = it % kTcStages;
+            const int stage = c_stage;
             if (warp == 0) {  // keep the ring two tiles ahead of the tile about to be consumed
                 while (ok && p_it < n_tiles_cta && p_it <= it + kTcStages - 1) ok = produce_one();
                 if (!ok) break;
             }
-            ok = mbar_wait(bar_full + 8 * stage, (it / kTcStages) & 1, abort_flag);
+            ok = mbar_wait(bar_full + 8 * stage, c_par, abort_flag);
             if (!ok) break;
+            if (++c_stage == kTcStages) { c_stage = 0; c_par ^= 1u; }
             const unsigned char *sK = smem + stage * LT::kStage + LT::kKOff;
             const unsigned char *sV = smem + stage * LT::kStage + LT::kVOff;
             const unsigned char *sKs = smem + stage * LT::kStage + LT::kKsOff;
