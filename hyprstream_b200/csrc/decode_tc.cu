@@ -68,6 +68,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
+// counts an arrival in shared memory (release: this warp's reads of the stage are done; acquire: the warp that
+// arrives last has seen everyone else's) and returns the count before it
+__device__ __forceinline__ uint32_t smem_arrive_count(uint32_t addr) {
+    uint32_t prev;
+    asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(prev) : "r"(addr) : "memory");
+    return prev;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
@@ -139,8 +146,8 @@ struct TcLayout {
     static constexpr int kXBarOff = kBarOff + 2 * kStages * 8 + 16;    // 4 mbarriers: score exchange of a warp pair (WIDE)
     static constexpr int kPrefOff = kXBarOff + 32;                     // int tile-count prefix [kTcMaxSeqs + 1]
     static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
-    static constexpr int kDescOff = kLenOff + kTcMaxSeqs * 4;          // uint64 [32 tiles][4 tables]: source addresses of the next tiles
-    static constexpr int kXOff = (kDescOff + 32 * 4 * 8 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
+    static constexpr int kDescOff = kLenOff + kTcMaxSeqs * 4;          // uint64 [64 tiles][4 tables]: source addresses of the next tiles
+    static constexpr int kXOff = (kDescOff + 64 * 4 * 8 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
     static constexpr int kLutOff = kXOff + (WIDE ? 4 * 2 * 2 * 512 : 0);        // uint32 [256][32] (4-bit kinds only)
     static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
     static constexpr uint32_t kTxBytes = 2u * kTile * kRow + 2u * kTile * kSRow;
@@ -178,7 +185,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     int *s_pref = reinterpret_cast<int *>(smem + LT::kPrefOff);
     int *s_len = reinterpret_cast<int *>(smem + LT::kLenOff);
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t bar_full = smem_base + LT::kBarOff, bar_empty = bar_full + kTcStages * 8;
+    const uint32_t bar_full = smem_base + LT::kBarOff;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cap = view.page_tokens * view.pages_per_seq;
 
@@ -202,7 +209,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, kTcConsumers);
+            *reinterpret_cast<unsigned long long *>(smem + LT::kBarOff + (kTcStages + s) * 8) = 0ULL;  // arrival count of the stage
         }
         mbar_init(bar_full + 2 * kTcStages * 8 + 8, 1);  // the merge's staging barrier
         if constexpr (WIDE)
@@ -267,13 +274,16 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         r_first = lo;
     }
 
-    // ---- producer (warp 0) ----
+    // ---- feeding the ring ----
     // Where a tile's rows lie (sequence, page, offset in the page -> four source addresses: K codes, V codes, K scales,
-    // V scales) is worked out for 32 tiles at a time, one tile per lane, and parked in shared memory; issuing a tile's
-    // copies is then one 8-byte shared load per issuing lane.  The warp that issues also consumes, so every instruction
-    // it spends here delays the whole ring.
+    // V scales) is worked out by warp 0 for 32 tiles at a time, one tile per lane, and parked in shared memory (64
+    // slots: the batch being written never overlaps one still in use).  Nobody waits for a ring stage to become free:
+    // every warp counts its arrival when it is done with a tile, and the warp that arrives last (all eight have then
+    // read the stage) issues the copies of the tile three (four) further on into it - one 8-byte shared load and one
+    // bulk copy per issuing lane.
     const int n_tiles_cta = has_work ? t_end - t_begin : 0;
     unsigned long long *s_desc = reinterpret_cast<unsigned long long *>(smem + LT::kDescOff);
+    const uint32_t stage_count = smem_base + LT::kBarOff + kTcStages * 8;  // uint32 arrival counts, 8 bytes apart, never reset
     const uint64_t stream_policy = l2_evict_first_policy();
     auto fill_desc = [&](int p_base) {  // all lanes of warp 0: the addresses of tiles p_base .. p_base + 31 of this CTA
         const int p = p_base + lane;
@@ -292,21 +302,19 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             const unsigned char *pv = reinterpret_cast<const unsigned char *>(view.v_pages[pidx]);
             const unsigned char *pks = reinterpret_cast<const unsigned char *>(view.k_scale_pages[pidx]);
             const unsigned char *pvs = reinterpret_cast<const unsigned char *>(view.v_scale_pages[pidx]);
-            ulonglong2 *d = reinterpret_cast<ulonglong2 *>(s_desc + 4 * lane);
+            ulonglong2 *d = reinterpret_cast<ulonglong2 *>(s_desc + 4 * (p & 63));
             d[0] = make_ulonglong2(reinterpret_cast<unsigned long long>(pk + in_page * LT::kRow), reinterpret_cast<unsigned long long>(pv + in_page * LT::kRow));
             d[1] = make_ulonglong2(reinterpret_cast<unsigned long long>(pks + in_page * LT::kSRow), reinterpret_cast<unsigned long long>(pvs + in_page * LT::kSRow));
         }
+        __threadfence_block();  // the warp that issues such a tile is ordered after this by warp 0's later arrival counts
         __syncwarp();
     };
-    int p_it = 0, p_stage = 0, p_round = 0;  // tiles issued; ring stage and trip of the next one
-    // issue the copies of the next tile (warp 0, all lanes call); false on a timed-out wait
-    auto produce_one = [&]() -> bool {
-        if ((p_it & 31) == 0 && p_it > 0) fill_desc(p_it);  // (every earlier tile's copies have been issued)
-        if (p_round > 0 && !mbar_wait(bar_empty + 8 * p_stage, (p_round - 1) & 1, abort_flag)) return false;
+    // the copies of this CTA's tile p into ring stage `stage` (all lanes of the calling warp)
+    auto issue_tile = [&](int p, int stage) {
         if (lane < 4) {
-            const unsigned char *src = reinterpret_cast<const unsigned char *>(s_desc[4 * (p_it & 31) + lane]);
-            const uint32_t full = bar_full + 8 * p_stage;
-            const uint32_t sbase = smem_base + p_stage * LT::kStage;
+            const unsigned char *src = reinterpret_cast<const unsigned char *>(s_desc[4 * (p & 63) + lane]);
+            const uint32_t full = bar_full + 8 * stage;
+            const uint32_t sbase = smem_base + stage * LT::kStage;
             if (lane == 0) mbar_expect_tx(full, LT::kTxBytes);
             __syncwarp(0xfu);
             if (lane < 2)
@@ -315,14 +323,11 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 bulk_g2s_hint(sbase + (lane == 2 ? LT::kKsOff : LT::kVsOff), src, kTcTile * LT::kSRow, full, stream_policy);
         }
         __syncwarp();
-        ++p_it;
-        if (++p_stage == kTcStages) { p_stage = 0; ++p_round; }
-        return true;
     };
     bool ok = true;
     if (warp == 0 && has_work) {  // fill the ring before anything else touches global memory
         fill_desc(0);
-        while (ok && p_it < n_tiles_cta && p_it < kTcStages) ok = produce_one();
+        for (int p = 0; p < n_tiles_cta && p < kTcStages; ++p) issue_tile(p, p);
     }
 
     // ================================ consumer warps ================================
@@ -404,10 +409,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 
         for (int tile = lo - base; tile < hi - base; ++tile, ++it) {
             const int stage = c_stage;
-            if (warp == 0) {  // keep the ring two tiles ahead of the tile about to be consumed
-                while (ok && p_it < n_tiles_cta && p_it <= it + kTcStages - 1) ok = produce_one();
-                if (!ok) break;
-            }
+            // the next batch of tile addresses, half a batch before its first tile is issued
+            if (warp == 0 && it >= 16 && ((it - 16) & 31) == 0 && it + 16 < n_tiles_cta) fill_desc(it + 16);
             ok = mbar_wait(bar_full + 8 * stage, c_par, abort_flag);
             if (!ok) break;
             if (++c_stage == kTcStages) { c_stage = 0; c_par ^= 1u; }
@@ -566,7 +569,10 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+            uint32_t before = 0;
+            if (lane == 0) before = smem_arrive_count(stage_count + 8 * stage);
+            before = __shfl_sync(0xffffffffu, before, 0);
+            if ((before & (kTcConsumers - 1)) == kTcConsumers - 1 && it + kTcStages < n_tiles_cta) issue_tile(it + kTcStages, stage);
         }
         if (!ok) break;
         HS_TC_STAMP(seg_idx < 2 ? 4 + 4 * seg_idx : 16);
