@@ -7,7 +7,9 @@
 //     so ragged batches balance without padding;
 //   * each tile of the [tokens, kv_heads, 128] u8 cache is streamed into a 3-stage shared memory ring with
 //     four bulk async copies (cp.async.bulk: K codes, V codes, K scales, V scales; each a single contiguous
-//     run of 16 token rows, completion on an mbarrier), issued two tiles ahead by lanes 0-3 of warp 0;
+//     run of 16 token rows, completion on an mbarrier).  Warp 0 works out the source addresses of 32 tiles at a
+//     time; the warp that is last to finish a tile issues the copies of the tile three further on, so no warp
+//     ever waits for a free stage;
 //   * 8 warps: warp h owns kv head h and the 4 query heads that share it.
 //     Codes are widened to fp16 with byte permutes only (the bytes become 1024 + code exactly); the
 //     constant 1151 = 1024 + 127 is removed algebraically: q.(1024+c) - 1151*sum(q) and
@@ -28,7 +30,7 @@
 
 namespace hs {
 
-constexpr int kTcConsumers = 8;       // every warp consumes; warp 0 also issues the copies
+constexpr int kTcConsumers = 8;       // every warp consumes; whichever finishes a tile last refills its stage
 constexpr int kTcThreads = kTcConsumers * 32;
 constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence, in eighths of a tile (measured: 10-20 are alike)
 constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory
