@@ -3,11 +3,12 @@
 // One CTA = two 128-row query tiles of one head (256 rows) sharing every K/V tile.  Roles (10 warps):
 //   warp 8  loader: TMA tensor loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the two Q tiles
 //           once and of K/V tiles of 128 keys into a 2-stage shared-memory ring; completion on mbarriers
-//   warp 9  MMA issuer: one elected thread issues, per query tile x and key tile j,
+//   warp 9  MMA issuer: the warp walks a fixed schedule with one elected lane issuing, per query tile x and key tile j,
 //             S_j = Q_x . K_j^T    (both operands K-major in shared memory, accumulator 128 x 128 fp32 in TMEM)
 //             O_x += P_j . V_j     (P_j read from TMEM as bf16, V_j MN-major in shared memory)
-//           and tcgen05.commit to the mbarriers that hand results over; a polling scheduler issues whichever
-//           tile's next operation is ready, so one tile's MMAs run under the other tile's softmax
+//           in the order P.V^0_j, S^0_{j+1}, P.V^1_j, S^1_{j+1} (no wait between a P.V and the S that overwrites its P: MMAs
+//           execute in issue order), and tcgen05.commit to the mbarriers that hand results over; one tile's MMAs run
+//           under the other tile's softmax
 //   warps 0-3 / 4-7  softmax of tile 0 / 1: thread = query row (TMEM lane).  Two passes of tcgen05.ld over the
 //           score row (maximum, then exp2 and P as bf16 pairs written back over the scores with tcgen05.st); the
 //           output accumulator in TMEM is rescaled only when a row maximum grew by more than 2^8 (the final
@@ -465,8 +466,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 //   The two groups share a row's reference maximum through shared memory: a group publishes it (and rescales O if it
 //   grew by more than 2^8) right after its maximum pass, the other group's next tile starts from there; each group keeps
 //   its own partial row sum with the reference it was last brought to, and the two are combined at the end.
-//   Per key tile: S = Q.K^T is 16 MMAs 128x64x16 (operands in shared memory), O += P.V is 4 MMAs 128x256x16 (P from TMEM,
-//   V MN-major: its four 64-column boxes are 8 KB apart).
+//   S = Q.K^T is issued per pair of key tiles: 16 MMAs 128x128x16 on K ring stages of [128 keys][128 columns of d] (the Q
+//   slice is read from shared memory once per 128 keys); O += P.V per key tile: 4 MMAs 128x256x16 (P from TMEM, V
+//   MN-major: its four 64-column boxes are 8 KB apart).
 #ifdef HS_W5_PROF
 __device__ unsigned long long g_w5_prof[8];
 #define W5_T(var) const long long var = clock64()
