@@ -87,6 +87,7 @@ struct Slab {
         for (int i = 0; i < 4; ++i) {
             if (p[i]) g_free(p[i]);
             p[i] = nullptr;
+            bytes[i] = 0;
         }
         tokens = 0;
     }
@@ -403,6 +404,70 @@ int64_t hs_cache_memory_usage(const hs_cache *cache) {
         return static_cast<int64_t>(per * cache->blocks.size());
     }
     return static_cast<int64_t>(cache->slab.total());
+}
+
+// ---- CPU offload / restore (LayerKVCache::to_device, kv_cache.rs:1838-1858) ----
+// The reference moves full-precision K/V to the other device and does nothing for quantised (already on the host
+// there) and paged storage ("use block pool eviction instead").  Here every kind lives in HBM, so every kind can be
+// parked in host memory: the used rows go out as [K data][V data][K scales][V scales], the device storage (or the
+// pages) is released, and restore brings the same bytes back - codes and scales are never re-quantised.
+int64_t hs_cache_offload_bytes(const hs_cache *cache) {
+    if (!cache) return 0;
+    return static_cast<int64_t>(2 * (cache->geo.row_bytes() + cache->geo.scale_row_bytes())) * cache->seq_pos;
+}
+
+// copies `n` token rows of all four arrays between the cache's storage and a packed host image
+static int32_t copy_rows(hs_cache *cache, unsigned char *host, int n, bool to_host, cudaStream_t s, const char *who) {
+    const size_t row[4] = {cache->geo.row_bytes(), cache->geo.row_bytes(), cache->geo.scale_row_bytes(), cache->geo.scale_row_bytes()};
+    const int pt = cache->pool ? cache->pool->page_tokens : std::max(cache->capacity, 1);
+    std::vector<void *> rows[4];
+    cache->page_rows(pt, rows);
+    size_t off = 0;
+    for (int a = 0; a < 4; ++a) {
+        if (row[a] == 0) continue;
+        for (int t0 = 0, page = 0; t0 < n; t0 += pt, ++page) {
+            const size_t bytes = row[a] * static_cast<size_t>(std::min(pt, n - t0));
+            unsigned char *dev = static_cast<unsigned char *>(rows[a][page]);
+            cudaError_t e = to_host ? cudaMemcpyAsync(host + off, dev, bytes, cudaMemcpyDeviceToHost, s)
+                                    : cudaMemcpyAsync(dev, host + off, bytes, cudaMemcpyHostToDevice, s);
+            if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "%s: %s", who, cudaGetErrorString(e));
+            off += bytes;
+        }
+    }
+    cudaError_t e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "%s: %s", who, cudaGetErrorString(e));
+    return HS_OK;
+}
+
+int32_t hs_cache_offload(hs_cache *cache, void *host_buf, int64_t host_bytes, hs_stream_t stream) {
+    if (!cache || (!host_buf && cache->seq_pos > 0)) return fail(HS_ERR_ARG, "hs_cache_offload: bad arguments");
+    if (host_bytes < hs_cache_offload_bytes(cache))
+        return fail(HS_ERR_ARG, "hs_cache_offload: host buffer of %lld bytes, %lld needed", static_cast<long long>(host_bytes),
+                    static_cast<long long>(hs_cache_offload_bytes(cache)));
+    if (cache->seq_pos > 0)
+        if (int32_t st = copy_rows(cache, static_cast<unsigned char *>(host_buf), cache->seq_pos, true, as_stream(stream), "hs_cache_offload")) return st;
+    cache->seq_pos = 0;
+    cache->release_pages(0);
+    cache->slab.release();
+    if (!cache->pool) cache->capacity = 0;
+    return HS_OK;
+}
+
+int32_t hs_cache_restore(hs_cache *cache, const void *host_buf, int64_t host_bytes, int32_t n_tokens, hs_stream_t stream) {
+    if (!cache || n_tokens < 0 || (!host_buf && n_tokens > 0)) return fail(HS_ERR_ARG, "hs_cache_restore: bad arguments");
+    if (cache->seq_pos != 0) return fail(HS_ERR_ARG, "hs_cache_restore: the cache holds %d tokens; clear it first", cache->seq_pos);
+    if (n_tokens > cache->max_seq_len)
+        return fail(HS_ERR_CACHE_OVERFLOW, "hs_cache_restore: %d tokens exceed max_seq_len %d", n_tokens, cache->max_seq_len);
+    const int64_t need = static_cast<int64_t>(2 * (cache->geo.row_bytes() + cache->geo.scale_row_bytes())) * n_tokens;
+    if (host_bytes < need)
+        return fail(HS_ERR_ARG, "hs_cache_restore: host image of %lld bytes, %lld needed", static_cast<long long>(host_bytes), static_cast<long long>(need));
+    if (n_tokens == 0) return HS_OK;
+    if (int32_t st = cache->reserve(n_tokens)) return st;
+    if (int32_t st = copy_rows(cache, const_cast<unsigned char *>(static_cast<const unsigned char *>(host_buf)), n_tokens, false, as_stream(stream),
+                               "hs_cache_restore"))
+        return st;
+    cache->seq_pos = n_tokens;
+    return HS_OK;
 }
 
 int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out) {

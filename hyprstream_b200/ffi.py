@@ -84,6 +84,9 @@ _SIGS = {
     "hs_cache_capacity": (c_int32, [c_void_p]),
     "hs_cache_num_pages": (c_int32, [c_void_p]),
     "hs_cache_memory_usage": (c_int64, [c_void_p]),
+    "hs_cache_offload_bytes": (c_int64, [c_void_p]),
+    "hs_cache_offload": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "hs_cache_restore": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "hs_view_create": (c_int32, [POINTER(c_void_p), c_int32, POINTER(c_void_p)]),
     "hs_view_get": (c_void_p, [c_void_p]),
     "hs_view_destroy": (None, [c_void_p]),

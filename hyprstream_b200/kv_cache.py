@@ -152,6 +152,30 @@ class LayerKVCache:
         """Bytes held (cf. QuantizedTensor::memory_usage, kv_cache.rs:960-962)."""
         return lib.hs_cache_memory_usage(self._h)
 
+    def to_device(self, device) -> None:
+        """kv_cache.rs:1838-1858 `to_device` (CPU offload / restore).  `cpu` parks the used rows - codes and scales as
+        they are, or bf16 values - in pinned host memory and releases the device storage (pages go back to the pool);
+        the cache's own device brings them back byte for byte.  Works for every storage kind (the reference moves
+        full-precision tensors only)."""
+        device = torch.device(device)
+        with torch.cuda.device(self.device):
+            if device.type == "cpu":
+                if getattr(self, "_host_image", None) is not None:
+                    return
+                n = self.seq_pos
+                nbytes = lib.hs_cache_offload_bytes(self._h)
+                image = torch.empty(max(nbytes, 1), dtype=torch.uint8).pin_memory()
+                _check(lib.hs_cache_offload(self._h, image.data_ptr(), nbytes, _stream()))
+                self._host_image = (image, nbytes, n)
+            else:
+                if device != self.device and device.index is not None and device.index != self.device.index:
+                    raise ValueError("a cache is restored to the device it was created on")
+                if getattr(self, "_host_image", None) is None:
+                    return
+                image, nbytes, n = self._host_image
+                _check(lib.hs_cache_restore(self._h, image.data_ptr(), nbytes, n, _stream()))
+                self._host_image = None
+
     def __del__(self):
         if getattr(self, "_h", None):
             lib.hs_cache_destroy(self._h)  # pages go back to the pool on drop (kv_cache.rs:1889-1898)

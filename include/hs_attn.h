@@ -301,6 +301,15 @@ int32_t hs_cache_set_seq_pos(hs_cache *cache, int32_t n_tokens); /* after writin
 int32_t hs_cache_capacity(const hs_cache *cache);
 int32_t hs_cache_num_pages(const hs_cache *cache);
 int64_t hs_cache_memory_usage(const hs_cache *cache);
+/* CPU offload / restore (LayerKVCache::to_device, kv_cache.rs:1838-1858; there a no-op for quantised and paged
+ * storage, here available for every kind).  hs_cache_offload copies the seq_pos used token rows - K data, V data,
+ * K scales, V scales, in that order, hs_cache_offload_bytes() bytes - into the caller's host buffer (pinned memory
+ * makes the copies asynchronous up to the call's final synchronise), then releases the device storage or returns
+ * the pages to the pool and leaves the cache empty.  hs_cache_restore refills an empty cache from such an image
+ * (n_tokens = the seq_pos it was taken at); codes and scales come back byte for byte. */
+int64_t hs_cache_offload_bytes(const hs_cache *cache);
+int32_t hs_cache_offload(hs_cache *cache, void *host_buf, int64_t host_bytes, hs_stream_t stream);
+int32_t hs_cache_restore(hs_cache *cache, const void *host_buf, int64_t host_bytes, int32_t n_tokens, hs_stream_t stream);
 /* One hs_kv_view over the caches of a batch (one sequence each); the handle owns the device pointer tables. */
 int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out);
 const hs_kv_view *hs_view_get(const hs_view *view);

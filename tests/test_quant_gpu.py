@@ -140,6 +140,57 @@ def test_kv_write_and_get_match_flat_quantiser(cuda, kind, kn, paged):
     no_device_error()
 
 
+@pytest.mark.parametrize("kind,kn", [(qr.INT8, "int8"), (qr.NF4, "nf4"), (0, "bf16")])
+@pytest.mark.parametrize("paged", [False, True])
+def test_cache_offload_restore_round_trip(cuda, kind, kn, paged):
+    """LayerKVCache.to_device(cpu) / to_device(cuda) (kv_cache.rs:1838-1858): the used rows are parked in host memory,
+    the device storage (or the pages) is released, and the restored cache returns the same values bit for bit,
+    decodes to the same output and accepts further appends."""
+    from hyprstream_b200 import kv_cache as kc
+    from hyprstream_b200 import ops
+
+    torch.manual_seed(7)
+    hq, hkv, d, n = 32, 8, 128, 83
+    pool = None
+    if paged:
+        pool = kc.BlockPool(8, hkv, d, cuda, kind=kind, page_tokens=32)
+        cache = kc.LayerKVCache.new_paged(200, pool, owner="a")
+    else:
+        cache = kc.LayerKVCache(4096, kc.KVQuantType(kind), hkv, d, cuda)
+    k = torch.randn(1, n + 1, hkv, d).bfloat16().to(cuda)
+    v = torch.randn(1, n + 1, hkv, d).bfloat16().to(cuda)
+    cache.update(k[:, :n], v[:, :n], 0)
+    k0, v0 = cache.get()
+    q = torch.randn(1, hq, d).bfloat16().to(cuda)
+    lens = torch.tensor([n], dtype=torch.int32, device=cuda)
+    view, keep = kc.make_view([cache])
+    out0 = ops.decode_attention(q, view, lens).clone()
+    del view, keep
+    used = cache.memory_usage()
+    assert used > 0
+
+    cache.to_device("cpu")
+    assert cache.seq_pos == 0 and cache.memory_usage() == 0
+    if paged:
+        assert pool.num_free() == 8  # the pages went back to the pool
+    with pytest.raises(ValueError):
+        cache.get()  # "Cache is empty", like the reference's get() on an empty cache
+    cache.to_device("cpu")  # a second offload is a no-op
+
+    cache.to_device(cuda)
+    assert cache.seq_pos == n
+    k1, v1 = cache.get()
+    assert torch.equal(k1, k0) and torch.equal(v1, v0)
+    view, keep = kc.make_view([cache])
+    out1 = ops.decode_attention(q, view, lens)
+    assert torch.equal(out1, out0)
+    del view, keep
+    cache.update(k[:, n:], v[:, n:], n)  # the restored cache keeps growing
+    k2, _ = cache.get()
+    assert torch.equal(k2[:, :n], k0) and k2.shape[1] == n + 1
+    no_device_error()
+
+
 def test_kv_write_fused_rope_equals_rope_then_quantise(cuda):
     from hyprstream_b200 import kv_cache as kc
     from hyprstream_b200 import ops
