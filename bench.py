@@ -285,14 +285,18 @@ def main():
     kernel_bytes = sum(l + 1 for l in lens) * token_bytes(block, sf16) + BATCH * HQ * D * 2  # cache + q; partials excluded
 
     # ---- end to end through the public API with host buffers ----------------------------------
-    q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+    # the step's inputs (q, new K, new V) sit back to back in one pinned host buffer and travel in one copy
+    sizes = [q.numel(), k_new.numel(), v_new.numel()]
+    host_in = torch.empty(sum(sizes), dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty(sum(sizes), dtype=torch.bfloat16, device=dev)
+    q_h, k_h, v_h = (h.view_as(t) for h, t in zip(host_in.split(sizes), (q, k_new, v_new)))
+    for h, t in zip((q_h, k_h, v_h), (q, k_new, v_new)):
+        h.copy_(t)
+    q_d, k_d, v_d = (d_.view_as(t) for d_, t in zip(dev_in.split(sizes), (q, k_new, v_new)))
     out_h = torch.empty_like(q_h).pin_memory()
-    q_d, k_d, v_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
 
     def e2e_step():
-        q_d.copy_(q_h, non_blocking=True)
-        k_d.copy_(k_h, non_blocking=True)
-        v_d.copy_(v_h, non_blocking=True)
+        dev_in.copy_(host_in, non_blocking=True)
         ops.kv_quantize_write(view, k_d, v_d, dst_pos)
         ops.decode_attention(q_d, view, seq_lens, out=out, workspace=ws)
         out_h.copy_(out, non_blocking=True)

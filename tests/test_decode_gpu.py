@@ -201,6 +201,51 @@ def test_shards_merge_to_unsplit(cuda):
     no_device_error()
 
 
+@pytest.mark.parametrize("kind,block,sdt,hq,hkv,d", [(1, 128, 1, 32, 8, 128), (2, 64, 0, 32, 8, 128), (1, 64, 0, 16, 2, 256)])
+def test_long_ranges_many_tiles_per_cta(cuda, kind, block, sdt, hq, hkv, d):
+    """Half a million cached tokens: every CTA of the tensor-core kernel walks about a hundred tiles, so the tile
+    addresses are worked out in several batches and their shared-memory slots are reused, ring stages are refilled
+    dozens of times by whichever warp finishes last, and sequences are cut across many CTAs.  Checked against an fp32
+    recomputation over the dequantised cache (plain torch ops on the GPU), relative to the size of the outputs, and
+    paged storage against contiguous storage bit for bit."""
+    from hyprstream_b200 import kv_cache as kc
+
+    lens = [120000, 90001, 131072, 140000]
+    if d == 256:
+        lens = [2 * l for l in lens]  # 32-token tiles at head_dim 256
+    g = torch.Generator(device=cuda).manual_seed(11)
+    pt = 256
+    pool = kc.BlockPool(sum((l + pt - 1) // pt for l in lens) + 1, hkv, d, cuda, kind=kind, block=block, scale_dtype=sdt, page_tokens=pt)
+    flat, paged = [], []
+    torch.manual_seed(12)
+    q = (torch.randn(len(lens), hq, d) * 3.0).bfloat16().to(cuda)  # peaked softmax: outputs of order 0.1 - 1, not averages near 0
+    refs = []
+    for i, l in enumerate(lens):
+        k = torch.randn(1, l, hkv, d, device=cuda, generator=g).bfloat16()
+        v = torch.randn(1, l, hkv, d, device=cuda, generator=g).bfloat16()
+        c = kc.LayerKVCache(1 << 20, kc.KVQuantType(kind), hkv, d, cuda, block=block, scale_dtype=sdt)
+        c.update(k, v, 0)
+        p = kc.LayerKVCache.new_paged(1 << 20, pool, owner=i)
+        p.update(k, v, 0)
+        flat.append(c); paged.append(p)
+        kd, vd = c.get()  # what the reference's get() hands to attention: the dequantised history
+        kf = kd[0].float().repeat_interleave(hq // hkv, dim=1)  # [L, Hq, D]
+        vf = vd[0].float().repeat_interleave(hq // hkv, dim=1)
+        scores = torch.einsum("hd,lhd->hl", q[i].float(), kf) / math.sqrt(d)
+        refs.append(torch.einsum("hl,lhd->hd", torch.softmax(scores, dim=-1), vf))
+        del k, v, kd, vd, kf, vf, scores
+    ref = torch.stack(refs)
+    out = run_decode(cuda, flat, q, lens)
+    diff = (out.float() - ref).abs()
+    assert torch.isfinite(out.float()).all()
+    assert ref.abs().max().item() > 0.2, "the case must have outputs large enough for the bound to mean something"
+    assert diff.max().item() <= 2e-2 and diff.mean().item() <= 2e-3, (diff.max().item(), diff.mean().item())
+    assert diff.max().item() <= 0.03 * ref.abs().max().item(), (diff.max().item(), ref.abs().max().item())
+    out_paged = run_decode(cuda, paged, q, lens)
+    assert torch.equal(out_paged, out)
+    no_device_error()
+
+
 def test_config1_full_size(cuda):
     """BASELINE config 1: B=1, 32 q / 8 kv heads, d=128, L=4096 bf16 cache, RoPE base 500000, vs the oracle."""
     from hyprstream_b200 import kv_cache as kc
