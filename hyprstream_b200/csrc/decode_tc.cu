@@ -33,7 +33,7 @@ namespace hs {
 constexpr int kTcConsumers = 8;       // every warp consumes; whichever finishes a tile last refills its stage
 constexpr int kTcThreads = kTcConsumers * 32;
 constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence, in eighths of a tile (measured: 10-20 are alike)
-constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory
+constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory (half as many for the head_dim 256 shape)
 constexpr long long kTcWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -146,15 +146,18 @@ struct TcLayout {
     static constexpr int kStage = (kVsOff + kTile * kSRow + 127) / 128 * 128;
     static constexpr int kBarOff = kStages * kStage;
     static constexpr int kXBarOff = kBarOff + 2 * kStages * 8 + 16;    // 4 mbarriers: score exchange of a warp pair (WIDE)
-    static constexpr int kPrefOff = kXBarOff + 32;                     // int tile-count prefix [kTcMaxSeqs + 1]
-    static constexpr int kLenOff = kPrefOff + (kTcMaxSeqs + 4) * 4;    // int clamped lengths [kTcMaxSeqs]
-    static constexpr int kDescOff = kLenOff + kTcMaxSeqs * 4;          // uint64 [64 tiles][4 tables]: source addresses of the next tiles
+    static constexpr int kMaxSeqs = WIDE ? kTcMaxSeqs / 2 : kTcMaxSeqs;  // (the head_dim 256 shape also holds the exchange buffers)
+    static constexpr int kPrefOff = kXBarOff + 32;                     // int tile-count prefix [kMaxSeqs + 1]
+    static constexpr int kLenOff = kPrefOff + (kMaxSeqs + 4) * 4;      // int clamped lengths [kMaxSeqs]
+    static constexpr int kDescOff = kLenOff + kMaxSeqs * 4;            // uint64 [64 tiles][4 tables]: source addresses of the next tiles
     static constexpr int kXOff = (kDescOff + 64 * 4 * 8 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
     static constexpr int kLutOff = kXOff + (WIDE ? 4 * 2 * 2 * 512 : 0);        // uint32 [256][32] (4-bit kinds only)
     static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
     static constexpr uint32_t kTxBytes = 2u * kTile * kRow + 2u * kTile * kSRow;
     static_assert(kDescOff % 16 == 0, "tile addresses are stored 16 bytes at a time");
-    static_assert(WIDE || 2 * (kTotal + 1024) <= 228 * 1024, "two CTAs per SM");
+    // two CTAs per SM (228 KB, 1 KB reserved per CTA, 128 B of static shared memory) for every layout but the head_dim 256
+    // shape with block 64 and f32 scales, which runs one CTA per SM
+    static_assert((WIDE && BPR == 2 && !SF16) || 2 * (kTotal + 1024 + 128) <= 228 * 1024, "two CTAs per SM");
 };
 
 // Outputs of the merge that runs inside the kernel after a grid-wide barrier (cooperative launch only).
@@ -162,9 +165,12 @@ struct TcMergeArgs {
     uint16_t *out;        // bf16 [n_seqs, Hq, 128] or NULL
     const uint16_t *gate; // optional
     float *o_shard, *lse_shard;  // optional fp32 shard outputs
+    int counter;          // which grid-barrier counter the launch uses: one per grid size (CTAs per SM - 1)
 };
 
-__device__ unsigned long long g_tc_barrier;  // arrivals of all launches so far (see the grid barrier in the kernel)
+// Arrivals of all launches so far (see the grid barrier in the kernel), one counter per grid size: a launch's CTAs
+// find their target from their ticket and the grid size, so every launch that shares a counter must have the same one.
+__device__ unsigned long long g_tc_barrier[2];
 
 #ifdef HS_TC_TIMING  // diagnostic build only: per-CTA timestamps (ns) written to a harness-owned buffer
 __constant__ unsigned long long *g_tc_timing;
@@ -667,9 +673,10 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     const bool has_item = static_cast<int>(blockIdx.x) < n_seqs * groups;
     if (has_item) item_parts(blockIdx.x, r, h0, c_lo, np);
 
-    // All CTAs are co-resident (cooperative launch).  g_tc_barrier only ever counts up: a CTA's ticket tells it which
-    // multiple of the grid size completes its launch (every launch of this kernel family uses the same grid size and every
-    // CTA, even one whose waits ran out, takes exactly one ticket).  The wait is bounded.
+    // All CTAs are co-resident (cooperative launch).  The counter only ever counts up: a CTA's ticket tells it which
+    // multiple of the grid size completes its launch (every launch that uses this counter has the same grid size - one
+    // counter for one CTA per SM, one for two - and every CTA, even one whose waits ran out, takes exactly one ticket).
+    // The wait is bounded.
     __shared__ int s_bar_ok;
     __syncthreads();
     HS_TC_STAMP(10);
@@ -679,14 +686,14 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         unsigned long long ticket;
         // release: this CTA's partials are visible device-wide before it is counted; acquire: the CTA that arrives last sees
         // everyone else's
-        asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(&g_tc_barrier) : "memory");
+        asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(&g_tc_barrier[mg.counter]) : "memory");
         const unsigned long long target = (ticket / n + 1ULL) * n;
         int good = 1;
         if (ticket + 1ULL != target) {
             const long long t0b = clock64();
             while (true) {
                 unsigned long long seen;
-                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(&g_tc_barrier) : "memory");
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(&g_tc_barrier[mg.counter]) : "memory");
                 if (seen >= target) break;
                 if (clock64() - t0b > kTcWaitCycles) { good = 0; break; }
                 __nanosleep(32);
@@ -765,11 +772,12 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 
 template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
 static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads, float kmul,
-                         float *o_part, float *lse_part, int *err, int n_ctas, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
+                         float *o_part, float *lse_part, int *err, int *n_ctas_io, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
     using LT = TcLayout<FOURBIT, BPR, SF16, WIDE>;
     auto kern = decode_int8_tc_kernel<FOURBIT, BPR, SF16, WIDE>;
     static bool configured = false;  // per instantiation
     static bool coop_ok = true;      // cleared when a cooperative launch is refused
+    static int ctas_per_sm = 2;      // 1 for the layouts whose shared memory does not fit twice on an SM
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LT::kTotal);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode: %s", cudaGetErrorString(e));
@@ -777,11 +785,16 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kTcThreads, LT::kTotal);
-        coop_ok = coop != 0 && per_sm * sm_count() >= n_ctas;
+        ctas_per_sm = per_sm >= 2 ? 2 : 1;
+        coop_ok = coop != 0 && per_sm >= 1;
         configured = true;
     }
     *fused_out = 0;
     if (!coop_ok) return HS_OK;
+    const int n_ctas = ctas_per_sm * sm_count();  // never more than the caller sized the partial slots for (two per SM)
+    if (n_ctas > *n_ctas_io) return HS_OK;
+    *n_ctas_io = n_ctas;
+    mg.counter = ctas_per_sm - 1;
     ViewDev vv = v;
     void *args[] = {&vv, &q, &seq_lens, &n_seqs, &n_q_heads, &kmul, &o_part, &lse_part, &err, &mg};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
@@ -805,7 +818,7 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     // covered shapes: 8 kv heads x 128 with 4 query heads each, and 2 kv heads x 256 with 8 query heads each
     const bool wide = v.head_dim == 256 && v.n_kv_heads == 2 && n_q_heads == 16;
     if (v.kind == HS_KV_BF16 || !(wide || (v.head_dim == 128 && v.n_kv_heads == 8 && n_q_heads == 32))) return HS_OK;
-    if (v.page_tokens % 32 != 0 || n_seqs > kTcMaxSeqs) return HS_OK;
+    if (v.page_tokens % 32 != 0 || n_seqs > (wide ? kTcMaxSeqs / 2 : kTcMaxSeqs)) return HS_OK;
     // the merge writes 4-byte pairs
     if ((out && !aligned(out, 4)) || (gate && !aligned(gate, 4)) || (o_shard && !aligned(o_shard, 8))) return HS_OK;
     const bool four = v.kind != HS_KV_INT8;
@@ -813,11 +826,11 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     if (bpr != 1 && bpr != 2) return HS_OK;
     if (four && (bpr != 2 || wide)) return HS_OK;  // 4-bit caches: the reference's block of 64, Llama shape
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
-    const int n_ctas = 2 * sm_count();
+    int n_ctas = 2 * sm_count();  // upper bound; the launch settles on one or two CTAs per SM
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
-    TcMergeArgs mg{out, gate, o_shard, lse_shard};
+    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0};
     int32_t st;
-#define HS_TC_LAUNCH(F, B, S, W) launch_tc<F, B, S, W>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, n_ctas, mg, s, merged_out)
+#define HS_TC_LAUNCH(F, B, S, W) launch_tc<F, B, S, W>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, &n_ctas, mg, s, merged_out)
     if (wide) {
         if (bpr == 2 && !sf16) st = HS_TC_LAUNCH(false, 2, false, true);
         else if (bpr == 2) st = HS_TC_LAUNCH(false, 2, true, true);

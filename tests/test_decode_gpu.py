@@ -132,7 +132,7 @@ def test_ragged_batch_equals_serial_and_oracle(cuda, kind, block, sdt):
     no_device_error()
 
 
-@pytest.mark.parametrize("block,sdt,paged", [(128, 1, False), (128, 1, True), (64, 1, False), (128, 0, False)])
+@pytest.mark.parametrize("block,sdt,paged", [(128, 1, False), (128, 1, True), (64, 1, False), (128, 0, False), (64, 0, False)])
 def test_qwen_shape_ragged_gated_decode(cuda, block, sdt, paged):
     """Qwen3.5 full-attention decode shape (16 q / 2 kv heads, head_dim 256, int8 cache, output gate,
     qwen3_5.rs:992-1059) on a ragged batch: the oracle's gated core and the fp32 recomputation, row by row, and one
@@ -144,7 +144,12 @@ def test_qwen_shape_ragged_gated_decode(cuda, block, sdt, paged):
     torch.manual_seed(8)
     q = torch.randn(len(lens), hq, d).bfloat16()
     gate = torch.randn(len(lens), hq, d).bfloat16()
+    from hyprstream_b200 import ffi
+    n0 = ffi.launch_count()
     out = run_decode(cuda, caches, q, lens, gate=gate)
+    # every layout of this shape is served by the tensor-core kernel, which merges its own partials: one launch (the
+    # reference layout - block 64, f32 absmax - fits only one CTA per SM and runs with a grid of that size)
+    assert ffi.launch_count() - n0 == 1
     plain = run_decode(cuda, caches, q, lens)
     for r, l in enumerate(lens):
         oracle = ar.qwen_gated_attention_core(q[r].reshape(1, 1, hq, d), gate[r].reshape(1, 1, hq, d), ks[r], vs[r], hq).reshape(hq, d)
