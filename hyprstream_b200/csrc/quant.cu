@@ -27,10 +27,9 @@ __device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(
 // memory, so the rare path costs two loads and not four divisions for every lane of the warp).
 __device__ __forceinline__ int index_int8(float y, const float *smid) {
     float t = __fmul_rn(y, 127.0f);
-    int c = __float2int_rn(t) + 127;
-    c = max(0, min(255, c));
-    float fr = t - floorf(t);
-    if (fabsf(fr - 0.5f) < 1e-3f) {
+    const float r = rintf(t);
+    int c = max(0, min(255, static_cast<int>(r) + 127));
+    if (fabsf(t - r) > 0.499f) {  // within 1e-3 of a half-integer
         if (c > 0 && !(y > smid[c - 1])) c--;
         else if (c < 255 && y > smid[c]) c++;
     }
@@ -250,15 +249,19 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
     void *const *scale_pages = is_v ? view.v_scale_pages : view.k_scale_pages;
     const int tpb = view.block / 8;
     const int bpr = D / view.block;  // blocks per (token, head) row
+    // head_dim and the block are powers of two (64, 128, 256), the number of kv heads usually is: shifts instead of divisions
+    const int cpr_shift = __ffs(static_cast<int>(cpr)) - 1, block_shift = __ffs(view.block) - 1;
+    const bool h_pow2 = (H & (H - 1)) == 0;
+    const int h_shift = __ffs(H) - 1;
 #pragma unroll 2
     for (int u = 0; u < kWriteUnroll; ++u) {
         const uint32_t chunk = (blockIdx.x * static_cast<uint32_t>(kWriteUnroll) + u) * static_cast<uint32_t>(kQThreads) + threadIdx.x;
         if (chunk - threadIdx.x >= total) break;  // (uniform over the block)
         const bool live = chunk < total;
         const uint32_t cc = live ? chunk : 0u;  // dead lanes still take part in the shuffles
-        const uint32_t row_in_seq = cc / cpr;   // (token, head)
-        const int d0 = static_cast<int>(cc - row_in_seq * cpr) * 8;
-        const int t = static_cast<int>(row_in_seq / static_cast<uint32_t>(H));
+        const uint32_t row_in_seq = cc >> cpr_shift;   // (token, head)
+        const int d0 = static_cast<int>(cc & (cpr - 1u)) * 8;
+        const int t = static_cast<int>(h_pow2 ? row_in_seq >> h_shift : row_in_seq / static_cast<uint32_t>(H));
         const int h = static_cast<int>(row_in_seq - static_cast<uint32_t>(t) * static_cast<uint32_t>(H));
         const int64_t row = static_cast<int64_t>(s) * n_tokens * H + row_in_seq;  // (seq, token, head)
         const int pos = base_pos + t;
@@ -286,7 +289,7 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
         if (!ok) continue;
         uint8_t *codes = reinterpret_cast<uint8_t *>(data_pages[pidx]);
         void *scales = scale_pages[pidx];
-        if ((d0 % view.block) == 0) store_scale(scales, in_page * bpr + d0 / view.block, view.scale_dtype, a);
+        if ((d0 & (view.block - 1)) == 0) store_scale(scales, in_page * bpr + (d0 >> block_shift), view.scale_dtype, a);
         const int64_t e0 = in_page * D + d0;
         store_codes8<QK>(codes, e0, e0 + 8, c, true);
     }
