@@ -17,7 +17,7 @@
 namespace hs {
 
 constexpr int kQThreads = 256;
-constexpr int kWriteUnroll = 8;  // 8-element chunks per thread of the quantise-on-write kernel
+constexpr int kWriteElems = 64;  // elements per thread of the quantise-on-write kernel (as 8- or 16-element chunks)
 
 __device__ __forceinline__ float code8(int i) { return __fdiv_rn(static_cast<float>(i) - 127.0f, 127.0f); }
 __device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(code8(j), code8(j + 1))); }
@@ -61,27 +61,31 @@ __device__ __forceinline__ float f16_sat_round(float a) {
 
 // Quantise the 8 values of this thread; `tpb` consecutive lanes (a power of two <= 32) share a block.
 // Returns the stored scale (already rounded in f16 mode); codes[] receives 8 indices.
-template <int KIND>
-__device__ __forceinline__ float quantize8(const float (&x)[8], int tpb, int scale_dtype, const float *smid,
-                                           int (&codes)[8]) {
+template <int KIND, int N>
+__device__ __forceinline__ float quantize_n(const float (&x)[N], int tpb, int scale_dtype, const float *smid,
+                                            int (&codes)[N]) {
     float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(x[i]));
     for (int o = 1; o < tpb; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float a = scale_dtype == HS_SCALE_F16 ? f16_sat_round(amax) : amax;
     if (a == 0.0f) {
         const int zc = KIND == HS_KV_INT8 ? 127 : (KIND == HS_KV_NF4 ? 7 : 0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) codes[i] = zc;
+        for (int i = 0; i < N; ++i) codes[i] = zc;
         return a;
     }
     float inv = __fdiv_rn(1.0f, a);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < N; ++i) {
         float y = __fmul_rn(x[i], inv);
         codes[i] = KIND == HS_KV_INT8 ? index_int8(y, smid) : index_4bit(y, smid);
     }
     return a;
+}
+template <int KIND>
+__device__ __forceinline__ float quantize8(const float (&x)[8], int tpb, int scale_dtype, const float *smid, int (&codes)[8]) {
+    return quantize_n<KIND, 8>(x, tpb, scale_dtype, smid, codes);
 }
 
 __device__ __forceinline__ void store_scale(void *p, int64_t idx, int scale_dtype, float a) {
@@ -226,7 +230,9 @@ __global__ void __launch_bounds__(kQThreads) rope_kernel(const uint16_t *__restr
 }
 
 // ---- quantise-on-write into a cache view ----------------------------------------------------------------
-template <int KIND>
+// E = elements per thread: 16 for long writes (prefill: bound by instruction issue, so the per-chunk costs are paid
+// half as often), 8 for short ones (a decode step's single token per sequence: latency matters, not throughput).
+template <int KIND, int E>
 __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const uint16_t *__restrict__ k_new,
                                                              const uint16_t *__restrict__ v_new, int n_seqs, int n_tokens,
                                                              const int32_t *__restrict__ dst_pos,
@@ -235,32 +241,33 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
     __shared__ float smid[256];
     fill_midpoints(KIND, smid);
     __syncthreads();
-    // grid: x = groups of kWriteUnroll * 256 8-element chunks of one sequence's new rows, y = 2 * sequence + (0: K, 1: V).
-    // The sequence and K/V come from the block index and the chunk index inside a sequence fits 32 bits, so the (token,
-    // head, chunk) split costs four 32-bit divisions per chunk; a thread handles kWriteUnroll chunks, which spreads the
-    // block's fixed costs (launch, midpoint table, barrier).
+    // grid: x = groups of kUnroll * 256 E-element chunks of one sequence's new rows, y = 2 * sequence + (0: K, 1: V).
+    // A thread owns E consecutive elements of a (token, head) row (16-byte loads; at E = 16 one 16-byte store of int8
+    // codes): the index split, the page division, the pointer loads, the IEEE division of the scale and the shuffles
+    // are paid once per chunk.  head_dim and the block are powers of two (64, 128, 256), the number of kv heads usually
+    // is: shifts instead of divisions.
     const bool is_v = (blockIdx.y & 1) != 0;
     const int s = static_cast<int>(blockIdx.y >> 1);
     const int D = view.head_dim, H = view.n_kv_heads;
-    const uint32_t cpr = static_cast<uint32_t>(D) / 8u;
+    constexpr int kUnroll = kWriteElems / E;
+    const uint32_t cpr = static_cast<uint32_t>(D) / static_cast<uint32_t>(E);
     const uint32_t total = static_cast<uint32_t>(n_tokens) * static_cast<uint32_t>(H) * cpr;
     const int base_pos = dst_pos ? dst_pos[s] : 0;
     void *const *data_pages = is_v ? view.v_pages : view.k_pages;
     void *const *scale_pages = is_v ? view.v_scale_pages : view.k_scale_pages;
-    const int tpb = view.block / 8;
+    const int tpb = view.block / E;
     const int bpr = D / view.block;  // blocks per (token, head) row
-    // head_dim and the block are powers of two (64, 128, 256), the number of kv heads usually is: shifts instead of divisions
     const int cpr_shift = __ffs(static_cast<int>(cpr)) - 1, block_shift = __ffs(view.block) - 1;
     const bool h_pow2 = (H & (H - 1)) == 0;
     const int h_shift = __ffs(H) - 1;
 #pragma unroll 2
-    for (int u = 0; u < kWriteUnroll; ++u) {
-        const uint32_t chunk = (blockIdx.x * static_cast<uint32_t>(kWriteUnroll) + u) * static_cast<uint32_t>(kQThreads) + threadIdx.x;
+    for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t chunk = (blockIdx.x * static_cast<uint32_t>(kUnroll) + u) * static_cast<uint32_t>(kQThreads) + threadIdx.x;
         if (chunk - threadIdx.x >= total) break;  // (uniform over the block)
         const bool live = chunk < total;
         const uint32_t cc = live ? chunk : 0u;  // dead lanes still take part in the shuffles
         const uint32_t row_in_seq = cc >> cpr_shift;   // (token, head)
-        const int d0 = static_cast<int>(cc & (cpr - 1u)) * 8;
+        const int d0 = static_cast<int>(cc & (cpr - 1u)) * E;
         const int t = static_cast<int>(h_pow2 ? row_in_seq >> h_shift : row_in_seq / static_cast<uint32_t>(H));
         const int h = static_cast<int>(row_in_seq - static_cast<uint32_t>(t) * static_cast<uint32_t>(H));
         const int64_t row = static_cast<int64_t>(s) * n_tokens * H + row_in_seq;  // (seq, token, head)
@@ -270,28 +277,52 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
         if (!is_v && sin != nullptr && (pos < 0 || pos >= n_positions)) ok = false;
         if (live && !ok) atomicExch(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
         const uint16_t *src = (is_v ? v_new : k_new) + row * D;
-        float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (ok) load_row8_rope(src, d0, is_v ? nullptr : sin, cos, pos, rotary_dim, x);
+        float x[E];
+#pragma unroll
+        for (int part = 0; part < E / 8; ++part) {
+            float p8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (ok) load_row8_rope(src, d0 + 8 * part, is_v ? nullptr : sin, cos, pos, rotary_dim, p8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[8 * part + i] = p8[i];
+        }
         const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + h;  // (token, head) row inside the page
         const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
         if (KIND == HS_KV_BF16) {
             if (ok) {
                 uint16_t *dst = reinterpret_cast<uint16_t *>(data_pages[pidx]) + in_page * D + d0;
-                uint4 w;
-                w.x = pack_bf16(x[0], x[1]); w.y = pack_bf16(x[2], x[3]); w.z = pack_bf16(x[4], x[5]); w.w = pack_bf16(x[6], x[7]);
-                *reinterpret_cast<uint4 *>(dst) = w;
+#pragma unroll
+                for (int part = 0; part < E / 8; ++part) {
+                    uint4 w;
+                    w.x = pack_bf16(x[8 * part], x[8 * part + 1]); w.y = pack_bf16(x[8 * part + 2], x[8 * part + 3]);
+                    w.z = pack_bf16(x[8 * part + 4], x[8 * part + 5]); w.w = pack_bf16(x[8 * part + 6], x[8 * part + 7]);
+                    reinterpret_cast<uint4 *>(dst)[part] = w;
+                }
             }
             continue;
         }
         constexpr int QK = KIND == HS_KV_BF16 ? HS_KV_INT8 : KIND;
-        int c[8];
-        float a = quantize8<QK>(x, tpb, view.scale_dtype, smid, c);
+        int c[E];
+        float a = quantize_n<QK, E>(x, tpb, view.scale_dtype, smid, c);
         if (!ok) continue;
         uint8_t *codes = reinterpret_cast<uint8_t *>(data_pages[pidx]);
         void *scales = scale_pages[pidx];
         if ((d0 & (view.block - 1)) == 0) store_scale(scales, in_page * bpr + (d0 >> block_shift), view.scale_dtype, a);
         const int64_t e0 = in_page * D + d0;
-        store_codes8<QK>(codes, e0, e0 + 8, c, true);
+        if constexpr (E == 8) {
+            store_codes8<QK>(codes, e0, e0 + 8, c, true);
+        } else if (QK == HS_KV_INT8) {
+            uint4 w;
+            w.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+            w.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+            w.z = c[8] | (c[9] << 8) | (c[10] << 16) | (c[11] << 24);
+            w.w = c[12] | (c[13] << 8) | (c[14] << 16) | (c[15] << 24);
+            *reinterpret_cast<uint4 *>(codes + e0) = w;
+        } else {  // the even element in the high nibble
+            uint2 w;
+            w.x = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8) | (((c[4] << 4) | c[5]) << 16) | (((c[6] << 4) | c[7]) << 24);
+            w.y = ((c[8] << 4) | c[9]) | (((c[10] << 4) | c[11]) << 8) | (((c[12] << 4) | c[13]) << 16) | (((c[14] << 4) | c[15]) << 24);
+            *reinterpret_cast<uint2 *>(codes + (e0 >> 1)) = w;
+        }
     }
 }
 
@@ -431,20 +462,24 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
             return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: rotary_dim must be a positive multiple of 16 <= head_dim");
     }
     ViewDev d = to_dev(view);
-    const int64_t chunks = static_cast<int64_t>(n_tokens) * d.n_kv_heads * (d.head_dim / 8);  // per sequence and per K / V
-    if (chunks > 0x7fffffffLL || n_seqs > 32767) return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: more than 2^31 chunks per sequence or 32767 sequences in one call");
-    dim3 grid(static_cast<unsigned>((chunks + kQThreads * kWriteUnroll - 1) / (kQThreads * kWriteUnroll)), 2u * static_cast<unsigned>(n_seqs));
+    const int64_t elems = static_cast<int64_t>(n_tokens) * d.n_kv_heads * d.head_dim;  // per sequence and per K / V
+    if (elems / 8 > 0x7fffffffLL || n_seqs > 32767) return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: more than 2^31 chunks per sequence or 32767 sequences in one call");
+    const bool wide = elems >= (1 << 16);  // long writes: 16 elements per thread
+    dim3 grid(static_cast<unsigned>((elems + static_cast<int64_t>(kQThreads) * kWriteElems - 1) / (static_cast<int64_t>(kQThreads) * kWriteElems)), 2u * static_cast<unsigned>(n_seqs));
     cudaStream_t s = as_stream(stream);
     int *err = device_error_word();
     if (!err) return fail(HS_ERR_DEVICE, "hs_kv_quantize_write: device error word unavailable");
     const uint16_t *k = reinterpret_cast<const uint16_t *>(k_new), *v = reinterpret_cast<const uint16_t *>(v_new);
     const uint16_t *sn = reinterpret_cast<const uint16_t *>(sin), *cs = reinterpret_cast<const uint16_t *>(cos);
+#define HS_KV_WRITE(K) do { if (wide) kv_write_kernel<K, 16><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); \
+                            else kv_write_kernel<K, 8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); } while (0)
     switch (view->kind) {
-        case HS_KV_BF16: kv_write_kernel<HS_KV_BF16><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
-        case HS_KV_INT8: kv_write_kernel<HS_KV_INT8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
-        case HS_KV_NF4: kv_write_kernel<HS_KV_NF4><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
-        default: kv_write_kernel<HS_KV_FP4><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); break;
+        case HS_KV_BF16: HS_KV_WRITE(HS_KV_BF16); break;
+        case HS_KV_INT8: HS_KV_WRITE(HS_KV_INT8); break;
+        case HS_KV_NF4: HS_KV_WRITE(HS_KV_NF4); break;
+        default: HS_KV_WRITE(HS_KV_FP4); break;
     }
+#undef HS_KV_WRITE
     return check_launch("hs_kv_quantize_write");
 }
 
