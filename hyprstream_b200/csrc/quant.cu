@@ -17,6 +17,9 @@
 namespace hs {
 
 constexpr int kQThreads = 256;
+#ifndef HS_KV_WRITE_WIDE
+#define HS_KV_WRITE_WIDE 16
+#endif
 constexpr int kWriteElems = 64;  // elements per thread of the quantise-on-write kernel (as 8- or 16-element chunks)
 
 __device__ __forceinline__ float code8(int i) { return __fdiv_rn(static_cast<float>(i) - 127.0f, 127.0f); }
@@ -310,18 +313,24 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
         const int64_t e0 = in_page * D + d0;
         if constexpr (E == 8) {
             store_codes8<QK>(codes, e0, e0 + 8, c, true);
-        } else if (QK == HS_KV_INT8) {
-            uint4 w;
-            w.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-            w.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
-            w.z = c[8] | (c[9] << 8) | (c[10] << 16) | (c[11] << 24);
-            w.w = c[12] | (c[13] << 8) | (c[14] << 16) | (c[15] << 24);
-            *reinterpret_cast<uint4 *>(codes + e0) = w;
-        } else {  // the even element in the high nibble
-            uint2 w;
-            w.x = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8) | (((c[4] << 4) | c[5]) << 16) | (((c[6] << 4) | c[7]) << 24);
-            w.y = ((c[8] << 4) | c[9]) | (((c[10] << 4) | c[11]) << 8) | (((c[12] << 4) | c[13]) << 16) | (((c[14] << 4) | c[15]) << 24);
-            *reinterpret_cast<uint2 *>(codes + (e0 >> 1)) = w;
+        } else {
+#pragma unroll
+            for (int part = 0; part < E / 16; ++part) {
+                const int *cp = c + 16 * part;
+                if (QK == HS_KV_INT8) {
+                    uint4 w;
+                    w.x = cp[0] | (cp[1] << 8) | (cp[2] << 16) | (cp[3] << 24);
+                    w.y = cp[4] | (cp[5] << 8) | (cp[6] << 16) | (cp[7] << 24);
+                    w.z = cp[8] | (cp[9] << 8) | (cp[10] << 16) | (cp[11] << 24);
+                    w.w = cp[12] | (cp[13] << 8) | (cp[14] << 16) | (cp[15] << 24);
+                    reinterpret_cast<uint4 *>(codes + e0)[part] = w;
+                } else {  // the even element in the high nibble
+                    uint2 w;
+                    w.x = ((cp[0] << 4) | cp[1]) | (((cp[2] << 4) | cp[3]) << 8) | (((cp[4] << 4) | cp[5]) << 16) | (((cp[6] << 4) | cp[7]) << 24);
+                    w.y = ((cp[8] << 4) | cp[9]) | (((cp[10] << 4) | cp[11]) << 8) | (((cp[12] << 4) | cp[13]) << 16) | (((cp[14] << 4) | cp[15]) << 24);
+                    reinterpret_cast<uint2 *>(codes + (e0 >> 1))[part] = w;
+                }
+            }
         }
     }
 }
@@ -471,7 +480,7 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
     if (!err) return fail(HS_ERR_DEVICE, "hs_kv_quantize_write: device error word unavailable");
     const uint16_t *k = reinterpret_cast<const uint16_t *>(k_new), *v = reinterpret_cast<const uint16_t *>(v_new);
     const uint16_t *sn = reinterpret_cast<const uint16_t *>(sin), *cs = reinterpret_cast<const uint16_t *>(cos);
-#define HS_KV_WRITE(K) do { if (wide) kv_write_kernel<K, 16><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); \
+#define HS_KV_WRITE(K) do { if (wide) kv_write_kernel<K, HS_KV_WRITE_WIDE><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); \
                             else kv_write_kernel<K, 8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); } while (0)
     switch (view->kind) {
         case HS_KV_BF16: HS_KV_WRITE(HS_KV_BF16); break;
