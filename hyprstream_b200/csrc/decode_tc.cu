@@ -170,15 +170,12 @@ struct TcMergeArgs {
 
 // Arrivals of all launches so far (see the grid barrier in the kernel), one counter per grid size: a launch's CTAs
 // find their target from their ticket and the grid size, so every launch that shares a counter must have the same one.
+// INVARIANT: the tickets of two launches on one device must not interleave, i.e. two launches of this kernel must not be
+// in flight on a device at the same time.  Launches on one stream are ordered by the stream.  Launches on different
+// streams (or from different host threads) of one device must be serialised by the caller; include/hs_attn.h says so
+// at hs_attn_decode.  Nothing in the library depends on "a full cooperative grid leaves no room for a second one".
+// If the rule is broken, the bounded wait turns it into HS_DEVERR_WAIT_TIMEOUT and an undefined result, not into a hang.
 __device__ unsigned long long g_tc_barrier[2];
-
-#ifdef HS_TC_TIMING  // diagnostic build only: per-CTA timestamps (ns) written to a harness-owned buffer
-__constant__ unsigned long long *g_tc_timing;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) :: "memory"); return t; }
-#define HS_TC_STAMP(slot) do { if (g_tc_timing && lane == 0 && (slot) < 16) g_tc_timing[(blockIdx.x * 20 + warp) * 16 + (slot)] = gtime(); } while (0)
-#else
-#define HS_TC_STAMP(slot) do {} while (0)
-#endif
 
 template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
 __global__ void __launch_bounds__(kTcThreads, 2)
@@ -197,7 +194,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cap = view.page_tokens * view.pages_per_seq;
 
-    HS_TC_STAMP(0);
     // ---- tile counts of all sequences (one coalesced pass), exclusive prefix by warp 0 ----
     bool over = false;
     for (int i = threadIdx.x; i < n_seqs; i += kTcThreads) {
@@ -359,13 +355,10 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     uint32_t c_par = 0;  // ring stage and barrier parity of tile `it`
     int pair_it = 0;  // tiles this warp pair has exchanged scores for (WIDE)
     (void)pair_it;
-    int seg_idx = 0;
-    (void)seg_idx;
     for (int r = r_first; r < n_seqs && s_pref[r] < t_end && ok; ++r) {
         const int base = s_pref[r];
         const int lo = max(t_begin, base), hi = min(t_end, s_pref[r + 1]);
         if (lo >= hi) continue;
-        HS_TC_STAMP(seg_idx < 2 ? 2 + 4 * seg_idx : 16);
         const int L = s_len[r];
 
         // ---- query fragments: fp16, d permuted so that one 16-byte K load feeds 4 k-steps; per-block sums ----
@@ -407,7 +400,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                     break;
                 }
         }
-        HS_TC_STAMP(seg_idx < 2 ? 3 + 4 * seg_idx : 16);
         // running softmax state of query head g (row layout of the q.K^T accumulators)
         float m = -INFINITY, l_part = 0.0f, ps_part[2] = {0.0f, 0.0f};
         // O^T accumulators: tile (b, mt): rows d = 64b + 8g + 4*(mt>>1) + 2*(mt&1) (+1 for regs 2,3), cols heads 2j, 2j+1
@@ -427,9 +419,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             const unsigned char *sKs = smem + stage * LT::kStage + LT::kKsOff;
             const unsigned char *sVs = smem + stage * LT::kStage + LT::kVsOff;
             const int tl0 = 16 * th;
-#ifdef HS_TC_DRAIN_ONLY  // diagnostic build only: consumers drain the ring without computing (measures the copy pipeline)
-            if (false)
-#endif
             {
                 // ---- S = q.(1024 + K)^T for 16 tokens (two n-tiles of 8), one accumulator per 64-wide d block ----
                 float sacc[2][2][4];
@@ -583,7 +572,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             if ((before & (kTcConsumers - 1)) == kTcConsumers - 1 && it + kTcStages < n_tiles_cta) issue_tile(it + kTcStages, stage);
         }
         if (!ok) break;
-        HS_TC_STAMP(seg_idx < 2 ? 4 + 4 * seg_idx : 16);
         // ---- partial of this (CTA, sequence) pair ----
         float l = l_part;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -622,10 +610,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         if (g < kTcG && j == 0 && half == 0)
             lse_part[slot * n_q_heads + kvh * kTcG + g] = l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        HS_TC_STAMP(seg_idx < 2 ? 5 + 4 * seg_idx : 16);
-        ++seg_idx;
     }
-    HS_TC_STAMP(1);
     if (!ok) {
         // a wait ran out: give the copies already in flight a bounded chance to land before the CTA's shared
         // memory is released, then report
@@ -679,7 +664,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     // The wait is bounded.
     __shared__ int s_bar_ok;
     __syncthreads();
-    HS_TC_STAMP(10);
     if (threadIdx.x == 0) {
         if (has_item && np > 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(min(kChunk, np)) * 2064u);
         const unsigned long long n = gridDim.x;
@@ -702,7 +686,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         s_bar_ok = good;
     }
     __syncthreads();
-    HS_TC_STAMP(11);
     if (!s_bar_ok) {
         if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
         return;
@@ -713,7 +696,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         if (!first_item) item_parts(item, r, h0, c_lo, np);
         const int hh = threadIdx.x / (kD / 2), d = (threadIdx.x % (kD / 2)) * 2;  // thread = (head, column pair)
         const int h0a = h0 & ~3, hl = h0 - h0a + hh;                            // log-sum-exps travel in aligned groups of 4 heads
-        HS_TC_STAMP(12);
         float M = -INFINITY, den = 0.0f;
         float2 num = make_float2(0.0f, 0.0f);
         for (int p0 = 0; p0 < np; p0 += kChunk) {
@@ -733,7 +715,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 return;
             }
             mphase ^= 1u;
-            HS_TC_STAMP(13);
             float Mc = M;
             for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hl]);
             if (Mc != -INFINITY) {
@@ -765,9 +746,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             }
             *reinterpret_cast<uint32_t *>(mg.out + row * kD + d) = pack_bf16(r0, r1);
         }
-        HS_TC_STAMP(14);
     }
-    HS_TC_STAMP(15);
 }
 
 template <bool FOURBIT, int BPR, bool SF16, bool WIDE>
@@ -775,22 +754,22 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
                          float *o_part, float *lse_part, int *err, int *n_ctas_io, TcMergeArgs mg, cudaStream_t s, int *fused_out) {
     using LT = TcLayout<FOURBIT, BPR, SF16, WIDE>;
     auto kern = decode_int8_tc_kernel<FOURBIT, BPR, SF16, WIDE>;
-    static bool configured = false;  // per instantiation
-    static bool coop_ok = true;      // cleared when a cooperative launch is refused
-    static int ctas_per_sm = 2;      // 1 for the layouts whose shared memory does not fit twice on an SM
-    if (!configured) {
+    // per instantiation and device: 0 = not configured, 1 / 2 = CTAs per SM of the cooperative grid, -1 = the device does not
+    // take this kernel as a cooperative launch (the generic kernel serves it)
+    static PerDeviceState config;
+    const int dev = current_device();
+    int ctas_per_sm = config.get(dev);
+    if (ctas_per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LT::kTotal);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode: %s", cudaGetErrorString(e));
-        int dev = 0, coop = 0, per_sm = 0;
-        cudaGetDevice(&dev);
+        int coop = 0, per_sm = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kTcThreads, LT::kTotal);
-        ctas_per_sm = per_sm >= 2 ? 2 : 1;
-        coop_ok = coop != 0 && per_sm >= 1;
-        configured = true;
+        ctas_per_sm = (coop != 0 && per_sm >= 1) ? (per_sm >= 2 ? 2 : 1) : -1;
+        config.set(dev, ctas_per_sm);
     }
     *fused_out = 0;
-    if (!coop_ok) return HS_OK;
+    if (ctas_per_sm < 0) return HS_OK;
     const int n_ctas = ctas_per_sm * sm_count();  // never more than the caller sized the partial slots for (two per SM)
     if (n_ctas > *n_ctas_io) return HS_OK;
     *n_ctas_io = n_ctas;
@@ -803,7 +782,7 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
         return HS_OK;
     }
     cudaGetLastError();  // refused (e.g. the device is shared and cannot hold the whole grid): the generic kernel takes over for good
-    coop_ok = false;
+    config.set(dev, -1);
     return HS_OK;
 }
 

@@ -414,11 +414,12 @@ int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, con
     if (!gc_make_map(&mq, q, n_seqs, n_tokens, n_k_heads) || !gc_make_map(&mk, k, n_seqs, n_tokens, n_k_heads) ||
         !gc_make_map(&mv, v, n_seqs, n_tokens, n_v_heads))
         return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: the driver refused the tensor maps (use hs_gdn_recurrent)");
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceState configured;
+    const int dev = current_device();
+    if (!configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(GcSmem) + 128));
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.set(dev, 1);
     }
     cudaStream_t s = as_stream(stream);
     dim3 grid(n_v_heads, n_seqs);

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -18,9 +19,23 @@ int32_t fail(int32_t code, const char *fmt, ...);
 int32_t check_device();             // HS_OK on compute capability 10.x, else HS_ERR_DEVICE
 int32_t check_launch(const char *what);  // cudaGetLastError -> status
 int sm_count();
-// Address (on the current device) of the error word that kernels set instead of faulting when they
-// meet an out-of-range index; hs_attn_take_device_error() reads and clears it.
+int current_device();  // ordinal of the current device, -1 if there is none
+// Address (on the current device) of the error words: word 0 holds the HS_DEVERR_* flags that kernels set instead of
+// faulting (hs_attn_take_device_error() reads and clears it); word 1 holds the id of the latest launch in which a bounded
+// wait ran out, so that the remaining CTAs of THAT launch can return at once (later launches carry another id and are
+// not affected by it).  The address is looked up once per device.
 int *device_error_word();
+uint32_t next_launch_id();  // never 0
+
+// Launch configuration is per device (cudaFuncSetAttribute, occupancy, whether cooperative launches are accepted): a
+// process that drives several GPUs configures each kernel once on each.  One int of state per device ordinal, 0 = not
+// configured yet.  Two threads may both configure a device; the calls are idempotent.
+constexpr int kMaxDevices = 64;
+struct PerDeviceState {
+    std::atomic<int> v[kMaxDevices];
+    int get(int dev) const { return dev >= 0 && dev < kMaxDevices ? v[dev].load(std::memory_order_acquire) : 0; }
+    void set(int dev, int x) { if (dev >= 0 && dev < kMaxDevices) v[dev].store(x, std::memory_order_release); }
+};
 
 static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 static inline cudaStream_t as_stream(hs_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }

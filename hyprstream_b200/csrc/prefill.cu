@@ -209,11 +209,12 @@ static int32_t launch_prefill(const uint16_t *q, const uint16_t *k, const uint16
                               int n_seqs, int q_len, int kv_len, int hq, int hkv, float scale_log2, cudaStream_t s) {
     constexpr int smem = kPfM * D * 2 + 4 * BN * D * 2;
     auto kern = prefill_mma_kernel<D, BN>;
-    static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
+    static PerDeviceState configured;  // per instantiation and device
+    const int dev = current_device();
+    if (smem > 48 * 1024 && !configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.set(dev, 1);
     }
     dim3 grid((q_len + kPfM - 1) / kPfM, hq, n_seqs);
     kern<<<grid, kPfThreads, smem, s>>>(q, k, v, out, gate, q_len, kv_len, hq, hkv, scale_log2);

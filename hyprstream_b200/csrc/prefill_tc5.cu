@@ -167,7 +167,7 @@ __device__ __forceinline__ float t5_ex2(float x) {
 __global__ void __launch_bounds__(kT5Threads, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
-                   int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err) {
+                   int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) T5Bars bars;
     __shared__ uint32_t s_tmem;
@@ -193,7 +193,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         init(&bars.q, 1);
         for (int s = 0; s < kT5Stages; ++s) { init(&bars.kfull[s], 1); init(&bars.vfull[s], 1); init(&bars.kvempty[s], 1); }
         for (int i = 0; i < 2; ++i) { init(&bars.sfull[i], 1); init(&bars.pready[i], kT5M); init(&bars.odone[i], 1); }
-        s_abort = (*reinterpret_cast<volatile int *>(err) & HS_DEVERR_WAIT_TIMEOUT) ? 1 : 0;  // a recorded time-out ends every later CTA at once
+        s_abort = *reinterpret_cast<volatile uint32_t *>(err + 1) == launch_id ? 1 : 0;  // a time-out recorded by this launch ends its later CTAs at once
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -446,7 +446,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*abort_flag) {
-        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        if (threadIdx.x == 0) { atomicOr(err, HS_DEVERR_WAIT_TIMEOUT); atomicExch(reinterpret_cast<unsigned int *>(err + 1), launch_id); }
         const long long t0c = clock64();
         while (clock64() - t0c < 2000000LL) {}  // bounded grace period for copies and MMAs still in flight
     }
@@ -469,14 +469,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 //   S = Q.K^T is issued per pair of key tiles: 16 MMAs 128x128x16 on K ring stages of [128 keys][128 columns of d] (the Q
 //   slice is read from shared memory once per 128 keys); O += P.V per key tile: 4 MMAs 128x256x16 (P from TMEM, V
 //   MN-major: its four 64-column boxes are 8 KB apart).
-#ifdef HS_W5_PROF
-__device__ unsigned long long g_w5_prof[8];
-#define W5_T(var) const long long var = clock64()
-#define W5_ACC(i, t0, t1) prof[i] += (t1) - (t0)
-#else
-#define W5_T(var)
-#define W5_ACC(i, t0, t1)
-#endif
 constexpr int kW5D = 256, kW5M = 128, kW5N = 64;
 constexpr int kW5KStages = 3, kW5VStages = 2, kW5SBufs = 4;
 constexpr int kW5Threads = 320;  // warps 0-3 / 4-7: softmax of even / odd key tiles, warp 8: loader, warp 9: MMA issuer
@@ -494,7 +486,7 @@ struct W5Bars {
 __global__ void __launch_bounds__(kW5Threads, 1)
 prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
-                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err) {
+                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) W5Bars bars;
     __shared__ uint32_t s_tmem;
@@ -527,7 +519,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int s = 0; s < kW5VStages; ++s) { init(&bars.vfull[s], 1); init(&bars.vempty[s], 1); }
         for (int i = 0; i < 2; ++i) init(&bars.sfull[i], 1);
         for (int i = 0; i < kW5SBufs; ++i) { init(&bars.pready[i], kW5M); init(&bars.pvdone[i], 1); }
-        s_abort = (*reinterpret_cast<volatile int *>(err) & HS_DEVERR_WAIT_TIMEOUT) ? 1 : 0;  // a recorded time-out ends every later CTA at once
+        s_abort = *reinterpret_cast<volatile uint32_t *>(err + 1) == launch_id ? 1 : 0;  // a time-out recorded by this launch ends its later CTAs at once
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -551,9 +543,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             auto load_k = [&](int n) -> bool {  // half n: pair n >> 1, columns 128 (n & 1) ..
                 const int s = n % kW5KStages;
                 if (n >= kW5KStages && !t5_wait(t5_s32(&bars.kempty[s]), (n / kW5KStages - 1) & 1, abort_flag)) return false;
-#ifdef HS_W5_NOLOAD
-                if (n >= kW5KStages) { t5_arrive(t5_s32(&bars.kfull[s])); return true; }
-#endif
                 t5_expect_tx(t5_s32(&bars.kfull[s]), kW5KVBytes);
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
@@ -563,9 +552,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             auto load_v = [&](int j) -> bool {
                 const int s = j % kW5VStages;
                 if (j >= kW5VStages && !t5_wait(t5_s32(&bars.vempty[s]), (j / kW5VStages - 1) & 1, abort_flag)) return false;
-#ifdef HS_W5_NOLOAD
-                if (j >= kW5VStages) { t5_arrive(t5_s32(&bars.vfull[s])); return true; }
-#endif
                 t5_expect_tx(t5_s32(&bars.vfull[s]), kW5KVBytes);
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -591,9 +577,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (((2 * kW5N) >> 3) << 17) | ((kW5M >> 4) << 24);
         const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kW5D >> 3) << 17) | ((kW5M >> 4) << 24);
         const uint64_t dq = t5_desc(sQ, 16, 1024), dk0 = t5_desc(sK, 16, 1024), dv0 = t5_desc(sV, kW5KVBox, 1024);
-#ifdef HS_W5_PROF
-        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
         // S(pair) into score buffers 2 pb, 2 pb + 1; its K halves are n0 and n0 + 1 (n0 = 2 * pair; ring stage n % 3, phase n / 3)
         auto issue_s = [&](int pb, int st0, uint32_t ph0, int st1, uint32_t ph1) -> bool {
 #pragma unroll
@@ -602,12 +585,8 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!__all_sync(0xffffffffu, t5_wait(t5_s32(&bars.kfull[st]), hf ? ph1 : ph0, abort_flag))) return false;
                 t5_fence_after();
                 if (t5_elect()) {
-#ifdef HS_W5_NOQK
-                    for (int ks = 0; ks < 1; ++ks)
-#else
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks)
-#endif
                         t5_mma_ss(tm + pb * 2 * kW5N, dq + (((2 * hf + (ks >> 2)) * kW5QBox + (ks & 3) * 32) >> 4),
                                   dk0 + ((st * kW5KVBytes + (ks >> 2) * kW5QBox + (ks & 3) * 32) >> 4), idesc_qk, (hf > 0 || ks > 0) ? 1u : 0u);
                     t5_commit(t5_s32(&bars.kempty[st]));
@@ -631,46 +610,27 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int u = (2 * i + e) & 3;
-                    W5_T(ta);
                     ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.pready[u]), p6 ^ (((2 * i + e) >> 2) & 1), abort_flag) &&
                                                      t5_wait(t5_s32(&bars.vfull[e]), i & 1, abort_flag));
-                    W5_T(tc);
-                    W5_ACC(0, ta, tc);
                     if (!ok) break;
                     t5_fence_after();
                     if (t5_elect()) {
-#ifdef HS_W5_NOPV
-                        for (int ks = 0; ks < 1; ++ks)
-#else
 #pragma unroll
                         for (int ks = 0; ks < kW5N / 16; ++ks)
-#endif
                             t5_mma_ts(tm + 256, tm + u * kW5N + ks * 8, dv0 + ((e * kW5KVBytes + ks * 2048) >> 4), idesc_pv,
                                       (t > 0 || e > 0 || ks > 0) ? 1u : 0u);
                         t5_commit(t5_s32(&bars.pvdone[u]));  // one phase per four tiles: what the softmax warps wait on
                         t5_commit(t5_s32(&bars.vempty[e]));
                     }
                     __syncwarp();
-                    W5_T(td);
-                    W5_ACC(2, tc, td);
                 }
                 if (!ok) break;
                 // ---- S(pair t+2): halves n = 2(t+2) + hf = 12 q + 2i + 4 + hf, stage n % 3, phase n / 3 = 4q + (2i + 4 + hf) / 3 ----
                 if (t + 2 < n_pairs) {
-                    W5_T(tf);
                     ok = issue_s(i & 1, (2 * i + 4) % 3, ((2 * i + 4) / 3) & 1, (2 * i + 5) % 3, ((2 * i + 5) / 3) & 1);
-                    W5_T(tg);
-                    W5_ACC(5, tf, tg);
-#ifdef HS_W5_PROF
-                    prof[6] += 2;
-#endif
                 }
             }
         }
-#ifdef HS_W5_PROF
-        if (lane == 0)
-            for (int i = 0; i < 8; ++i) atomicAdd(&g_w5_prof[i], static_cast<unsigned long long>(prof[i]));
-#endif
     } else {
         // ================================ softmax: thread = query row, group = parity of the key tile ================================
         const int grp = warp >> 2, r_local = threadIdx.x & 127;
@@ -685,11 +645,6 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             ok = __all_sync(0xffffffffu, t5_wait(t5_s32(&bars.sfull[(j >> 1) & 1]), (j >> 2) & 1, abort_flag));
             if (!ok) break;
             t5_fence_after();
-#ifdef HS_W5_NOSOFTMAX
-            t5_fence_before();
-            t5_arrive(t5_s32(&bars.pready[j & 3]));
-            continue;
-#endif
             const int n0 = j * kW5N;
             const bool masked = n0 + kW5N > min(kv_len, off + m0 + 1);
             const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
@@ -782,11 +737,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     for (int i = 0; i < 16; ++i) {
                         float x0, x1;
                         t5_unpack2(t5_fma2(t5_pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2), x0, x1);
-#ifdef HS_W5_NOEXP
-                        const float p0 = x0, p1 = x1;
-#else
                         const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);
-#endif
                         if (i & 1) acc_b = t5_add2(acc_b, t5_pack2(p0, p1)); else acc_a = t5_add2(acc_a, t5_pack2(p0, p1));
                         w[i] = t5_pack_bf16x2(p0, p1);
                     }
@@ -862,7 +813,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*abort_flag) {
-        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        if (threadIdx.x == 0) { atomicOr(err, HS_DEVERR_WAIT_TIMEOUT); atomicExch(reinterpret_cast<unsigned int *>(err + 1), launch_id); }
         const long long t0c = clock64();
         while (clock64() - t0c < 2000000LL) {}  // bounded grace period for copies and MMAs still in flight
     }
@@ -918,14 +869,15 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
             return HS_OK;
         int *errw = device_error_word();
         if (!errw) return fail(HS_ERR_DEVICE, "hs_attn_prefill_causal: device error word unavailable");
-        static bool configured_w = false;
-        if (!configured_w) {
+        static PerDeviceState configured_w;
+        const int dev = current_device();
+        if (!configured_w.get(dev)) {
             cudaError_t e = cudaFuncSetAttribute(prefill_tc5_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kW5SmemBytes);
             if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
-            configured_w = true;
+            configured_w.set(dev, 1);
         }
         dim3 gridw((q_len + kW5M - 1) / kW5M, n_q_heads, n_seqs);
-        prefill_tc5_wide_kernel<<<gridw, kW5Threads, kW5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, errw);
+        prefill_tc5_wide_kernel<<<gridw, kW5Threads, kW5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, errw, next_launch_id());
         *taken = 1;
         return HS_OK;
     }
@@ -936,27 +888,18 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
         return HS_OK;
     int *err = device_error_word();
     if (!err) return fail(HS_ERR_DEVICE, "hs_attn_prefill_causal: device error word unavailable");
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceState configured;
+    const int dev = current_device();
+    if (!configured.get(dev)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5SmemBytes);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_prefill_causal: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.set(dev, 1);
     }
     dim3 grid((q_len + kT5BlockM - 1) / kT5BlockM, n_q_heads, n_seqs);
-    prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err);
+    prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err, next_launch_id());
     *taken = 1;
     return HS_OK;
 }
 
 }  // namespace hs
 
-#ifdef HS_W5_PROF
-extern "C" int hs_w5_prof_read(unsigned long long *out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, hs::g_w5_prof, sizeof(unsigned long long) * 8);
-    if (e == cudaSuccess && reset) {
-        unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        e = cudaMemcpyToSymbol(hs::g_w5_prof, z, sizeof(z));
-    }
-    return static_cast<int>(e);
-}
-#endif

@@ -65,7 +65,7 @@ qk_norm_rope_kernel(const uint16_t *__restrict__ x, int64_t token_stride, int64_
         const int half = rotary_dim >> 1;
         const int pos = live ? positions[tok] : 0;
         const bool in_table = pos >= 0 && pos < n_positions;
-        if (live && !in_table && l == 0) atomicExch(err, HS_DEVERR_ROPE_RANGE);  // recorded; the row is left unrotated
+        if (live && !in_table && l == 0) atomicOr(err, HS_DEVERR_ROPE_RANGE);  // recorded; the row is left unrotated
         const bool rot = d0 < rotary_dim, first = d0 < half;
         // the partner chunk (d0 +- half) sits half/8 lanes away in the same row
         const int partner_lane = (threadIdx.x & 31) + (first ? half / 8 : -(half / 8));

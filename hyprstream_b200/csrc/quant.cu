@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(kQThreads) rope_kernel(const uint16_t *__restr
     float v[8];
     const int pos = positions[r];
     const bool in_table = pos >= 0 && pos < n_positions;
-    if (!in_table) atomicExch(err, HS_DEVERR_ROPE_RANGE);  // recorded; the row is copied unrotated
+    if (!in_table) atomicOr(err, HS_DEVERR_ROPE_RANGE);  // recorded; the row is copied unrotated
     load_row8_rope(x + rh * head_dim, d0, in_table ? sin : nullptr, cos, in_table ? pos : 0, rotary_dim, v);
     uint4 w;
     w.x = pack_bf16(v[0], v[1]); w.y = pack_bf16(v[2], v[3]); w.z = pack_bf16(v[4], v[5]); w.w = pack_bf16(v[6], v[7]);
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
         const int page = pos / view.page_tokens;
         bool ok = live && pos >= 0 && page < view.pages_per_seq;
         if (!is_v && sin != nullptr && (pos < 0 || pos >= n_positions)) ok = false;
-        if (live && !ok) atomicExch(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
+        if (live && !ok) atomicOr(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
         const uint16_t *src = (is_v ? v_new : k_new) + row * D;
         float x[E];
 #pragma unroll

@@ -8,16 +8,39 @@
 namespace hs {
 
 static thread_local char g_err[512] = "";
-// word 0: error flags; words 1, 2: arrival count and generation of the grid barrier used by fused kernels
+// word 0: HS_DEVERR_* flags; word 1: id of the latest launch that recorded a wait time-out (see hs_common.cuh)
 static __device__ int g_device_error[4];
+static std::atomic<int *> g_device_error_ptr[kMaxDevices];
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return dev;
+}
 
 int *device_error_word() {
+    const int dev = current_device();
+    if (dev < 0) return nullptr;
+    if (dev < kMaxDevices) {
+        if (int *p = g_device_error_ptr[dev].load(std::memory_order_acquire)) return p;
+    }
     int *p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_device_error) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
+    if (dev < kMaxDevices) g_device_error_ptr[dev].store(p, std::memory_order_release);
     return p;
+}
+
+uint32_t next_launch_id() {
+    static std::atomic<uint32_t> g_id{0};
+    uint32_t id = g_id.fetch_add(1, std::memory_order_relaxed) + 1;
+    if (id == 0) id = g_id.fetch_add(1, std::memory_order_relaxed) + 1;
+    return id;
 }
 
 void set_error(const char *fmt, ...) {
@@ -61,9 +84,14 @@ int32_t check_device() {
 }
 
 int sm_count() {
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
+    static PerDeviceState cache;
+    const int dev = current_device();
+    if (int n = cache.get(dev)) return n;
+    int n = 148;
+    if (dev >= 0) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    cache.set(dev, n);
+    return n;
 }
 
 static std::atomic<long long> g_launches{0};
@@ -152,12 +180,21 @@ int32_t hs_attn_take_device_error(int32_t *flags) {
     if (int32_t st = hs::check_device()) return st;
     int v = 0, zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, hs::g_device_error, sizeof v);
-    if (e == cudaSuccess && v != 0) {
-        e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero);                   // clear the flags
-        if (e == cudaSuccess) e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero, sizeof(int));  // and a barrier count a timed-out kernel may have left
-    }
+    if (e == cudaSuccess && v != 0) e = cudaMemcpyToSymbol(hs::g_device_error, &zero, sizeof zero);  // clear the flags
     if (e != cudaSuccess) return hs::fail(static_cast<int32_t>(e), "hs_attn_take_device_error: %s", cudaGetErrorString(e));
     *flags = v;
+    return HS_OK;
+}
+
+// Test hook: ORs `flags` into the current device's error word from the host (a plain copy; no kernel, no fault), so
+// that the behaviour of the entry points with flags pending can be tested without making a wait run out.
+int32_t hs_attn_inject_device_error(int32_t flags) {
+    if (int32_t st = hs::check_device()) return st;
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, hs::g_device_error, sizeof v);
+    v |= flags;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(hs::g_device_error, &v, sizeof v);
+    if (e != cudaSuccess) return hs::fail(static_cast<int32_t>(e), "hs_attn_inject_device_error: %s", cudaGetErrorString(e));
     return HS_OK;
 }
 

@@ -48,6 +48,7 @@ _SIGS = {
     "hs_attn_device_check": (c_int32, [c_int32]),
     "hs_attn_last_error": (c_char_p, []),
     "hs_attn_take_device_error": (c_int32, [POINTER(c_int32)]),
+    "hs_attn_inject_device_error": (c_int32, [c_int32]),
     "hs_attn_set_profiling": (c_int32, [c_int32]),
     "hs_attn_last_kernel_ms": (c_int32, [POINTER(c_float)]),
     "hs_attn_launch_count": (c_int64, []),

@@ -95,6 +95,10 @@ const char *hs_attn_last_error(void);
 #define HS_DEVERR_DECODE_RANGE 4   /* hs_attn_decode: seq_len beyond the view's pages; tokens past them ignored */
 #define HS_DEVERR_WAIT_TIMEOUT 8   /* a bounded device-side wait ran out */
 int32_t hs_attn_take_device_error(int32_t *flags);
+/* The flags are a report, not a precondition: entry points launch and produce valid results while flags are pending
+ * (a kernel only cuts a launch short for a wait that ran out inside that same launch).  Test hook: ORs `flags` into the
+ * current device's word from the host, so that this can be checked without making a wait run out. */
+int32_t hs_attn_inject_device_error(int32_t flags);
 
 /* Tracing hook: while profiling is on, each compute entry point brackets its dominant kernel with two
  * CUDA events on the launch stream; hs_attn_last_kernel_ms() waits for the latest pair and returns the
