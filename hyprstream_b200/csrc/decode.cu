@@ -351,7 +351,8 @@ constexpr int kMaxPartsPerPair = 2;
 // decode_tc.cu: tensor-core kernel for the int8 / head_dim 128 / 8 kv heads / group 4 shape
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
-                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out);
+                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out,
+                           const ShardArgs *shard);
 
 template <int KIND, int D, int G>
 static int32_t launch_generic(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
@@ -427,6 +428,10 @@ static int32_t static_scratch_for_current_device(void **out) {
     return HS_OK;
 }
 
+int32_t decode_impl(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale,
+                    void *out, const void *gate, void *workspace, int64_t workspace_bytes, float *o_shard, float *lse_shard,
+                    const ShardArgs *shard, hs_stream_t stream);
+
 }  // namespace hs
 
 using namespace hs;
@@ -442,6 +447,17 @@ int64_t hs_attn_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, int32_
 int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
                        float softmax_scale, void *out, const void *gate, void *workspace, int64_t workspace_bytes,
                        float *o_shard, float *lse_shard, hs_stream_t stream) {
+    return hs::decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, workspace, workspace_bytes, o_shard, lse_shard,
+                           nullptr, stream);
+}
+
+}  // extern "C"
+
+// The body of hs_attn_decode; `shard` (optional) makes the tensor-core kernel exchange its result with the other GPUs of
+// a shard group and merge again (hs_attn_decode_sharded); only that kernel can, so other shapes are refused then.
+int32_t hs::decode_impl(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                        float softmax_scale, void *out, const void *gate, void *workspace, int64_t workspace_bytes,
+                        float *o_shard, float *lse_shard, const ShardArgs *shard, hs_stream_t stream) {
     if (int32_t st = check_device()) return st;
     if (int32_t st = validate_view(view)) return st;
     if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode: bad sizes");
@@ -449,7 +465,7 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     if (n_q_heads % view->n_kv_heads != 0) return fail(HS_ERR_ARG, "hs_attn_decode: n_q_heads %d not a multiple of n_kv_heads %d", n_q_heads, view->n_kv_heads);
     if (!q || !seq_lens || !workspace) return fail(HS_ERR_ARG, "hs_attn_decode: NULL pointer");
     if ((o_shard == nullptr) != (lse_shard == nullptr)) return fail(HS_ERR_ARG, "hs_attn_decode: o_shard and lse_shard go together");
-    if (!o_shard && !out) return fail(HS_ERR_ARG, "hs_attn_decode: no output");
+    if (!o_shard && !out && !(shard && shard->push_only)) return fail(HS_ERR_ARG, "hs_attn_decode: no output");
     if (!aligned(q, 16) || !aligned(workspace, 16) || (out && !aligned(out, 2)) || (gate && !aligned(gate, 2)) || !aligned(seq_lens, 4))
         return fail(HS_ERR_ARG, "hs_attn_decode: q and workspace must be 16-byte aligned");
     const int D = view->head_dim, G = n_q_heads / view->n_kv_heads;
@@ -471,7 +487,13 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
     int tile = kDecTile, tc_ctas = 0, ppp = 1, merged = 0;
     prof_begin(s);
     st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas,
-                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard, lse_shard, &merged);
+                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard, lse_shard, &merged, shard);
+    if (st == HS_OK && shard && tc_ctas == 0) {
+        prof_end(s);
+        return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode_sharded: only the tensor-core decode kernel exchanges shard results (quantised cache, 8 kv heads x 128 "
+                                        "with 32 query heads or 2 x 256 with 16, cooperative launch available); use hs_attn_decode with o_shard / lse_shard, an "
+                                        "all-gather and hs_attn_merge_partials_strided for this shape");
+    }
     if (st == HS_OK && tc_ctas > 0) {
         n_ctas = tc_ctas;
         tile = 16;
@@ -493,6 +515,8 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
                                             o_shard, lse_shard);
     return check_launch("hs_attn_decode (merge)");
 }
+
+extern "C" {
 
 int32_t hs_attn_merge_partials_strided(const float *o_parts, const float *lse_parts, int32_t n_parts, int64_t part_stride_o,
                                        int64_t part_stride_lse, int64_t n_rows, int32_t head_dim, void *out, const void *gate,
@@ -533,6 +557,35 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
     // Nothing in the scratch has to start at zero: each launch writes every partial slot it later reads.
     return hs_attn_decode(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, scratch, kStaticScratchBytes, nullptr,
                           nullptr, stream);
+}
+
+
+int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *dev_in, const int32_t *dst_pos, const int32_t *seq_lens,
+                            int32_t n_seqs, int32_t n_q_heads, float softmax_scale, const void *sin, const void *cos, int32_t rotary_dim,
+                            int32_t n_positions, void *dev_out, void *host_out, void *workspace, int64_t workspace_bytes, int32_t flags,
+                            hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (int32_t st = validate_view(view)) return st;
+    if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode_step: bad sizes");
+    if (n_seqs == 0) return HS_OK;
+    if (!host_in || !dev_in || !dev_out || !host_out || !dst_pos || !seq_lens)
+        return fail(HS_ERR_ARG, "hs_attn_decode_step: NULL pointer");
+    if (!aligned(dev_in, 16)) return fail(HS_ERR_ARG, "hs_attn_decode_step: dev_in must be 16-byte aligned");
+    const int64_t D = view->head_dim;
+    const int64_t q_elems = static_cast<int64_t>(n_seqs) * n_q_heads * D, kv_elems = static_cast<int64_t>(n_seqs) * view->n_kv_heads * D;
+    if ((q_elems * 2) % 16 != 0 || (kv_elems * 2) % 16 != 0) return fail(HS_ERR_ARG, "hs_attn_decode_step: q and k/v parts must be multiples of 16 bytes");
+    cudaStream_t s = as_stream(stream);
+    cudaError_t e = cudaMemcpyAsync(dev_in, host_in, static_cast<size_t>(q_elems + 2 * kv_elems) * 2, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode_step: %s", cudaGetErrorString(e));
+    uint16_t *qd = reinterpret_cast<uint16_t *>(dev_in), *kd = qd + q_elems, *vd = kd + kv_elems;
+    if (int32_t st = hs_kv_quantize_write(view, kd, vd, n_seqs, 1, dst_pos, sin, cos, rotary_dim, n_positions, stream)) return st;
+    if (int32_t st = hs_attn_decode(qd, view, seq_lens, n_seqs, n_q_heads, softmax_scale, dev_out, nullptr, workspace, workspace_bytes, nullptr,
+                                    nullptr, stream))
+        return st;
+    e = cudaMemcpyAsync(host_out, dev_out, static_cast<size_t>(q_elems) * 2, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && (flags & HS_STEP_SYNC)) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode_step: %s", cudaGetErrorString(e));
+    return HS_OK;
 }
 
 }  // extern "C"

@@ -166,7 +166,28 @@ struct TcMergeArgs {
     const uint16_t *gate; // optional
     float *o_shard, *lse_shard;  // optional fp32 shard outputs
     int counter;          // which grid-barrier counter the launch uses: one per grid size (CTAs per SM - 1)
+    ShardArgs shard;      // world > 0: the merged result is a KV-length shard's; exchange it with the other GPUs and merge again
 };
+
+// ---- peer exchange primitives (ordinary stores and loads on peer-mapped memory; system scope) ----
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys(const float *p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ld_relaxed_sys2(const float *p) {
+    float2 v;
+    asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 // Arrivals of all launches so far (see the grid barrier in the kernel), one counter per grid size: a launch's CTAs
 // find their target from their ticket and the grid size, so every launch that shares a counter must have the same one.
@@ -733,7 +754,61 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             }
         }
         const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
-        const float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
+        float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
+        if (mg.shard.world > 0) {
+            // ---- KV-length shards on several GPUs: deliver this shard's (o, lse) of the item to every rank's inbox with
+            // ordinary stores, publish it with a release store of the epoch, wait (bounded) for the other ranks' parts of the
+            // same item in the own inbox, and merge them.  All deliveries of a CTA precede its first wait.
+            const ShardArgs &sh = mg.shard;
+            const int W = sh.world;
+            const long long half = sh.epoch & 1u;
+            const float lse_mine = den > 0.0f ? M + __logf(den) : -INFINITY;
+            const long long o_at = ((half * W + sh.rank) * sh.rows_cap + row) * kD + d;
+            const long long l_at = 2LL * W * sh.rows_cap * kD + (half * W + sh.rank) * sh.rows_cap + row;
+            for (int s2 = 0; s2 < W; ++s2) {
+                *reinterpret_cast<float2 *>(sh.inbox[s2] + o_at) = make_float2(o0, o1);
+                if (d == 0) sh.inbox[s2][l_at] = lse_mine;
+            }
+            __syncthreads();  // every thread's stores are ordered before the release stores below (barrier + cumulative fence)
+            if (threadIdx.x < W) {
+                __threadfence_system();
+                st_release_sys(sh.flags[threadIdx.x] + (half * W + sh.rank) * sh.items_cap + item, sh.epoch);
+            }
+            if (sh.push_only) continue;
+            __shared__ int s_shard_ok;
+            if (threadIdx.x == 0) s_shard_ok = 1;
+            __syncthreads();
+            if (threadIdx.x < W) {
+                const unsigned int *f = sh.flags[sh.rank] + (half * W + threadIdx.x) * sh.items_cap + item;
+                if (ld_acquire_sys(f) != sh.epoch) {
+                    const long long t0s = clock64();
+                    while (ld_acquire_sys(f) != sh.epoch) {
+                        if (clock64() - t0s > sh.wait_cycles) { s_shard_ok = 0; break; }
+                        __nanosleep(64);
+                    }
+                }
+            }
+            __syncthreads();
+            if (!s_shard_ok) {  // a rank did not deliver in time: recorded, this item gets no output, the launch goes on
+                if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+                __syncthreads();
+                continue;
+            }
+            const float *box = sh.inbox[sh.rank];
+            float Mx = -INFINITY;
+            for (int s2 = 0; s2 < W; ++s2)
+                Mx = fmaxf(Mx, ld_relaxed_sys(box + 2LL * W * sh.rows_cap * kD + (half * W + s2) * sh.rows_cap + row));
+            float nx = 0.0f, ny = 0.0f, dn = 0.0f;
+            for (int s2 = 0; s2 < W; ++s2) {
+                const float ls = ld_relaxed_sys(box + 2LL * W * sh.rows_cap * kD + (half * W + s2) * sh.rows_cap + row);
+                const float w = ls == -INFINITY ? 0.0f : __expf(ls - Mx);
+                const float2 v = ld_relaxed_sys2(box + ((half * W + s2) * sh.rows_cap + row) * kD + d);
+                nx = fmaf(w, v.x, nx); ny = fmaf(w, v.y, ny); dn += w;
+            }
+            o0 = dn > 0.0f ? nx / dn : 0.0f;
+            o1 = dn > 0.0f ? ny / dn : 0.0f;
+            __syncthreads();  // s_shard_ok is rewritten by the next item
+        }
         if (mg.o_shard != nullptr) {
             *reinterpret_cast<float2 *>(mg.o_shard + row * kD + d) = make_float2(o0, o1);
             if (d == 0) mg.lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
@@ -791,7 +866,8 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
 // the device refuses cooperative launches, and the caller should use the generic kernel.
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
-                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out) {
+                           uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out,
+                           const ShardArgs *shard) {
     *n_ctas_out = 0;
     *merged_out = 0;
     // covered shapes: 8 kv heads x 128 with 4 query heads each, and 2 kv heads x 256 with 8 query heads each
@@ -807,7 +883,9 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     int n_ctas = 2 * sm_count();  // upper bound; the launch settles on one or two CTAs per SM
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
-    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0};
+    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0, ShardArgs{}};
+    mg.shard.world = 0;
+    if (shard) mg.shard = *shard;
     int32_t st;
 #define HS_TC_LAUNCH(F, B, S, W) launch_tc<F, B, S, W>(v, q, seq_lens, n_seqs, n_q_heads, kmul, o_part, lse_part, err, &n_ctas, mg, s, merged_out)
     if (wide) {

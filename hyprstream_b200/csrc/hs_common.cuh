@@ -59,6 +59,25 @@ static inline ViewDev to_dev(const hs_kv_view *v) {
     return d;
 }
 
+// ---- exchange of KV-length-shard results between GPUs inside the decode kernel -----------------------
+// Every rank owns an "inbox" that all ranks can address (its own memory for itself, a peer mapping for the others).
+// Layout, with W = world, R = rows_cap, D = head_dim, I = items_cap and h = epoch & 1 (two halves, so that a rank that is
+// one step ahead never overwrites what a slower rank still reads):
+//   data  (floats):  o of source s in half h at ((h * W + s) * R) * D;  lse at 2 * W * R * D + (h * W + s) * R
+//   flags (uint32):  [(h * W + s) * I + item] = the epoch in which source s last delivered `item`
+// An item is one merge work item of the decode kernel (a sequence and a group of query heads: 512 output floats).
+constexpr int kShardMaxWorld = 8;
+struct ShardArgs {
+    float *inbox[kShardMaxWorld];
+    unsigned int *flags[kShardMaxWorld];
+    int rank, world;          // world == 0: no exchange
+    unsigned int epoch;       // never 0
+    int push_only;            // deliver this rank's part, do not wait for the others, write no output
+    long long wait_cycles;    // limit of the wait for the other ranks' parts
+    long long rows_cap;
+    int items_cap;
+};
+
 // ---- device helpers --------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }

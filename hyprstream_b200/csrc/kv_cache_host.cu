@@ -133,6 +133,9 @@ struct hs_pool {
 struct hs_cache {
     hs::Geometry geo;
     int max_seq_len = 0, seq_pos = 0, capacity = 0;
+    // bumped whenever storage that a view's pointer tables may reference is released or replaced (growth of a contiguous
+    // cache, pages returned by clear / truncate_to / offload, restore); a view records it per cache and compares
+    unsigned long long generation = 1;
     hs::Slab slab;              // contiguous storage
     hs_pool *pool = nullptr;    // paged storage
     int64_t owner = 0;
@@ -164,6 +167,14 @@ struct hs_cache {
         const int new_cap = std::min((max_seq_len + 31) / 32 * 32, (end_pos + kDefaultChunk - 1) / kDefaultChunk * kDefaultChunk);
         Slab grown;
         if (int32_t st = grown.allocate(geo, new_cap)) return st;
+        // writes to the old slab may be in flight on any stream: wait for the device before copying it (growth is rare)
+        if (slab.p[0]) {
+            cudaError_t es = cudaDeviceSynchronize();
+            if (es != cudaSuccess) {
+                grown.release();
+                return fail(static_cast<int32_t>(es), "cache growth: %s", cudaGetErrorString(es));
+            }
+        }
         for (int i = 0; i < 4; ++i) {
             if (!grown.p[i]) continue;
             cudaError_t e = cudaSuccess;
@@ -174,6 +185,7 @@ struct hs_cache {
                 return fail(static_cast<int32_t>(e), "cache growth: %s", cudaGetErrorString(e));
             }
         }
+        if (slab.p[0]) ++generation;  // views built on the old slab are stale
         slab.release();
         slab = grown;
         capacity = new_cap;
@@ -181,6 +193,7 @@ struct hs_cache {
     }
     void release_pages(size_t keep) {
         if (!pool) return;
+        if (keep < blocks.size()) ++generation;
         for (size_t i = keep; i < blocks.size(); ++i) pool->release(owner, blocks[i]);
         blocks.resize(std::min(keep, blocks.size()));
         capacity = static_cast<int>(blocks.size()) * pool->page_tokens;
@@ -209,6 +222,9 @@ struct hs_cache {
 struct hs_view {
     hs_kv_view view{};
     void **table = nullptr;  // device: [4][n][pages_per_seq]
+    std::vector<const hs_cache *> caches;           // the caches the tables were built from ...
+    std::vector<unsigned long long> generations;    // ... and their generation at that time
+    std::vector<int> capacities;                    // a paged cache that grew has pages the tables do not list
 };
 
 using namespace hs;
@@ -259,6 +275,13 @@ static int32_t build_view(hs_cache *const *caches, int n, hs_view *out) {
     v.k_pages = out->table; v.v_pages = out->table + stride;
     v.k_scale_pages = v.kind == HS_KV_BF16 ? nullptr : out->table + 2 * stride;
     v.v_scale_pages = v.kind == HS_KV_BF16 ? nullptr : out->table + 3 * stride;
+    out->caches.assign(caches, caches + n);
+    out->generations.resize(n);
+    out->capacities.resize(n);
+    for (int i = 0; i < n; ++i) {
+        out->generations[i] = caches[i]->generation;
+        out->capacities[i] = caches[i]->capacity;
+    }
     return HS_OK;
 }
 
@@ -448,9 +471,19 @@ int32_t hs_cache_offload(hs_cache *cache, void *host_buf, int64_t host_bytes, hs
         if (int32_t st = copy_rows(cache, static_cast<unsigned char *>(host_buf), cache->seq_pos, true, as_stream(stream), "hs_cache_offload")) return st;
     cache->seq_pos = 0;
     cache->release_pages(0);
+    if (cache->slab.p[0]) ++cache->generation;
     cache->slab.release();
     if (!cache->pool) cache->capacity = 0;
     return HS_OK;
+}
+
+int32_t hs_cache_snapshot(const hs_cache *cache, void *host_buf, int64_t host_bytes, hs_stream_t stream) {
+    if (!cache || (!host_buf && cache->seq_pos > 0)) return fail(HS_ERR_ARG, "hs_cache_snapshot: bad arguments");
+    if (host_bytes < hs_cache_offload_bytes(cache))
+        return fail(HS_ERR_ARG, "hs_cache_snapshot: host buffer of %lld bytes, %lld needed", static_cast<long long>(host_bytes),
+                    static_cast<long long>(hs_cache_offload_bytes(cache)));
+    if (cache->seq_pos == 0) return HS_OK;
+    return copy_rows(const_cast<hs_cache *>(cache), static_cast<unsigned char *>(host_buf), cache->seq_pos, true, as_stream(stream), "hs_cache_snapshot");
 }
 
 int32_t hs_cache_restore(hs_cache *cache, const void *host_buf, int64_t host_bytes, int32_t n_tokens, hs_stream_t stream) {
@@ -479,6 +512,19 @@ int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out)
     return HS_OK;
 }
 const hs_kv_view *hs_view_get(const hs_view *view) { return view ? &view->view : nullptr; }
+int32_t hs_view_is_current(const hs_view *view) {
+    if (!view) return fail(HS_ERR_ARG, "hs_view_is_current: NULL view");
+    for (size_t i = 0; i < view->caches.size(); ++i) {
+        const hs_cache *c = view->caches[i];
+        if (c->generation != view->generations[i])
+            return fail(HS_ERR_ARG, "hs_view_is_current: cache %zu released or replaced storage after the view was built (growth, clear, "
+                                    "truncate_to, offload); build a new view", i);
+        if (c->capacity != view->capacities[i])
+            return fail(HS_ERR_ARG, "hs_view_is_current: cache %zu changed capacity (%d -> %d tokens) after the view was built; its new pages "
+                                    "are not in the view's tables", i, view->capacities[i], c->capacity);
+    }
+    return HS_OK;
+}
 void hs_view_destroy(hs_view *view) {
     if (!view) return;
     if (view->table) g_free(view->table);

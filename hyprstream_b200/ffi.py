@@ -19,6 +19,7 @@ KV_BF16, KV_INT8, KV_NF4, KV_FP4 = 0, 1, 2, 3
 SCALE_F32, SCALE_F16 = 0, 1
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 DEVERR_KV_WRITE_RANGE, DEVERR_ROPE_RANGE, DEVERR_DECODE_RANGE, DEVERR_WAIT_TIMEOUT = 1, 2, 4, 8
+STEP_SYNC, SHARD_PUSH_ONLY = 1, 1
 
 
 class HsError(RuntimeError):
@@ -63,6 +64,20 @@ _SIGS = {
     "hs_attn_decode": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "hs_attn_decode_static_max_bytes": (c_int64, []),
     "hs_attn_decode_static": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_decode_step": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p,
+                                      c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+    "hs_shard_group_create": (c_int32, [c_int32] * 5 + [POINTER(c_void_p)]),
+    "hs_shard_group_handle_bytes": (c_int32, []),
+    "hs_shard_group_export": (c_int32, [c_void_p, c_void_p]),
+    "hs_shard_group_connect": (c_int32, [c_void_p, c_void_p]),
+    "hs_shard_group_connect_local": (c_int32, [POINTER(c_void_p), c_int32]),
+    "hs_shard_group_set_wait_ms": (c_int32, [c_void_p, c_int32]),
+    "hs_shard_group_epoch": (c_int32, [c_void_p]),
+    "hs_shard_group_destroy": (None, [c_void_p]),
+    "hs_attn_decode_sharded": (c_int32, [c_void_p, c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p,
+                                         c_int64, c_int32, c_void_p]),
+    "hs_cache_snapshot": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "hs_view_is_current": (c_int32, [c_void_p]),
     "hs_attn_prefill_causal": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_float, c_void_p]),
     "hs_gdn_recurrent": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
     "hs_gdn_chunk_prefill": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),

@@ -152,6 +152,28 @@ class LayerKVCache:
         """Bytes held (cf. QuantizedTensor::memory_usage, kv_cache.rs:960-962)."""
         return lib.hs_cache_memory_usage(self._h)
 
+    def snapshot(self):
+        """The stored rows as they are (hs_cache_snapshot): (k_data, v_data, k_scales, v_scales) as CPU tensors - uint8
+        codes [seq_pos, Hkv, D or D/2] (bf16 values for an unquantised cache) and f32 / f16 scales [seq_pos, Hkv, D/block]
+        (None for an unquantised cache).  The cache keeps its contents."""
+        n = self.seq_pos
+        nbytes = lib.hs_cache_offload_bytes(self._h)
+        image = torch.empty(max(nbytes, 1), dtype=torch.uint8).pin_memory()
+        with torch.cuda.device(self.device):
+            _check(lib.hs_cache_snapshot(self._h, image.data_ptr(), nbytes, _stream()))
+        h, d = self.n_kv_heads, self.head_dim
+        if self.kind == ffi.KV_BF16:
+            row = h * d * 2
+            k, v = (image[i * n * row:(i + 1) * n * row].view(torch.bfloat16).view(n, h, d) for i in range(2))
+            return k, v, None, None
+        row = h * (d if self.kind == ffi.KV_INT8 else d // 2)
+        sdt, sb = (torch.float16, 2) if self.scale_dtype == ffi.SCALE_F16 else (torch.float32, 4)
+        srow = h * (d // self.block) * sb
+        k, v = (image[i * n * row:(i + 1) * n * row].view(n, h, row // h) for i in range(2))
+        off = 2 * n * row
+        ks, vs = (image[off + i * n * srow:off + (i + 1) * n * srow].view(sdt).view(n, h, d // self.block) for i in range(2))
+        return k, v, ks, vs
+
     def to_device(self, device) -> None:
         """kv_cache.rs:1838-1858 `to_device` (CPU offload / restore).  `cpu` parks the used rows - codes and scales as
         they are, or bf16 values - in pinned host memory and releases the device storage (pages go back to the pool);
@@ -204,3 +226,9 @@ def make_view(caches: Sequence[LayerKVCache]) -> Tuple[KVView, list]:
     holder = _ViewHandle(h)
     view = KVView.from_address(lib.hs_view_get(h))
     return view, [holder, list(caches)]
+
+
+def view_is_current(keepalive: list) -> bool:
+    """False once a cache of the view released or replaced storage after the view was built (hs_view_is_current):
+    the view's pointer tables are stale then and the view must be rebuilt."""
+    return lib.hs_view_is_current(keepalive[0].handle) == ffi.HS_OK

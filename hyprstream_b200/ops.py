@@ -157,6 +157,35 @@ def decode_attention(q: torch.Tensor, view: KVView, seq_lens: torch.Tensor, soft
     return out
 
 
+class DecodeStep:
+    """One decode step of a batch as one C-ABI call (hs_attn_decode_step): the step's q, new K and new V travel from one
+    pinned host buffer in one copy, the new token is quantised into the caches, the batch is attended, and the result
+    comes back into a pinned host buffer.  Mirrors the reference engine's one-forward-per-step loop
+    (torch_engine.rs:3719-3731).  Fill ``q_host`` / ``k_host`` / ``v_host`` (views of the pinned input buffer), call
+    ``run()``, read ``out_host``."""
+
+    def __init__(self, view: KVView, n_seqs: int, n_q_heads: int, device: torch.device, softmax_scale: Optional[float] = None):
+        self.view, self.n_seqs, self.hq = view, n_seqs, n_q_heads
+        hkv, d = view.n_kv_heads, view.head_dim
+        self.scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
+        sizes = [n_seqs * n_q_heads * d, n_seqs * hkv * d, n_seqs * hkv * d]
+        self.host_in = torch.empty(sum(sizes), dtype=torch.bfloat16).pin_memory()
+        self.q_host, self.k_host, self.v_host = (t.view(n_seqs, h, d) for t, h in zip(self.host_in.split(sizes), (n_q_heads, hkv, hkv)))
+        self.dev_in = torch.empty(sum(sizes), dtype=torch.bfloat16, device=device)
+        self.dev_out = torch.empty(n_seqs, n_q_heads, d, dtype=torch.bfloat16, device=device)
+        self.out_host = torch.empty(n_seqs, n_q_heads, d, dtype=torch.bfloat16).pin_memory()
+        self.ws = decode_workspace(n_seqs, n_q_heads, d, device)
+        self.h2d_bytes, self.d2h_bytes = self.host_in.numel() * 2, self.out_host.numel() * 2
+
+    def run(self, dst_pos: torch.Tensor, seq_lens: torch.Tensor, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+            rotary_dim: int = 0, sync: bool = True) -> torch.Tensor:
+        check(lib.hs_attn_decode_step(ctypes.byref(self.view), self.host_in.data_ptr(), self.dev_in.data_ptr(), _ptr(dst_pos), _ptr(seq_lens),
+                                      self.n_seqs, self.hq, self.scale, _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0],
+                                      self.dev_out.data_ptr(), self.out_host.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
+                                      ffi.STEP_SYNC if sync else 0, _stream()))
+        return self.out_host
+
+
 def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """LSE merge of partials: o_parts fp32 [P, n_seqs, Hq, D], lse_parts fp32 [P, n_seqs, Hq] -> bf16 [n_seqs, Hq, D]."""
     _need_cuda(o_parts, lse_parts, gate)

@@ -1,4 +1,4 @@
-"""KV-length sharding of one long context across the GPUs of a node (BASELINE.json configs[2]).
+"""KV-length sharding of one long context across the GPUs of a node (long-context decode: batch 4, 131072 tokens).
 
 The reference has no collectives (its multi-GPU story is replicas and a layer split); this is
 new design.  Each rank owns a contiguous, page-aligned slice of every sequence's KV cache, runs the
@@ -107,6 +107,68 @@ class ShardedDecoder:
         else:
             src = self.msg
         return ops.merge_gathered(src, self.world, self.n_seqs, self.hq, self.d, out=self.out, gate=gate)
+
+
+def exchange_handles(handle: bytes, group: Optional[dist.ProcessGroup] = None) -> bytes:
+    """All-gather one fixed-size byte string per rank (a CUDA IPC handle) over any backend; returns them concatenated
+    in rank order.  Host set-up of FusedShardedDecoder, once per process."""
+    world = dist.get_world_size(group)
+    backend = dist.get_backend(group)
+    dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
+    buf = torch.empty(world * len(handle), dtype=torch.uint8, device=dev)
+    dist.all_gather_into_tensor(buf, mine, group=group)
+    return bytes(buf.cpu().numpy().tobytes())
+
+
+class FusedShardedDecoder:
+    """KV-length-sharded decode as ONE launch per GPU and step (hs_attn_decode_sharded): the decode kernel stores its
+    shard's (o, lse) into every rank's inbox over NVLink, waits - bounded - for the others' and merges.  The process
+    group is used once, at set-up, to exchange the inboxes' IPC handles; no collective runs per step.  Every rank must
+    call ``step`` the same number of times."""
+
+    def __init__(self, n_seqs: int, n_q_heads: int, head_dim: int, device: torch.device, group: Optional[dist.ProcessGroup] = None,
+                 wait_ms: Optional[int] = None):
+        import ctypes
+
+        from . import ffi, ops
+
+        self.n_seqs, self.hq, self.d = n_seqs, n_q_heads, head_dim
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._h = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            ffi.check(ffi.lib.hs_shard_group_create(self.rank, self.world, n_seqs, n_q_heads, head_dim, ctypes.byref(self._h)))
+            if self.world > 1:
+                hb = ffi.lib.hs_shard_group_handle_bytes()
+                mine = ctypes.create_string_buffer(hb)
+                ffi.check(ffi.lib.hs_shard_group_export(self._h, mine))
+                handles = exchange_handles(mine.raw, group)
+                ffi.check(ffi.lib.hs_shard_group_connect(self._h, handles))
+            if wait_ms is not None:
+                ffi.check(ffi.lib.hs_shard_group_set_wait_ms(self._h, wait_ms))
+        self.out = torch.empty(n_seqs, n_q_heads, head_dim, dtype=torch.bfloat16, device=device)
+        self.ws = ops.decode_workspace(n_seqs, n_q_heads, head_dim, device)
+
+    def step(self, q: torch.Tensor, local_view, local_lens: torch.Tensor, softmax_scale: Optional[float] = None,
+             gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        import ctypes
+        import math
+
+        from . import ffi
+
+        scale = 1.0 / math.sqrt(self.d) if softmax_scale is None else softmax_scale
+        ffi.check(ffi.lib.hs_attn_decode_sharded(self._h, q.data_ptr(), ctypes.byref(local_view), local_lens.data_ptr(), self.n_seqs, self.hq,
+                                                 scale, self.out.data_ptr(), None if gate is None else gate.data_ptr(), self.ws.data_ptr(),
+                                                 self.ws.numel(), 0, torch.cuda.current_stream().cuda_stream))
+        return self.out
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            from . import ffi
+
+            ffi.lib.hs_shard_group_destroy(self._h)
+            self._h = None
 
 
 def sharded_decode(q: torch.Tensor, local_view, local_lens: torch.Tensor, softmax_scale: Optional[float] = None,

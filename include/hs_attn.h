@@ -177,24 +177,87 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
                        int32_t n_q_heads, float softmax_scale, void *out, const void *gate, void *workspace,
                        int64_t workspace_bytes, float *o_shard, float *lse_shard, hs_stream_t stream);
 
+/* Concurrency: two hs_attn_decode (/ _static / _step / _sharded) launches must not be in flight on one device at the
+ * same time.  Launches on one stream are ordered by the stream; launches on different streams of one device, or from
+ * different host threads, must be serialised by the caller (an event between them is enough).  The tensor-core kernel
+ * is a cooperative launch whose CTAs meet at a grid-wide barrier that counts arrivals in a per-device counter; the
+ * arrivals of two overlapping launches would mix.  If the rule is broken the barrier's bounded wait runs out:
+ * HS_DEVERR_WAIT_TIMEOUT is recorded and that step's result is undefined; nothing hangs. */
+
 /* hs_attn_decode for callers that cannot hand over a workspace.  (No counterpart in the reference: there the
  * caller allocates every buffer with libtorch.)  Some hosts of this library cannot allocate device memory at
- * the point where they decode: a serving loop that is being captured into a CUDA graph (allocation is not a
- * capturable operation), an embedder whose whole device budget is owned by another allocator, or a worker
- * that must not synchronise the device, which cudaMalloc/cudaFree do.  For them the split-KV partials go into
- * an array that is part of the library image itself: 24 MiB (hs_attn_decode_static_max_bytes()), resident on
- * every GPU that loads the library for as long as the process lives.  Inputs and outputs are still the
- * caller's; the arguments mean what they mean for hs_attn_decode, minus workspace and shard outputs.
+ * the point where they decode: an embedder whose whole device budget is owned by another allocator, a worker
+ * that must not synchronise the device (cudaMalloc / cudaFree do), or a step function that runs where allocation
+ * is forbidden.  For them the split-KV partials go into an array that is part of the library image itself: 24 MiB
+ * (hs_attn_decode_static_max_bytes()), resident on every GPU that loads the library for as long as the process
+ * lives.  Inputs and outputs are still the caller's; the arguments mean what they mean for hs_attn_decode, minus
+ * workspace and shard outputs.
  *   - Shapes whose hs_attn_decode_workspace_bytes() exceeds the array are refused with HS_ERR_WORKSPACE and a
  *     message that states both sizes (at 32 query heads and head_dim 128 that is n_seqs above 170).
- *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
- *     first call before any stream capture begins.  No call allocates or frees.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress), and the first call
+ *     per device and cache layout (kind, block, scale type, head shape) configures that layout's kernel
+ *     (cudaFuncSetAttribute, an occupancy query).  Make those first calls before any stream capture begins.
+ *     No call allocates or frees device memory (tested: the device's free-memory figure does not move).
  *   - All calls share the one array, and it keeps whatever the previous call left; nothing in it needs to be
  *     zero, because a launch only reads partial slots it has just written.  Two calls whose kernels overlap on
  *     the GPU (different streams, or different host threads on one device) race on it: serialise them. */
 int64_t hs_attn_decode_static_max_bytes(void);
 int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs,
                               int32_t n_q_heads, float softmax_scale, void *out, const void *gate, hs_stream_t stream);
+
+/* One decode step of a batch as ONE call, for a host whose step inputs and result live in host memory: the
+ * reference's engine loop runs one forward per step on one thread and reads the result back
+ * (crates/hyprstream/src/runtime/torch_engine.rs:3719-3731, forward_batched_step :1475-1501); through this entry that
+ * host pays one FFI call per layer and step instead of four (copy in, cache update, attention, copy out).
+ *   host_in   pinned host memory, bf16: q [n_seqs, n_q_heads, D] | k_new [n_seqs, n_kv_heads, D] | v_new [same]
+ *   dev_in    device staging buffer of the same size (16-byte aligned); dev_out device bf16 [n_seqs, n_q_heads, D]
+ *   host_out  pinned host memory for the result, same shape as q
+ *   dst_pos, seq_lens  device int32 [n_seqs]: where each sequence's new token goes, and the length attended
+ *             (normally dst_pos + 1); sin / cos / rotary_dim / n_positions as for hs_kv_quantize_write (K rotated)
+ * Enqueues on `stream`: one host-to-device copy, hs_kv_quantize_write of the one new token per sequence,
+ * hs_attn_decode, one device-to-host copy.  With HS_STEP_SYNC in `flags` the call returns when host_out is valid;
+ * otherwise the caller synchronises the stream. */
+#define HS_STEP_SYNC 1
+int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *dev_in, const int32_t *dst_pos,
+                            const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale, const void *sin,
+                            const void *cos, int32_t rotary_dim, int32_t n_positions, void *dev_out, void *host_out,
+                            void *workspace, int64_t workspace_bytes, int32_t flags, hs_stream_t stream);
+
+/* ---- KV-length shards across GPUs, one launch per GPU and step -------------------------------------
+ * New design (the reference has no collective: crates/hyprstream/src/runtime/architectures/llama.rs:776-781 keeps
+ * every sequence's cache on one device).  One long context is cut into contiguous KV-length shards, one per GPU;
+ * every GPU runs hs_attn_decode_sharded over its shard with the same q.  Inside that one launch the kernel merges its
+ * own split-KV partials, stores the shard's (o, lse) into every rank's inbox with ordinary stores over NVLink,
+ * publishes them with a release store, waits - bounded - for the other ranks' parts and merges them: every rank ends
+ * with the same bf16 out.  (The three-call form - hs_attn_decode with o_shard / lse_shard, an all-gather,
+ * hs_attn_merge_partials_strided - stays available and serves the shapes the tensor-core kernel does not cover.)
+ *
+ * hs_shard_group owns this rank's inbox (one cudaMalloc allocation sized for max_seqs x n_q_heads rows).
+ *   several processes (one per GPU): create -> export (hs_shard_group_handle_bytes() bytes, a CUDA IPC handle) ->
+ *     exchange the handles by any host channel -> connect with all `world` handles in rank order;
+ *   one process: create every rank's group (each with its device current) -> hs_shard_group_connect_local.
+ * Every rank must call hs_attn_decode_sharded the same number of times (the step number is counted per group); a rank
+ * may run at most one step ahead of the slowest.  If a rank does not deliver within the wait limit (default 2000 ms,
+ * hs_shard_group_set_wait_ms), the waiting ranks record HS_DEVERR_WAIT_TIMEOUT, leave the affected rows of `out`
+ * unwritten and finish the launch; the context stays usable.  HS_SHARD_PUSH_ONLY makes a call deliver its part
+ * without waiting or writing an output (out may be NULL): for a rank that does not need the result, and for running
+ * several ranks one after the other on one GPU; such a rank is not held back by the others, so the caller paces it.
+ * Supported shapes: those of the tensor-core decode kernel (quantised cache; 8 kv heads x 128 with 32 query heads, or
+ * 2 x 256 with 16); others return HS_ERR_UNSUPPORTED.  No multicast load of any kind touches peer memory. */
+typedef struct hs_shard_group hs_shard_group;
+#define HS_SHARD_PUSH_ONLY 1
+int32_t hs_shard_group_create(int32_t rank, int32_t world, int32_t max_seqs, int32_t n_q_heads, int32_t head_dim,
+                              hs_shard_group **out);
+int32_t hs_shard_group_handle_bytes(void);
+int32_t hs_shard_group_export(hs_shard_group *group, void *handle_out);
+int32_t hs_shard_group_connect(hs_shard_group *group, const void *handles);
+int32_t hs_shard_group_connect_local(hs_shard_group *const *groups, int32_t world);
+int32_t hs_shard_group_set_wait_ms(hs_shard_group *group, int32_t wait_ms);
+int32_t hs_shard_group_epoch(const hs_shard_group *group); /* steps delivered so far */
+void hs_shard_group_destroy(hs_shard_group *group);
+int32_t hs_attn_decode_sharded(hs_shard_group *group, const void *q, const hs_kv_view *view, const int32_t *seq_lens,
+                               int32_t n_seqs, int32_t n_q_heads, float softmax_scale, void *out, const void *gate,
+                               void *workspace, int64_t workspace_bytes, int32_t flags, hs_stream_t stream);
 
 /* Log-sum-exp merge of `n_parts` partial results: o_parts fp32 [n_parts, n_rows, head_dim],
  * lse_parts fp32 [n_parts, n_rows] (n_rows = n_seqs * n_q_heads) -> out bf16 [n_rows, head_dim],
@@ -314,9 +377,22 @@ int64_t hs_cache_memory_usage(const hs_cache *cache);
 int64_t hs_cache_offload_bytes(const hs_cache *cache);
 int32_t hs_cache_offload(hs_cache *cache, void *host_buf, int64_t host_bytes, hs_stream_t stream);
 int32_t hs_cache_restore(hs_cache *cache, const void *host_buf, int64_t host_bytes, int32_t n_tokens, hs_stream_t stream);
-/* One hs_kv_view over the caches of a batch (one sequence each); the handle owns the device pointer tables. */
+/* The same image as hs_cache_offload writes (codes and scales as stored), but the cache keeps its contents: for
+ * checkpointing a sequence's cache and for checking stored codes (QuantizedTensor's data / absmax, kv_cache.rs:721-732). */
+int32_t hs_cache_snapshot(const hs_cache *cache, void *host_buf, int64_t host_bytes, hs_stream_t stream);
+/* One hs_kv_view over the caches of a batch (one sequence each); the handle owns the device pointer tables.
+ * The tables hold the addresses the caches had when the view was built.  These calls release or replace storage and so
+ * INVALIDATE every view built on the cache before them: hs_cache_update / hs_cache_reserve when they grow a contiguous
+ * cache past its capacity (a new, larger slab replaces the old one: 1024-token chunks) or add pages to a paged one
+ * (the new pages are not in the tables), hs_cache_clear, hs_cache_truncate_to (paged: whole pages go back to the
+ * pool), hs_cache_offload / hs_cache_restore, hs_cache_destroy.  A kernel given a stale view reads or writes memory
+ * that may belong to somebody else and cannot notice.  Reserve the capacity a decode loop will need before building
+ * its view, or check with hs_view_is_current (host-only, cheap: HS_OK, or HS_ERR_ARG naming the cache that changed)
+ * and rebuild.  The caches must outlive the view, and a pool its caches.  Growth copies on the legacy default stream
+ * and synchronises the device, so writes in flight on other streams are complete before the old slab is released. */
 int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out);
 const hs_kv_view *hs_view_get(const hs_view *view);
+int32_t hs_view_is_current(const hs_view *view);
 void hs_view_destroy(hs_view *view);
 
 #ifdef __cplusplus
