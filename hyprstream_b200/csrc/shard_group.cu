@@ -33,6 +33,7 @@ struct hs_shard_group {
     bool connected = false;
     unsigned int epoch = 0;
     int wait_ms = 2000;
+    int clock_khz = 1965000;  // SM clock of the device, read once (the attribute query is slow)
 };
 
 using namespace hs;
@@ -68,6 +69,9 @@ int32_t hs_shard_group_create(int32_t rank, int32_t world, int32_t max_seqs, int
     }
     g->base = static_cast<unsigned char *>(p);
     g->peer_base[rank] = g->base;
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, g->device) == cudaSuccess && khz > 0) g->clock_khz = khz;
+    cudaGetLastError();
     if (world == 1) g->connected = true;
     *out = g;
     return HS_OK;
@@ -188,9 +192,7 @@ int32_t hs_attn_decode_sharded(hs_shard_group *group, const void *q, const hs_kv
     if (epoch == 0) epoch = 2;  // never 0 (the cleared flags), and the halves keep alternating
     sh.epoch = epoch;
     sh.push_only = push_only ? 1 : 0;
-    int khz = 1965000;
-    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, group->device);
-    sh.wait_cycles = static_cast<long long>(group->wait_ms) * khz;
+    sh.wait_cycles = static_cast<long long>(group->wait_ms) * group->clock_khz;
     sh.rows_cap = group->rows_cap;
     sh.items_cap = group->items_cap;
     int32_t st = decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, push_only ? nullptr : out, gate, workspace, workspace_bytes,

@@ -55,6 +55,36 @@ def balance_sequences(lengths: Sequence[int], n_ranks: int) -> List[List[int]]:
     return [sorted(ix) for ix in out]
 
 
+def partition_units(n_seqs: int, n_head_groups: int, n_ranks: int) -> List[List[Tuple[int, int, int]]]:
+    """Deal the independent units of prefill and of the gated-DeltaNet layers to `n_ranks` GPUs with no data-path
+    collective: causal prefill is independent per (sequence, kv head) (architectures/llama.rs:776-781: every sequence
+    has its own cache; query heads travel with their kv head) and the DeltaNet state per (sequence, value head)
+    (qwen3_5.rs:697-699).  Sequences are dealt first; only when there are more ranks than sequences is a sequence's head
+    range cut, into equal contiguous groups.
+
+    Returns, rank by rank, a list of (sequence, head_group_begin, head_group_end) with `n_head_groups` groups per
+    sequence; every (sequence, group) appears exactly once.  A rank may get nothing when the units do not divide."""
+    if n_seqs <= 0 or n_head_groups <= 0 or n_ranks <= 0:
+        raise ValueError("partition_units: positive counts required")
+    out: List[List[Tuple[int, int, int]]] = [[] for _ in range(n_ranks)]
+    if n_ranks <= n_seqs:
+        for s in range(n_seqs):
+            out[s % n_ranks].append((s, 0, n_head_groups))
+        return out
+    per_seq = max(1, min(n_head_groups, n_ranks // n_seqs))  # ranks that share one sequence
+    while n_head_groups % per_seq != 0:
+        per_seq -= 1
+    width = n_head_groups // per_seq
+    for s in range(n_seqs):
+        for j in range(per_seq):
+            r = s * per_seq + j
+            if r < n_ranks:
+                out[r].append((s, j * width, (j + 1) * width))
+            else:  # more units than ranks after rounding: wrap around
+                out[r % n_ranks].append((s, j * width, (j + 1) * width))
+    return out
+
+
 def pack_partial(o: torch.Tensor, lse: torch.Tensor) -> torch.Tensor:
     """(o [B,Hq,D], lse [B,Hq]) -> one [B,Hq,D+1] fp32 message, so a step is a single all-gather."""
     return torch.cat([o, lse.unsqueeze(-1)], dim=-1).contiguous()
