@@ -19,7 +19,7 @@ The same JSON line carries, measured after the headline's timed regions:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference --steps 3 --warmup 1     # the reference's CPU op sequence (oracle port)
-    python bench.py --config 3|4|5 [--full]                   # one of the secondary workloads alone, as its own line
+    python bench.py --config 3|4|5                            # one of the secondary workloads alone, as its own line
 
 Multi-GPU, headline: sequences are independent (each owns its cache), so every rank decodes its own batch of 32
 sequences with no data-path collective - weak scaling; the time is the max over ranks.
@@ -528,6 +528,8 @@ def run_longctx(ctx: Ctx, context: int = 131072, steps: int = 30, warmup: int = 
 
     if world == 1:
         res["one_gpu"] = report(ctx.timed(lambda: ops.decode_attention(q, view, lens), warmup, steps))
+    else:  # this rank's shard alone, no exchange: what the exchange adds is the difference to the forms below
+        res["local_shard_decode_ms"] = ctx.timed(lambda: ops.decode_attention(q, view, lens), warmup, steps)
     res["collective"] = dict(report(ctx.timed(lambda: coll.step(q, view, lens), warmup, steps)),
                              step="decode launch + NCCL all-gather of (o, lse) + merge launch" if world > 1 else "decode launch + merge launch")
     if fused is not None:

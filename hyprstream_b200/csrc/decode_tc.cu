@@ -169,24 +169,23 @@ struct TcMergeArgs {
     ShardArgs shard;      // world > 0: the merged result is a KV-length shard's; exchange it with the other GPUs and merge again
 };
 
-// ---- peer exchange primitives (ordinary stores and loads on peer-mapped memory; system scope) ----
-__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// ---- peer exchange primitives: {value, epoch} words on peer-mapped memory, ordinary 8- and 16-byte stores and loads ----
+__device__ __forceinline__ void st_word(unsigned long long *p, float v, unsigned int epoch) {
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ void st_word2(unsigned long long *p, float v0, float v1, unsigned int epoch) {  // two adjacent words, 16-byte aligned
+    asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(v0)), "r"(epoch), "r"(__float_as_uint(v1)), "r"(epoch)
+                 : "memory");
 }
-__device__ __forceinline__ float ld_relaxed_sys(const float *p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ uint2 ld_word(const unsigned long long *p) {
+    uint2 w;
+    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+    return w;
 }
-__device__ __forceinline__ float2 ld_relaxed_sys2(const float *p) {
-    float2 v;
-    asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ uint4 ld_word2(const unsigned long long *p) {  // each 8-byte half is delivered whole; the two halves are checked separately
+    uint4 w;
+    asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(p) : "memory");
+    return w;
 }
 
 // Arrivals of all launches so far (see the grid barrier in the kernel), one counter per grid size: a launch's CTAs
@@ -756,58 +755,50 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
         float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
         if (mg.shard.world > 0) {
-            // ---- KV-length shards on several GPUs: deliver this shard's (o, lse) of the item to every rank's inbox with
-            // ordinary stores, publish it with a release store of the epoch, wait (bounded) for the other ranks' parts of the
-            // same item in the own inbox, and merge them.  All deliveries of a CTA precede its first wait.
+            // ---- KV-length shards on several GPUs: deliver this shard's (o, lse) of the item to every rank's inbox as
+            // {value, epoch} words (ordinary stores over NVLink), then wait - bounded - until the other ranks' words of the
+            // same rows carry this step's epoch in the own inbox, and merge them.  A CTA's deliveries precede its waits.
             const ShardArgs &sh = mg.shard;
             const int W = sh.world;
-            const long long half = sh.epoch & 1u;
+            const long long half = sh.epoch & 1u, stride = kD + 2;
             const float lse_mine = den > 0.0f ? M + __logf(den) : -INFINITY;
-            const long long o_at = ((half * W + sh.rank) * sh.rows_cap + row) * kD + d;
-            const long long l_at = 2LL * W * sh.rows_cap * kD + (half * W + sh.rank) * sh.rows_cap + row;
+            const long long w_mine = ((half * W + sh.rank) * sh.rows_cap + row) * stride;
             for (int s2 = 0; s2 < W; ++s2) {
-                *reinterpret_cast<float2 *>(sh.inbox[s2] + o_at) = make_float2(o0, o1);
-                if (d == 0) sh.inbox[s2][l_at] = lse_mine;
-            }
-            __syncthreads();  // every thread's stores are ordered before the release stores below (barrier + cumulative fence)
-            if (threadIdx.x < W) {
-                __threadfence_system();
-                st_release_sys(sh.flags[threadIdx.x] + (half * W + sh.rank) * sh.items_cap + item, sh.epoch);
+                st_word2(sh.inbox[s2] + w_mine + d, o0, o1, sh.epoch);
+                if (d == 0) st_word(sh.inbox[s2] + w_mine + kD, lse_mine, sh.epoch);
             }
             if (sh.push_only) continue;
-            __shared__ int s_shard_ok;
-            if (threadIdx.x == 0) s_shard_ok = 1;
-            __syncthreads();
-            if (threadIdx.x < W) {
-                const unsigned int *f = sh.flags[sh.rank] + (half * W + threadIdx.x) * sh.items_cap + item;
-                if (ld_acquire_sys(f) != sh.epoch) {
-                    const long long t0s = clock64();
-                    while (ld_acquire_sys(f) != sh.epoch) {
-                        if (clock64() - t0s > sh.wait_cycles) { s_shard_ok = 0; break; }
-                        __nanosleep(64);
+            const unsigned long long *box = sh.inbox[sh.rank];
+            int arrived = 1;
+            float Mx = -INFINITY;
+            const long long t0s = clock64();
+            for (int s2 = 0; s2 < W && arrived; ++s2) {  // every word this thread will read, from every source
+                const unsigned long long *rp = box + ((half * W + s2) * sh.rows_cap + row) * stride;
+                while (true) {
+                    const uint2 wl = ld_word(rp + kD);
+                    const uint4 wo = ld_word2(rp + d);
+                    if (wl.y == sh.epoch && wo.y == sh.epoch && wo.w == sh.epoch) {
+                        Mx = fmaxf(Mx, __uint_as_float(wl.x));
+                        break;
                     }
+                    if (clock64() - t0s > sh.wait_cycles) { arrived = 0; break; }
+                    __nanosleep(40);
                 }
             }
-            __syncthreads();
-            if (!s_shard_ok) {  // a rank did not deliver in time: recorded, this item gets no output, the launch goes on
+            if (!__syncthreads_and(arrived)) {  // a rank did not deliver in time: recorded, this item gets no output, the launch goes on
                 if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
-                __syncthreads();
                 continue;
             }
-            const float *box = sh.inbox[sh.rank];
-            float Mx = -INFINITY;
-            for (int s2 = 0; s2 < W; ++s2)
-                Mx = fmaxf(Mx, ld_relaxed_sys(box + 2LL * W * sh.rows_cap * kD + (half * W + s2) * sh.rows_cap + row));
             float nx = 0.0f, ny = 0.0f, dn = 0.0f;
             for (int s2 = 0; s2 < W; ++s2) {
-                const float ls = ld_relaxed_sys(box + 2LL * W * sh.rows_cap * kD + (half * W + s2) * sh.rows_cap + row);
+                const unsigned long long *rp = box + ((half * W + s2) * sh.rows_cap + row) * stride;
+                const float ls = __uint_as_float(ld_word(rp + kD).x);
+                const uint4 wo = ld_word2(rp + d);
                 const float w = ls == -INFINITY ? 0.0f : __expf(ls - Mx);
-                const float2 v = ld_relaxed_sys2(box + ((half * W + s2) * sh.rows_cap + row) * kD + d);
-                nx = fmaf(w, v.x, nx); ny = fmaf(w, v.y, ny); dn += w;
+                nx = fmaf(w, __uint_as_float(wo.x), nx); ny = fmaf(w, __uint_as_float(wo.z), ny); dn += w;
             }
             o0 = dn > 0.0f ? nx / dn : 0.0f;
             o1 = dn > 0.0f ? ny / dn : 0.0f;
-            __syncthreads();  // s_shard_ok is rewritten by the next item
         }
         if (mg.o_shard != nullptr) {
             *reinterpret_cast<float2 *>(mg.o_shard + row * kD + d) = make_float2(o0, o1);

@@ -61,21 +61,20 @@ static inline ViewDev to_dev(const hs_kv_view *v) {
 
 // ---- exchange of KV-length-shard results between GPUs inside the decode kernel -----------------------
 // Every rank owns an "inbox" that all ranks can address (its own memory for itself, a peer mapping for the others).
-// Layout, with W = world, R = rows_cap, D = head_dim, I = items_cap and h = epoch & 1 (two halves, so that a rank that is
-// one step ahead never overwrites what a slower rank still reads):
-//   data  (floats):  o of source s in half h at ((h * W + s) * R) * D;  lse at 2 * W * R * D + (h * W + s) * R
-//   flags (uint32):  [(h * W + s) * I + item] = the epoch in which source s last delivered `item`
-// An item is one merge work item of the decode kernel (a sequence and a group of query heads: 512 output floats).
+// A value travels as one 8-byte word {value, epoch}: 8-byte stores and loads are single transactions, so a reader that
+// sees this step's epoch in a word also sees its value - no fence and no separate flag are needed, and the latency of an
+// exchange is one trip over NVLink plus the reader's poll.  Layout in 8-byte words, with W = world, R = rows_cap,
+// D = head_dim and h = epoch & 1 (two halves, so that a rank that is one step ahead never overwrites what a slower
+// rank still reads): row `row` of source s in half h starts at ((h * W + s) * R + row) * (D + 2); words 0 .. D-1 hold the
+// normalised output, word D the log-sum-exp, word D+1 pads the row to 16 bytes.
 constexpr int kShardMaxWorld = 8;
 struct ShardArgs {
-    float *inbox[kShardMaxWorld];
-    unsigned int *flags[kShardMaxWorld];
+    unsigned long long *inbox[kShardMaxWorld];
     int rank, world;          // world == 0: no exchange
-    unsigned int epoch;       // never 0
+    unsigned int epoch;       // never 0 (a cleared inbox holds epoch 0)
     int push_only;            // deliver this rank's part, do not wait for the others, write no output
     long long wait_cycles;    // limit of the wait for the other ranks' parts
     long long rows_cap;
-    int items_cap;
 };
 
 // ---- device helpers --------------------------------------------------------------------------

@@ -3,9 +3,9 @@
 // The reference has no collective on this path (its multi-GPU support is replicas and a layer split).  A context too
 // long for one GPU is cut into contiguous KV-length shards, one per GPU; a decode step needs every shard's normalised
 // output and log-sum-exp on every GPU.  Here the decode kernel itself delivers them: after its own split-KV merge each
-// rank stores its (o, lse) into every rank's inbox with ordinary stores over NVLink (peer-mapped memory), publishes each
-// item with a release store of the step's epoch, waits - bounded - for the other ranks' parts in its own inbox and merges
-// them.  No collective library call, no second launch, nothing allocated per step.
+// rank stores its (o, lse) into every rank's inbox with ordinary stores over NVLink (peer-mapped memory) as 8-byte
+// {value, epoch} words, waits - bounded - until the other ranks' words in its own inbox carry the step's epoch and merges
+// them.  No collective library call, no second launch, no fence, nothing allocated per step.
 //
 // An inbox is one cudaMalloc allocation (so that it can be exported as a CUDA IPC handle to the other ranks' processes)
 // laid out as hs_common.cuh describes at ShardArgs.  Groups that live in one process (one host thread driving several
@@ -25,9 +25,8 @@ struct hs_shard_group {
     int rank = 0, world = 0, device = 0;
     int n_q_heads = 0, head_dim = 0;
     long long rows_cap = 0;
-    int items_cap = 0;
-    size_t data_bytes = 0, flag_bytes = 0;
-    unsigned char *base = nullptr;                      // this rank's inbox: [data | flags]
+    size_t bytes = 0;
+    unsigned char *base = nullptr;                      // this rank's inbox
     unsigned char *peer_base[hs::kShardMaxWorld] = {};  // every rank's inbox as addressable from this device
     bool peer_opened[hs::kShardMaxWorld] = {};          // mapped with cudaIpcOpenMemHandle (to be closed)
     bool connected = false;
@@ -52,14 +51,10 @@ int32_t hs_shard_group_create(int32_t rank, int32_t world, int32_t max_seqs, int
     g->rank = rank; g->world = world; g->device = current_device();
     g->n_q_heads = n_q_heads; g->head_dim = head_dim;
     g->rows_cap = static_cast<long long>(max_seqs) * n_q_heads;
-    const int heads_per_item = 512 / head_dim;
-    g->items_cap = max_seqs * ((n_q_heads + heads_per_item - 1) / heads_per_item);
-    g->data_bytes = static_cast<size_t>(2) * world * g->rows_cap * (head_dim + 1) * sizeof(float);
-    g->data_bytes = (g->data_bytes + 255) / 256 * 256;
-    g->flag_bytes = static_cast<size_t>(2) * world * g->items_cap * sizeof(unsigned int);
+    g->bytes = static_cast<size_t>(2) * world * g->rows_cap * (head_dim + 2) * sizeof(unsigned long long);
     void *p = nullptr;
-    cudaError_t e = cudaMalloc(&p, g->data_bytes + g->flag_bytes);  // never the replaceable allocator: the handle must name a whole allocation
-    if (e == cudaSuccess) e = cudaMemset(p, 0, g->data_bytes + g->flag_bytes);  // flags start at 0, which is never an epoch
+    cudaError_t e = cudaMalloc(&p, g->bytes);  // never the replaceable allocator: the handle must name a whole allocation
+    if (e == cudaSuccess) e = cudaMemset(p, 0, g->bytes);  // every word starts with epoch 0, which no step carries
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -182,10 +177,7 @@ int32_t hs_attn_decode_sharded(hs_shard_group *group, const void *q, const hs_kv
     if (!push_only && !out) return fail(HS_ERR_ARG, "hs_attn_decode_sharded: no output");
     ShardArgs sh;
     std::memset(&sh, 0, sizeof sh);
-    for (int s = 0; s < group->world; ++s) {
-        sh.inbox[s] = reinterpret_cast<float *>(group->peer_base[s]);
-        sh.flags[s] = reinterpret_cast<unsigned int *>(group->peer_base[s] + group->data_bytes);
-    }
+    for (int s = 0; s < group->world; ++s) sh.inbox[s] = reinterpret_cast<unsigned long long *>(group->peer_base[s]);
     sh.rank = group->rank;
     sh.world = group->world;
     unsigned int epoch = group->epoch + 1;
@@ -194,7 +186,6 @@ int32_t hs_attn_decode_sharded(hs_shard_group *group, const void *q, const hs_kv
     sh.push_only = push_only ? 1 : 0;
     sh.wait_cycles = static_cast<long long>(group->wait_ms) * group->clock_khz;
     sh.rows_cap = group->rows_cap;
-    sh.items_cap = group->items_cap;
     int32_t st = decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, push_only ? nullptr : out, gate, workspace, workspace_bytes,
                              nullptr, nullptr, &sh, stream);
     if (st == HS_OK) group->epoch = epoch;  // a refused call delivered nothing: the step number stands

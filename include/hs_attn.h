@@ -230,9 +230,9 @@ int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *d
  * New design (the reference has no collective: crates/hyprstream/src/runtime/architectures/llama.rs:776-781 keeps
  * every sequence's cache on one device).  One long context is cut into contiguous KV-length shards, one per GPU;
  * every GPU runs hs_attn_decode_sharded over its shard with the same q.  Inside that one launch the kernel merges its
- * own split-KV partials, stores the shard's (o, lse) into every rank's inbox with ordinary stores over NVLink,
- * publishes them with a release store, waits - bounded - for the other ranks' parts and merges them: every rank ends
- * with the same bf16 out.  (The three-call form - hs_attn_decode with o_shard / lse_shard, an all-gather,
+ * own split-KV partials, stores the shard's (o, lse) into every rank's inbox with ordinary stores over NVLink - each
+ * value travels in one 8-byte word together with the step's number, so a reader that sees the number sees the value -
+ * waits, bounded, for the other ranks' parts and merges them: every rank ends with the same bf16 out.  (The three-call form - hs_attn_decode with o_shard / lse_shard, an all-gather,
  * hs_attn_merge_partials_strided - stays available and serves the shapes the tensor-core kernel does not cover.)
  *
  * hs_shard_group owns this rank's inbox (one cudaMalloc allocation sized for max_seqs x n_q_heads rows).
