@@ -117,6 +117,15 @@ __device__ __forceinline__ float h2_sum(uint32_t w) {
     return f.x + f.y;
 }
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
+// 4-bit caches: the fp16x2 pair of code byte `k` (0..3) of word `w`, from the byte -> fp16x2 table replicated per lane in
+// shared memory (`lut_lane` = shared address of this lane's column, entries 128 bytes apart): one byte permute, one
+// multiply-add for the address, one shared load
+__device__ __forceinline__ uint32_t lut_pair(uint32_t lut_lane, uint32_t w, uint32_t k) {
+    const uint32_t byte = __byte_perm(w, 0u, 0x4440u | k);
+    uint32_t v;
+    asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(byte * 128u + lut_lane));
+    return v;
+}
 
 // FOURBIT = false: u8 codes (128 B per head row).  FOURBIT = true: NF4 / FP4 codes (64 B per head row), widened through a
 // 256-entry byte -> fp16x2 table replicated per lane (bank-conflict-free lookups).
@@ -166,6 +175,7 @@ struct TcMergeArgs {
     const uint16_t *gate; // optional
     float *o_shard, *lse_shard;  // optional fp32 shard outputs
     int counter;          // which grid-barrier counter the launch uses: one per grid size (CTAs per SM - 1)
+    int fine_items;       // merge work items of one query head instead of 512 / D (set when the batch gives the grid too few items)
     ShardArgs shard;      // world > 0: the merged result is a KV-length shard's; exchange it with the other GPUs and merge again
 };
 
@@ -223,7 +233,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         s_pref[i + 1] = (s_len[i] + kTcTile - 1) / kTcTile;
     }
     if (over && blockIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
-    const uint32_t *s_lut = reinterpret_cast<const uint32_t *>(smem + LT::kLutOff) + lane;  // entry of byte x: s_lut[32 x]
+    const uint32_t lut_lane = smem_u32(smem + LT::kLutOff) + 4u * lane;  // this lane's column of the table; entry of byte x at + 128 x
     if constexpr (FOURBIT) {
         // byte -> (table[high nibble], table[low nibble]) as fp16x2, low half = the even (first) element
         const float *tab = view.kind == HS_KV_NF4 ? c_nf4 : c_fp4;
@@ -395,7 +405,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 for (int s = 0; s < 4; ++s) {
                     qa[b][s][0] = pack_h2(clamp_h(bf16lo(ww[2 * s])), clamp_h(bf16hi(ww[2 * s])));
                     qa[b][s][1] = pack_h2(clamp_h(bf16lo(ww[2 * s + 1])), clamp_h(bf16hi(ww[2 * s + 1])));
-                    qsum[b] += h2_sum(qa[b][s][0]) + h2_sum(qa[b][s][1]);
+                    if constexpr (!FOURBIT) qsum[b] += h2_sum(qa[b][s][0]) + h2_sum(qa[b][s][1]);  // (4-bit table values carry no bias)
                 }
             }
         } else {
@@ -467,7 +477,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
 #pragma unroll
                             for (int s = 0; s < 4; ++s) {
                                 const uint32_t w = s < 2 ? kv.x : kv.y;
-                                const uint32_t b0 = s_lut[((w >> (16 * (s & 1))) & 0xffu) << 5], b1 = s_lut[((w >> (16 * (s & 1) + 8)) & 0xffu) << 5];
+                                const uint32_t b0 = lut_pair(lut_lane, w, 2 * (s & 1)), b1 = lut_pair(lut_lane, w, 2 * (s & 1) + 1);
                                 mma_rows8(sacc[nt][b], qa[b][s][0], qa[b][s][1], b0, b1);
                             }
                         }
@@ -547,7 +557,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                 for (int b = 0; b < 2; ++b) {
                     const uint32_t b0 = pack_h2(p[0][0] * pv[0][0][b], p[0][1] * pv[0][1][b]);
                     const uint32_t b1 = pack_h2(p[1][0] * pv[1][0][b], p[1][1] * pv[1][1][b]);
-                    ps_part[b] += h2_sum(b0) + h2_sum(b1);
+                    if constexpr (!FOURBIT) ps_part[b] += h2_sum(b0) + h2_sum(b1);
                     if constexpr (!FOURBIT) {
                         uint2 x[2][2];
 #pragma unroll
@@ -577,8 +587,8 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
                                 x[nt][e] = *reinterpret_cast<const uint32_t *>(sV + (tl0 + nt * 8 + 2 * j + e) * LT::kRow + head * 64 + 32 * b + 4 * g);
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint32_t la = s_lut[((x[0][0] >> (8 * k)) & 0xffu) << 5], lb = s_lut[((x[0][1] >> (8 * k)) & 0xffu) << 5];
-                            const uint32_t lc = s_lut[((x[1][0] >> (8 * k)) & 0xffu) << 5], ld = s_lut[((x[1][1] >> (8 * k)) & 0xffu) << 5];
+                            const uint32_t la = lut_pair(lut_lane, x[0][0], k), lb = lut_pair(lut_lane, x[0][1], k);
+                            const uint32_t lc = lut_pair(lut_lane, x[1][0], k), ld = lut_pair(lut_lane, x[1][1], k);
                             mma_full(O[4 * b + k], __byte_perm(la, lb, 0x5410), __byte_perm(la, lb, 0x7632), __byte_perm(lc, ld, 0x5410),
                                      __byte_perm(lc, ld, 0x7632), b0, b1);
                         }
@@ -642,18 +652,28 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     }
 
     // ================================ grid barrier, then the log-sum-exp merge ================================
-    // Work item = (sequence, group of 4 query heads).  The ring is idle after the barrier: the item's partials (2 KB of
-    // outputs and 16 bytes of log-sum-exps per contributing CTA) are brought into it with bulk copies that are all in
-    // flight at once, up to kChunk partials per round, so the merge costs one trip to L2 instead of one per batch of loads.
+    // Work item = (sequence, group of `hpi` query heads).  The ring is idle after the barrier: the item's partials (hpi * D
+    // floats of outputs and 16 bytes of log-sum-exps per contributing CTA) are brought into it with bulk copies that are all
+    // in flight at once, up to `chunk` partials per round, so the merge costs one trip to L2 instead of one per batch of
+    // loads.  hpi = 512 / D heads (2 KB per partial, 32 partials per round, a thread per output pair) when that gives the
+    // grid enough items; for a batch of few, long sequences - many partials per sequence, few items - hpi = 1: four (two)
+    // times as many items, every partial of an item in one round (120 / 60 per round), and the CTA's thread groups share
+    // an item's partials and add their sums through shared memory.
     // Everything that does not depend on other CTAs (which partials the first item needs) is worked out before the wait.
-    constexpr int kChunk = 32;
-    static_assert(kChunk * 2064 <= LT::kBarOff, "merge staging must fit in the ring");
-    float *m_val = reinterpret_cast<float *>(smem);                  // [kChunk][4][128]
-    float *m_lse = reinterpret_cast<float *>(smem + kChunk * 2048);  // [kChunk][4]
+    constexpr int kHpiCoarse = 512 / kD;
+    const int hpi = mg.fine_items ? 1 : kHpiCoarse;
+    const int row_floats = hpi * kD;                               // staged outputs per partial
+    const uint32_t part_bytes = static_cast<uint32_t>(row_floats) * 4u + 16u;
+    const int chunk = mg.fine_items ? (kD == 128 ? 120 : 60) : 32;
+    static_assert(32 * 2064 <= LT::kBarOff && 120 * 528 <= LT::kBarOff && 60 * 1040 <= LT::kBarOff, "merge staging must fit in the ring");
+    float *m_val = reinterpret_cast<float *>(smem);                                            // [chunk][hpi][D]
+    float *m_lse = reinterpret_cast<float *>(smem + static_cast<size_t>(chunk) * row_floats * 4);  // [chunk][4]
     const uint32_t bar_merge = bar_full + 2 * kTcStages * 8 + 8;
     uint32_t mphase = 0;
-    constexpr int kHpi = 512 / kD;  // query heads per work item: 2 KB of partial outputs either way
-    const int groups = n_q_heads / kHpi;
+    const int groups = n_q_heads / hpi;
+    const int item_threads = row_floats / 2;                       // a thread per output pair of the item
+    const int tgroups = kTcThreads / item_threads;                 // thread groups that share an item's partials (1, 2 or 4)
+    const int tg = threadIdx.x / item_threads, within = threadIdx.x - tg * item_threads;
     auto owner = [&](int64_t t, int r) -> int64_t {  // the CTA whose range holds tile t of sequence r
         const int64_t v = 8 * t + static_cast<int64_t>(kTcPadUnits) * (r + 1);  // the tile's first virtual unit
         int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(v) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(vtotal)) : v * n_ctas / vtotal;
@@ -664,7 +684,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     };
     auto item_parts = [&](int item, int &r, int &h0, int64_t &c_lo, int &np) {
         r = item / groups;
-        h0 = (item - r * groups) * kHpi;
+        h0 = (item - r * groups) * hpi;
         const int64_t before = s_pref[r], nt = s_pref[r + 1] - s_pref[r];
         c_lo = 0;
         np = 0;
@@ -685,7 +705,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     __shared__ int s_bar_ok;
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (has_item && np > 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(min(kChunk, np)) * 2064u);
+        if (has_item && np > 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(min(chunk, np)) * part_bytes);
         const unsigned long long n = gridDim.x;
         unsigned long long ticket;
         // release: this CTA's partials are visible device-wide before it is counted; acquire: the CTA that arrives last sees
@@ -714,20 +734,20 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     for (int item = blockIdx.x; item < n_seqs * groups; item += gridDim.x) {
         const bool first_item = item == static_cast<int>(blockIdx.x);
         if (!first_item) item_parts(item, r, h0, c_lo, np);
-        const int hh = threadIdx.x / (kD / 2), d = (threadIdx.x % (kD / 2)) * 2;  // thread = (head, column pair)
-        const int h0a = h0 & ~3, hl = h0 - h0a + hh;                            // log-sum-exps travel in aligned groups of 4 heads
+        const int hh = within / (kD / 2), d = (within % (kD / 2)) * 2;  // thread = (head of the item, column pair)
+        const int h0a = h0 & ~3, hl = h0 - h0a + hh;                    // log-sum-exps travel in aligned groups of 4 heads
         float M = -INFINITY, den = 0.0f;
         float2 num = make_float2(0.0f, 0.0f);
-        for (int p0 = 0; p0 < np; p0 += kChunk) {
-            const int n = min(kChunk, np - p0);
+        for (int p0 = 0; p0 < np; p0 += chunk) {
+            const int n = min(chunk, np - p0);
             if (!(first_item && p0 == 0)) {  // (the first round's byte count was posted before the grid barrier)
                 __syncthreads();  // the previous round's readers are done with the staging area
-                if (threadIdx.x == 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(n) * 2064u);
+                if (threadIdx.x == 0) mbar_expect_tx(bar_merge, static_cast<uint32_t>(n) * part_bytes);
                 __syncthreads();
             }
             if (threadIdx.x < n) {
                 const int64_t slot = (c_lo + r) * LT::kTH + p0 + threadIdx.x;
-                bulk_g2s(smem_u32(m_val + threadIdx.x * 512), o_part + (slot * n_q_heads + h0) * kD, 2048u, bar_merge);
+                bulk_g2s(smem_u32(m_val + threadIdx.x * row_floats), o_part + (slot * n_q_heads + h0) * kD, static_cast<uint32_t>(row_floats) * 4u, bar_merge);
                 bulk_g2s(smem_u32(m_lse + threadIdx.x * 4), lse_part + slot * n_q_heads + h0a, 16u, bar_merge);
             }
             if (!mbar_wait(bar_merge, mphase, abort_flag)) {
@@ -736,22 +756,37 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             }
             mphase ^= 1u;
             float Mc = M;
-            for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hl]);
+            for (int pi = 0; pi < n; ++pi) Mc = fmaxf(Mc, m_lse[pi * 4 + hl]);  // every thread group sees every partial's log-sum-exp
             if (Mc != -INFINITY) {
                 const float resc = M == -INFINITY ? 0.0f : __expf(M - Mc);
                 num.x *= resc; num.y *= resc; den *= resc;
                 M = Mc;
 #pragma unroll 4
-                for (int pi = 0; pi < n; ++pi) {
+                for (int pi = tg; pi < n; pi += tgroups) {  // this thread group's share of the partials
                     const float ls = m_lse[pi * 4 + hl];
                     const float w = ls == -INFINITY ? 0.0f : __expf(ls - M);
-                    const float2 v = *reinterpret_cast<const float2 *>(m_val + pi * 512 + hh * kD + d);
+                    const float2 v = *reinterpret_cast<const float2 *>(m_val + pi * row_floats + hh * kD + d);
                     den += w;
                     num.x = fmaf(w, v.x, num.x);
                     num.y = fmaf(w, v.y, num.y);
                 }
             }
         }
+        if (tgroups > 1) {  // add the thread groups' sums (same M in all of them) in group 0, through the staging area
+            __syncthreads();
+            float *red = reinterpret_cast<float *>(smem);  // [tgroups - 1][item_threads][3]
+            if (tg > 0) {
+                float *p = red + (static_cast<size_t>(tg - 1) * item_threads + within) * 3;
+                p[0] = num.x; p[1] = num.y; p[2] = den;
+            }
+            __syncthreads();
+            if (tg == 0)
+                for (int g2 = 1; g2 < tgroups; ++g2) {
+                    const float *p = red + (static_cast<size_t>(g2 - 1) * item_threads + within) * 3;
+                    num.x += p[0]; num.y += p[1]; den += p[2];
+                }
+        }
+        const bool active = tg == 0;  // the threads that own an output pair of the item
         const int64_t row = static_cast<int64_t>(r) * n_q_heads + h0 + hh;
         float o0 = den > 0.0f ? num.x / den : 0.0f, o1 = den > 0.0f ? num.y / den : 0.0f;
         if (mg.shard.world > 0) {
@@ -763,16 +798,17 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             const long long half = sh.epoch & 1u, stride = kD + 2;
             const float lse_mine = den > 0.0f ? M + __logf(den) : -INFINITY;
             const long long w_mine = ((half * W + sh.rank) * sh.rows_cap + row) * stride;
-            for (int s2 = 0; s2 < W; ++s2) {
-                st_word2(sh.inbox[s2] + w_mine + d, o0, o1, sh.epoch);
-                if (d == 0) st_word(sh.inbox[s2] + w_mine + kD, lse_mine, sh.epoch);
-            }
+            if (active)
+                for (int s2 = 0; s2 < W; ++s2) {
+                    st_word2(sh.inbox[s2] + w_mine + d, o0, o1, sh.epoch);
+                    if (d == 0) st_word(sh.inbox[s2] + w_mine + kD, lse_mine, sh.epoch);
+                }
             if (sh.push_only) continue;
             const unsigned long long *box = sh.inbox[sh.rank];
             int arrived = 1;
             float Mx = -INFINITY;
             const long long t0s = clock64();
-            for (int s2 = 0; s2 < W && arrived; ++s2) {  // every word this thread will read, from every source
+            for (int s2 = 0; s2 < W && arrived && active; ++s2) {  // every word this thread will read, from every source
                 const unsigned long long *rp = box + ((half * W + s2) * sh.rows_cap + row) * stride;
                 while (true) {
                     const uint2 wl = ld_word(rp + kD);
@@ -800,6 +836,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             o0 = dn > 0.0f ? nx / dn : 0.0f;
             o1 = dn > 0.0f ? ny / dn : 0.0f;
         }
+        if (!active) continue;
         if (mg.o_shard != nullptr) {
             *reinterpret_cast<float2 *>(mg.o_shard + row * kD + d) = make_float2(o0, o1);
             if (d == 0) mg.lse_shard[row] = den > 0.0f ? M + __logf(den) : -INFINITY;
@@ -874,7 +911,9 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     int n_ctas = 2 * sm_count();  // upper bound; the launch settles on one or two CTAs per SM
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
-    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0, ShardArgs{}};
+    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0, 0, ShardArgs{}};
+    // few, long sequences: with 512 / D heads per merge item less than half of the SMs would merge, each in several rounds
+    mg.fine_items = static_cast<int64_t>(n_seqs) * n_q_heads / (512 / v.head_dim) * 2 <= sm_count() ? 1 : 0;
     mg.shard.world = 0;
     if (shard) mg.shard = *shard;
     int32_t st;

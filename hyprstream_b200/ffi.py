@@ -19,7 +19,7 @@ KV_BF16, KV_INT8, KV_NF4, KV_FP4 = 0, 1, 2, 3
 SCALE_F32, SCALE_F16 = 0, 1
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 DEVERR_KV_WRITE_RANGE, DEVERR_ROPE_RANGE, DEVERR_DECODE_RANGE, DEVERR_WAIT_TIMEOUT = 1, 2, 4, 8
-STEP_SYNC, STEP_OUT_MAPPED, SHARD_PUSH_ONLY = 1, 2, 1
+STEP_SYNC, SHARD_PUSH_ONLY = 1, 1
 
 
 class HsError(RuntimeError):

@@ -178,11 +178,11 @@ class DecodeStep:
         self.h2d_bytes, self.d2h_bytes = self.host_in.numel() * 2, self.out_host.numel() * 2
 
     def run(self, dst_pos: torch.Tensor, seq_lens: torch.Tensor, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
-            rotary_dim: int = 0, sync: bool = True, direct_out: bool = True) -> torch.Tensor:
+            rotary_dim: int = 0, sync: bool = True) -> torch.Tensor:
         check(lib.hs_attn_decode_step(ctypes.byref(self.view), self.host_in.data_ptr(), self.dev_in.data_ptr(), _ptr(dst_pos), _ptr(seq_lens),
                                       self.n_seqs, self.hq, self.scale, _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0],
                                       self.dev_out.data_ptr(), self.out_host.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
-                                      (ffi.STEP_SYNC if sync else 0) | (ffi.STEP_OUT_MAPPED if direct_out else 0), _stream()))
+                                      ffi.STEP_SYNC if sync else 0, _stream()))
         return self.out_host
 
 

@@ -216,11 +216,8 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
  *             (normally dst_pos + 1); sin / cos / rotary_dim / n_positions as for hs_kv_quantize_write (K rotated)
  * Enqueues on `stream`: one host-to-device copy, hs_kv_quantize_write of the one new token per sequence,
  * hs_attn_decode, one device-to-host copy.  With HS_STEP_SYNC in `flags` the call returns when host_out is valid;
- * otherwise the caller synchronises the stream.  With HS_STEP_OUT_MAPPED, and host_out pinned memory that the device
- * can address (cudaHostAlloc / a registered range), the attention kernel stores its result into host_out directly and
- * the device-to-host copy falls away (dev_out is not written then); memory that is not mapped is served by the copy. */
+ * otherwise the caller synchronises the stream. */
 #define HS_STEP_SYNC 1
-#define HS_STEP_OUT_MAPPED 2
 int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *dev_in, const int32_t *dst_pos,
                             const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale, const void *sin,
                             const void *cos, int32_t rotary_dim, int32_t n_positions, void *dev_out, void *host_out,
