@@ -19,7 +19,7 @@ KV_BF16, KV_INT8, KV_NF4, KV_FP4 = 0, 1, 2, 3
 SCALE_F32, SCALE_F16 = 0, 1
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 DEVERR_KV_WRITE_RANGE, DEVERR_ROPE_RANGE, DEVERR_DECODE_RANGE, DEVERR_WAIT_TIMEOUT = 1, 2, 4, 8
-STEP_SYNC, SHARD_PUSH_ONLY = 1, 1
+STEP_SYNC, SHARD_PUSH_ONLY, SCHED_DEVICE_OBJECTS = 1, 1, 1
 
 
 class HsError(RuntimeError):
@@ -28,6 +28,45 @@ class HsError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"hs_attn status {status}: {message}")
         self.status = status
+
+
+class GdnLayerParams(ctypes.Structure):
+    """struct hs_gdn_layer_params."""
+    _fields_ = [("conv_weight", c_void_p), ("neg_a_exp", c_void_p), ("dt_bias", c_void_p), ("norm_weight", c_void_p), ("norm_eps", c_float),
+                ("n_k_heads", c_int32), ("n_v_heads", c_int32), ("head_k_dim", c_int32), ("head_v_dim", c_int32), ("kernel_size", c_int32)]
+
+
+class GdnLayerIO(ctypes.Structure):
+    """struct hs_gdn_layer_io."""
+    _fields_ = [("mixed_qkv", c_void_p), ("z", c_void_p), ("a_in", c_void_p), ("b_in", c_void_p), ("conv_state", c_void_p),
+                ("rec_state", c_void_p), ("y", c_void_p)]
+
+
+class QwenAttnParams(ctypes.Structure):
+    """struct hs_qwen_attn_params."""
+    _fields_ = [("q_norm_weight", c_void_p), ("k_norm_weight", c_void_p), ("norm_eps", c_float), ("sin", c_void_p), ("cos", c_void_p),
+                ("n_positions", c_int32), ("rotary_dim", c_int32), ("n_q_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
+                ("softmax_scale", c_float)]
+
+
+class QwenAttnIO(ctypes.Structure):
+    """struct hs_qwen_attn_io."""
+    _fields_ = [("q_proj", c_void_p), ("k_proj", c_void_p), ("v_proj", c_void_p), ("view", c_void_p), ("positions", c_void_p),
+                ("dst_pos", c_void_p), ("seq_lens", c_void_p), ("out", c_void_p)]
+
+
+class SchedPlan(ctypes.Structure):
+    """struct hs_sched_plan."""
+    _fields_ = [("n_prefill", c_int32), ("prefill_ids", POINTER(c_int64)), ("prefill_lens", POINTER(c_int32)), ("prefill_caches", POINTER(c_void_p)),
+                ("n_decode", c_int32), ("decode_ids", POINTER(c_int64)), ("decode_caches", POINTER(c_void_p)), ("host_dst_pos", POINTER(c_int32)),
+                ("view", c_void_p), ("dst_pos", c_void_p), ("seq_lens", c_void_p),
+                ("n_deferred", c_int32), ("n_stalled", c_int32), ("n_waiting", c_int32), ("n_running", c_int32)]
+
+
+class SchedStats(ctypes.Structure):
+    """struct hs_sched_stats_t."""
+    _fields_ = [("n_waiting", c_int32), ("n_running", c_int32), ("pages_free", c_int32), ("reserved", c_int32),
+                ("n_admitted", c_int64), ("n_retired", c_int64), ("n_deferred", c_int64), ("n_stalled", c_int64), ("n_steps", c_int64)]
 
 
 class KVView(ctypes.Structure):
@@ -83,6 +122,19 @@ _SIGS = {
     "hs_gdn_chunk_prefill": (c_int32, [c_void_p] * 7 + [c_int32] * 6 + [c_void_p]),
     "hs_gdn_prologue": (c_int32, [c_void_p] * 3 + [c_int32] + [c_void_p] * 9 + [c_int32] * 7 + [c_void_p]),
     "hs_gdn_epilogue": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_void_p]),
+    "hs_gdn_layer_workspace_bytes": (c_int64, [c_void_p, c_int32, c_int32]),
+    "hs_gdn_layer_forward": (c_int32, [c_void_p] * 7 + [c_int32] * 3 + [c_void_p, c_void_p, c_int64, c_void_p]),
+    "hs_qwen_attn_layer_workspace_bytes": (c_int64, [c_void_p, c_int32, c_int32]),
+    "hs_qwen_attn_layer_forward": (c_int32, [c_void_p] * 4 + [POINTER(KVView)] + [c_void_p] * 3 + [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
+    "hs_qwen_block_workspace_bytes": (c_int64, [c_void_p, c_int32, c_void_p, c_int32, c_int32]),
+    "hs_qwen_block_forward": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]),
+    "hs_sched_create": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),
+    "hs_sched_destroy": (None, [c_void_p]),
+    "hs_sched_submit": (c_int32, [c_void_p, c_int64, c_int32, c_int32]),
+    "hs_sched_plan_step": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p]),
+    "hs_sched_commit_step": (c_int32, [c_void_p, c_void_p, c_int32]),
+    "hs_sched_cancel": (c_int32, [c_void_p, c_int64]),
+    "hs_sched_stats": (c_int32, [c_void_p, c_void_p]),
     "hs_host_set_allocator": (c_int32, [c_void_p, c_void_p]),
     "hs_pool_create": (c_int32, [c_int32] * 7 + [POINTER(c_void_p)]),
     "hs_pool_destroy": (None, [c_void_p]),

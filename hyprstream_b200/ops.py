@@ -269,6 +269,102 @@ def gdn_epilogue(o: torch.Tensor, z: torch.Tensor, norm_weight: torch.Tensor, ep
     return y
 
 
+class GdnLayer:
+    """The weights of one gated-DeltaNet layer that its elementwise steps use, and the batched layer call
+    (hs_gdn_layer_forward: conv1d + SiLU + split + L2 norm + gates -> delta rule -> RMSNormGated; qwen3_5.rs:606-802
+    between in_proj and out_proj)."""
+
+    def __init__(self, conv_weight: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor, n_k_heads: int,
+                 n_v_heads: int, head_k_dim: int = 128, head_v_dim: int = 128, norm_eps: float = 1e-6):
+        _need_cuda(conv_weight, a_log, dt_bias, norm_weight)
+        self.conv_weight = conv_weight.reshape(conv_weight.shape[0], -1).contiguous()
+        self.neg_a_exp = (-a_log.float().exp()).contiguous()
+        self.dt_bias, self.norm_weight = dt_bias.float().contiguous(), norm_weight.float().contiguous()
+        self.nk, self.nv, self.hk, self.hv = n_k_heads, n_v_heads, head_k_dim, head_v_dim
+        self.params = ffi.GdnLayerParams(self.conv_weight.data_ptr(), self.neg_a_exp.data_ptr(), self.dt_bias.data_ptr(), self.norm_weight.data_ptr(),
+                                         float(norm_eps), n_k_heads, n_v_heads, head_k_dim, head_v_dim, self.conv_weight.shape[1])
+
+    def new_states(self, n_seqs: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(conv_state bf16 [B, conv_dim, ks-1], rec_state f32 [B, nv, hk, hv]), one row per sequence."""
+        conv_dim = (2 * self.nk * self.hk) + self.nv * self.hv
+        return (torch.zeros(n_seqs, conv_dim, self.conv_weight.shape[1] - 1, dtype=torch.bfloat16, device=device),
+                torch.zeros(n_seqs, self.nv, self.hk, self.hv, dtype=torch.float32, device=device))
+
+    def workspace(self, n_seqs: int, n_tokens: int, device) -> torch.Tensor:
+        need = lib.hs_gdn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)
+        return torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+
+    def forward(self, mixed_qkv: torch.Tensor, z: torch.Tensor, a_in: torch.Tensor, b_in: torch.Tensor, conv_state: torch.Tensor,
+                rec_state: torch.Tensor, has_state: bool, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """mixed_qkv bf16 [B, T, conv_dim]; z bf16 [B, T, nv, hv]; a_in, b_in bf16 [B, T, nv]; states updated in place.
+        Returns y bf16 [B, T, nv, hv]."""
+        _need_cuda(mixed_qkv, z, a_in, b_in, conv_state, rec_state)
+        b, t = mixed_qkv.shape[0], mixed_qkv.shape[1]
+        ws = self.workspace(b, t, mixed_qkv.device) if workspace is None else workspace
+        y = torch.empty(b, t, self.nv, self.hv, dtype=torch.bfloat16, device=mixed_qkv.device)
+        check(lib.hs_gdn_layer_forward(ctypes.byref(self.params), _ptr(mixed_qkv), _ptr(z), _ptr(a_in), _ptr(b_in), _ptr(conv_state), _ptr(rec_state),
+                                       1 if has_state else 0, b, t, _ptr(y), _ptr(ws), ws.numel(), _stream()))
+        return y
+
+
+class QwenAttnLayer:
+    """Qwen3.5 gated full attention between its projections (hs_qwen_attn_layer_forward; qwen3_5.rs:902-1075): QK-norm
+    with (1 + w), partial RoPE, gate split, cache update, decode or prompt attention, output gate."""
+
+    def __init__(self, q_norm_weight: torch.Tensor, k_norm_weight: torch.Tensor, sin: torch.Tensor, cos: torch.Tensor, rotary_dim: int,
+                 n_q_heads: int, n_kv_heads: int, head_dim: int, norm_eps: float = 1e-6, softmax_scale: Optional[float] = None):
+        _need_cuda(q_norm_weight, k_norm_weight, sin, cos)
+        self.qw, self.kw, self.sin, self.cos = q_norm_weight.float().contiguous(), k_norm_weight.float().contiguous(), sin, cos
+        self.hq, self.hkv, self.d = n_q_heads, n_kv_heads, head_dim
+        scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else softmax_scale
+        self.params = ffi.QwenAttnParams(self.qw.data_ptr(), self.kw.data_ptr(), float(norm_eps), sin.data_ptr(), cos.data_ptr(), sin.shape[0],
+                                         rotary_dim, n_q_heads, n_kv_heads, head_dim, float(scale))
+
+    def workspace(self, n_seqs: int, n_tokens: int, device) -> torch.Tensor:
+        need = lib.hs_qwen_attn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)
+        return torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+
+    def forward(self, q_proj: torch.Tensor, k_proj: torch.Tensor, v_proj: torch.Tensor, view: KVView, positions: torch.Tensor,
+                dst_pos: torch.Tensor, seq_lens: Optional[torch.Tensor], n_seqs: int, n_tokens: int,
+                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """q_proj bf16 [B*T, Hq*2*D]; k_proj bf16 [B*T, Hkv*D]; v_proj bf16 [B, T, Hkv, D]; positions int32 [B*T]; dst_pos,
+        seq_lens int32 [B].  Returns bf16 [B, T, Hq, D]."""
+        _need_cuda(q_proj, k_proj, v_proj, positions, dst_pos, seq_lens)
+        ws = self.workspace(n_seqs, n_tokens, q_proj.device) if workspace is None else workspace
+        out = torch.empty(n_seqs, n_tokens, self.hq, self.d, dtype=torch.bfloat16, device=q_proj.device)
+        check(lib.hs_qwen_attn_layer_forward(ctypes.byref(self.params), _ptr(q_proj), _ptr(k_proj), _ptr(v_proj), ctypes.byref(view), _ptr(positions),
+                                             _ptr(dst_pos), _ptr(seq_lens), n_seqs, n_tokens, _ptr(out), _ptr(ws), ws.numel(), _stream()))
+        return out
+
+
+def qwen_block_forward(gdn_layers: Sequence[GdnLayer], gdn_inputs: Sequence[tuple], attn: Optional[QwenAttnLayer], attn_inputs: Optional[tuple],
+                       has_state: bool, n_seqs: int, n_tokens: int, device, workspace: Optional[torch.Tensor] = None):
+    """hs_qwen_block_forward: the DeltaNet layers of a block, then its full-attention layer, in one call.
+
+    gdn_inputs[i] = (mixed_qkv, z, a_in, b_in, conv_state, rec_state); attn_inputs = (q_proj, k_proj, v_proj, view, positions,
+    dst_pos, seq_lens).  Returns ([y_i bf16 [B, T, nv, hv]], out bf16 [B, T, Hq, D] or None)."""
+    n = len(gdn_layers)
+    params = (ffi.GdnLayerParams * max(n, 1))(*[l.params for l in gdn_layers])
+    ys, ios = [], (ffi.GdnLayerIO * max(n, 1))()
+    for i, (layer, inp) in enumerate(zip(gdn_layers, gdn_inputs)):
+        _need_cuda(*inp)
+        y = torch.empty(n_seqs, n_tokens, layer.nv, layer.hv, dtype=torch.bfloat16, device=device)
+        ys.append(y)
+        ios[i] = ffi.GdnLayerIO(*[_ptr(t) for t in inp], _ptr(y))
+    out, ap, aio = None, None, None
+    if attn is not None:
+        q_proj, k_proj, v_proj, view, positions, dst_pos, seq_lens = attn_inputs
+        _need_cuda(q_proj, k_proj, v_proj, positions, dst_pos, seq_lens)
+        out = torch.empty(n_seqs, n_tokens, attn.hq, attn.d, dtype=torch.bfloat16, device=device)
+        ap = ctypes.byref(attn.params)
+        aio = ffi.QwenAttnIO(_ptr(q_proj), _ptr(k_proj), _ptr(v_proj), ctypes.addressof(view), _ptr(positions), _ptr(dst_pos), _ptr(seq_lens), _ptr(out))
+    need = lib.hs_qwen_block_workspace_bytes(params, n, ap, n_seqs, n_tokens)
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=device) if workspace is None else workspace
+    check(lib.hs_qwen_block_forward(params, ios, n, ap, None if aio is None else ctypes.byref(aio), 1 if has_state else 0, n_seqs, n_tokens,
+                                    _ptr(ws), ws.numel(), _stream()))
+    return ys, out
+
+
 def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: Optional[float] = None,
                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal GQA prefill (llama.rs:1023-1119; qwen3_5.rs:1012-1059 with `gate`).

@@ -330,6 +330,76 @@ int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *co
 int32_t hs_gdn_epilogue(const float *o, const void *z, const float *norm_weight, float eps, void *y, int64_t n_rows,
                         int32_t head_v_dim, hs_stream_t stream);
 
+/* ---- Qwen3.5 hybrid layers, batched -----------------------------------------------------------
+ * What GatedDeltaNetLayer::forward (architectures/qwen3_5.rs:606-802) and Qwen3_5FullAttention::forward
+ * (qwen3_5.rs:902-1075) do between their input and output projections, for a batch of sequences, one call per layer;
+ * and a run of DeltaNet layers followed by one full-attention layer as one call.  The reference has no batched entry
+ * for this architecture (ModelOperations::forward_batched is Llama-only, the trait default errors:
+ * architectures/mod.rs:268-280; its layer dispatch qwen3_5.rs:1864-1933 keeps one rec_state / conv_state slot per
+ * layer): here the states are batch-major tensors of the caller, one row per sequence, updated in place, and row s of a
+ * batch computes exactly what the unbatched call computes for sequence s.  The projections (GEMMs) stay with the host.
+ *
+ * DeltaNet layer: hs_gdn_prologue -> hs_gdn_recurrent (n_tokens == 1, the decode step) or hs_gdn_chunk_prefill
+ * (n_tokens > 1, the prompt; qwen3_5.rs:725-769) -> hs_gdn_epilogue.
+ *   mixed_qkv, a_in, b_in, conv_state  as for hs_gdn_prologue;  z bf16 [n_seqs, n_tokens, n_v_heads, head_v_dim]
+ *   rec_state  f32 [n_seqs, n_v_heads, head_k_dim, head_v_dim] in/out; has_state == 0 starts conv_state and rec_state at zero
+ *   y          bf16 [n_seqs, n_tokens, n_v_heads, head_v_dim] -> the input of out_proj
+ * Full-attention layer: hs_qk_norm_rope on q (gate split, (1 + w) norm, partial RoPE) and k -> hs_kv_quantize_write ->
+ * hs_attn_decode over the cache (n_tokens == 1) or hs_attn_prefill_causal over the fresh K/V (n_tokens > 1: a prompt
+ * that starts at position 0; a continued prompt goes through hs_kv_gather_dequantize and hs_attn_prefill_causal with
+ * kv_len > q_len), with the output gate.
+ *   q_proj bf16 [n_seqs * n_tokens, n_q_heads * 2 * head_dim] (per head: query | gate, qwen3_5.rs:965-967)
+ *   k_proj bf16 [n_seqs * n_tokens, n_kv_heads * head_dim];  v_proj bf16 [n_seqs, n_tokens, n_kv_heads, head_dim]
+ *   positions device int32 [n_seqs * n_tokens] (RoPE rows); dst_pos device int32 [n_seqs] (cache position of each
+ *   sequence's first new token); seq_lens device int32 [n_seqs] (length attended by a decode step, dst_pos + 1)
+ *   out bf16 [n_seqs, n_tokens, n_q_heads, head_dim] -> the input of o_proj
+ * Workspaces: 256-byte aligned device memory of at least the *_workspace_bytes() figure; nothing is allocated. */
+typedef struct hs_gdn_layer_params {
+    const void *conv_weight;   /* bf16 [conv_dim, kernel_size] */
+    const float *neg_a_exp;    /* f32 [n_v_heads] = -exp(A_log) */
+    const float *dt_bias;      /* f32 [n_v_heads] */
+    const float *norm_weight;  /* f32 [head_v_dim] */
+    float norm_eps;
+    int32_t n_k_heads, n_v_heads, head_k_dim, head_v_dim, kernel_size;
+} hs_gdn_layer_params;
+typedef struct hs_gdn_layer_io {
+    const void *mixed_qkv, *z, *a_in, *b_in;
+    void *conv_state;
+    float *rec_state;
+    void *y;
+} hs_gdn_layer_io;
+typedef struct hs_qwen_attn_params {
+    const float *q_norm_weight, *k_norm_weight; /* f32 [head_dim], applied as (1 + w) */
+    float norm_eps;
+    const void *sin, *cos;                      /* bf16 [n_positions, rotary_dim / 2] */
+    int32_t n_positions, rotary_dim;
+    int32_t n_q_heads, n_kv_heads, head_dim;
+    float softmax_scale;
+} hs_qwen_attn_params;
+typedef struct hs_qwen_attn_io {
+    const void *q_proj, *k_proj, *v_proj;
+    const hs_kv_view *view;
+    const int32_t *positions, *dst_pos, *seq_lens;
+    void *out;
+} hs_qwen_attn_io;
+int64_t hs_gdn_layer_workspace_bytes(const hs_gdn_layer_params *params, int32_t n_seqs, int32_t n_tokens);
+int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixed_qkv, const void *z, const void *a_in,
+                             const void *b_in, void *conv_state, float *rec_state, int32_t has_state, int32_t n_seqs,
+                             int32_t n_tokens, void *y, void *workspace, int64_t workspace_bytes, hs_stream_t stream);
+int64_t hs_qwen_attn_layer_workspace_bytes(const hs_qwen_attn_params *params, int32_t n_seqs, int32_t n_tokens);
+int32_t hs_qwen_attn_layer_forward(const hs_qwen_attn_params *params, const void *q_proj, const void *k_proj,
+                                   const void *v_proj, const hs_kv_view *view, const int32_t *positions,
+                                   const int32_t *dst_pos, const int32_t *seq_lens, int32_t n_seqs, int32_t n_tokens,
+                                   void *out, void *workspace, int64_t workspace_bytes, hs_stream_t stream);
+/* n_gdn DeltaNet layers (parameters gdn[i], tensors gdn_io[i]) and then, if attn is non-NULL, one full-attention layer,
+ * all for the same batch and token count, sharing one workspace (hs_qwen_block_workspace_bytes: the largest need). */
+int64_t hs_qwen_block_workspace_bytes(const hs_gdn_layer_params *gdn, int32_t n_gdn, const hs_qwen_attn_params *attn,
+                                      int32_t n_seqs, int32_t n_tokens);
+int32_t hs_qwen_block_forward(const hs_gdn_layer_params *gdn, const hs_gdn_layer_io *gdn_io, int32_t n_gdn,
+                              const hs_qwen_attn_params *attn, const hs_qwen_attn_io *attn_io, int32_t has_state,
+                              int32_t n_seqs, int32_t n_tokens, void *workspace, int64_t workspace_bytes,
+                              hs_stream_t stream);
+
 /* ---- host-side cache objects ------------------------------------------------------------------
  * C++ mirror of the reference's per-layer cache (crates/hyprstream/src/runtime/kv_cache.rs): LayerKVCache
  * (:1029-1900: new / new_paged / update / get / clear / truncate_to / seq_pos / memory_usage) and BlockPool
@@ -394,6 +464,55 @@ int32_t hs_view_create(hs_cache *const *caches, int32_t n_caches, hs_view **out)
 const hs_kv_view *hs_view_get(const hs_view *view);
 int32_t hs_view_is_current(const hs_view *view);
 void hs_view_destroy(hs_view *view);
+
+/* ---- continuous-batching scheduler ---------------------------------------------------------------
+ * The loop around the batched decode step that the reference leaves open: its engine has the batched step
+ * (crates/hyprstream/src/runtime/torch_engine.rs:1475-1501 forward_batched_step) and two settings
+ * (crates/hyprstream/src/config/mod.rs:2146-2152: continuous_batching, continuous_batch_max = 16) but no caller, and
+ * its pool's typed exhaustion error says what a scheduler is to do with it (kv_cache.rs:482-505: defer admission and
+ * retry once other sequences release blocks).  One scheduler serves one layer stack's pool; the host drives it from
+ * the engine's single thread:
+ *     hs_sched_submit(...)                                  any time: queue a sequence (prompt length, token budget)
+ *     loop:  hs_sched_plan_step(..., &plan)                 admit while pages last (FIFO; a sequence whose prompt does not
+ *                                                           fit is DEFERRED, not failed), plan the decode batch
+ *            run the plan: prefill plan.prefill_caches[i] with its prompt (hs_cache_update + prefill attention), and
+ *            one batched decode step over plan.view with plan.dst_pos / plan.seq_lens (hs_kv_quantize_write +
+ *            hs_attn_decode, or hs_attn_decode_step)
+ *            hs_sched_commit_step(..., finished ids)        positions advance, finished sequences are retired and their
+ *                                                           pages go back to the pool for the deferred ones
+ * Running sequences come before new ones: a running sequence that cannot get a page for its next token sits the step
+ * out (n_stalled) and keeps its pages; there is no preemption, so when nothing at all can move the plan call returns
+ * HS_ERR_POOL_EXHAUSTED and the host must retire something.  Sequence ids are >= 0 and tag the pool's pages.
+ * Pointers in a plan belong to the scheduler and are valid until the next plan or commit; dst_pos / seq_lens / view
+ * are device objects, built only with HS_SCHED_DEVICE_OBJECTS (without it the call is pure host logic). */
+typedef struct hs_sched hs_sched;
+#define HS_SCHED_DEVICE_OBJECTS 1
+typedef struct hs_sched_plan {
+    int32_t n_prefill;                 /* sequences admitted by this plan: prefill them before the decode step */
+    const int64_t *prefill_ids;
+    const int32_t *prefill_lens;
+    hs_cache *const *prefill_caches;
+    int32_t n_decode;                  /* the decode batch, in admission order */
+    const int64_t *decode_ids;
+    hs_cache *const *decode_caches;
+    const int32_t *host_dst_pos;       /* host copy of dst_pos */
+    const hs_kv_view *view;            /* device objects (NULL without HS_SCHED_DEVICE_OBJECTS or with an empty batch) */
+    const int32_t *dst_pos, *seq_lens; /* device int32 [n_decode]: cache position of the new token, length attended */
+    int32_t n_deferred, n_stalled, n_waiting, n_running;
+} hs_sched_plan;
+typedef struct hs_sched_stats_t {
+    int32_t n_waiting, n_running, pages_free, reserved;
+    int64_t n_admitted, n_retired, n_deferred, n_stalled, n_steps;
+} hs_sched_stats_t;
+int32_t hs_sched_create(hs_pool *pool, int32_t continuous_batch_max, int32_t max_seq_len, hs_sched **out);
+void hs_sched_destroy(hs_sched *sched);
+int32_t hs_sched_submit(hs_sched *sched, int64_t seq_id, int32_t prompt_len, int32_t max_new_tokens);
+int32_t hs_sched_plan_step(hs_sched *sched, int32_t flags, hs_sched_plan *plan, hs_stream_t stream);
+int32_t hs_sched_commit_step(hs_sched *sched, const int64_t *finished_ids, int32_t n_finished);
+/* Between steps: drop a queued sequence, or retire a running one and return its pages (a client that went away; the way
+ * out when hs_sched_plan_step reports that nothing can make progress). */
+int32_t hs_sched_cancel(hs_sched *sched, int64_t seq_id);
+int32_t hs_sched_stats(const hs_sched *sched, hs_sched_stats_t *out);
 
 #ifdef __cplusplus
 }
