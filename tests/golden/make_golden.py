@@ -6,6 +6,12 @@ The reference holds no golden vectors for this path, so these fixtures are made 
                       quantiser specification (oracle/quant_spec.c), both restatements agreeing;
 * attn_*.npz        — small seeded attention cases with the outputs of the ATen op-for-op
                       restatement (oracle/attention_ref.py);
+* attn_hf_*.npz     — attention cases whose expected outputs come from the independent implementation in
+                      `transformers` (models/llama/modeling_llama.py: apply_rotary_pos_emb, repeat_kv,
+                      eager_attention_forward; models/qwen3_5/modeling_qwen3_5.py: Qwen3_5RMSNorm, its partial-rotary
+                      apply_rotary_pos_emb, eager_attention_forward, and the gate arithmetic of Qwen3_5Attention.forward):
+                      the functions are imported and called, so the oracle in oracle/attention_ref.py is checked against
+                      something other than itself;
 * gdn_hf_*.npz      — gated-DeltaNet cases whose expected outputs come from the independent
                       implementation in `transformers` (models/qwen3_5/modeling_qwen3_5.py:
                       torch_chunk_gated_delta_rule / torch_recurrent_gated_delta_rule), the function the
@@ -112,9 +118,75 @@ def gdn_cases():
                         state_rec=s_r.float().numpy())
 
 
+def attn_hf_cases():
+    """Llama RoPE + eager attention and Qwen3.5 gated attention computed by `transformers` (imported, not restated)."""
+    import types
+
+    from transformers.models.llama import modeling_llama as ml
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as mq
+
+    def hf_tables(dim, base, n_pos):
+        # the inverse frequencies and angles as LlamaRotaryEmbedding forms them (fp32), cos / sin cast to the model dtype
+        inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim))
+        freqs = torch.arange(n_pos, dtype=torch.float32)[:, None] * inv[None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+
+    def causal_additive(q_len, kv_len):
+        m = torch.zeros(q_len, kv_len)
+        m.masked_fill_(torch.arange(kv_len)[None, :] > torch.arange(q_len)[:, None] + (kv_len - q_len), float("-inf"))
+        return m[None, None]
+
+    torch.manual_seed(21)
+    # ---- Llama: 8 q / 2 kv heads, d = 128, 90 cached tokens; one decode token and a 5-token forward at start_pos 85
+    hq, hkv, d, L = 8, 2, 128, 90
+    cos, sin = hf_tables(d, 500000.0, 128)
+    k = torch.randn(1, L, hkv, d).bfloat16()
+    v = torch.randn(1, L, hkv, d).bfloat16()
+    out = {"k": bf16_bits(k), "v": bf16_bits(v)}
+    mod = types.SimpleNamespace(num_key_value_groups=hq // hkv, training=False)
+    for name, ql in (("decode", 1), ("cached5", 5)):
+        q = torch.randn(1, ql, hq, d).bfloat16()
+        pos_q = torch.arange(L - ql, L)
+        q_r, _ = ml.apply_rotary_pos_emb(q.transpose(1, 2), q.transpose(1, 2), cos[pos_q][None], sin[pos_q][None])
+        k_r, _ = ml.apply_rotary_pos_emb(k.transpose(1, 2), k.transpose(1, 2), cos[:L][None], sin[:L][None])
+        # fp32 operands: the reference upcasts q, K and V before the contraction (llama.rs:1044-1068)
+        o, _ = ml.eager_attention_forward(mod, q_r.float(), k_r.float(), v.transpose(1, 2).float(), causal_additive(ql, L) if ql > 1 else None,
+                                          scaling=d ** -0.5)
+        out.update({f"q_{name}": bf16_bits(q), f"q_rope_{name}": bf16_bits(q_r.transpose(1, 2)), f"out_{name}": o.float().numpy()})
+        out["k_rope"] = bf16_bits(k_r.transpose(1, 2))
+    np.savez_compressed(os.path.join(OUT, "attn_hf_llama.npz"), **out)
+    # ---- Qwen3.5 gated full attention: 8 q / 2 kv heads, d = 256, rotary 64, 70 cached tokens, decode and 4-token forward
+    hq, hkv, d, rd, L = 8, 2, 256, 64, 70
+    cos, sin = hf_tables(rd, 10000.0, 128)
+    qn, kn = mq.Qwen3_5RMSNorm(d, eps=1e-6), mq.Qwen3_5RMSNorm(d, eps=1e-6)
+    with torch.no_grad():
+        qn.weight.copy_(0.1 * torch.randn(d)); kn.weight.copy_(0.1 * torch.randn(d))
+    k_proj = torch.randn(1, L, hkv, d).bfloat16()
+    v = torch.randn(1, L, hkv, d).bfloat16()
+    mod = types.SimpleNamespace(num_key_value_groups=hq // hkv, training=False)
+    out = {"k_proj": bf16_bits(k_proj), "v": bf16_bits(v), "q_norm_w": qn.weight.detach().numpy(), "k_norm_w": kn.weight.detach().numpy()}
+    with torch.no_grad():
+        for name, ql in (("decode", 1), ("cached4", 4)):
+            q_proj = torch.randn(1, ql, hq, 2 * d).bfloat16()                    # per head: query | gate
+            query, gate = torch.chunk(q_proj, 2, dim=-1)
+            pos_q = torch.arange(L - ql, L)
+            qs = qn(query).transpose(1, 2)
+            ks = kn(k_proj).transpose(1, 2)
+            qs_r, _ = mq.apply_rotary_pos_emb(qs, qs, cos[pos_q][None], sin[pos_q][None])
+            ks_r, _ = mq.apply_rotary_pos_emb(ks, ks, cos[:L][None], sin[:L][None])
+            o, _ = mq.eager_attention_forward(mod, qs_r, ks_r, v.transpose(1, 2), causal_additive(ql, L).bfloat16() if ql > 1 else None,
+                                              scaling=d ** -0.5)
+            o = o.reshape(1, ql, -1) * torch.sigmoid(gate.reshape(1, ql, -1))
+            out.update({f"q_proj_{name}": bf16_bits(q_proj), f"q_rope_{name}": bf16_bits(qs_r.transpose(1, 2)), f"out_{name}": bf16_bits(o.reshape(1, ql, hq, d))})
+            out["k_rope"] = bf16_bits(ks_r.transpose(1, 2))
+    np.savez_compressed(os.path.join(OUT, "attn_hf_qwen.npz"), **out)
+
+
 if __name__ == "__main__":
     quant_cases()
     attn_cases()
+    attn_hf_cases()
     gdn_cases()
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):

@@ -146,3 +146,65 @@ def test_gdn_oracle_matches_independent_implementation():
     o2, s2 = gr.recurrent_sequence(qs, k, v, gg, beta, s0)
     assert np.abs(o2.numpy() - g["out_rec"]).max() < 1e-5 and np.abs(s2.numpy() - g["state_rec"]).max() < 1e-5
     assert (o - o2).abs().max() < 1e-4 and (s - s2).abs().max() < 1e-4  # chunked == recurrent
+
+
+# ---- the attention oracle against `transformers` (fixtures made by tests/golden/make_golden.py::attn_hf_cases) ----
+def _mostly_equal_bf16(mine: torch.Tensor, ref: torch.Tensor, what: str, frac: float = 0.97):
+    """bf16 results of two implementations that differ only in fp32 operation order: nearly all elements equal bit for
+    bit, none further apart than two bf16 steps of the row's scale."""
+    a, b = mine.float(), ref.float()
+    diff = (a - b).abs()
+    scale = b.abs().amax(dim=-1, keepdim=True).clamp_min(1e-6)
+    assert torch.all(diff <= 2 ** -6 * scale), f"{what}: max diff {diff.max().item():.3g}"
+    assert (diff == 0).float().mean().item() >= frac, f"{what}: only {(diff == 0).float().mean().item():.4f} equal"
+
+
+def test_llama_rope_and_attention_oracle_match_transformers():
+    """RoPE::apply_rotary_pos_emb (rope.rs:100-248) and the Llama attention core (llama.rs:1023-1119) as restated by the
+    oracle, against transformers' apply_rotary_pos_emb / repeat_kv / eager_attention_forward on the same inputs: one
+    decode token and a 5-token forward over a cached prefix."""
+    g = np.load(os.path.join(GOLD, "attn_hf_llama.npz"))
+    k, v = bf16_from_bits(g["k"]), bf16_from_bits(g["v"])
+    L, hkv, d = k.shape[1], k.shape[2], k.shape[3]
+    sin, cos = ar.rope_tables(d, 500000.0, 128, torch.bfloat16)
+    k_rot = ar.apply_rope(k, sin, cos, torch.arange(L))
+    _mostly_equal_bf16(k_rot, bf16_from_bits(g["k_rope"]), "k rope")
+    for name, ql in (("decode", 1), ("cached5", 5)):
+        q = bf16_from_bits(g[f"q_{name}"])
+        hq = q.shape[2]
+        q_rot = ar.apply_rope(q, sin, cos, torch.arange(L - ql, L))
+        _mostly_equal_bf16(q_rot, bf16_from_bits(g[f"q_rope_{name}"]), f"q rope {name}")
+        # the attention core on transformers' own rotated tensors, so that only the attention arithmetic is compared
+        out = ar.llama_attention_core(bf16_from_bits(g[f"q_rope_{name}"]), bf16_from_bits(g["k_rope"]), v, hq).reshape(1, ql, hq, d)
+        ref = torch.from_numpy(g[f"out_{name}"])                      # fp32 [1, ql, Hq, D]
+        _mostly_equal_bf16(out, ref.bfloat16(), f"attention {name}", frac=0.95)
+        diff = (out.float() - ref).abs()
+        assert diff.max().item() <= 2e-2 and diff.mean().item() <= 2e-3
+        # and the fp32 recomputation that anchors the kernels' tolerance is the same mathematics
+        fp32 = ar.attention_fp32(bf16_from_bits(g[f"q_rope_{name}"]), bf16_from_bits(g["k_rope"]), v)
+        assert (fp32 - ref).abs().max().item() <= 1e-5
+
+
+def test_qwen_gated_attention_oracle_matches_transformers():
+    """QK-norm with (1 + w), partial RoPE, gate split and the gated attention core (qwen3_5.rs:902-1091) as restated by
+    the oracle, against transformers' Qwen3_5RMSNorm, apply_rotary_pos_emb, eager_attention_forward and the gate
+    arithmetic of Qwen3_5Attention.forward."""
+    g = np.load(os.path.join(GOLD, "attn_hf_qwen.npz"))
+    k_proj, v = bf16_from_bits(g["k_proj"]), bf16_from_bits(g["v"])
+    qw, kw = torch.from_numpy(g["q_norm_w"]), torch.from_numpy(g["k_norm_w"])
+    L, hkv, d = k_proj.shape[1], k_proj.shape[2], k_proj.shape[3]
+    rd = 64
+    sin, cos = ar.rope_tables(rd, 10000.0, 128, torch.bfloat16)
+    k_rot = ar.apply_partial_rope(ar.qk_norm(k_proj, kw, 1e-6), sin, cos, torch.arange(L), rd)
+    _mostly_equal_bf16(k_rot, bf16_from_bits(g["k_rope"]), "k norm + rope")
+    for name, ql in (("decode", 1), ("cached4", 4)):
+        q_proj = bf16_from_bits(g[f"q_proj_{name}"])                 # [1, ql, Hq, 2 D]: query | gate
+        hq = q_proj.shape[2]
+        query, gate = q_proj[..., :d], q_proj[..., d:]
+        q_rot = ar.apply_partial_rope(ar.qk_norm(query, qw, 1e-6), sin, cos, torch.arange(L - ql, L), rd)
+        _mostly_equal_bf16(q_rot, bf16_from_bits(g[f"q_rope_{name}"]), f"q norm + rope {name}")
+        out = ar.qwen_gated_attention_core(bf16_from_bits(g[f"q_rope_{name}"]), gate.contiguous(), bf16_from_bits(g["k_rope"]), v, hq).reshape(1, ql, hq, d)
+        ref = bf16_from_bits(g[f"out_{name}"]).float()
+        # transformers forms the scores in bf16, the reference in fp32 (qwen3_5.rs:1021-1032): equal within the path's tolerance
+        diff = (out.float() - ref).abs()
+        assert diff.max().item() <= 2e-2 and diff.mean().item() <= 2e-3, (name, diff.max().item(), diff.mean().item())

@@ -100,3 +100,84 @@ def test_balance_sequences_equalises_token_sums():
 
     with pytest.raises(ValueError):
         balance_sequences([1, 2, 3], 2)
+
+
+def test_partition_units_covers_every_unit_once():
+    """Prefill / DeltaNet partition: sequences first, head groups only when there are more ranks than sequences."""
+    from hyprstream_b200.sharded import partition_units
+
+    for n_seqs, n_groups, n_ranks in [(8, 8, 1), (8, 8, 2), (8, 8, 8), (4, 2, 8), (4, 32, 8), (4, 2, 2), (4, 2, 4), (4, 1, 8), (3, 4, 8), (64, 1, 8)]:
+        parts = partition_units(n_seqs, n_groups, n_ranks)
+        assert len(parts) == n_ranks
+        units = sorted((s, g) for p in parts for (s, lo, hi) in p for g in range(lo, hi))
+        assert units == [(s, g) for s in range(n_seqs) for g in range(n_groups)], (n_seqs, n_groups, n_ranks)
+        assert parts == partition_units(n_seqs, n_groups, n_ranks)
+        widths = {hi - lo for p in parts for (_, lo, hi) in p}
+        assert len(widths) == 1  # every unit of a run has the same head width: one kernel shape per rank
+    assert partition_units(8, 8, 8) == [[(i, 0, 8)] for i in range(8)]                       # prefill 8 x 8192 on 8 GPUs: a sequence each
+    assert partition_units(4, 2, 8) == [[(i // 2, i % 2, i % 2 + 1)] for i in range(8)]    # the 4 x 32768 block: (sequence, head half)
+    with pytest.raises(ValueError):
+        partition_units(0, 1, 1)
+
+
+def _gdn_worker(rank, world, port, q, k, v, g, beta, ret):
+    """Each rank runs the oracle's recurrence on its (sequence, value-head range) units only; one all-gather of the
+    outputs shows that the union is the unpartitioned result (no data-path exchange is needed to compute it)."""
+    from oracle import gdn_ref as gr
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        b, nv = v.shape[0], v.shape[1]
+        r = nv // k.shape[1]
+        out = torch.zeros_like(v)
+        for (s, lo, hi) in sharded.partition_units(b, 2, world)[rank]:  # two head groups per sequence
+            h0, h1 = lo * nv // 2, hi * nv // 2
+            qh = q[s:s + 1].repeat_interleave(r, dim=1)[:, h0:h1]
+            kh = k[s:s + 1].repeat_interleave(r, dim=1)[:, h0:h1]
+            o, _ = gr.recurrent_sequence(qh, kh, v[s:s + 1, h0:h1], g[s:s + 1, h0:h1], beta[s:s + 1, h0:h1], None)
+            out[s, h0:h1] = o[0]
+        dist.all_reduce(out)  # disjoint supports: the sum is the union
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_deltanet_partition_equals_unpartitioned():
+    from oracle import gdn_ref as gr
+
+    torch.manual_seed(1)
+    b, nk, nv, t, d = 1, 2, 4, 12, 16   # one sequence, two ranks: the value heads are cut in halves
+    q = torch.nn.functional.normalize(torch.randn(b, nk, t, d), dim=-1) * d ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(b, nk, t, d), dim=-1)
+    v = torch.randn(b, nv, t, d)
+    g = torch.nn.functional.logsigmoid(torch.randn(b, nv, t))
+    beta = torch.sigmoid(torch.randn(b, nv, t))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_gdn_worker, args=(2, port, q, k, v, g, beta, ret), nprocs=2, join=True)
+    r = nv // nk
+    full, _ = gr.recurrent_sequence(q.repeat_interleave(r, dim=1), k.repeat_interleave(r, dim=1), v, g, beta, None)
+    assert torch.allclose(ret[0], full, rtol=1e-6, atol=1e-6) and torch.equal(ret[0], ret[1])
+
+
+def test_exchange_handles_two_rank_gloo():
+    """Host set-up of the one-launch sharded decode: every rank ends with all ranks' handles in rank order."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_handles_worker, args=(2, port, ret), nprocs=2, join=True)
+    want = bytes([7] * 64) + bytes([8] * 64)
+    assert ret[0] == want and ret[1] == want
+
+
+def _handles_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ret[rank] = sharded.exchange_handles(bytes([7 + rank] * 64))
+    finally:
+        dist.destroy_process_group()
