@@ -668,76 +668,58 @@ def run_qwen_block(ctx: Ctx, prefill_batch: int = 4, prefill_tokens: int = 32768
     nk, nv, hq, hkv = int(NK * frac), int(NV * frac), int(HQ5 * frac), int(HKV5 * frac)
     conv_dim = (2 * nk + nv) * HD
     if units:
-        conv_w = [(rnd(conv_dim, 1, KS) * 0.5).bfloat16() for _ in range(N_GDN)]
-        neg_a = [-torch.rand(nv, device=dev, generator=g) for _ in range(N_GDN)]
-        dt_b = [rnd(nv) * 0.3 for _ in range(N_GDN)]
-        norm_w = [1.0 + 0.1 * rnd(HD) for _ in range(N_GDN)]
-        qn_w, kn_w = 0.1 * rnd(D5), 0.1 * rnd(D5)
+        layers = [ops.GdnLayer((rnd(conv_dim, 1, KS) * 0.5).bfloat16(), torch.log(torch.rand(nv, device=dev, generator=g) + 1e-3), rnd(nv) * 0.3,
+                               1.0 + 0.1 * rnd(HD), nk, nv) for _ in range(N_GDN)]
+        attn = ops.QwenAttnLayer(0.1 * rnd(D5), 0.1 * rnd(D5), sin, cos, RD, hq, hkv, D5)
         x = rnd(b, t, conv_dim).bfloat16()
         z = rnd(b, t, nv, HD).bfloat16()
         a_in, b_in = rnd(b, t, nv).bfloat16(), rnd(b, t, nv).bfloat16()
         q_full = rnd(b * t, hq * 2 * D5).bfloat16()
         k_proj, v_proj = rnd(b * t, hkv * D5).bfloat16(), rnd(b, t, hkv, D5).bfloat16()
         pos = torch.arange(t, device=dev, dtype=torch.int32).repeat(b)
-        conv = [torch.zeros(b, conv_dim, KS - 1, dtype=torch.bfloat16, device=dev) for _ in range(N_GDN)]
-        rec = [torch.zeros(b, nv, HD, HD, device=dev) for _ in range(N_GDN)]
+        states = [l.new_states(b, dev) for l in layers]
         caches = [kc.LayerKVCache(t, kc.KVQuantType.INT8, hkv, D5, dev, block=128, scale_dtype=ffi.SCALE_F16) for _ in range(b)]
         for c in caches:
             c._ensure_capacity(t)
         view, keep = kc.make_view(caches)
         zeros = torch.zeros(b, dtype=torch.int32, device=dev)
-
-        def gdn_layer_prefill(i):
-            q_, k_, v_, gg, beta = ops.gdn_prologue(x, conv_w[i], conv[i], False, a_in, b_in, neg_a[i], dt_b[i], nk, nv)
-            o = ops.gdn_chunk_prefill(q_, k_, v_, gg, beta, rec[i])
-            return ops.gdn_epilogue(o, z, norm_w[i], 1e-6)
-
-        def attn_layer_prefill():
-            query, gate = ops.qk_norm_rope(q_full, hq, D5, qn_w, 1e-6, True, sin, cos, pos, RD, with_gate=True)
-            k_ = ops.qk_norm_rope(k_proj, hkv, D5, kn_w, 1e-6, True, sin, cos, pos, RD)
-            ops.kv_quantize_write(view, k_.view(b, t, hkv, D5), v_proj, zeros)
-            return ops.prefill_attention(query.view(b, t, hq, D5), k_.view(b, t, hkv, D5), v_proj, gate=gate.view(b, t, hq, D5))
-
-        for i in range(N_GDN):  # warm-up (also builds tensor maps, sets attributes)
-            gdn_layer_prefill(i)
-        attn_layer_prefill()
-        for r_ in rec:
-            r_.zero_()
+        gin = [(x, z, a_in, b_in) + states[i] for i in range(N_GDN)]
+        ain = (q_full, k_proj, v_proj, view, pos, zeros, zeros + 1)
+        ws = torch.empty(max(layers[0].workspace_bytes(b, t), attn.workspace_bytes(b, t)), dtype=torch.uint8, device=dev)
+        # warm-up (also builds tensor maps, sets attributes): the whole block through the one block-level call
+        ops.qwen_block_forward(layers, gin, attn, ain, False, b, t, dev, workspace=ws)
     ctx.barrier()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     e[0].record()
     if units:
-        for i in range(N_GDN):
-            gdn_layer_prefill(i)
+        ops.qwen_block_forward(layers, gin, None, None, False, b, t, dev, workspace=ws)   # the three DeltaNet layers
     e[1].record()
     if units:
-        attn_layer_prefill()
+        ops.qwen_block_forward([], [], attn, ain, False, b, t, dev, workspace=ws)         # the full-attention layer
     e[2].record()
     ctx.barrier()
     gdn_ms, attn_ms = ctx.max(e[0].elapsed_time(e[1])), ctx.max(e[1].elapsed_time(e[2]))
     block_ms = ctx.max(e[0].elapsed_time(e[2]))
     attn_flops = 4.0 * prefill_batch * HQ5 * D5 * t * (t + 1) / 2
     res["prefill"] = {"batch": prefill_batch, "tokens": t, "units_per_gpu": f"{b} x ({nv} v heads, {hq} q heads)",
-                      "gdn_layers_ms": gdn_ms, "full_attention_layer_ms": attn_ms, "block_ms": block_ms,
+                      "api": "hs_qwen_block_forward", "gdn_layers_ms": gdn_ms, "full_attention_layer_ms": attn_ms, "block_ms": block_ms,
                       "tokens_per_s": prefill_batch * t / block_ms * 1e3,
                       "full_attention_useful_tflops_incl_edges": attn_flops / attn_ms / 1e9}
     if units:
-        del x, z, a_in, b_in, q_full, k_proj, v_proj, caches, view, keep, conv, rec
+        del x, z, a_in, b_in, q_full, k_proj, v_proj, caches, view, keep, states, gin, ain, ws, layers, attn
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ decode (by sequence, full heads)
     bl = len(sharded.partition_units(decode_batch, 1, world)[rank])
     L = context
     conv_dim = (2 * NK + NV) * HD
-    conv_w = [(rnd(conv_dim, 1, KS) * 0.5).bfloat16() for _ in range(N_GDN)]
-    neg_a = [-torch.rand(NV, device=dev, generator=g) for _ in range(N_GDN)]
-    dt_b = [rnd(NV) * 0.3 for _ in range(N_GDN)]
-    norm_w = [1.0 + 0.1 * rnd(HD) for _ in range(N_GDN)]
-    qn_w, kn_w = 0.1 * rnd(D5), 0.1 * rnd(D5)
     if bl:
+        layers = [ops.GdnLayer((rnd(conv_dim, 1, KS) * 0.5).bfloat16(), torch.log(torch.rand(NV, device=dev, generator=g) + 1e-3), rnd(NV) * 0.3,
+                               1.0 + 0.1 * rnd(HD), NK, NV) for _ in range(N_GDN)]
+        attn = ops.QwenAttnLayer(0.1 * rnd(D5), 0.1 * rnd(D5), sin, cos, RD, HQ5, HKV5, D5)
         caches = []
         cap = (L + decode_steps + 8 + 1023) // 1024 * 1024  # whole 1024-token growth chunks (kv_cache.rs:700)
-        for s in range(bl):
+        for s_ in range(bl):
             c = kc.LayerKVCache(cap, kc.KVQuantType.INT8, HKV5, D5, dev, block=128, scale_dtype=ffi.SCALE_F16)
             for t0 in range(0, L, 8192):
                 n = min(8192, L - t0)
@@ -750,21 +732,17 @@ def run_qwen_block(ctx: Ctx, prefill_batch: int = 4, prefill_tokens: int = 32768
         a_in, b_in = rnd(bl, 1, NV).bfloat16(), rnd(bl, 1, NV).bfloat16()
         q_full = rnd(bl, HQ5 * 2 * D5).bfloat16()
         k_proj, v_proj = rnd(bl, HKV5 * D5).bfloat16(), rnd(bl, 1, HKV5, D5).bfloat16()
-        conv = [rnd(bl, conv_dim, KS - 1).bfloat16() for _ in range(N_GDN)]
-        rec = [rnd(bl, NV, HD, HD) * 0.1 for _ in range(N_GDN)]
-        ws = ops.decode_workspace(bl, HQ5, D5, dev)
-        lens = torch.full((bl,), L, dtype=torch.int32, device=dev)
+        states = [(rnd(bl, conv_dim, KS - 1).bfloat16(), rnd(bl, NV, HD, HD) * 0.1) for _ in range(N_GDN)]
+        dst = torch.full((bl,), L, dtype=torch.int32, device=dev)
+        lens = dst + 1
+        gin = [(x, z, a_in, b_in) + states[i] for i in range(N_GDN)]
+        ain = (q_full, k_proj, v_proj, view, dst, dst, lens)   # one new token per sequence: its RoPE row is its cache position
+        ws = torch.empty(max(layers[0].workspace_bytes(bl, 1), attn.workspace_bytes(bl, 1)), dtype=torch.uint8, device=dev)
 
-        def decode_step():
-            for i in range(N_GDN):
-                q_, k_, v_, gg, beta = ops.gdn_prologue(x, conv_w[i], conv[i], True, a_in, b_in, neg_a[i], dt_b[i], NK, NV)
-                o = ops.gdn_recurrent(q_, k_, v_, gg, beta, rec[i])
-                ops.gdn_epilogue(o, z, norm_w[i], 1e-6)
-            query, gate = ops.qk_norm_rope(q_full, HQ5, D5, qn_w, 1e-6, True, sin, cos, lens, RD, with_gate=True)
-            k_ = ops.qk_norm_rope(k_proj, HKV5, D5, kn_w, 1e-6, True, sin, cos, lens, RD)
-            ops.kv_quantize_write(view, k_.view(bl, 1, HKV5, D5), v_proj, lens)
+        def decode_step():  # one block step = one hs_qwen_block_forward call
+            ops.qwen_block_forward(layers, gin, attn, ain, True, bl, 1, dev, workspace=ws)
+            dst.add_(1)
             lens.add_(1)
-            return ops.decode_attention(query, view, lens, gate=gate, workspace=ws)
     else:
         def decode_step():
             pass
@@ -772,7 +750,8 @@ def run_qwen_block(ctx: Ctx, prefill_batch: int = 4, prefill_tokens: int = 32768
     kv_bytes = decode_batch * (L + 3 + decode_steps / 2) * token_bytes(128, 1, HKV5, D5)
     state_bytes = N_GDN * 2 * decode_batch * NV * HD * HD * 4
     peak = float(ctx.peaks.get("hbm_gbs", 6650.0))
-    res["decode"] = {"batch": decode_batch, "context": L, "steps": decode_steps, "ms_per_step": ms, "tokens_per_s": decode_batch / ms * 1e3,
+    res["decode"] = {"batch": decode_batch, "context": L, "steps": decode_steps, "api": "hs_qwen_block_forward (one call per block step)",
+                     "ms_per_step": ms, "tokens_per_s": decode_batch / ms * 1e3,
                      "algorithmic_bytes_per_step": kv_bytes + state_bytes, "hbm_gbps": (kv_bytes + state_bytes) / ms / 1e6,
                      "frac_of_hbm_peak_per_gpu": (kv_bytes + state_bytes) / world / ms / 1e6 / peak}
     torch.cuda.synchronize()

@@ -290,9 +290,11 @@ class GdnLayer:
         return (torch.zeros(n_seqs, conv_dim, self.conv_weight.shape[1] - 1, dtype=torch.bfloat16, device=device),
                 torch.zeros(n_seqs, self.nv, self.hk, self.hv, dtype=torch.float32, device=device))
 
+    def workspace_bytes(self, n_seqs: int, n_tokens: int) -> int:
+        return max(int(lib.hs_gdn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)), 256)
+
     def workspace(self, n_seqs: int, n_tokens: int, device) -> torch.Tensor:
-        need = lib.hs_gdn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)
-        return torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+        return torch.empty(self.workspace_bytes(n_seqs, n_tokens), dtype=torch.uint8, device=device)
 
     def forward(self, mixed_qkv: torch.Tensor, z: torch.Tensor, a_in: torch.Tensor, b_in: torch.Tensor, conv_state: torch.Tensor,
                 rec_state: torch.Tensor, has_state: bool, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -320,9 +322,11 @@ class QwenAttnLayer:
         self.params = ffi.QwenAttnParams(self.qw.data_ptr(), self.kw.data_ptr(), float(norm_eps), sin.data_ptr(), cos.data_ptr(), sin.shape[0],
                                          rotary_dim, n_q_heads, n_kv_heads, head_dim, float(scale))
 
+    def workspace_bytes(self, n_seqs: int, n_tokens: int) -> int:
+        return max(int(lib.hs_qwen_attn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)), 256)
+
     def workspace(self, n_seqs: int, n_tokens: int, device) -> torch.Tensor:
-        need = lib.hs_qwen_attn_layer_workspace_bytes(ctypes.byref(self.params), n_seqs, n_tokens)
-        return torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+        return torch.empty(self.workspace_bytes(n_seqs, n_tokens), dtype=torch.uint8, device=device)
 
     def forward(self, q_proj: torch.Tensor, k_proj: torch.Tensor, v_proj: torch.Tensor, view: KVView, positions: torch.Tensor,
                 dst_pos: torch.Tensor, seq_lens: Optional[torch.Tensor], n_seqs: int, n_tokens: int,

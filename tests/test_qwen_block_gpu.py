@@ -59,7 +59,11 @@ def test_gdn_layer_prompt_then_decode_matches_oracle_and_serial(cuda):
     torch.cuda.synchronize()
     y, y_ref = torch.cat(ys, 1).cpu().float(), torch.cat(ys_ref, 1).float()
     diff = (y - y_ref).abs()
-    assert torch.all(diff <= 2e-2 + 2 ** -7 * y_ref.abs()) and diff.mean().item() <= 2e-3, (diff.max().item(), diff.mean().item())
+    # the prompt runs through the tensor-core chunked rule (bf16 operands: within 2e-2 / 2e-3 of the fp32 rule on outputs of
+    # unit scale); RMSNormGated then divides a row by its rms and multiplies by silu(z), so the bound carries to y relative to
+    # the row's scale
+    scale = y_ref.abs().amax(dim=-1, keepdim=True).clamp_min(1.0)
+    assert torch.all(diff <= 2e-2 * scale) and diff.mean().item() <= 2e-3, (diff.max().item(), diff.mean().item())
     assert (rec.cpu() - rec_ref).abs().max().item() <= 2e-2 * max(1.0, rec_ref.abs().max().item())
     assert torch.equal(conv.cpu(), conv_ref)
     # batched == serial: every row alone gives the same outputs and states
