@@ -232,6 +232,14 @@ __global__ void __launch_bounds__(kQThreads) rope_kernel(const uint16_t *__restr
     *reinterpret_cast<uint4 *>(out + rh * head_dim + d0) = w;
 }
 
+// Optional per-head RMS norm of K fused into quantise-on-write (weight == NULL: off).
+struct KNormArgs {
+    const float *weight;  // f32 [head_dim]
+    float eps;
+    int plus_one;         // multiply by (1 + w) instead of w
+    uint16_t *k_out;      // optional bf16 [n_seqs, n_tokens, n_kv_heads, head_dim]: the normed, rotated keys
+};
+
 // ---- quantise-on-write into a cache view ----------------------------------------------------------------
 // E = elements per thread: 16 for long writes (prefill: bound by instruction issue, so the per-chunk costs are paid
 // half as often), 8 for short ones (a decode step's single token per sequence: latency matters, not throughput).
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
                                                              const uint16_t *__restrict__ v_new, int n_seqs, int n_tokens,
                                                              const int32_t *__restrict__ dst_pos,
                                                              const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
-                                                             int rotary_dim, int n_positions, int *__restrict__ err) {
+                                                             int rotary_dim, int n_positions, int *__restrict__ err, KNormArgs kn) {
     __shared__ float smid[256];
     fill_midpoints(KIND, smid);
     __syncthreads();
@@ -281,12 +289,62 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
         if (live && !ok) atomicOr(err, HS_DEVERR_KV_WRITE_RANGE);  // recorded, access skipped
         const uint16_t *src = (is_v ? v_new : k_new) + row * D;
         float x[E];
+        if (kn.weight != nullptr && !is_v) {
+            // ---- K with its per-head RMS norm fused in (qwen3_5.rs:1077-1091; llama.rs:929-992): the row's sum of squares is
+            // formed exactly as hs_qk_norm_rope forms it (an 8-element chain per 16-byte chunk, then pairwise over the chunks
+            // of the row), so the normed, rotated values - and with them the stored codes - equal the two-kernel route bit
+            // for bit.  Dead and refused lanes carry zeros and still take part in the shuffles.
+            float ssq[E / 8];
 #pragma unroll
-        for (int part = 0; part < E / 8; ++part) {
-            float p8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (ok) load_row8_rope(src, d0 + 8 * part, is_v ? nullptr : sin, cos, pos, rotary_dim, p8);
+            for (int part = 0; part < E / 8; ++part) {
+                float p8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (ok) unpack8_bf16(*reinterpret_cast<const uint4 *>(src + d0 + 8 * part), p8);
+                float ss = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[8 * part + i] = p8[i];
+                for (int i = 0; i < 8; ++i) { x[8 * part + i] = p8[i]; ss = fmaf(p8[i], p8[i], ss); }
+                ssq[part] = ss;
+            }
+            float ss = ssq[0];
+            if constexpr (E == 16) ss += ssq[1];
+            for (uint32_t off = 1; off < cpr; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            const float rrms = rsqrtf(ss * (1.0f / static_cast<float>(D)) + kn.eps);
+            const float add = kn.plus_one ? 1.0f : 0.0f;
+            const bool rope = sin != nullptr && ok;
+            const int half = rotary_dim >> 1;
+#pragma unroll
+            for (int part = 0; part < E / 8; ++part) {
+                const int dd = d0 + 8 * part;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[8 * part + i] = bf16_round(x[8 * part + i] * rrms * (kn.weight[dd + i] + add));
+                if (rope && dd < rotary_dim) {
+                    const bool first = dd < half;
+                    const int pd = first ? dd + half : dd - half;  // the rotation partner's chunk, normed the same way
+                    float p8[8];
+                    unpack8_bf16(*reinterpret_cast<const uint4 *>(src + pd), p8);
+                    const int j0 = first ? dd : dd - half;
+                    const uint16_t *srow = sin + static_cast<int64_t>(pos) * half + j0;
+                    const uint16_t *crow = cos + static_cast<int64_t>(pos) * half + j0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float pn = bf16_round(p8[i] * rrms * (kn.weight[pd + i] + add));
+                        x[8 * part + i] = rope_elem(x[8 * part + i], pn, bf16_bits_to_f32(srow[i]), bf16_bits_to_f32(crow[i]), first);
+                    }
+                }
+                if (kn.k_out != nullptr && ok) {  // the normed, rotated keys in bf16, for a prompt's own attention
+                    uint4 w;
+                    w.x = pack_bf16(x[8 * part], x[8 * part + 1]); w.y = pack_bf16(x[8 * part + 2], x[8 * part + 3]);
+                    w.z = pack_bf16(x[8 * part + 4], x[8 * part + 5]); w.w = pack_bf16(x[8 * part + 6], x[8 * part + 7]);
+                    *reinterpret_cast<uint4 *>(kn.k_out + row * D + dd) = w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int part = 0; part < E / 8; ++part) {
+                float p8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (ok) load_row8_rope(src, d0 + 8 * part, is_v ? nullptr : sin, cos, pos, rotary_dim, p8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[8 * part + i] = p8[i];
+            }
         }
         const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + h;  // (token, head) row inside the page
         const int64_t pidx = static_cast<int64_t>(s) * view.pages_per_seq + page;
@@ -456,32 +514,34 @@ int32_t hs_rope_apply(const void *x, void *out, const void *sin, const void *cos
     return check_launch("hs_rope_apply");
 }
 
-int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, int32_t n_tokens,
-                             const int32_t *dst_pos, const void *sin, const void *cos, int32_t rotary_dim,
-                             int32_t n_positions, hs_stream_t stream) {
+static int32_t kv_write_impl(const char *who, const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, int32_t n_tokens,
+                             const int32_t *dst_pos, const void *sin, const void *cos, int32_t rotary_dim, int32_t n_positions, hs::KNormArgs kn,
+                             hs_stream_t stream) {
     if (int32_t st = check_device()) return st;
     if (int32_t st = validate_view(view)) return st;
-    if (n_seqs < 0 || n_tokens < 0) return fail(HS_ERR_ARG, "hs_kv_quantize_write: negative sizes");
+    if (n_seqs < 0 || n_tokens < 0) return fail(HS_ERR_ARG, "%s: negative sizes", who);
     if (n_seqs == 0 || n_tokens == 0) return HS_OK;
-    if (!k_new || !v_new) return fail(HS_ERR_ARG, "hs_kv_quantize_write: NULL input");
-    if (!aligned(k_new, 16) || !aligned(v_new, 16)) return fail(HS_ERR_ARG, "hs_kv_quantize_write: inputs must be 16-byte aligned");
+    if (!k_new || !v_new) return fail(HS_ERR_ARG, "%s: NULL input", who);
+    if (!aligned(k_new, 16) || !aligned(v_new, 16)) return fail(HS_ERR_ARG, "%s: inputs must be 16-byte aligned", who);
     if (sin != nullptr) {
-        if (!cos) return fail(HS_ERR_ARG, "hs_kv_quantize_write: sin given without cos");
+        if (!cos) return fail(HS_ERR_ARG, "%s: sin given without cos", who);
         if (rotary_dim <= 0 || rotary_dim % 16 != 0 || rotary_dim > view->head_dim || n_positions <= 0)
-            return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: rotary_dim must be a positive multiple of 16 <= head_dim");
+            return fail(HS_ERR_UNSUPPORTED, "%s: rotary_dim must be a positive multiple of 16 <= head_dim", who);
     }
+    if (kn.weight != nullptr && (!aligned(kn.weight, 16) || (kn.k_out && !aligned(kn.k_out, 16))))
+        return fail(HS_ERR_ARG, "%s: the norm weight and the key output must be 16-byte aligned", who);
     ViewDev d = to_dev(view);
     const int64_t elems = static_cast<int64_t>(n_tokens) * d.n_kv_heads * d.head_dim;  // per sequence and per K / V
-    if (elems / 8 > 0x7fffffffLL || n_seqs > 32767) return fail(HS_ERR_UNSUPPORTED, "hs_kv_quantize_write: more than 2^31 chunks per sequence or 32767 sequences in one call");
+    if (elems / 8 > 0x7fffffffLL || n_seqs > 32767) return fail(HS_ERR_UNSUPPORTED, "%s: more than 2^31 chunks per sequence or 32767 sequences in one call", who);
     const bool wide = elems >= (1 << 16);  // long writes: 16 elements per thread
     dim3 grid(static_cast<unsigned>((elems + static_cast<int64_t>(kQThreads) * kWriteElems - 1) / (static_cast<int64_t>(kQThreads) * kWriteElems)), 2u * static_cast<unsigned>(n_seqs));
     cudaStream_t s = as_stream(stream);
     int *err = device_error_word();
-    if (!err) return fail(HS_ERR_DEVICE, "hs_kv_quantize_write: device error word unavailable");
+    if (!err) return fail(HS_ERR_DEVICE, "%s: device error word unavailable", who);
     const uint16_t *k = reinterpret_cast<const uint16_t *>(k_new), *v = reinterpret_cast<const uint16_t *>(v_new);
     const uint16_t *sn = reinterpret_cast<const uint16_t *>(sin), *cs = reinterpret_cast<const uint16_t *>(cos);
-#define HS_KV_WRITE(K) do { if (wide) kv_write_kernel<K, HS_KV_WRITE_WIDE><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); \
-                            else kv_write_kernel<K, 8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err); } while (0)
+#define HS_KV_WRITE(K) do { if (wide) kv_write_kernel<K, HS_KV_WRITE_WIDE><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err, kn); \
+                            else kv_write_kernel<K, 8><<<grid, kQThreads, 0, s>>>(d, k, v, n_seqs, n_tokens, dst_pos, sn, cs, rotary_dim, n_positions, err, kn); } while (0)
     switch (view->kind) {
         case HS_KV_BF16: HS_KV_WRITE(HS_KV_BF16); break;
         case HS_KV_INT8: HS_KV_WRITE(HS_KV_INT8); break;
@@ -489,7 +549,22 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
         default: HS_KV_WRITE(HS_KV_FP4); break;
     }
 #undef HS_KV_WRITE
-    return check_launch("hs_kv_quantize_write");
+    return check_launch(who);
+}
+
+int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, int32_t n_tokens,
+                             const int32_t *dst_pos, const void *sin, const void *cos, int32_t rotary_dim,
+                             int32_t n_positions, hs_stream_t stream) {
+    return kv_write_impl("hs_kv_quantize_write", view, k_new, v_new, n_seqs, n_tokens, dst_pos, sin, cos, rotary_dim, n_positions,
+                         hs::KNormArgs{nullptr, 0.0f, 0, nullptr}, stream);
+}
+
+int32_t hs_kv_norm_rope_quantize_write(const hs_kv_view *view, const void *k_proj, const void *v_new, int32_t n_seqs, int32_t n_tokens,
+                                       const int32_t *dst_pos, const float *k_norm_weight, float eps, int32_t weight_plus_one, const void *sin,
+                                       const void *cos, int32_t rotary_dim, int32_t n_positions, void *k_out, hs_stream_t stream) {
+    if (!k_norm_weight) return fail(HS_ERR_ARG, "hs_kv_norm_rope_quantize_write: NULL norm weight (use hs_kv_quantize_write)");
+    return kv_write_impl("hs_kv_norm_rope_quantize_write", view, k_proj, v_new, n_seqs, n_tokens, dst_pos, sin, cos, rotary_dim, n_positions,
+                         hs::KNormArgs{k_norm_weight, eps, weight_plus_one, reinterpret_cast<uint16_t *>(k_out)}, stream);
 }
 
 int32_t hs_kv_gather_dequantize(const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t out_tokens,

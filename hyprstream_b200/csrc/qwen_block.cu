@@ -129,11 +129,12 @@ int32_t hs_qwen_attn_layer_forward(const hs_qwen_attn_params *params, const void
     if (int32_t st = hs_qk_norm_rope(q_proj, static_cast<int64_t>(hq) * 2 * d, 2 * d, query, gate, params->q_norm_weight, params->norm_eps, 1, params->sin,
                                      params->cos, positions, params->n_positions, params->rotary_dim, rows, hq, d, stream))
         return st;
-    if (int32_t st = hs_qk_norm_rope(k_proj, static_cast<int64_t>(hkv) * d, d, k_rot, nullptr, params->k_norm_weight, params->norm_eps, 1, params->sin,
-                                     params->cos, positions, params->n_positions, params->rotary_dim, rows, hkv, d, stream))
+    // K: norm + rotation + cache update in one pass over the new keys (qwen3_5.rs:971-999); a prompt also keeps the normed,
+    // rotated keys in bf16 for its own attention.  The keys' RoPE rows are their cache positions dst_pos[s] + t, which is
+    // what `positions` holds for the queries.
+    if (int32_t st = hs_kv_norm_rope_quantize_write(view, k_proj, v_proj, n_seqs, n_tokens, dst_pos, params->k_norm_weight, params->norm_eps, 1, params->sin,
+                                                    params->cos, params->rotary_dim, params->n_positions, n_tokens == 1 ? nullptr : k_rot, stream))
         return st;
-    // cache update (qwen3_5.rs:992-999), then attention over the cache (decode) or over the fresh K/V (prompt)
-    if (int32_t st = hs_kv_quantize_write(view, k_rot, v_proj, n_seqs, n_tokens, dst_pos, nullptr, nullptr, 0, 0, stream)) return st;
     if (n_tokens == 1)
         return hs_attn_decode(query, view, seq_lens, n_seqs, hq, params->softmax_scale, out, gate, dec_ws,
                               hs_attn_decode_workspace_bytes(n_seqs, hq, d), nullptr, nullptr, stream);

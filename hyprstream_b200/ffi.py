@@ -98,6 +98,8 @@ _SIGS = {
     "hs_qk_norm_rope": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p,
                                   c_int32, c_int32, c_int64, c_int32, c_int32, c_void_p]),
     "hs_kv_quantize_write": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    "hs_kv_norm_rope_quantize_write": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_float, c_int32, c_void_p, c_void_p,
+                                                 c_int32, c_int32, c_void_p, c_void_p]),
     "hs_kv_gather_dequantize": (c_int32, [POINTER(KVView), c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "hs_attn_decode_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),
     "hs_attn_decode": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),

@@ -102,6 +102,21 @@ def kv_quantize_write(view: KVView, k_new: torch.Tensor, v_new: torch.Tensor, ds
                                    _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0], _stream()))
 
 
+def kv_norm_rope_quantize_write(view: KVView, k_proj: torch.Tensor, v_new: torch.Tensor, dst_pos: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                                eps: float = 1e-6, weight_plus_one: bool = True, sin: Optional[torch.Tensor] = None,
+                                cos: Optional[torch.Tensor] = None, rotary_dim: int = 0, want_keys: bool = False) -> Optional[torch.Tensor]:
+    """K's per-head RMS norm + (partial) RoPE + cache update in one pass (qwen3_5.rs:971-999): k_proj is the raw k projection
+    [n_seqs, n_tokens, Hkv, D]; what is stored equals hs_qk_norm_rope followed by hs_kv_quantize_write, bit for bit.
+    With ``want_keys`` the normed, rotated keys come back in bf16 (for a prompt's own attention)."""
+    _need_cuda(k_proj, v_new, dst_pos, norm_weight, sin, cos)
+    n_seqs, n_tokens = k_proj.shape[0], k_proj.shape[1]
+    k_out = torch.empty_like(k_proj) if want_keys else None
+    check(lib.hs_kv_norm_rope_quantize_write(ctypes.byref(view), _ptr(k_proj), _ptr(v_new), n_seqs, n_tokens, _ptr(dst_pos), _ptr(norm_weight),
+                                             float(eps), 1 if weight_plus_one else 0, _ptr(sin), _ptr(cos), rotary_dim,
+                                             0 if sin is None else sin.shape[0], _ptr(k_out), _stream()))
+    return k_out
+
+
 def kv_gather_dequantize(view: KVView, seq_lens: torch.Tensor, out_tokens: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """LayerKVCache::get (kv_cache.rs:1499-1643): bf16 [n_seqs, out_tokens, Hkv, D], zero past each length."""
     _need_cuda(seq_lens)

@@ -153,6 +153,17 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
                              int32_t n_tokens, const int32_t *dst_pos, const void *sin, const void *cos,
                              int32_t rotary_dim, int32_t n_positions, hs_stream_t stream);
 
+/* The same with K's per-head RMS norm fused in front of the rotation: k_proj is the raw k projection
+ * [n_seqs, n_tokens, n_kv_heads, head_dim]; K = rope(bf16(k * rsqrt(mean(k^2) + eps) * (w or 1 + w))) at position
+ * dst_pos[s] + t is what gets quantised and stored (Qwen3_5FullAttention::forward, architectures/qwen3_5.rs:971-999:
+ * apply_qknorm :1077-1091, partial RoPE, cache.update; LlamaAttention's optional QK-norm, llama.rs:929-992), in one pass
+ * over the new keys instead of hs_qk_norm_rope followed by hs_kv_quantize_write - bit-identical to that route.
+ * k_out (optional, bf16, same shape) receives the normed, rotated keys for a prompt's own attention. */
+int32_t hs_kv_norm_rope_quantize_write(const hs_kv_view *view, const void *k_proj, const void *v_new, int32_t n_seqs,
+                                       int32_t n_tokens, const int32_t *dst_pos, const float *k_norm_weight, float eps,
+                                       int32_t weight_plus_one, const void *sin, const void *cos, int32_t rotary_dim,
+                                       int32_t n_positions, void *k_out, hs_stream_t stream);
+
 /* LayerKVCache::get (kv_cache.rs:1499-1643) compatibility path: dequantise (or copy) tokens
  * [0, seq_lens[s]) of every sequence into k_out/v_out [n_seqs, out_tokens, n_kv_heads, head_dim] bf16;
  * rows past seq_lens[s] are zero-filled like the reference's right padding (llama.rs:787-813). */
@@ -344,7 +355,8 @@ int32_t hs_gdn_epilogue(const float *o, const void *z, const float *norm_weight,
  *   mixed_qkv, a_in, b_in, conv_state  as for hs_gdn_prologue;  z bf16 [n_seqs, n_tokens, n_v_heads, head_v_dim]
  *   rec_state  f32 [n_seqs, n_v_heads, head_k_dim, head_v_dim] in/out; has_state == 0 starts conv_state and rec_state at zero
  *   y          bf16 [n_seqs, n_tokens, n_v_heads, head_v_dim] -> the input of out_proj
- * Full-attention layer: hs_qk_norm_rope on q (gate split, (1 + w) norm, partial RoPE) and k -> hs_kv_quantize_write ->
+ * Full-attention layer: hs_qk_norm_rope on q (gate split, (1 + w) norm, partial RoPE) -> hs_kv_norm_rope_quantize_write
+ * (k normed, rotated at its cache position dst_pos[s] + t, quantised and stored in one pass) ->
  * hs_attn_decode over the cache (n_tokens == 1) or hs_attn_prefill_causal over the fresh K/V (n_tokens > 1: a prompt
  * that starts at position 0; a continued prompt goes through hs_kv_gather_dequantize and hs_attn_prefill_causal with
  * kv_len > q_len), with the output gate.

@@ -74,3 +74,48 @@ def test_position_outside_table_is_recorded(cuda):
     torch.cuda.synchronize()
     assert ffi.take_device_error() & ffi.DEVERR_ROPE_RANGE
     assert torch.equal(out[2].cpu(), x[2].reshape(nh, hd).cpu())  # left unrotated
+
+
+@pytest.mark.parametrize("kind,block,sdt,hkv,d,rd,t,paged", [(1, 128, 1, 2, 256, 64, 5, False), (1, 128, 1, 2, 256, 64, 300, False),
+                                                              (2, 64, 1, 8, 128, 128, 70, False), (1, 64, 0, 8, 128, 128, 260, True),
+                                                              (0, 64, 0, 2, 256, 64, 40, False)])
+def test_fused_norm_rope_cache_write_equals_the_two_kernel_route(cuda, kind, block, sdt, hkv, d, rd, t, paged):
+    """hs_kv_norm_rope_quantize_write (K normed, rotated, quantised and stored in one pass) against hs_qk_norm_rope followed
+    by hs_kv_quantize_write: the same stored codes and scales and the same bf16 keys, bit for bit; short and long writes
+    (8 and 16 elements per thread), cache positions that do not start at 0, contiguous and paged storage."""
+    from hyprstream_b200 import kv_cache as kc, ops
+
+    b = 2
+    g = torch.Generator().manual_seed(t + d)
+    k_proj = torch.randn(b, t, hkv, d, generator=g).bfloat16().to(cuda)
+    v = torch.randn(b, t, hkv, d, generator=g).bfloat16().to(cuda)
+    w = (0.1 * torch.randn(d, generator=g)).to(cuda)
+    sin, cos = (x.to(cuda) for x in ar.rope_tables(rd, 10000.0, 512, torch.bfloat16))
+    start = torch.tensor([0, 37], dtype=torch.int32, device=cuda)
+
+    def caches():
+        if paged:
+            pool = kc.BlockPool(8, hkv, d, cuda, kind=kind, block=block, scale_dtype=sdt)
+            cs = [kc.LayerKVCache.new_paged(2048, pool, owner=i) for i in range(b)]
+        else:
+            cs = [kc.LayerKVCache(2048, kc.KVQuantType(kind), hkv, d, cuda, block=block, scale_dtype=sdt) for _ in range(b)]
+        for c in cs:
+            c._ensure_capacity(37 + t)
+        return cs
+
+    ca, cb = caches(), caches()
+    va, keep_a = kc.make_view(ca)
+    vb, keep_b = kc.make_view(cb)
+    k_fused = ops.kv_norm_rope_quantize_write(va, k_proj, v, start, w, 1e-6, True, sin, cos, rd, want_keys=True)
+    positions = (start[:, None] + torch.arange(t, dtype=torch.int32, device=cuda)[None, :]).reshape(-1).contiguous()
+    k_two = ops.qk_norm_rope(k_proj.reshape(b * t, -1), hkv, d, w, 1e-6, True, sin, cos, positions, rd).view(b, t, hkv, d)
+    ops.kv_quantize_write(vb, k_two, v, start)
+    torch.cuda.synchronize()
+    assert torch.equal(k_fused, k_two)
+    for i, (x, y) in enumerate(zip(ca, cb)):
+        x.seq_pos = y.seq_pos = int(start[i]) + t
+        for u, w_ in zip(x.snapshot(), y.snapshot()):
+            if u is not None:
+                lo = int(start[i])
+                assert torch.equal(u[lo:].view(torch.uint8), w_[lo:].view(torch.uint8)), f"sequence {i}"
+    no_device_error()
