@@ -352,7 +352,7 @@ constexpr int kMaxPartsPerPair = 2;
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
                            uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out,
-                           const ShardArgs *shard);
+                           const ShardArgs *shard, int after_write, const AppendArgs *append);
 
 template <int KIND, int D, int G>
 static int32_t launch_generic(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
@@ -430,7 +430,7 @@ static int32_t static_scratch_for_current_device(void **out) {
 
 int32_t decode_impl(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale,
                     void *out, const void *gate, void *workspace, int64_t workspace_bytes, float *o_shard, float *lse_shard,
-                    const ShardArgs *shard, hs_stream_t stream);
+                    const ShardArgs *shard, hs_stream_t stream, int after_write = 0, const AppendArgs *append = nullptr, int *appended = nullptr);
 
 }  // namespace hs
 
@@ -457,7 +457,9 @@ int32_t hs_attn_decode(const void *q, const hs_kv_view *view, const int32_t *seq
 // a shard group and merge again (hs_attn_decode_sharded); only that kernel can, so other shapes are refused then.
 int32_t hs::decode_impl(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
                         float softmax_scale, void *out, const void *gate, void *workspace, int64_t workspace_bytes,
-                        float *o_shard, float *lse_shard, const ShardArgs *shard, hs_stream_t stream) {
+                        float *o_shard, float *lse_shard, const ShardArgs *shard, hs_stream_t stream, int after_write, const AppendArgs *append,
+                        int *appended) {
+    if (appended) *appended = 0;
     if (int32_t st = check_device()) return st;
     if (int32_t st = validate_view(view)) return st;
     if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode: bad sizes");
@@ -487,7 +489,12 @@ int32_t hs::decode_impl(const void *q, const hs_kv_view *view, const int32_t *se
     int tile = kDecTile, tc_ctas = 0, ppp = 1, merged = 0;
     prof_begin(s);
     st = decode_int8_tc_try(v, qp, seq_lens, n_seqs, n_q_heads, softmax_scale, o_part, lse_part, err, s, &tc_ctas,
-                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard, lse_shard, &merged, shard);
+                            reinterpret_cast<uint16_t *>(out), reinterpret_cast<const uint16_t *>(gate), o_shard, lse_shard, &merged, shard, after_write, append);
+    if (st == HS_OK && append && tc_ctas == 0) {  // the tensor-core kernel did not take the launch: nothing was written, the caller writes
+        prof_end(s);
+        return HS_OK;
+    }
+    if (appended && append && tc_ctas > 0) *appended = 1;
     if (st == HS_OK && shard && tc_ctas == 0) {
         prof_end(s);
         return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode_sharded: only the tensor-core decode kernel exchanges shard results (quantised cache, 8 kv heads x 128 "
@@ -560,6 +567,33 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
 }
 
 
+int32_t hs_attn_decode_append(const void *q, const void *k_new, const void *v_new, const hs_kv_view *view, const int32_t *dst_pos,
+                              const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale, const void *sin, const void *cos,
+                              int32_t rotary_dim, int32_t n_positions, void *out, const void *gate, void *workspace, int64_t workspace_bytes,
+                              hs_stream_t stream) {
+    if (!k_new || !v_new) return fail(HS_ERR_ARG, "hs_attn_decode_append: NULL new token");
+    if (dst_pos == nullptr) {
+        // the new token goes to position seq_lens[s] - 1: the attention kernel can write it itself (u8 caches on the tensor-core
+        // kernel: one launch per step); otherwise the write kernel runs first, at those positions
+        if (!aligned(k_new, 16) || !aligned(v_new, 16)) return fail(HS_ERR_ARG, "hs_attn_decode_append: inputs must be 16-byte aligned");
+        if (sin != nullptr && (!cos || rotary_dim <= 0 || rotary_dim % 16 != 0 || (view && rotary_dim > view->head_dim) || n_positions <= 0))
+            return fail(HS_ERR_UNSUPPORTED, "hs_attn_decode_append: rotary_dim must be a positive multiple of 16 <= head_dim");
+        AppendArgs ap{reinterpret_cast<const uint16_t *>(k_new), reinterpret_cast<const uint16_t *>(v_new), reinterpret_cast<const uint16_t *>(sin),
+                      reinterpret_cast<const uint16_t *>(cos), rotary_dim, n_positions};
+        int appended = 0;
+        if (view && view->kind == HS_KV_INT8) {
+            if (int32_t st = decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, workspace, workspace_bytes, nullptr, nullptr,
+                                         nullptr, stream, 0, &ap, &appended))
+                return st;
+            if (appended || n_seqs == 0) return HS_OK;
+        }
+        if (int32_t st = kv_write_at_end(view, k_new, v_new, n_seqs, seq_lens, sin, cos, rotary_dim, n_positions, stream)) return st;
+        return decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, workspace, workspace_bytes, nullptr, nullptr, nullptr, stream, 1);
+    }
+    if (int32_t st = hs_kv_quantize_write(view, k_new, v_new, n_seqs, 1, dst_pos, sin, cos, rotary_dim, n_positions, stream)) return st;
+    return decode_impl(q, view, seq_lens, n_seqs, n_q_heads, softmax_scale, out, gate, workspace, workspace_bytes, nullptr, nullptr, nullptr, stream, 1);
+}
+
 int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *dev_in, const int32_t *dst_pos, const int32_t *seq_lens,
                             int32_t n_seqs, int32_t n_q_heads, float softmax_scale, const void *sin, const void *cos, int32_t rotary_dim,
                             int32_t n_positions, void *dev_out, void *host_out, void *workspace, int64_t workspace_bytes, int32_t flags,
@@ -568,7 +602,7 @@ int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *d
     if (int32_t st = validate_view(view)) return st;
     if (n_seqs < 0 || n_q_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_decode_step: bad sizes");
     if (n_seqs == 0) return HS_OK;
-    if (!host_in || !dev_in || !dev_out || !host_out || !dst_pos || !seq_lens)
+    if (!host_in || !dev_in || !dev_out || !host_out || !seq_lens)
         return fail(HS_ERR_ARG, "hs_attn_decode_step: NULL pointer");
     if (!aligned(dev_in, 16)) return fail(HS_ERR_ARG, "hs_attn_decode_step: dev_in must be 16-byte aligned");
     const int64_t D = view->head_dim;
@@ -578,9 +612,10 @@ int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *d
     cudaError_t e = cudaMemcpyAsync(dev_in, host_in, static_cast<size_t>(q_elems + 2 * kv_elems) * 2, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode_step: %s", cudaGetErrorString(e));
     uint16_t *qd = reinterpret_cast<uint16_t *>(dev_in), *kd = qd + q_elems, *vd = kd + kv_elems;
-    if (int32_t st = hs_kv_quantize_write(view, kd, vd, n_seqs, 1, dst_pos, sin, cos, rotary_dim, n_positions, stream)) return st;
-    if (int32_t st = hs_attn_decode(qd, view, seq_lens, n_seqs, n_q_heads, softmax_scale, dev_out, nullptr, workspace, workspace_bytes, nullptr,
-                                    nullptr, stream))
+    // cache update + attention: one launch when the new tokens go to seq_lens - 1 (dst_pos == NULL) on a u8 cache, else the write
+    // kernel and the attention kernel as its programmatic dependent; q came with the copy before both
+    if (int32_t st = hs_attn_decode_append(qd, kd, vd, view, dst_pos, seq_lens, n_seqs, n_q_heads, softmax_scale, sin, cos, rotary_dim, n_positions, dev_out,
+                                           nullptr, workspace, workspace_bytes, stream))
         return st;
     // (letting the kernel store into mapped host memory instead of this copy was measured: 9 us slower per step)
     e = cudaMemcpyAsync(host_out, dev_out, static_cast<size_t>(q_elems) * 2, cudaMemcpyDeviceToHost, s);

@@ -27,12 +27,17 @@
 #include <cuda_fp16.h>
 
 #include "hs_common.cuh"
+#include "quant_dev.cuh"
 
 namespace hs {
 
 constexpr int kTcConsumers = 8;       // every warp consumes; whichever finishes a tile last refills its stage
 constexpr int kTcThreads = kTcConsumers * 32;
 constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence, in eighths of a tile (measured: 10-20 are alike)
+#ifndef HS_TC_APPEND_UNITS
+#define HS_TC_APPEND_UNITS 10
+#endif
+constexpr int kTcAppendUnits = HS_TC_APPEND_UNITS;  // ... and of writing a sequence's new token before its last tile is streamed
 constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory (half as many for the head_dim 256 shape)
 constexpr long long kTcWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -176,6 +181,8 @@ struct TcMergeArgs {
     float *o_shard, *lse_shard;  // optional fp32 shard outputs
     int counter;          // which grid-barrier counter the launch uses: one per grid size (CTAs per SM - 1)
     int fine_items;       // merge work items of one query head instead of 512 / D (set when the batch gives the grid too few items)
+    int after_write;      // launched as a programmatic dependent of the quantise-on-write kernel: wait for it before the first cache read
+    AppendArgs append;    // k_new != NULL: the kernel writes the step's new token of every sequence itself (u8 caches)
     ShardArgs shard;      // world > 0: the merged result is a KV-length shard's; exchange it with the other GPUs and merge again
 };
 
@@ -277,7 +284,9 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     // working CTAs than tiles, so that every CTA has at least 8 units and no CTA inside a sequence's span comes out empty.
     const int64_t cta = blockIdx.x;
     const int64_t n_ctas = total < static_cast<int64_t>(gridDim.x) ? (total > 0 ? total : 1) : static_cast<int64_t>(gridDim.x);
-    const int64_t vtotal = 8 * total + static_cast<int64_t>(kTcPadUnits) * n_seqs;
+    // (when the kernel also writes the step's new tokens, the CTA that ends a sequence pays for that too: a wider gap)
+    const int pad_units = kTcPadUnits + (mg.append.k_new != nullptr ? kTcAppendUnits : 0);
+    const int64_t vtotal = 8 * total + static_cast<int64_t>(pad_units) * n_seqs;
     const bool small = vtotal * n_ctas < (1LL << 32);  // 32-bit divisions when they are exact
     auto vbegin = [&](int64_t c) -> int64_t {  // first virtual unit of CTA c
         return small ? static_cast<int64_t>(static_cast<uint32_t>(vtotal) * static_cast<uint32_t>(c) / static_cast<uint32_t>(n_ctas)) : vtotal * c / n_ctas;
@@ -287,9 +296,9 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         int lo = 0, hi = n_seqs;  // invariant: start(lo) <= v < start(hi), start(r) = 8 s_pref[r] + pad r
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if (8LL * s_pref[mid] + static_cast<int64_t>(kTcPadUnits) * mid <= v) lo = mid; else hi = mid;
+            if (8LL * s_pref[mid] + static_cast<int64_t>(pad_units) * mid <= v) lo = mid; else hi = mid;
         }
-        const int64_t off = v - (8LL * s_pref[lo] + static_cast<int64_t>(kTcPadUnits) * lo) - kTcPadUnits;
+        const int64_t off = v - (8LL * s_pref[lo] + static_cast<int64_t>(pad_units) * lo) - pad_units;
         int64_t k = off <= 0 ? 0 : (off + 7) >> 3;
         const int64_t nt = s_pref[lo + 1] - s_pref[lo];
         if (k > nt) k = nt;
@@ -358,11 +367,67 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         }
         __syncwarp();
     };
+    // Programmatic dependent launch: this grid may have started while the quantise-on-write kernel of the same step still
+    // runs (its launch latency and everything above - lengths, prefix, partition - overlap with it); the cache itself must
+    // not be read before that kernel has completed.  Every thread waits, because any warp may issue a tile's copies later.
+    if (mg.after_write) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // ---- the step's new tokens (LayerKVCache::update fused into the attention launch, kv_cache.rs:1275-1496) ----
+    // The token of sequence r sits at position L_r - 1, in the sequence's last tile; the CTA that owns that tile quantises the
+    // token's K and V rows into the cache - same arithmetic, same codes and scales as the write kernel - before the tile's
+    // copies are issued: ordinary stores, a proxy fence, a block barrier, then the bulk copies may read them.  A thread takes
+    // 8 consecutive elements (threads [0, Hkv*D/8) the K row, the next Hkv*D/8 the V row).  Where the CTA's first ring-full
+    // of tiles does not contain such a tile, the write runs after those copies are issued, under their latency.
+    bool append_pending = false, append_early = false;
+    if constexpr (!FOURBIT) {
+        if (mg.append.k_new != nullptr && has_work)
+            for (int r = r_first; r < n_seqs && s_pref[r] < t_end; ++r) {
+                const int last = s_pref[r + 1] - 1;
+                if (s_pref[r + 1] == s_pref[r] || last < t_begin || last >= t_end) continue;
+                append_pending = true;
+                append_early |= last - t_begin < kTcStages;
+            }
+    }
+    auto write_new_tokens = [&]() {  // all threads; CTA-uniform control flow
+        if constexpr (!FOURBIT) {
+            const int H = view.n_kv_heads, cpt = H * kD / 8;                   // 8-element chunks per K (or V) row of a token
+            const bool is_v = static_cast<int>(threadIdx.x) >= cpt;
+            const int chunk = static_cast<int>(threadIdx.x) - (is_v ? cpt : 0);
+            const bool lane_live = chunk < cpt;
+            const int hh = lane_live ? chunk / (kD / 8) : 0, d0 = lane_live ? (chunk % (kD / 8)) * 8 : 0;
+            const int tpb = view.block / 8, bpr = kD / view.block;
+            for (int r = r_first; r < n_seqs && s_pref[r] < t_end; ++r) {
+                const int last = s_pref[r + 1] - 1;                               // the sequence's last tile
+                if (s_pref[r + 1] == s_pref[r] || last < t_begin || last >= t_end) continue;
+                const int pos = s_len[r] - 1;
+                const int page = pos / view.page_tokens;
+                const bool rope = !is_v && mg.append.sin != nullptr;
+                bool okw = lane_live;
+                if (rope && pos >= mg.append.n_positions) { okw = false; if (lane_live && chunk == 0) atomicOr(err, HS_DEVERR_KV_WRITE_RANGE); }
+                float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                const uint16_t *src = (is_v ? mg.append.v_new : mg.append.k_new) + (static_cast<int64_t>(r) * H + hh) * kD;
+                if (okw) load_row8_rope(src, d0, rope ? mg.append.sin : nullptr, mg.append.cos, pos, mg.append.rotary_dim, x);
+                int c[8];
+                const float a = quantize_n<HS_KV_INT8, 8>(x, tpb, view.scale_dtype, nullptr, c);  // (every lane takes part in the shuffles)
+                if (!okw) continue;
+                const int64_t pidx = static_cast<int64_t>(r) * view.pages_per_seq + page;
+                const int64_t in_page = static_cast<int64_t>(pos - page * view.page_tokens) * H + hh;
+                uint8_t *codes = reinterpret_cast<uint8_t *>((is_v ? view.v_pages : view.k_pages)[pidx]);
+                void *scales = (is_v ? view.v_scale_pages : view.k_scale_pages)[pidx];
+                if ((d0 & (view.block - 1)) == 0) store_scale(scales, in_page * bpr + d0 / view.block, view.scale_dtype, a);
+                store_codes8<HS_KV_INT8>(codes, in_page * kD + d0, in_page * kD + d0 + 8, c, true);
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __syncthreads();
+        }
+    };
+    if (append_pending && append_early) write_new_tokens();
     bool ok = true;
     if (warp == 0 && has_work) {  // fill the ring before anything else touches global memory
         fill_desc(0);
         for (int p = 0; p < n_tiles_cta && p < kTcStages; ++p) issue_tile(p, p);
     }
+
+    if (append_pending && !append_early) write_new_tokens();  // (under the latency of the copies just issued)
 
     // ================================ consumer warps ================================
     // warp -> (128-wide half `head` of the token row, 16-token group `th` of the tile); `kvh`, `half`: the kv head and
@@ -675,7 +740,7 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
     const int tgroups = kTcThreads / item_threads;                 // thread groups that share an item's partials (1, 2 or 4)
     const int tg = threadIdx.x / item_threads, within = threadIdx.x - tg * item_threads;
     auto owner = [&](int64_t t, int r) -> int64_t {  // the CTA whose range holds tile t of sequence r
-        const int64_t v = 8 * t + static_cast<int64_t>(kTcPadUnits) * (r + 1);  // the tile's first virtual unit
+        const int64_t v = 8 * t + static_cast<int64_t>(pad_units) * (r + 1);  // the tile's first virtual unit
         int64_t c = small ? static_cast<int64_t>(static_cast<uint32_t>(v) * static_cast<uint32_t>(n_ctas) / static_cast<uint32_t>(vtotal)) : v * n_ctas / vtotal;
         if (c > n_ctas - 1) c = n_ctas - 1;
         while (c > 0 && vbegin(c) > v) --c;
@@ -879,7 +944,35 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
     mg.counter = ctas_per_sm - 1;
     ViewDev vv = v;
     void *args[] = {&vv, &q, &seq_lens, &n_seqs, &n_q_heads, &kmul, &o_part, &lse_part, &err, &mg};
-    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
+    cudaError_t e = cudaErrorUnknown;
+    if (mg.after_write) {
+        // cooperative + programmatic stream serialisation; a driver that refuses the combination gets the plain launch for good
+        static PerDeviceState pdl;  // 0 = untried, 1 = accepted, -1 = refused
+        if (pdl.get(dev) >= 0) {
+            cudaLaunchAttribute attrs[2];
+            attrs[0].id = cudaLaunchAttributeCooperative;
+            attrs[0].val.cooperative = 1;
+            attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[1].val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(n_ctas);
+            cfg.blockDim = dim3(kTcThreads);
+            cfg.dynamicSmemBytes = LT::kTotal;
+            cfg.stream = s;
+            cfg.attrs = attrs;
+            cfg.numAttrs = 2;
+            e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void *>(kern), args);
+            if (e == cudaSuccess) {
+                pdl.set(dev, 1);
+                *fused_out = 1;
+                return HS_OK;
+            }
+            cudaGetLastError();
+            pdl.set(dev, -1);
+        }
+        mg.after_write = 0;  // ordinary stream order: the write kernel has completed when this grid starts
+    }
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(n_ctas), dim3(kTcThreads), args, LT::kTotal, s);
     if (e == cudaSuccess) {
         *fused_out = 1;
         return HS_OK;
@@ -895,7 +988,7 @@ static int32_t launch_tc(const ViewDev &v, const uint16_t *q, const int32_t *seq
 int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *seq_lens, int n_seqs, int n_q_heads,
                            float softmax_scale, float *o_part, float *lse_part, int *err, cudaStream_t s, int *n_ctas_out,
                            uint16_t *out, const uint16_t *gate, float *o_shard, float *lse_shard, int *merged_out,
-                           const ShardArgs *shard) {
+                           const ShardArgs *shard, int after_write, const AppendArgs *append) {
     *n_ctas_out = 0;
     *merged_out = 0;
     // covered shapes: 8 kv heads x 128 with 4 query heads each, and 2 kv heads x 256 with 8 query heads each
@@ -911,7 +1004,12 @@ int32_t decode_int8_tc_try(const ViewDev &v, const uint16_t *q, const int32_t *s
     const bool sf16 = v.scale_dtype == HS_SCALE_F16;
     int n_ctas = 2 * sm_count();  // upper bound; the launch settles on one or two CTAs per SM
     const float kmul = softmax_scale * 1.4426950408889634f / (four ? 1.0f : 127.0f);
-    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0, 0, ShardArgs{}};
+    TcMergeArgs mg{out, gate, o_shard, lse_shard, 0, 0, after_write, AppendArgs{}, ShardArgs{}};
+    mg.append.k_new = nullptr;
+    if (append) {
+        if (four) return HS_OK;  // only u8 caches are written inside the kernel: the caller launches the write kernel
+        mg.append = *append;
+    }
     // few, long sequences: with 512 / D heads per merge item less than half of the SMs would merge, each in several rounds
     mg.fine_items = static_cast<int64_t>(n_seqs) * n_q_heads / (512 / v.head_dim) * 2 <= sm_count() ? 1 : 0;
     mg.shard.world = 0;

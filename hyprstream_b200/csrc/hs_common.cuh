@@ -77,6 +77,16 @@ struct ShardArgs {
     long long rows_cap;
 };
 
+// One new token per sequence that the decode kernel writes into the cache itself (int8 caches) before it attends:
+// k_new == NULL: off.  The token of sequence s goes to position seq_lens[s] - 1.
+struct AppendArgs {
+    const uint16_t *k_new, *v_new;  // bf16 [n_seqs, 1, n_kv_heads, head_dim]
+    const uint16_t *sin, *cos;      // optional fused K rotation
+    int rotary_dim, n_positions;
+};
+int32_t kv_write_at_end(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, const int32_t *seq_lens, const void *sin,
+                        const void *cos, int32_t rotary_dim, int32_t n_positions, hs_stream_t stream);
+
 // ---- device helpers --------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }

@@ -13,6 +13,7 @@
 // All kernels here are HBM-streaming: one thread owns 8 consecutive elements (one 16-byte bf16
 // load, one 8-byte int8 store), a block's absmax is reduced with warp shuffles, nothing is staged.
 #include "hs_common.cuh"
+#include "quant_dev.cuh"
 
 namespace hs {
 
@@ -21,116 +22,6 @@ constexpr int kQThreads = 256;
 #define HS_KV_WRITE_WIDE 16
 #endif
 constexpr int kWriteElems = 64;  // elements per thread of the quantise-on-write kernel (as 8- or 16-element chunks)
-
-__device__ __forceinline__ float code8(int i) { return __fdiv_rn(static_cast<float>(i) - 127.0f, 127.0f); }
-__device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(code8(j), code8(j + 1))); }
-
-// Index of y in the 8-bit linear codebook.  The candidate round(y*127)+127 is exact unless y*127 sits
-// within 1e-3 of a half-integer; only then are the true f32 midpoints consulted (smid: the 255 midpoints in shared
-// memory, so the rare path costs two loads and not four divisions for every lane of the warp).
-__device__ __forceinline__ int index_int8(float y, const float *smid) {
-    float t = __fmul_rn(y, 127.0f);
-    const float r = rintf(t);
-    int c = max(0, min(255, static_cast<int>(r) + 127));
-    if (fabsf(t - r) > 0.499f) {  // within 1e-3 of a half-integer
-        if (c > 0 && !(y > smid[c - 1])) c--;
-        else if (c < 255 && y > smid[c]) c++;
-    }
-    return c;
-}
-
-// Index of y in a 16-entry ascending codebook whose 15 midpoints are in shared memory.
-__device__ __forceinline__ int index_4bit(float y, const float *smid) {
-    int c = 0;
-#pragma unroll
-    for (int j = 0; j < 15; ++j) c += (y > smid[j]) ? 1 : 0;
-    return c;
-}
-
-// smid: 256 floats; the block has at least 255 threads
-__device__ __forceinline__ void fill_midpoints(int kind, float *smid) {
-    if (kind == HS_KV_INT8) {
-        if (threadIdx.x < 255) smid[threadIdx.x] = mid8(threadIdx.x);
-    } else if (threadIdx.x < 15) {
-        const float *t = kind == HS_KV_NF4 ? c_nf4 : c_fp4;
-        smid[threadIdx.x] = __fmul_rn(0.5f, __fadd_rn(t[threadIdx.x], t[threadIdx.x + 1]));
-    }
-}
-
-__device__ __forceinline__ float f16_sat_round(float a) {
-    // nearest-even to f16, saturating: anything that would round past 65504 stays 65504
-    return a >= 65520.0f ? 65504.0f : __half2float(__float2half_rn(a));
-}
-
-// Quantise the 8 values of this thread; `tpb` consecutive lanes (a power of two <= 32) share a block.
-// Returns the stored scale (already rounded in f16 mode); codes[] receives 8 indices.
-template <int KIND, int N>
-__device__ __forceinline__ float quantize_n(const float (&x)[N], int tpb, int scale_dtype, const float *smid,
-                                            int (&codes)[N]) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(x[i]));
-    for (int o = 1; o < tpb; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    float a = scale_dtype == HS_SCALE_F16 ? f16_sat_round(amax) : amax;
-    if (a == 0.0f) {
-        const int zc = KIND == HS_KV_INT8 ? 127 : (KIND == HS_KV_NF4 ? 7 : 0);
-#pragma unroll
-        for (int i = 0; i < N; ++i) codes[i] = zc;
-        return a;
-    }
-    float inv = __fdiv_rn(1.0f, a);
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-        float y = __fmul_rn(x[i], inv);
-        codes[i] = KIND == HS_KV_INT8 ? index_int8(y, smid) : index_4bit(y, smid);
-    }
-    return a;
-}
-template <int KIND>
-__device__ __forceinline__ float quantize8(const float (&x)[8], int tpb, int scale_dtype, const float *smid, int (&codes)[8]) {
-    return quantize_n<KIND, 8>(x, tpb, scale_dtype, smid, codes);
-}
-
-__device__ __forceinline__ void store_scale(void *p, int64_t idx, int scale_dtype, float a) {
-    if (scale_dtype == HS_SCALE_F16) reinterpret_cast<__half *>(p)[idx] = __float2half_rn(a);
-    else reinterpret_cast<float *>(p)[idx] = a;
-}
-
-__device__ __forceinline__ float load_elem(const void *src, int dtype, int64_t i) {
-    if (dtype == HS_DTYPE_BF16) return bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(src)[i]);
-    if (dtype == HS_DTYPE_F16) return __half2float(reinterpret_cast<const __half *>(src)[i]);
-    return reinterpret_cast<const float *>(src)[i];
-}
-
-__device__ __forceinline__ void unpack8_bf16(const uint4 &w, float (&x)[8]) {
-    x[0] = bf16lo(w.x); x[1] = bf16hi(w.x); x[2] = bf16lo(w.y); x[3] = bf16hi(w.y);
-    x[4] = bf16lo(w.z); x[5] = bf16hi(w.z); x[6] = bf16lo(w.w); x[7] = bf16hi(w.w);
-}
-
-template <int KIND>
-__device__ __forceinline__ void store_codes8(uint8_t *codes, int64_t e0, int64_t n, const int (&c)[8], bool full) {
-    if (KIND == HS_KV_INT8) {
-        if (full) {
-            uint2 w;
-            w.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-            w.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
-            *reinterpret_cast<uint2 *>(codes + e0) = w;
-        } else {
-            for (int i = 0; i < 8 && e0 + i < n; ++i) codes[e0 + i] = static_cast<uint8_t>(c[i]);
-        }
-    } else {
-        if (full) {
-            uint32_t w = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8) | (((c[4] << 4) | c[5]) << 16) |
-                         (((c[6] << 4) | c[7]) << 24);
-            *reinterpret_cast<uint32_t *>(codes + (e0 >> 1)) = w;
-        } else {
-            for (int i = 0; i < 8 && e0 + i < n; i += 2) {
-                int lo = (e0 + i + 1 < n) ? c[i + 1] : 0;
-                codes[(e0 + i) >> 1] = static_cast<uint8_t>((c[i] << 4) | lo);
-            }
-        }
-    }
-}
 
 // ---- flat quantise ----------------------------------------------------------------------------
 template <int KIND>
@@ -186,31 +77,7 @@ __global__ void __launch_bounds__(kQThreads) dequantize_flat_kernel(int kind, co
     }
 }
 
-// ---- RoPE ------------------------------------------------------------------------------------------
-// Rotated value of element d of a row, given the row's unrotated elements `own` (at d) and `partner`
-// (at d +- rotary_dim/2).  Every product, difference and sum is rounded to bf16 (rope.rs:243-244).
-__device__ __forceinline__ float rope_elem(float own, float partner, float s, float c, bool first_half) {
-    if (first_half) return bf16_round(bf16_round(own * c) - bf16_round(partner * s));  // x1*cos - x2*sin
-    return bf16_round(bf16_round(partner * s) + bf16_round(own * c));                 // x1*sin + x2*cos
-}
-
-// Loads the 8 bf16 elements [d0, d0+8) of a row, rotated when sin != NULL.
-__device__ __forceinline__ void load_row8_rope(const uint16_t *row, int d0, const uint16_t *sin, const uint16_t *cos,
-                                               int pos, int rotary_dim, float (&x)[8]) {
-    unpack8_bf16(*reinterpret_cast<const uint4 *>(row + d0), x);
-    if (sin != nullptr && d0 < rotary_dim) {
-        const int half = rotary_dim >> 1;
-        const bool first = d0 < half;
-        float p[8];
-        unpack8_bf16(*reinterpret_cast<const uint4 *>(row + (first ? d0 + half : d0 - half)), p);
-        const int j0 = first ? d0 : d0 - half;
-        const uint16_t *srow = sin + static_cast<int64_t>(pos) * half + j0;
-        const uint16_t *crow = cos + static_cast<int64_t>(pos) * half + j0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = rope_elem(x[i], p[i], bf16_bits_to_f32(srow[i]), bf16_bits_to_f32(crow[i]), first);
-    }
-}
-
+// ---- RoPE (device helpers in quant_dev.cuh) ------------------------------------------------------------
 __global__ void __launch_bounds__(kQThreads) rope_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out,
                                                          const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
                                                          const int32_t *__restrict__ positions, int64_t n_rows, int n_heads,
@@ -238,6 +105,7 @@ struct KNormArgs {
     float eps;
     int plus_one;         // multiply by (1 + w) instead of w
     uint16_t *k_out;      // optional bf16 [n_seqs, n_tokens, n_kv_heads, head_dim]: the normed, rotated keys
+    int pos_bias;         // added to dst_pos[s]: -1 when the caller hands the attended lengths instead of positions
 };
 
 // ---- quantise-on-write into a cache view ----------------------------------------------------------------
@@ -249,6 +117,9 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
                                                              const int32_t *__restrict__ dst_pos,
                                                              const uint16_t *__restrict__ sin, const uint16_t *__restrict__ cos,
                                                              int rotary_dim, int n_positions, int *__restrict__ err, KNormArgs kn) {
+    // a decode launch that follows as a programmatic dependent may start now (it waits for this grid's completion before
+    // it reads the cache); a no-op for every other successor
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float smid[256];
     fill_midpoints(KIND, smid);
     __syncthreads();
@@ -263,7 +134,7 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
     constexpr int kUnroll = kWriteElems / E;
     const uint32_t cpr = static_cast<uint32_t>(D) / static_cast<uint32_t>(E);
     const uint32_t total = static_cast<uint32_t>(n_tokens) * static_cast<uint32_t>(H) * cpr;
-    const int base_pos = dst_pos ? dst_pos[s] : 0;
+    const int base_pos = dst_pos ? dst_pos[s] + kn.pos_bias : 0;
     void *const *data_pages = is_v ? view.v_pages : view.k_pages;
     void *const *scale_pages = is_v ? view.v_scale_pages : view.k_scale_pages;
     const int tpb = view.block / E;
@@ -556,15 +427,27 @@ int32_t hs_kv_quantize_write(const hs_kv_view *view, const void *k_new, const vo
                              const int32_t *dst_pos, const void *sin, const void *cos, int32_t rotary_dim,
                              int32_t n_positions, hs_stream_t stream) {
     return kv_write_impl("hs_kv_quantize_write", view, k_new, v_new, n_seqs, n_tokens, dst_pos, sin, cos, rotary_dim, n_positions,
-                         hs::KNormArgs{nullptr, 0.0f, 0, nullptr}, stream);
+                         hs::KNormArgs{nullptr, 0.0f, 0, nullptr, 0}, stream);
 }
+
+}  // extern "C"
+
+// hs_kv_quantize_write of one new token per sequence at position seq_lens[s] - 1 (used by hs_attn_decode_append when the
+// caller gives no positions and the attention kernel does not take the write itself)
+int32_t hs::kv_write_at_end(const hs_kv_view *view, const void *k_new, const void *v_new, int32_t n_seqs, const int32_t *seq_lens, const void *sin,
+                            const void *cos, int32_t rotary_dim, int32_t n_positions, hs_stream_t stream) {
+    return kv_write_impl("hs_attn_decode_append", view, k_new, v_new, n_seqs, 1, seq_lens, sin, cos, rotary_dim, n_positions,
+                         hs::KNormArgs{nullptr, 0.0f, 0, nullptr, -1}, stream);
+}
+
+extern "C" {
 
 int32_t hs_kv_norm_rope_quantize_write(const hs_kv_view *view, const void *k_proj, const void *v_new, int32_t n_seqs, int32_t n_tokens,
                                        const int32_t *dst_pos, const float *k_norm_weight, float eps, int32_t weight_plus_one, const void *sin,
                                        const void *cos, int32_t rotary_dim, int32_t n_positions, void *k_out, hs_stream_t stream) {
     if (!k_norm_weight) return fail(HS_ERR_ARG, "hs_kv_norm_rope_quantize_write: NULL norm weight (use hs_kv_quantize_write)");
     return kv_write_impl("hs_kv_norm_rope_quantize_write", view, k_proj, v_new, n_seqs, n_tokens, dst_pos, sin, cos, rotary_dim, n_positions,
-                         hs::KNormArgs{k_norm_weight, eps, weight_plus_one, reinterpret_cast<uint16_t *>(k_out)}, stream);
+                         hs::KNormArgs{k_norm_weight, eps, weight_plus_one, reinterpret_cast<uint16_t *>(k_out), 0}, stream);
 }
 
 int32_t hs_kv_gather_dequantize(const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t out_tokens,

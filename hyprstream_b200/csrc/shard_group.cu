@@ -18,7 +18,7 @@
 namespace hs {
 int32_t decode_impl(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads, float softmax_scale,
                     void *out, const void *gate, void *workspace, int64_t workspace_bytes, float *o_shard, float *lse_shard,
-                    const ShardArgs *shard, hs_stream_t stream);
+                    const ShardArgs *shard, hs_stream_t stream, int after_write = 0, const AppendArgs *append = nullptr, int *appended = nullptr);
 }
 
 struct hs_shard_group {

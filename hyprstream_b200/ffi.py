@@ -105,6 +105,8 @@ _SIGS = {
     "hs_attn_decode": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "hs_attn_decode_static_max_bytes": (c_int64, []),
     "hs_attn_decode_static": (c_int32, [c_void_p, POINTER(KVView), c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p]),
+    "hs_attn_decode_append": (c_int32, [c_void_p, c_void_p, c_void_p, POINTER(KVView), c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p,
+                                        c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "hs_attn_decode_step": (c_int32, [POINTER(KVView), c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p, c_void_p,
                                       c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "hs_shard_group_create": (c_int32, [c_int32] * 5 + [POINTER(c_void_p)]),

@@ -172,6 +172,26 @@ def decode_attention(q: torch.Tensor, view: KVView, seq_lens: torch.Tensor, soft
     return out
 
 
+def decode_append(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, view: KVView, dst_pos: Optional[torch.Tensor], seq_lens: torch.Tensor,
+                  softmax_scale: Optional[float] = None, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                  rotary_dim: int = 0, gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Cache update of one new token per sequence + decode attention as one call (hs_attn_decode_append; llama.rs:598-640): the
+    new token of sequence s goes to ``dst_pos[s]``, or with ``dst_pos=None`` to ``seq_lens[s] - 1`` - then, on an int8 cache, the
+    attention kernel writes it itself (one launch per step).
+    q bf16 [n_seqs, Hq, D]; k_new, v_new bf16 [n_seqs, 1, Hkv, D]; dst_pos, seq_lens int32 [n_seqs]."""
+    _need_cuda(q, k_new, v_new, dst_pos, seq_lens, sin, cos, gate)
+    n_seqs, hq, d = q.shape
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
+    ws = decode_workspace(n_seqs, hq, d, q.device) if workspace is None else workspace
+    if out is None:
+        out = torch.empty_like(q)
+    check(lib.hs_attn_decode_append(_ptr(q), _ptr(k_new), _ptr(v_new), ctypes.byref(view), _ptr(dst_pos), _ptr(seq_lens), n_seqs, hq, scale,
+                                    _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0], _ptr(out), _ptr(gate), _ptr(ws),
+                                    ws.numel(), _stream()))
+    return out
+
+
 class DecodeStep:
     """One decode step of a batch as one C-ABI call (hs_attn_decode_step): the step's q, new K and new V travel from one
     pinned host buffer in one copy, the new token is quantised into the caches, the batch is attended, and the result
@@ -192,7 +212,7 @@ class DecodeStep:
         self.ws = decode_workspace(n_seqs, n_q_heads, d, device)
         self.h2d_bytes, self.d2h_bytes = self.host_in.numel() * 2, self.out_host.numel() * 2
 
-    def run(self, dst_pos: torch.Tensor, seq_lens: torch.Tensor, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+    def run(self, dst_pos: Optional[torch.Tensor], seq_lens: torch.Tensor, sin: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
             rotary_dim: int = 0, sync: bool = True) -> torch.Tensor:
         check(lib.hs_attn_decode_step(ctypes.byref(self.view), self.host_in.data_ptr(), self.dev_in.data_ptr(), _ptr(dst_pos), _ptr(seq_lens),
                                       self.n_seqs, self.hq, self.scale, _ptr(sin), _ptr(cos), rotary_dim, 0 if sin is None else sin.shape[0],

@@ -216,6 +216,21 @@ int64_t hs_attn_decode_static_max_bytes(void);
 int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32_t *seq_lens, int32_t n_seqs,
                               int32_t n_q_heads, float softmax_scale, void *out, const void *gate, hs_stream_t stream);
 
+/* LayerKVCache::update of one new token per sequence followed by the attention over the cache, as LlamaAttention::forward
+ * does them back to back (architectures/llama.rs:598-640; forward_batched :772-828): hs_kv_quantize_write (n_tokens = 1,
+ * optional fused K RoPE) + hs_attn_decode in one call.  k_new, v_new bf16 [n_seqs, 1, n_kv_heads, head_dim]; seq_lens the
+ * lengths attended, the new token included; dst_pos the new tokens' cache positions, or NULL for "position
+ * seq_lens[s] - 1", the normal case; the rest as for the two calls.
+ *   dst_pos == NULL, u8 cache, a shape the tensor-core decode kernel serves: ONE launch - the CTA that owns a sequence's
+ *     last tile quantises that sequence's new K and V rows into the cache (same codes and scales as the write kernel,
+ *     bit for bit) before it streams the tile.
+ *   otherwise: the write kernel, then the attention kernel launched as its programmatic dependent (its launch and set-up
+ *     run under the write; only its first cache read waits for it).  q may come from any earlier work on the stream. */
+int32_t hs_attn_decode_append(const void *q, const void *k_new, const void *v_new, const hs_kv_view *view,
+                              const int32_t *dst_pos, const int32_t *seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                              float softmax_scale, const void *sin, const void *cos, int32_t rotary_dim, int32_t n_positions,
+                              void *out, const void *gate, void *workspace, int64_t workspace_bytes, hs_stream_t stream);
+
 /* One decode step of a batch as ONE call, for a host whose step inputs and result live in host memory: the
  * reference's engine loop runs one forward per step on one thread and reads the result back
  * (crates/hyprstream/src/runtime/torch_engine.rs:3719-3731, forward_batched_step :1475-1501); through this entry that
@@ -223,8 +238,9 @@ int32_t hs_attn_decode_static(const void *q, const hs_kv_view *view, const int32
  *   host_in   pinned host memory, bf16: q [n_seqs, n_q_heads, D] | k_new [n_seqs, n_kv_heads, D] | v_new [same]
  *   dev_in    device staging buffer of the same size (16-byte aligned); dev_out device bf16 [n_seqs, n_q_heads, D]
  *   host_out  pinned host memory for the result, same shape as q
- *   dst_pos, seq_lens  device int32 [n_seqs]: where each sequence's new token goes, and the length attended
- *             (normally dst_pos + 1); sin / cos / rotary_dim / n_positions as for hs_kv_quantize_write (K rotated)
+ *   dst_pos, seq_lens  device int32 [n_seqs]: where each sequence's new token goes (NULL: seq_lens - 1, which lets the
+ *             attention kernel write it: see hs_attn_decode_append), and the length attended, the new token included;
+ *             sin / cos / rotary_dim / n_positions as for hs_kv_quantize_write (K rotated)
  * Enqueues on `stream`: one host-to-device copy, hs_kv_quantize_write of the one new token per sequence,
  * hs_attn_decode, one device-to-host copy.  With HS_STEP_SYNC in `flags` the call returns when host_out is valid;
  * otherwise the caller synchronises the stream. */

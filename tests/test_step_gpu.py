@@ -72,6 +72,46 @@ def test_decode_step_equals_the_separate_calls_and_the_oracle(cuda):
     no_device_error()
 
 
+@pytest.mark.parametrize("fused_write", [False, True])
+def test_decode_append_equals_write_then_decode(cuda, fused_write):
+    """hs_attn_decode_append == hs_kv_quantize_write followed by hs_attn_decode, over several steps in a row without any
+    host synchronisation between them, with the fused K rotation; the stored codes and scales are identical.  With explicit
+    positions the attention kernel is launched as a programmatic dependent of the write kernel (two launches); with
+    positions = seq_lens - 1 (dst_pos None) the attention kernel writes the new tokens itself (one launch)."""
+    from hyprstream_b200 import kv_cache as kc, ops
+
+    lens = [700, 33, 4000, 1, 512, 90]
+    a, _, _ = _batch(cuda, lens, seed=6)
+    b, _, _ = _batch(cuda, lens, seed=6)
+    va, keep_a = kc.make_view(a)
+    vb, keep_b = kc.make_view(b)
+    sin, cos = (t.to(cuda) for t in ar.rope_tables(128, 500000.0, 8192, torch.bfloat16))
+    pos = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    steps = 6
+    qs = torch.randn(steps, len(lens), 32, 128, device=cuda, generator=gen).bfloat16()
+    ks = torch.randn(steps, len(lens), 1, 8, 128, device=cuda, generator=gen).bfloat16()
+    vs = torch.randn(steps, len(lens), 1, 8, 128, device=cuda, generator=gen).bfloat16()
+    poss = torch.stack([pos + t for t in range(steps)])
+    lenss = poss + 1
+    from hyprstream_b200 import ffi
+    n0 = ffi.launch_count()
+    got = [ops.decode_append(qs[t], ks[t], vs[t], va, poss[t] if fused_write is False else None, lenss[t], sin=sin, cos=cos, rotary_dim=128)
+           for t in range(steps)]
+    torch.cuda.synchronize()
+    assert ffi.launch_count() - n0 == steps * (1 if fused_write else 2)
+    for t in range(steps):
+        ops.kv_quantize_write(vb, ks[t], vs[t], poss[t], sin, cos, 128)
+        ref = ops.decode_attention(qs[t], vb, lenss[t])
+        torch.cuda.synchronize()
+        assert (got[t].float() - ref.float()).abs().max().item() <= 4e-3, f"step {t}"
+    for x, y, l in zip(a, b, lens):
+        x.seq_pos = y.seq_pos = l + steps
+        for u, w in zip(x.snapshot(), y.snapshot()):
+            assert torch.equal(u.view(torch.uint8), w.view(torch.uint8))
+    no_device_error()
+
+
 def test_view_goes_stale_when_a_cache_grows_or_releases_storage(cuda):
     from hyprstream_b200 import ffi, kv_cache as kc
 
