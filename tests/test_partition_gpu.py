@@ -10,12 +10,12 @@ from tests.util import no_device_error
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [2, 8])
-def test_prefill_units_equal_unpartitioned(cuda, world):
+@pytest.mark.parametrize("world,hq,hkv,d", [(2, 32, 8, 128), (8, 32, 8, 128), (8, 16, 2, 256)])
+def test_prefill_units_equal_unpartitioned(cuda, world, hq, hkv, d):
     from hyprstream_b200 import ops
     from hyprstream_b200.sharded import partition_units
 
-    b, t, hq, hkv, d = 2, 300, 32, 8, 128
+    b, t = 2, 300
     g = torch.Generator(device=cuda).manual_seed(1)
     q = torch.randn(b, t, hq, d, device=cuda, generator=g).bfloat16()
     k = torch.randn(b, t, hkv, d, device=cuda, generator=g).bfloat16()
