@@ -39,7 +39,6 @@ constexpr int kTcPadUnits = 12;       // partition: cost of starting a sequence,
 #endif
 constexpr int kTcAppendUnits = HS_TC_APPEND_UNITS;  // ... and of writing a sequence's new token before its last tile is streamed
 constexpr int kTcMaxSeqs = 512;       // tile-count prefix and lengths kept in shared memory (half as many for the head_dim 256 shape)
-constexpr int kTcTabPages = 64;       // page-pointer tables of up to this many pages are copied to shared memory in the prologue (half for head_dim 256)
 constexpr long long kTcWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -167,9 +166,7 @@ struct TcLayout {
     static constexpr int kDescOff = kLenOff + kMaxSeqs * 4;            // uint64 [64 tiles][4 tables]: source addresses of the next tiles
     static constexpr int kXOff = (kDescOff + 64 * 4 * 8 + 127) / 128 * 128;  // float [4 pairs][2 parities][2 warps][32 lanes][4] (WIDE)
     static constexpr int kLutOff = kXOff + (WIDE ? 4 * 2 * 2 * 512 : 0);        // uint32 [256][32] (4-bit kinds only)
-    static constexpr int kTabOff = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);           // uint64 [4][kTabPages]: page pointers of a small batch
-    static constexpr int kTabPages = WIDE ? kTcTabPages / 2 : kTcTabPages;
-    static constexpr int kTotal = kTabOff + 4 * kTabPages * 8;
+    static constexpr int kTotal = kLutOff + (FOURBIT ? 256 * 32 * 4 : 0);
     static constexpr uint32_t kTxBytes = 2u * kTile * kRow + 2u * kTile * kSRow;
     static_assert(kDescOff % 16 == 0, "tile addresses are stored 16 bytes at a time");
     // two CTAs per SM (228 KB, 1 KB reserved per CTA, 128 B of static shared memory) for every layout but the head_dim 256
@@ -243,17 +240,6 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
         s_pref[i + 1] = (s_len[i] + kTcTile - 1) / kTcTile;
     }
     if (over && blockIdx.x == 0) atomicOr(err, HS_DEVERR_DECODE_RANGE);
-    // the four page-pointer tables of a small batch, fetched now, in the shadow of the lengths' load, so that the tile
-    // addresses below do not wait for a second trip to global memory
-    unsigned long long *s_tab = reinterpret_cast<unsigned long long *>(smem + LT::kTabOff);
-    const int n_tab = n_seqs * view.pages_per_seq;
-    const bool tab_in_smem = n_tab <= LT::kTabPages;
-    if (tab_in_smem)
-        for (int i = threadIdx.x; i < 4 * n_tab; i += kTcThreads) {
-            const int a = i / n_tab, j = i - a * n_tab;
-            void *const *src = a == 0 ? view.k_pages : (a == 1 ? view.v_pages : (a == 2 ? view.k_scale_pages : view.v_scale_pages));
-            s_tab[a * LT::kTabPages + j] = reinterpret_cast<unsigned long long>(src[j]);
-        }
     const uint32_t lut_lane = smem_u32(smem + LT::kLutOff) + 4u * lane;  // this lane's column of the table; entry of byte x at + 128 x
     if constexpr (FOURBIT) {
         // byte -> (table[high nibble], table[low nibble]) as fp16x2, low half = the even (first) element
@@ -355,18 +341,10 @@ decode_int8_tc_kernel(ViewDev view, const uint16_t *__restrict__ q, const int32_
             const int page = t0 / view.page_tokens;
             const int64_t in_page = t0 - page * view.page_tokens;
             const int64_t pidx = static_cast<int64_t>(lo) * view.pages_per_seq + page;
-            const unsigned char *pk, *pv, *pks, *pvs;
-            if (tab_in_smem) {
-                pk = reinterpret_cast<const unsigned char *>(s_tab[pidx]);
-                pv = reinterpret_cast<const unsigned char *>(s_tab[LT::kTabPages + pidx]);
-                pks = reinterpret_cast<const unsigned char *>(s_tab[2 * LT::kTabPages + pidx]);
-                pvs = reinterpret_cast<const unsigned char *>(s_tab[3 * LT::kTabPages + pidx]);
-            } else {
-                pk = reinterpret_cast<const unsigned char *>(view.k_pages[pidx]);
-                pv = reinterpret_cast<const unsigned char *>(view.v_pages[pidx]);
-                pks = reinterpret_cast<const unsigned char *>(view.k_scale_pages[pidx]);
-                pvs = reinterpret_cast<const unsigned char *>(view.v_scale_pages[pidx]);
-            }
+            const unsigned char *pk = reinterpret_cast<const unsigned char *>(view.k_pages[pidx]);
+            const unsigned char *pv = reinterpret_cast<const unsigned char *>(view.v_pages[pidx]);
+            const unsigned char *pks = reinterpret_cast<const unsigned char *>(view.k_scale_pages[pidx]);
+            const unsigned char *pvs = reinterpret_cast<const unsigned char *>(view.v_scale_pages[pidx]);
             ulonglong2 *d = reinterpret_cast<ulonglong2 *>(s_desc + 4 * (p & 63));
             d[0] = make_ulonglong2(reinterpret_cast<unsigned long long>(pk + in_page * LT::kRow), reinterpret_cast<unsigned long long>(pv + in_page * LT::kRow));
             d[1] = make_ulonglong2(reinterpret_cast<unsigned long long>(pks + in_page * LT::kSRow), reinterpret_cast<unsigned long long>(pvs + in_page * LT::kSRow));
