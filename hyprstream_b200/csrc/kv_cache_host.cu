@@ -13,6 +13,7 @@
 //
 // This file is host code only; it launches kernels solely through the C ABI in include/hs_attn.h.
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <numeric>
 #include <vector>
@@ -98,6 +99,7 @@ struct Slab {
 
 // ---- BlockPool (kv_cache.rs:515-680) ------------------------------------------------------------------
 struct hs_pool {
+    std::atomic<int> refs{1};       // the handle + every cache created from the pool (Arc<BlockPool>, kv_cache.rs:1111-1130)
     hs::Geometry geo;
     int page_tokens = 0, n_blocks = 0;
     hs::Slab slab;                  // one slab cut into n_blocks pages; a unit is a (K, V) page pair
@@ -311,11 +313,13 @@ int32_t hs_pool_create(int32_t n_blocks, int32_t page_tokens, int32_t kind, int3
     *out = p;
     return HS_OK;
 }
-void hs_pool_destroy(hs_pool *pool) {
-    if (!pool) return;
+// The pool's storage goes when the handle and every cache created from it are gone, whichever is dropped last.
+static void pool_unref(hs_pool *pool) {
+    if (!pool || pool->refs.fetch_sub(1, std::memory_order_acq_rel) != 1) return;
     pool->slab.release();
     delete pool;
 }
+void hs_pool_destroy(hs_pool *pool) { pool_unref(pool); }
 int32_t hs_pool_num_free(const hs_pool *pool) { return pool ? static_cast<int32_t>(pool->free_list.size()) : 0; }
 
 int32_t hs_cache_create(int32_t max_seq_len, int32_t kind, int32_t block, int32_t scale_dtype, int32_t n_kv_heads, int32_t head_dim,
@@ -336,6 +340,7 @@ int32_t hs_cache_create_paged(int32_t max_seq_len, hs_pool *pool, int64_t owner,
     if (!pool || max_seq_len <= 0 || owner < 0) return fail(HS_ERR_ARG, "hs_cache_create_paged: bad arguments");
     hs_cache *c = new hs_cache();
     c->geo = pool->geo; c->max_seq_len = max_seq_len; c->pool = pool; c->owner = owner;
+    pool->refs.fetch_add(1, std::memory_order_relaxed);
     *out = c;
     return HS_OK;
 }
@@ -343,6 +348,7 @@ void hs_cache_destroy(hs_cache *cache) {
     if (!cache) return;
     cache->release_pages(0);
     cache->slab.release();
+    pool_unref(cache->pool);
     delete cache;
 }
 int32_t hs_cache_reserve(hs_cache *cache, int32_t n_tokens) {

@@ -446,6 +446,8 @@ int32_t hs_host_set_allocator(hs_alloc_fn alloc_fn, hs_free_fn free_fn); /* NULL
 
 int32_t hs_pool_create(int32_t n_blocks, int32_t page_tokens, int32_t kind, int32_t block, int32_t scale_dtype,
                        int32_t n_kv_heads, int32_t head_dim, hs_pool **out);
+/* Drops the handle.  Caches created from the pool keep its storage alive (the reference's caches hold an Arc<BlockPool>,
+ * kv_cache.rs:1111-1130): it is freed when the handle and the last such cache are gone, in either order. */
 void hs_pool_destroy(hs_pool *pool);
 int32_t hs_pool_num_free(const hs_pool *pool);
 

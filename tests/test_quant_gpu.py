@@ -240,6 +240,30 @@ def test_cache_errors_mirror_reference(cuda):
     assert pool.num_free() == 2
 
 
+def test_pool_outlives_its_handle_while_caches_remain(cuda):
+    """A paged cache keeps its pool's storage alive (the reference's caches hold an Arc<BlockPool>, kv_cache.rs:1111-1130):
+    the pool handle may be dropped first, the cache still reads its pages and returns them when it is dropped itself."""
+    from hyprstream_b200 import ffi, kv_cache as kc
+
+    pool = kc.BlockPool(4, 2, 128, cuda, kind=1, page_tokens=16)
+    c = kc.LayerKVCache.new_paged(64, pool, "a")
+    g = torch.Generator(device=cuda).manual_seed(3)
+    k = torch.randn(1, 40, 2, 128, device=cuda, generator=g).bfloat16()
+    v = torch.randn(1, 40, 2, 128, device=cuda, generator=g).bfloat16()
+    c.update(k, v, 0)
+    k0, v0 = c.get()
+    ffi.lib.hs_pool_destroy(pool._h)  # the handle goes first
+    pool._h = None
+    c.pool = None
+    k1, v1 = c.get()
+    assert torch.equal(k0, k1) and torch.equal(v0, v1)
+    c.update(k[:, :8], v[:, :8], 40)  # the remaining page of the pool is still handed out
+    assert c.seq_pos == 48
+    del c
+    torch.cuda.synchronize()
+    no_device_error()
+
+
 def test_boundary_rejects_bad_arguments(cuda):
     """Null / misaligned pointers, negative sizes, unsupported geometry -> status code, no launch, no sticky CUDA error."""
     import ctypes
