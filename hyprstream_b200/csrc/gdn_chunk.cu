@@ -16,12 +16,15 @@
 // those accumulators (fp32 -> bf16 pairs), mma.sync.m16n8k16 bf16 x bf16 -> fp32:
 //   [K S0 | Q S0]^T = S^T . [K | Q]^T     (32 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (2 MMAs)
 //   O^T = Gamma (Q S0)^T + U^T . P^T      (2 MMAs)       S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K   (16 MMAs)
-// The per-chunk set-up that does not depend on S belongs to three more warps: one scans the decay, forms k.k on the tensor
-// cores (bf16 k), applies the decay and computes T in its own fragments, one forms q.k and P, one stages the next chunk's
-// fp32 inputs (three TMA tensor copies), all while the eight state warps already run the first product.  Gamma and exp(G_C - G) are folded
-// into accumulator columns, so the only operand tiles in shared memory are k and q as bf16.  Only MMA operands are rounded
-// to bf16; the state and all accumulation stay fp32.
-// Bound: latency of the per-chunk dependency chain (3 block barriers); FLOPs are far below the tensor peak.
+// The per-chunk set-up that does not depend on S runs ahead of the state warps in a ring of chunk slots: a staging warp issues
+// each chunk's three TMA tensor copies (k, q, v boxes of [16 tokens][128]; fp32 from the boundary, bf16 from the layer entry's
+// own prologue) as soon as the slot's previous chunk is done with; four set-up warps take a whole chunk each, round-robin (k, q
+// to bf16 tiles, the decay scan, k.k and q.k on the tensor cores, T in the warp's own fragments, P), and hand the slot to the
+// state warps through an mbarrier.  The eight state warps never meet a block barrier: each waits for the slot, runs its
+// products and signals the slot free.  Gamma and exp(G_C - G) are folded into accumulator columns, so the only operand tiles in
+// shared memory are k and q as bf16.  Only MMA operands are rounded to bf16; the state and all accumulation stay fp32.
+// Bound: the state warps' own chain, ~2,400 cycles per chunk against a tensor-pipe floor of ~900 (mma.sync.m16n8k16 issues at
+// one per 8 cycles and scheduler, 21 cycles dependent; 115 per chunk and scheduler); HBM traffic and FLOPs are far below their peaks.
 //
 // Accuracy: bf16 operand rounding (2^-9 relative) enters every S-dependent product, so outputs agree with the fp32 rule
 // to ~1e-3, inside the path's stated tolerance (max-abs 2e-2, mean-abs 2e-3); hs_gdn_recurrent remains the fp32-exact form.
@@ -34,22 +37,35 @@ namespace hs {
 
 constexpr int kGcC = 16;          // tokens per chunk
 constexpr int kGcD = 128;         // head_k_dim = head_v_dim
-constexpr int kGcThreads = 352;   // warps 0-7: one 16-column slice of the state each; 8: decay scan, k.k, T; 9: q.k, P; 10: staging
+constexpr int kGcChain = 8;       // warps 0-7: one 16-column slice of the state each
+constexpr int kGcPrep = 4;        // warps 8-11: the S-independent set-up of a chunk, a whole chunk per warp, chunks dealt round-robin
+constexpr int kGcThreads = (kGcChain + kGcPrep + 1) * 32;  // warp 12: staging
+// chunks in flight between the copies and the state warps: what fits beside fp32 (bf16) inputs
+template <typename TIn> constexpr int gc_slots() { return sizeof(TIn) == 4 ? 6 : 9; }
 constexpr int kGcRS = kGcD;       // fp32 row stride of the staged inputs (floats): dense, as the tensor copies write them
 constexpr int kGcBS = kGcD + 8;   // bf16 row stride of the [16][128] operand tiles
 constexpr int kGcPS = kGcC + 8;   // bf16 row stride of P, T and of Kd^T
 
-struct GcSmem {
-    __align__(128) float raw[2][3][kGcC][kGcRS];  // k, q, v of a chunk (fp32), double buffered
-    float g[2][kGcC], b[2][kGcC];
-    float G[kGcC], gam[kGcC], dec[kGcC];  // cumulative log-decay, exp(G), exp(G_C - G)
-    __nv_bfloat16 Tb[kGcC][kGcPS];      // (I + A')^-1 (lower)
-    __nv_bfloat16 Kb[kGcC][kGcBS], Qb[kGcC][kGcBS];    // k, q
-    __nv_bfloat16 P[kGcC][kGcPS];       // (q.k) exp(G_t - G_s), s <= t
-    __align__(8) uint64_t full[2];      // mbarriers: the bulk copies of a raw buffer have landed
+template <typename TIn>
+struct GcSlot {
+    __align__(128) TIn raw[3][kGcC][kGcRS];             // k, q, v of the chunk, as the tensor copies deliver them
+    __nv_bfloat16 Kb[kGcC][kGcBS], Qb[kGcC][kGcBS];     // k, q
+    __nv_bfloat16 Tb[kGcC][kGcPS];                      // (I + A')^-1 (lower)
+    __nv_bfloat16 P[kGcC][kGcPS];                       // (q.k) exp(G_t - G_s), s <= t
+    float g[kGcC], b[kGcC];
+    float G[kGcC], gam[kGcC], dec[kGcC];                // cumulative log-decay, exp(G), exp(G_C - G)
 };
+template <typename TIn>
+struct GcSmem {
+    GcSlot<TIn> slot[gc_slots<TIn>()];
+    __align__(8) uint64_t full[gc_slots<TIn>()];   // the tensor copies (and g, beta) of the slot's chunk have landed
+    uint64_t ready[gc_slots<TIn>()];               // its set-up (Kb, Qb, T, P, decays) is complete
+    uint64_t done[gc_slots<TIn>()];                // all state warps are through with it
+    int abort;                                     // a wait ran out somewhere in the CTA
+};
+static_assert(sizeof(GcSmem<float>) + 128 <= 227 * 1024 && sizeof(GcSmem<__nv_bfloat16>) + 128 <= 227 * 1024, "one CTA's shared memory");
 
-constexpr long long kGcWaitCycles = 4000000000LL;  // ~2 s: bound of the wait on the copies
+constexpr long long kGcWaitCycles = 4000000000LL;  // ~2 s: bound of every wait
 
 __device__ __forceinline__ uint32_t gc_s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ bool gc_try_wait(uint32_t bar, uint32_t parity) {
@@ -58,12 +74,18 @@ __device__ __forceinline__ bool gc_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity) {  // bounded
+// bounded; a wait that runs out raises the CTA's abort flag, which ends every other wait of the CTA at once
+__device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (gc_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!gc_try_wait(bar, parity))
-        if (clock64() - t0 > kGcWaitCycles) return false;
+    while (!gc_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kGcWaitCycles) { *abort_flag = 1; return false; }
+    }
     return true;
+}
+__device__ __forceinline__ void gc_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // one [16 tokens][128] fp32 box of a 4-D tensor (d, head, token, sequence); tokens past the tensor's end arrive as zeros
 __device__ __forceinline__ void gc_tma_box(uint32_t dst, const CUtensorMap *map, int head, int token, int seq, uint32_t bar) {
@@ -80,143 +102,144 @@ __device__ __forceinline__ void gc_mma(float (&d)[4], uint32_t a0, uint32_t a1, 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float gc_f32(float x) { return x; }
+__device__ __forceinline__ float gc_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ uint32_t gc_ld32(const __nv_bfloat16 *p) { return *reinterpret_cast<const uint32_t *>(p); }
 
 
+template <typename TIn>
 __global__ void __launch_bounds__(kGcThreads, 1)
 gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
                  int n_v_heads, int *__restrict__ err) {
     extern __shared__ unsigned char gc_smem_raw[];
-    GcSmem &sm = *reinterpret_cast<GcSmem *>((reinterpret_cast<uintptr_t>(gc_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+    constexpr int kGcSlots = gc_slots<TIn>();
+    using Slot = GcSlot<TIn>;
+    GcSmem<TIn> &sm = *reinterpret_cast<GcSmem<TIn> *>((reinterpret_cast<uintptr_t>(gc_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
     const int b = blockIdx.y, h = blockIdx.x, kh = h / (n_v_heads / n_k_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, jq = lane & 3;
-    const bool chain_warp = warp < 8;
-    const int v0 = (warp & 7) * 16;  // a chain warp's value columns
-
-    // S^T accumulators: tile i covers k columns [8i, 8i+8): St[i] = {S^T[v0+gq][8i+2jq], [..+1], S^T[v0+gq+8][8i+2jq], [..+1]}
-    float St[16][4];
-    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * kGcD * kGcD;  // [k][v]
-    if (chain_warp) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            St[i][0] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq];
-            St[i][1] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq];
-            St[i][2] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8];
-            St[i][3] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8];
-        }
-    }
-
-    // Staging (warp 10): one lane issues three TMA tensor copies per chunk (the [16 tokens][128] boxes of k, q and v; rows
-    // of a head are 512 bytes, strided by the number of heads); they complete on the buffer's mbarrier.  Tokens past the
-    // end of the sequence arrive as zeros (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).
-    // g and beta of a chunk are loaded one stage call ahead (registers gb_g, gb_b), so their global-memory latency is never
-    // waited for: stage(c) stores the values fetched during stage(c - 1) and fetches those of chunk c + 1.
-    float gb_g = 0.0f, gb_b = 0.0f;
-    auto fetch_gates = [&](int c) {
-        const int t = c * kGcC + lane;
-        const bool in = lane < kGcC && t < n_tokens;
-        const int64_t tok = static_cast<int64_t>(b) * n_tokens + t;
-        gb_g = in ? g[tok * n_v_heads + h] : 0.0f;
-        gb_b = in ? beta[tok * n_v_heads + h] : 0.0f;
-    };
-    auto stage = [&](int c, int buf) {  // called by warp 10 only
-        const int t0 = c * kGcC;
-        const uint32_t bar = gc_s32(&sm.full[buf]);
-        if (lane == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(3u * kGcC * kGcD * 4u) : "memory");
-            gc_tma_box(gc_s32(&sm.raw[buf][0][0][0]), &map_k, kh, t0, b, bar);
-            gc_tma_box(gc_s32(&sm.raw[buf][1][0][0]), &map_q, kh, t0, b, bar);
-            gc_tma_box(gc_s32(&sm.raw[buf][2][0][0]), &map_v, h, t0, b, bar);
-        }
-        if (lane < kGcC) {
-            sm.g[buf][lane] = gb_g;
-            sm.b[buf][lane] = gb_b;
-        }
-        fetch_gates(c + 1);
-    };
-
     const int n_chunks = (n_tokens + kGcC - 1) / kGcC;
+    volatile int *abort_flag = &sm.abort;
+
     if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.full[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.full[1])));
+        for (int i = 0; i < kGcSlots; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.full[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gc_s32(&sm.ready[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gc_s32(&sm.done[i])), "r"(kGcChain));
+        }
+        sm.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 10) {
-        fetch_gates(0);
-        stage(0, 0);
-    }
-    bool failed = false;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int buf = c & 1;
-        const bool landed = gc_wait(gc_s32(&sm.full[buf]), (c >> 1) & 1);
-        // chunk c has landed (and its zero-fill / g / beta stores are visible); every warp is done with the previous chunk's
-        // set-up buffers.  A wait that ran out ends the loop for the whole CTA.
-        if (!__syncthreads_and(landed)) { failed = true; break; }
 
-        // ---- Pa: k, q -> bf16 (warps 0-7) | cumulative decay (warp 8) ----
-        if (chain_warp) {
-            const int t = threadIdx.x >> 4, c8 = (threadIdx.x & 15) * 8;
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                const float4 x0 = *reinterpret_cast<const float4 *>(&sm.raw[buf][which][t][c8]);
-                const float4 x1 = *reinterpret_cast<const float4 *>(&sm.raw[buf][which][t][c8 + 4]);
-                *reinterpret_cast<uint4 *>(which ? &sm.Qb[t][c8] : &sm.Kb[t][c8]) =
-                    make_uint4(gc_pack(x0.x, x0.y), gc_pack(x0.z, x0.w), gc_pack(x1.x, x1.y), gc_pack(x1.z, x1.w));
+    if (warp == kGcChain + kGcPrep) {
+        // ================================ staging (one warp) ================================
+        // Chunk c goes into slot c mod kGcSlots once the state warps are through with the chunk that used the slot before: one
+        // lane issues three TMA tensor copies (the [16 tokens][128] boxes of k, q and v; rows of a head are 512 bytes, strided by
+        // the number of heads); they complete on the slot's `full` barrier.  Tokens past the end of the sequence arrive as zeros
+        // (beta = 0, g = 0, k = q = v = 0 leave state and outputs untouched).  g and beta of a chunk are loaded one chunk ahead
+        // (registers), so their global-memory latency is never waited for.
+        float gb_g = 0.0f, gb_b = 0.0f;
+        auto fetch_gates = [&](int c) {
+            const int t = c * kGcC + lane;
+            const bool in = lane < kGcC && c < n_chunks && t < n_tokens;
+            const int64_t tok = static_cast<int64_t>(b) * n_tokens + t;
+            gb_g = in ? g[tok * n_v_heads + h] : 0.0f;
+            gb_b = in ? beta[tok * n_v_heads + h] : 0.0f;
+        };
+        fetch_gates(0);
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % kGcSlots, use = c / kGcSlots;
+            Slot &sl = sm.slot[s];
+            if (use > 0 && !gc_wait(gc_s32(&sm.done[s]), (use - 1) & 1, abort_flag)) break;
+            if (lane < kGcC) {
+                sl.g[lane] = gb_g;
+                sl.b[lane] = gb_b;
             }
-        } else if (warp == 8) {
-            float x = lane < kGcC ? sm.g[buf][lane] : 0.0f;
-#pragma unroll
-            for (int off = 1; off < kGcC; off <<= 1) {
-                const float y = __shfl_up_sync(0xffffffffu, x, off);
-                if (lane >= off) x += y;
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t bar = gc_s32(&sm.full[s]);
+                const int t0 = c * kGcC;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(3u * kGcC * kGcD * static_cast<uint32_t>(sizeof(TIn))) : "memory");
+                gc_tma_box(gc_s32(&sl.raw[0][0][0]), &map_k, kh, t0, b, bar);
+                gc_tma_box(gc_s32(&sl.raw[1][0][0]), &map_q, kh, t0, b, bar);
+                gc_tma_box(gc_s32(&sl.raw[2][0][0]), &map_v, h, t0, b, bar);
             }
-            const float G_last = __shfl_sync(0xffffffffu, x, kGcC - 1);
-            if (lane < kGcC) { sm.G[lane] = x; sm.gam[lane] = __expf(x); sm.dec[lane] = __expf(G_last - x); }
+            fetch_gates(c + 1);
         }
-        __syncthreads();
-        // ---- C: k.k, decay, T = (I + A')^-1, all in its registers (warp 8) | q.k, decay, P (warp 9) | the next chunk's copies
-        //          (warp 10) | [K S0 | Q S0]^T and R^T (warps 0-7) ----
-        float X[4][4];
-        uint32_t r[4];
-        if (warp == 9) {
-            // P[t][s] = (q_t . k_s) exp(G_t - G_s), s <= t: tiles nt = columns s in [8nt, 8nt+8), two accumulators each
-            float acc[2][2][4];
+        // (every copy issued is waited for by a set-up warp, or the CTA has given up: then a bounded pause lets them land)
+        if (*abort_flag) {
+            const long long t0c = clock64();
+            while (clock64() - t0c < 2000000LL) {}
+            if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        }
+        return;
+    }
+
+    if (warp >= kGcChain) {
+        // ================================ set-up (four warps, a whole chunk each) ================================
+        // Everything of a chunk that does not depend on the state: k, q -> bf16; the cumulative decay; k.k on the tensor cores,
+        // the decay applied, T = (I + A')^-1 in the warp's own fragments; q.k, the decay applied, P.  Warp p takes chunks
+        // p, p + 4, ...: the warps never talk to each other, and the state warps never wait for any of this unless all four
+        // fall behind.
+        for (int c = warp - kGcChain; c < n_chunks; c += kGcPrep) {
+            const int s = c % kGcSlots, use = c / kGcSlots;
+            Slot &sl = sm.slot[s];
+            if (!gc_wait(gc_s32(&sm.full[s]), use & 1, abort_flag)) break;
+            // ---- k, q -> bf16 ----
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i >> 3][(i >> 2) & 1][i & 3] = 0.0f;
+            for (int which = 0; which < 2; ++which)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int idx = i * 32 + lane, t = idx >> 4, c8 = (idx & 15) * 8;
+                    uint4 packed;
+                    if constexpr (sizeof(TIn) == 4) {
+                        const float4 x0 = *reinterpret_cast<const float4 *>(&sl.raw[which][t][c8]);
+                        const float4 x1 = *reinterpret_cast<const float4 *>(&sl.raw[which][t][c8 + 4]);
+                        packed = make_uint4(gc_pack(x0.x, x0.y), gc_pack(x0.z, x0.w), gc_pack(x1.x, x1.y), gc_pack(x1.z, x1.w));
+                    } else {
+                        packed = *reinterpret_cast<const uint4 *>(&sl.raw[which][t][c8]);  // already bf16: into the padded rows
+                    }
+                    *reinterpret_cast<uint4 *>(which ? &sl.Qb[t][c8] : &sl.Kb[t][c8]) = packed;
+                }
+            // ---- cumulative decay ----
+            {
+                float x = lane < kGcC ? sl.g[lane] : 0.0f;
+#pragma unroll
+                for (int off = 1; off < kGcC; off <<= 1) {
+                    const float y = __shfl_up_sync(0xffffffffu, x, off);
+                    if (lane >= off) x += y;
+                }
+                const float G_last = __shfl_sync(0xffffffffu, x, kGcC - 1);
+                if (lane < kGcC) { sl.G[lane] = x; sl.gam[lane] = __expf(x); sl.dec[lane] = __expf(G_last - x); }
+            }
+            __syncwarp();
+            // ---- k_t . k_s and q_t . k_s: tiles nt = columns s in [8nt, 8nt+8), two accumulators each; the A fragments of the k
+            //      rows are the B fragments of the two tiles ----
+            float acc[2][2][4], acq[2][2][4];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i >> 3][(i >> 2) & 1][i & 3] = acq[i >> 3][(i >> 2) & 1][i & 3] = 0.0f;
 #pragma unroll
             for (int kk8 = 0; kk8 < 8; ++kk8) {
                 const int col = 16 * kk8 + 2 * jq;
-                const uint32_t k0 = gc_ld32(&sm.Kb[gq][col]), k1 = gc_ld32(&sm.Kb[gq + 8][col]), k2 = gc_ld32(&sm.Kb[gq][col + 8]), k3 = gc_ld32(&sm.Kb[gq + 8][col + 8]);
-                const uint32_t q0 = gc_ld32(&sm.Qb[gq][col]), q1 = gc_ld32(&sm.Qb[gq + 8][col]), q2 = gc_ld32(&sm.Qb[gq][col + 8]), q3 = gc_ld32(&sm.Qb[gq + 8][col + 8]);
-                gc_mma(acc[kk8 & 1][0], q0, q1, q2, q3, k0, k2);
-                gc_mma(acc[kk8 & 1][1], q0, q1, q2, q3, k1, k3);
+                const uint32_t k0 = gc_ld32(&sl.Kb[gq][col]), k1 = gc_ld32(&sl.Kb[gq + 8][col]), k2 = gc_ld32(&sl.Kb[gq][col + 8]), k3 = gc_ld32(&sl.Kb[gq + 8][col + 8]);
+                const uint32_t q0 = gc_ld32(&sl.Qb[gq][col]), q1 = gc_ld32(&sl.Qb[gq + 8][col]), q2 = gc_ld32(&sl.Qb[gq][col + 8]), q3 = gc_ld32(&sl.Qb[gq + 8][col + 8]);
+                gc_mma(acc[kk8 & 1][0], k0, k1, k2, k3, k0, k2);
+                gc_mma(acc[kk8 & 1][1], k0, k1, k2, k3, k1, k3);
+                gc_mma(acq[kk8 & 1][0], q0, q1, q2, q3, k0, k2);
+                gc_mma(acq[kk8 & 1][1], q0, q1, q2, q3, k1, k3);
             }
+            // P[t][s] = (q_t . k_s) exp(G_t - G_s), s <= t
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 float pv[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int row = gq + 8 * (e >> 1), col = 8 * nt + 2 * jq + (e & 1);
-                    pv[e] = col <= row ? (acc[0][nt][e] + acc[1][nt][e]) * __expf(sm.G[row] - sm.G[col]) : 0.0f;
+                    pv[e] = col <= row ? (acq[0][nt][e] + acq[1][nt][e]) * __expf(sl.G[row] - sl.G[col]) : 0.0f;
                 }
-                *reinterpret_cast<uint32_t *>(&sm.P[gq][8 * nt + 2 * jq]) = gc_pack(pv[0], pv[1]);
-                *reinterpret_cast<uint32_t *>(&sm.P[gq + 8][8 * nt + 2 * jq]) = gc_pack(pv[2], pv[3]);
-            }
-        } else if (warp == 10) {
-            if (c + 1 < n_chunks) stage(c + 1, buf ^ 1);
-        } else if (!chain_warp) {
-            // k_t . k_s: tiles nt = columns s in [8nt, 8nt+8); the A fragments of the k rows are the B fragments of the two tiles
-            float acc[2][2][4];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i >> 3][(i >> 2) & 1][i & 3] = 0.0f;
-#pragma unroll
-            for (int kk8 = 0; kk8 < 8; ++kk8) {
-                const int col = 16 * kk8 + 2 * jq;
-                const uint32_t k0 = gc_ld32(&sm.Kb[gq][col]), k1 = gc_ld32(&sm.Kb[gq + 8][col]), k2 = gc_ld32(&sm.Kb[gq][col + 8]), k3 = gc_ld32(&sm.Kb[gq + 8][col + 8]);
-                gc_mma(acc[kk8 & 1][0], k0, k1, k2, k3, k0, k2);
-                gc_mma(acc[kk8 & 1][1], k0, k1, k2, k3, k1, k3);
+                *reinterpret_cast<uint32_t *>(&sl.P[gq][8 * nt + 2 * jq]) = gc_pack(pv[0], pv[1]);
+                *reinterpret_cast<uint32_t *>(&sl.P[gq + 8][8 * nt + 2 * jq]) = gc_pack(pv[2], pv[3]);
             }
             // (I + A')^-1 = (I + M)(I + M^2)(I + M^4)(I + M^8) with M = -A' (strictly lower 16 x 16, so M^16 = 0): three
             // squarings and three products on the tensor cores, all in this warp's fragments.  m, pm: accumulator layout,
@@ -227,7 +250,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int row = gq + 8 * (e >> 1), col = 8 * nt + 2 * jq + (e & 1);
-                    m[nt][e] = col < row ? -sm.b[buf][row] * (acc[0][nt][e] + acc[1][nt][e]) * __expf(sm.G[row] - sm.G[col]) : 0.0f;  // -A'
+                    m[nt][e] = col < row ? -sl.b[row] * (acc[0][nt][e] + acc[1][nt][e]) * __expf(sl.G[row] - sl.G[col]) : 0.0f;  // -A'
                     pm[nt][e] = m[nt][e] + (row == col ? 1.0f : 0.0f);
                 }
             // A-form of a 16 x 16 matrix held in accumulator layout: its four 8 x 8 blocks as bf16 pairs; the B-form of the
@@ -264,92 +287,128 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                *reinterpret_cast<uint32_t *>(&sm.Tb[gq][8 * nt + 2 * jq]) = gc_pack(pm[nt][0], pm[nt][1]);
-                *reinterpret_cast<uint32_t *>(&sm.Tb[gq + 8][8 * nt + 2 * jq]) = gc_pack(pm[nt][2], pm[nt][3]);
+                *reinterpret_cast<uint32_t *>(&sl.Tb[gq][8 * nt + 2 * jq]) = gc_pack(pm[nt][0], pm[nt][1]);
+                *reinterpret_cast<uint32_t *>(&sl.Tb[gq + 8][8 * nt + 2 * jq]) = gc_pack(pm[nt][2], pm[nt][3]);
             }
-        } else {
-            // rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of q
+            __syncwarp();
+            if (lane == 0) gc_arrive(gc_s32(&sm.ready[s]));
+        }
+        if (*abort_flag && lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        return;
+    }
+
+    // ================================ state (eight warps, 16 value columns each) ================================
+    const int v0 = warp * 16;
+    // S^T accumulators: tile i covers k columns [8i, 8i+8): St[i] = {S^T[v0+gq][8i+2jq], [..+1], S^T[v0+gq+8][8i+2jq], [..+1]}
+    float St[16][4];
+    float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * kGcD * kGcD;  // [k][v]
 #pragma unroll
-            for (int n = 0; n < 4; ++n) X[n][0] = X[n][1] = X[n][2] = X[n][3] = 0.0f;
+    for (int i = 0; i < 16; ++i) {
+        St[i][0] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq];
+        St[i][1] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq];
+        St[i][2] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8];
+        St[i][3] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8];
+    }
+    bool failed = false;
+#ifdef HS_GC_STAGGER
+    if (warp >= 4) {  // the two state warps of a scheduler half a chunk apart: one's products under the other's dependent steps
+        const long long t0s = clock64();
+        while (clock64() - t0s < HS_GC_STAGGER) {}
+    }
+#endif
+    for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % kGcSlots, use = c / kGcSlots;
+        Slot &sl = sm.slot[s];
+        if (!gc_wait(gc_s32(&sm.ready[s]), use & 1, abort_flag)) { failed = true; break; }
+        // ---- [K S0 | Q S0]^T = S^T . [K | Q]^T: rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of q ----
+        float X[4][4];
 #pragma unroll
-            for (int kk8 = 0; kk8 < 8; ++kk8) {
-                const uint32_t a0 = gc_pack(St[2 * kk8][0], St[2 * kk8][1]), a1 = gc_pack(St[2 * kk8][2], St[2 * kk8][3]);
-                const uint32_t a2 = gc_pack(St[2 * kk8 + 1][0], St[2 * kk8 + 1][1]), a3 = gc_pack(St[2 * kk8 + 1][2], St[2 * kk8 + 1][3]);
+        for (int n = 0; n < 4; ++n) X[n][0] = X[n][1] = X[n][2] = X[n][3] = 0.0f;
+        // B operands: one ldmatrix.x4 per 16 state columns brings the four 8 x 8 blocks (tokens 0-7 / 8-15) x (columns +0 / +8) of k
+        // (and one of q): lane -> row address of matrix (lane >> 3) = token 8 (lane >> 4) + (lane & 7), column block (lane >> 3) & 1
+        const uint32_t xk_lane = gc_s32(&sl.Kb[8 * (lane >> 4) + (lane & 7)][8 * ((lane >> 3) & 1)]);
+        const uint32_t xq_lane = gc_s32(&sl.Qb[8 * (lane >> 4) + (lane & 7)][8 * ((lane >> 3) & 1)]);
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {
-                    const __nv_bfloat16 *row = n < 2 ? &sm.Kb[8 * n + gq][0] : &sm.Qb[8 * (n - 2) + gq][0];
-                    gc_mma(X[n], a0, a1, a2, a3, gc_ld32(row + 16 * kk8 + 2 * jq), gc_ld32(row + 16 * kk8 + 2 * jq + 8));
+        for (int kk8 = 0; kk8 < 8; ++kk8) {
+            const uint32_t a0 = gc_pack(St[2 * kk8][0], St[2 * kk8][1]), a1 = gc_pack(St[2 * kk8][2], St[2 * kk8][3]);
+            const uint32_t a2 = gc_pack(St[2 * kk8 + 1][0], St[2 * kk8 + 1][1]), a3 = gc_pack(St[2 * kk8 + 1][2], St[2 * kk8 + 1][3]);
+            uint32_t kb[4], qb[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(kb[0]), "=r"(kb[1]), "=r"(kb[2]), "=r"(kb[3]) : "r"(xk_lane + 32u * kk8));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(qb[0]), "=r"(qb[1]), "=r"(qb[2]), "=r"(qb[3]) : "r"(xq_lane + 32u * kk8));
+            gc_mma(X[0], a0, a1, a2, a3, kb[0], kb[1]);
+            gc_mma(X[1], a0, a1, a2, a3, kb[2], kb[3]);
+            gc_mma(X[2], a0, a1, a2, a3, qb[0], qb[1]);
+            gc_mma(X[3], a0, a1, a2, a3, qb[2], qb[3]);
+        }
+        // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T;
+        // (Gamma Q S0)^T = (Q S0)^T scaled per token column
+        uint32_t r[4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int s0 = 8 * n + 2 * jq;
+            const float b0 = sl.b[s0], b1 = sl.b[s0 + 1], g0 = sl.gam[s0], g1 = sl.gam[s0 + 1];
+            const float r00 = b0 * (gc_f32(sl.raw[2][s0][v0 + gq]) - g0 * X[n][0]), r01 = b1 * (gc_f32(sl.raw[2][s0 + 1][v0 + gq]) - g1 * X[n][1]);
+            const float r10 = b0 * (gc_f32(sl.raw[2][s0][v0 + gq + 8]) - g0 * X[n][2]), r11 = b1 * (gc_f32(sl.raw[2][s0 + 1][v0 + gq + 8]) - g1 * X[n][3]);
+            r[2 * n] = gc_pack(r00, r01);
+            r[2 * n + 1] = gc_pack(r10, r11);
+            X[2 + n][0] *= g0; X[2 + n][1] *= g1; X[2 + n][2] *= g0; X[2 + n][3] *= g1;
+        }
+        // ---- U^T = R^T . T^T; O^T = (Gamma Q S0)^T + U^T . P^T; S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K ----
+        float U[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            U[n][0] = U[n][1] = U[n][2] = U[n][3] = 0.0f;
+            gc_mma(U[n], r[0], r[1], r[2], r[3], gc_ld32(&sl.Tb[8 * n + gq][2 * jq]), gc_ld32(&sl.Tb[8 * n + gq][2 * jq + 8]));
+        }
+        const uint32_t u0 = gc_pack(U[0][0], U[0][1]), u1 = gc_pack(U[0][2], U[0][3]), u2 = gc_pack(U[1][0], U[1][1]), u3 = gc_pack(U[1][2], U[1][3]);
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+            gc_mma(X[2 + n], u0, u1, u2, u3, gc_ld32(&sl.P[8 * n + gq][2 * jq]), gc_ld32(&sl.P[8 * n + gq][2 * jq + 8]));
+        // token columns of U scaled by exp(G_C - G_s); k itself is the B operand, its 8 x 8 blocks transposed on load
+        const float d00 = sl.dec[2 * jq], d01 = sl.dec[2 * jq + 1], d10 = sl.dec[8 + 2 * jq], d11 = sl.dec[8 + 2 * jq + 1];
+        const uint32_t w0 = gc_pack(U[0][0] * d00, U[0][1] * d01), w1 = gc_pack(U[0][2] * d00, U[0][3] * d01);
+        const uint32_t w2 = gc_pack(U[1][0] * d10, U[1][1] * d11), w3 = gc_pack(U[1][2] * d10, U[1][3] * d11);
+        const float gC = sl.gam[kGcC - 1];
+        // lane -> row address of ldmatrix.x4.trans: matrix (lane >> 3): rows s = (lane & 7) + 8 (matrix & 1), column block + (matrix >> 1)
+        const uint32_t kb_lane = gc_s32(&sl.Kb[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(kb_lane + 16u * i));
+            St[i][0] *= gC; St[i][1] *= gC; St[i][2] *= gC; St[i][3] *= gC;
+            gc_mma(St[i], w0, w1, w2, w3, b0, b1);
+            St[i + 1][0] *= gC; St[i + 1][1] *= gC; St[i + 1][2] *= gC; St[i + 1][3] *= gC;
+            gc_mma(St[i + 1], w0, w1, w2, w3, b2, b3);
+        }
+        // this warp is through with the slot
+        __syncwarp();
+        if (lane == 0) gc_arrive(gc_s32(&sm.done[s]));
+        // outputs: X[2 + n] = O^T rows v0+gq (+8), tokens 8n + 2jq (+1)
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int t = c * kGcC + 8 * n + 2 * jq + e;
+                if (t < n_tokens) {
+                    float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
+                    op[0] = X[2 + n][e];
+                    op[8] = X[2 + n][2 + e];
                 }
             }
-            // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T;
-            // (Gamma Q S0)^T = (Q S0)^T scaled per token column
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int s0 = 8 * n + 2 * jq;
-                const float b0 = sm.b[buf][s0], b1 = sm.b[buf][s0 + 1], g0 = sm.gam[s0], g1 = sm.gam[s0 + 1];
-                const float r00 = b0 * (sm.raw[buf][2][s0][v0 + gq] - g0 * X[n][0]), r01 = b1 * (sm.raw[buf][2][s0 + 1][v0 + gq] - g1 * X[n][1]);
-                const float r10 = b0 * (sm.raw[buf][2][s0][v0 + gq + 8] - g0 * X[n][2]), r11 = b1 * (sm.raw[buf][2][s0 + 1][v0 + gq + 8] - g1 * X[n][3]);
-                r[2 * n] = gc_pack(r00, r01);
-                r[2 * n + 1] = gc_pack(r10, r11);
-                X[2 + n][0] *= g0; X[2 + n][1] *= g1; X[2 + n][2] *= g0; X[2 + n][3] *= g1;
-            }
-        }
-        __syncthreads();  // T and P are ready
-        if (chain_warp) {
-            // ---- D: U^T = R^T . T^T; O^T = (Gamma Q S0)^T + U^T . P^T; S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K ----
-            float U[2][4];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                U[n][0] = U[n][1] = U[n][2] = U[n][3] = 0.0f;
-                gc_mma(U[n], r[0], r[1], r[2], r[3], gc_ld32(&sm.Tb[8 * n + gq][2 * jq]), gc_ld32(&sm.Tb[8 * n + gq][2 * jq + 8]));
-            }
-            const uint32_t u0 = gc_pack(U[0][0], U[0][1]), u1 = gc_pack(U[0][2], U[0][3]), u2 = gc_pack(U[1][0], U[1][1]), u3 = gc_pack(U[1][2], U[1][3]);
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-                gc_mma(X[2 + n], u0, u1, u2, u3, gc_ld32(&sm.P[8 * n + gq][2 * jq]), gc_ld32(&sm.P[8 * n + gq][2 * jq + 8]));
-            // token columns of U scaled by exp(G_C - G_s); k itself is the B operand, its 8 x 8 blocks transposed on load
-            const float d00 = sm.dec[2 * jq], d01 = sm.dec[2 * jq + 1], d10 = sm.dec[8 + 2 * jq], d11 = sm.dec[8 + 2 * jq + 1];
-            const uint32_t w0 = gc_pack(U[0][0] * d00, U[0][1] * d01), w1 = gc_pack(U[0][2] * d00, U[0][3] * d01);
-            const uint32_t w2 = gc_pack(U[1][0] * d10, U[1][1] * d11), w3 = gc_pack(U[1][2] * d10, U[1][3] * d11);
-            const float gC = sm.gam[kGcC - 1];
-            // lane -> row address of ldmatrix.x4.trans: matrix (lane >> 3): rows s = (lane & 7) + 8 (matrix & 1), column block + (matrix >> 1)
-            const uint32_t kb_lane = gc_s32(&sm.Kb[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
-#pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                uint32_t b0, b1, b2, b3;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(kb_lane + 16u * i));
-                St[i][0] *= gC; St[i][1] *= gC; St[i][2] *= gC; St[i][3] *= gC;
-                gc_mma(St[i], w0, w1, w2, w3, b0, b1);
-                St[i + 1][0] *= gC; St[i + 1][1] *= gC; St[i + 1][2] *= gC; St[i + 1][3] *= gC;
-                gc_mma(St[i + 1], w0, w1, w2, w3, b2, b3);
-            }
-            // outputs: X[2 + n] = O^T rows v0+gq (+8), tokens 8n + 2jq (+1)
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int t = c * kGcC + 8 * n + 2 * jq + e;
-                    if (t < n_tokens) {
-                        float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
-                        op[0] = X[2 + n][e];
-                        op[8] = X[2 + n][2 + e];
-                    }
-                }
-        }
     }
     if (failed) {
-        if (threadIdx.x == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
+        if (lane == 0) atomicOr(err, HS_DEVERR_WAIT_TIMEOUT);
         return;  // the state is left as it was
     }
-    if (chain_warp) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            sp[(8 * i + 2 * jq) * kGcD + v0 + gq] = St[i][0];
-            sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq] = St[i][1];
-            sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8] = St[i][2];
-            sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8] = St[i][3];
-        }
+    for (int i = 0; i < 16; ++i) {
+        sp[(8 * i + 2 * jq) * kGcD + v0 + gq] = St[i][0];
+        sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq] = St[i][1];
+        sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8] = St[i][2];
+        sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8] = St[i][3];
     }
 }
 
@@ -376,28 +435,41 @@ static GcEncodeTiledFn gc_encode_fn() {
     return fn;
 }
 
-// [n_seqs, n_tokens, n_heads, 128] fp32 -> 4-D map (d, head, token, sequence), box 128 x 1 x 16 x 1, no swizzle
-static bool gc_make_map(CUtensorMap *map, const float *base, int n_seqs, int n_tokens, int n_heads) {
+// [n_seqs, n_tokens, n_heads, 128] fp32 or bf16 -> 4-D map (d, head, token, sequence), box 128 x 1 x 16 x 1, no swizzle
+static bool gc_make_map(CUtensorMap *map, const void *base, bool bf16, int n_seqs, int n_tokens, int n_heads) {
     GcEncodeTiledFn fn = gc_encode_fn();
     if (!fn) return false;
+    const cuuint64_t es = bf16 ? 2 : 4;
     const cuuint64_t dims[4] = {kGcD, static_cast<cuuint64_t>(n_heads), static_cast<cuuint64_t>(n_tokens), static_cast<cuuint64_t>(n_seqs)};
-    const cuuint64_t strides[3] = {kGcD * 4ull, static_cast<cuuint64_t>(n_heads) * kGcD * 4ull,
-                                   static_cast<cuuint64_t>(n_tokens) * n_heads * kGcD * 4ull};
+    const cuuint64_t strides[3] = {kGcD * es, static_cast<cuuint64_t>(n_heads) * kGcD * es, static_cast<cuuint64_t>(n_tokens) * n_heads * kGcD * es};
     const cuuint32_t box[4] = {kGcD, 1, kGcC, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-}  // namespace hs
+template <typename TIn>
+static int32_t gc_launch(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const float *g, const float *beta, float *state, float *out,
+                         int n_seqs, int n_tokens, int n_k_heads, int n_v_heads, int *err, cudaStream_t s) {
+    static PerDeviceState configured;
+    const int dev = current_device();
+    constexpr int kBytes = static_cast<int>(sizeof(GcSmem<TIn>) + 128);
+    if (!configured.get(dev)) {
+        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<TIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
+        configured.set(dev, 1);
+    }
+    dim3 grid(n_v_heads, n_seqs);
+    prof_begin(s);
+    gdn_chunk_kernel<TIn><<<grid, kGcThreads, kBytes, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
+    prof_end(s);
+    return check_launch("hs_gdn_chunk_prefill");
+}
 
-using namespace hs;
-
-extern "C" {
-
-int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
-                             float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
-                             int32_t head_v_dim, hs_stream_t stream) {
+// The body of hs_gdn_chunk_prefill; `in_bf16`: q, k, v are bf16 (the layer entry's own prologue writes them so: the kernel rounds
+// q and k to bf16 anyway and v is a bf16 value to begin with, so the results are the same bit for bit).
+int32_t gdn_chunk_impl(const void *q, const void *k, const void *v, bool in_bf16, const float *g, const float *beta, float *state, float *out,
+                       int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream) {
     if (int32_t st = check_device()) return st;
     if (n_seqs < 0 || n_tokens < 0 || n_k_heads <= 0 || n_v_heads <= 0) return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: bad sizes");
     if (n_v_heads % n_k_heads != 0) return fail(HS_ERR_ARG, "hs_gdn_chunk_prefill: n_v_heads %d not a multiple of n_k_heads %d", n_v_heads, n_k_heads);
@@ -411,22 +483,24 @@ int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, con
     int *err = device_error_word();
     if (!err) return fail(HS_ERR_DEVICE, "hs_gdn_chunk_prefill: device error word unavailable");
     CUtensorMap mq, mk, mv;
-    if (!gc_make_map(&mq, q, n_seqs, n_tokens, n_k_heads) || !gc_make_map(&mk, k, n_seqs, n_tokens, n_k_heads) ||
-        !gc_make_map(&mv, v, n_seqs, n_tokens, n_v_heads))
+    if (!gc_make_map(&mq, q, in_bf16, n_seqs, n_tokens, n_k_heads) || !gc_make_map(&mk, k, in_bf16, n_seqs, n_tokens, n_k_heads) ||
+        !gc_make_map(&mv, v, in_bf16, n_seqs, n_tokens, n_v_heads))
         return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: the driver refused the tensor maps (use hs_gdn_recurrent)");
-    static PerDeviceState configured;
-    const int dev = current_device();
-    if (!configured.get(dev)) {
-        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(GcSmem) + 128));
-        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
-        configured.set(dev, 1);
-    }
     cudaStream_t s = as_stream(stream);
-    dim3 grid(n_v_heads, n_seqs);
-    prof_begin(s);
-    gdn_chunk_kernel<<<grid, kGcThreads, sizeof(GcSmem) + 128, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
-    prof_end(s);
-    return check_launch("hs_gdn_chunk_prefill");
+    return in_bf16 ? gc_launch<__nv_bfloat16>(mq, mk, mv, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, err, s)
+                   : gc_launch<float>(mq, mk, mv, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, err, s);
+}
+
+}  // namespace hs
+
+using namespace hs;
+
+extern "C" {
+
+int32_t hs_gdn_chunk_prefill(const float *q, const float *k, const float *v, const float *g, const float *beta, float *state,
+                             float *out, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
+                             int32_t head_v_dim, hs_stream_t stream) {
+    return gdn_chunk_impl(q, k, v, false, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, head_k_dim, head_v_dim, stream);
 }
 
 }  // extern "C"

@@ -25,11 +25,13 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // Thread = 4 consecutive channels of one 128-channel group: a warp is one head, 8 heads per CTA; a CTA walks kEdgeTokens
 // tokens keeping the last ks-1 frames of its channels in registers.
 // Groups are heads: [0, nk) q heads, [nk, 2nk) k heads, [2nk, 2nk + nv) v heads (head dims are 128).
-template <int KS>
+// TOut: float (the boundary's tensors) or uint16_t = bf16 bits (the layer entry's route to the chunked rule, which rounds q and k
+// to bf16 itself and finds v a bf16 value already: half the bytes written here and read there, same results).
+template <int KS, typename TOut>
 __global__ void __launch_bounds__(kEdgeThreads)
 gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, const uint16_t *__restrict__ state_in,
                     const uint16_t *__restrict__ a_in, const uint16_t *__restrict__ b_in, const float *__restrict__ neg_a_exp,
-                    const float *__restrict__ dt_bias, float *__restrict__ q, float *__restrict__ k, float *__restrict__ v,
+                    const float *__restrict__ dt_bias, TOut *__restrict__ q, TOut *__restrict__ k, TOut *__restrict__ v,
                     float *__restrict__ g, float *__restrict__ beta, int n_tokens, int nk, int nv, float q_scale) {
     constexpr int C = 4;  // channels per thread
     const int conv_dim = (2 * nk + nv) * 128;
@@ -69,7 +71,7 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
     }
     const bool is_v = group >= 2 * nk;
     const bool is_q = group < nk;
-    float *dst = is_q ? q + (static_cast<int64_t>(b) * n_tokens * nk + group) * 128
+    TOut *dst = is_q ? q + (static_cast<int64_t>(b) * n_tokens * nk + group) * 128
                : (is_v ? v + (static_cast<int64_t>(b) * n_tokens * nv + (group - 2 * nk)) * 128
                        : k + (static_cast<int64_t>(b) * n_tokens * nk + (group - nk)) * 128);
     const int64_t tok_stride = static_cast<int64_t>(is_v ? nv : nk) * 128;
@@ -112,8 +114,14 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
                 mul = 1.0f / fmaxf(sqrtf(ss[u]), 1e-3f);  // x / clamp_min(norm, 1e-3), as a multiply by the reciprocal
                 if (is_q) mul *= q_scale;
             }
-            __stcs(reinterpret_cast<float4 *>(dst + (t0 + t) * tok_stride + lane * C),
-                   make_float4(y[u][0] * mul, y[u][1] * mul, y[u][2] * mul, y[u][3] * mul));
+            if constexpr (sizeof(TOut) == 4) {
+                __stcs(reinterpret_cast<float4 *>(dst + (t0 + t) * tok_stride + lane * C),
+                       make_float4(y[u][0] * mul, y[u][1] * mul, y[u][2] * mul, y[u][3] * mul));
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(y[u][0] * mul, y[u][1] * mul), hi = __floats2bfloat162_rn(y[u][2] * mul, y[u][3] * mul);
+                *reinterpret_cast<uint2 *>(dst + (t0 + t) * tok_stride + lane * C) =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+            }
         }
     }
 }
@@ -175,12 +183,13 @@ gdn_epilogue_kernel(const float *__restrict__ o, const uint16_t *__restrict__ z,
 
 using namespace hs;
 
-extern "C" {
+namespace hs {
 
-int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in,
-                        const void *b_in, const float *neg_a_exp, const float *dt_bias, float *q, float *k, float *v, float *g,
-                        float *beta, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
-                        int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream) {
+// The body of hs_gdn_prologue; `out_bf16`: q, k, v are written as bf16.
+int32_t gdn_prologue_impl(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in,
+                          const void *b_in, const float *neg_a_exp, const float *dt_bias, void *q, void *k, void *v, bool out_bf16, float *g,
+                          float *beta, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
+                          int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream) {
     if (int32_t st = check_device()) return st;
     if (n_seqs < 0 || n_tokens < 0 || n_k_heads <= 0 || n_v_heads <= 0) return fail(HS_ERR_ARG, "hs_gdn_prologue: bad sizes");
     if (head_k_dim != 128 || head_v_dim != 128) return fail(HS_ERR_UNSUPPORTED, "hs_gdn_prologue: head dims %d x %d (supported: 128 x 128)", head_k_dim, head_v_dim);
@@ -197,12 +206,16 @@ int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *co
     dim3 grid((groups + kEdgeThreads / 32 - 1) / (kEdgeThreads / 32), (n_tokens + kEdgeTokens - 1) / kEdgeTokens, n_seqs);
     const float q_scale = 1.0f / sqrtf(static_cast<float>(head_k_dim));
     prof_begin(s);
-#define HS_GDN_PRO(KS)                                                                                                              \
-    gdn_prologue_kernel<KS><<<grid, kEdgeThreads, 0, s>>>(                                                                          \
+#define HS_GDN_PRO(KS, T)                                                                                                           \
+    gdn_prologue_kernel<KS, T><<<grid, kEdgeThreads, 0, s>>>(                                                                       \
         reinterpret_cast<const uint16_t *>(mixed_qkv), reinterpret_cast<const uint16_t *>(conv_weight), st_in,                      \
-        reinterpret_cast<const uint16_t *>(a_in), reinterpret_cast<const uint16_t *>(b_in), neg_a_exp, dt_bias, q, k, v, g, beta,  \
-        n_tokens, n_k_heads, n_v_heads, q_scale)
-    if (kernel_size == 4) HS_GDN_PRO(4); else HS_GDN_PRO(2);
+        reinterpret_cast<const uint16_t *>(a_in), reinterpret_cast<const uint16_t *>(b_in), neg_a_exp, dt_bias,                     \
+        reinterpret_cast<T *>(q), reinterpret_cast<T *>(k), reinterpret_cast<T *>(v), g, beta, n_tokens, n_k_heads, n_v_heads, q_scale)
+    if (out_bf16) {
+        if (kernel_size == 4) HS_GDN_PRO(4, uint16_t); else HS_GDN_PRO(2, uint16_t);
+    } else {
+        if (kernel_size == 4) HS_GDN_PRO(4, float); else HS_GDN_PRO(2, float);
+    }
 #undef HS_GDN_PRO
     prof_end(s);
     if (int32_t e = check_launch("hs_gdn_prologue")) return e;
@@ -212,6 +225,18 @@ int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *co
     gdn_conv_state_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
         reinterpret_cast<const uint16_t *>(mixed_qkv), st_in, reinterpret_cast<uint16_t *>(conv_state), n_tokens, conv_dim, ks1, total);
     return check_launch("hs_gdn_prologue (conv state)");
+}
+
+}  // namespace hs
+
+extern "C" {
+
+int32_t hs_gdn_prologue(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in,
+                        const void *b_in, const float *neg_a_exp, const float *dt_bias, float *q, float *k, float *v, float *g,
+                        float *beta, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
+                        int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream) {
+    return hs::gdn_prologue_impl(mixed_qkv, conv_weight, conv_state, has_state, a_in, b_in, neg_a_exp, dt_bias, q, k, v, false, g, beta, n_seqs, n_tokens,
+                                 n_k_heads, n_v_heads, head_k_dim, head_v_dim, kernel_size, stream);
 }
 
 int32_t hs_gdn_epilogue(const float *o, const void *z, const float *norm_weight, float eps, void *y, int64_t n_rows, int32_t head_v_dim,

@@ -27,6 +27,14 @@ int current_device();  // ordinal of the current device, -1 if there is none
 int *device_error_word();
 uint32_t next_launch_id();  // never 0
 
+// Internal forms of hs_gdn_prologue / hs_gdn_chunk_prefill with bf16 q, k, v between them (gdn_edges.cu, gdn_chunk.cu).
+int32_t gdn_prologue_impl(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in,
+                          const void *b_in, const float *neg_a_exp, const float *dt_bias, void *q, void *k, void *v, bool out_bf16, float *g,
+                          float *beta, int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim,
+                          int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream);
+int32_t gdn_chunk_impl(const void *q, const void *k, const void *v, bool in_bf16, const float *g, const float *beta, float *state, float *out,
+                       int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
+
 // Launch configuration is per device (cudaFuncSetAttribute, occupancy, whether cooperative launches are accepted): a
 // process that drives several GPUs configures each kernel once on each.  One int of state per device ordinal, 0 = not
 // configured yet.  Two threads may both configure a device; the calls are idempotent.

@@ -73,10 +73,12 @@ int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixe
     GdnScratch s = gdn_scratch(params, n_seqs, n_tokens, static_cast<unsigned char *>(workspace));
     if (workspace_bytes < static_cast<int64_t>(s.total))
         return fail(HS_ERR_WORKSPACE, "hs_gdn_layer_forward: workspace %lld < %lld bytes", static_cast<long long>(workspace_bytes), static_cast<long long>(s.total));
-    // conv1d + SiLU + split + L2 norm + gates (qwen3_5.rs:627-701)
-    if (int32_t st = hs_gdn_prologue(mixed_qkv, params->conv_weight, conv_state, has_state, a_in, b_in, params->neg_a_exp, params->dt_bias, s.q, s.k, s.v,
-                                     s.g, s.beta, n_seqs, n_tokens, params->n_k_heads, params->n_v_heads, params->head_k_dim, params->head_v_dim,
-                                     params->kernel_size, stream))
+    // conv1d + SiLU + split + L2 norm + gates (qwen3_5.rs:627-701).  For a prompt q, k, v go to the chunked rule as bf16: that kernel
+    // rounds q and k to bf16 first thing and v is a bf16 value already, so the results are the same and half the bytes move.
+    const bool chunked = n_tokens > 1;
+    if (int32_t st = gdn_prologue_impl(mixed_qkv, params->conv_weight, conv_state, has_state, a_in, b_in, params->neg_a_exp, params->dt_bias, s.q, s.k, s.v,
+                                       chunked, s.g, s.beta, n_seqs, n_tokens, params->n_k_heads, params->n_v_heads, params->head_k_dim, params->head_v_dim,
+                                       params->kernel_size, stream))
         return st;
     // the rule: recurrent for a decode step, chunked for a prompt (qwen3_5.rs:725-769); a state that is being started is zero
     if (!has_state) {
@@ -88,8 +90,8 @@ int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixe
         st = hs_gdn_recurrent(s.q, s.k, s.v, s.g, s.beta, rec_state, s.o, n_seqs, 1, params->n_k_heads, params->n_v_heads, params->head_k_dim,
                               params->head_v_dim, stream);
     else
-        st = hs_gdn_chunk_prefill(s.q, s.k, s.v, s.g, s.beta, rec_state, s.o, n_seqs, n_tokens, params->n_k_heads, params->n_v_heads, params->head_k_dim,
-                                  params->head_v_dim, stream);
+        st = gdn_chunk_impl(s.q, s.k, s.v, true, s.g, s.beta, rec_state, s.o, n_seqs, n_tokens, params->n_k_heads, params->n_v_heads, params->head_k_dim,
+                            params->head_v_dim, stream);
     if (st != HS_OK) return st;
     // RMSNormGated (qwen3_5.rs:305-313,771-784)
     return hs_gdn_epilogue(s.o, z, params->norm_weight, params->norm_eps, y, static_cast<int64_t>(n_seqs) * n_tokens * params->n_v_heads, params->head_v_dim,
