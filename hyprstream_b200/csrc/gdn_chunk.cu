@@ -11,20 +11,25 @@
 // product (I + M)(I + M^2)(I + M^4)(I + M^8), M = -A', six small MMAs) and the other per-chunk set-up short enough to sit
 // in front of every chunk.
 //
-// Layout: warp w of 8 owns value columns [16w, 16w+16) and keeps S^T[v][k] (16 x 128 fp32) in its mma accumulator
-// registers; every S-dependent product of the chunk is warp-local, with the state or U^T as the A operand straight from
-// those accumulators (fp32 -> bf16 pairs), mma.sync.m16n8k16 bf16 x bf16 -> fp32:
-//   [K S0 | Q S0]^T = S^T . [K | Q]^T     (32 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (2 MMAs)
-//   O^T = Gamma (Q S0)^T + U^T . P^T      (2 MMAs)       S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K   (16 MMAs)
+// Layout: four state warps, one per scheduler; warp w owns value columns [32w, 32w+32) as two 16-row MMA tiles and keeps
+// S^T[v][k] (32 x 128 fp32, 128 registers a thread) in its mma accumulators.  Every S-dependent product of the chunk is
+// warp-local, with the state or U^T as the A operand straight from those accumulators (fp32 -> bf16 pairs) and every B operand
+// shared by the warp's two tiles, mma.sync.m16n8k16 bf16 x bf16 -> fp32, per warp and chunk:
+//   [K S0 | Q S0]^T = S^T . [K | Q]^T     (64 MMAs)      R^T = beta (V^T - Gamma (K S0)^T)      U^T = R^T . T^T   (4 MMAs)
+//   O^T = Gamma (Q S0)^T + U^T . P^T      (4 MMAs)       S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K   (32 MMAs)
 // The per-chunk set-up that does not depend on S runs ahead of the state warps in a ring of chunk slots: a staging warp issues
 // each chunk's three TMA tensor copies (k, q, v boxes of [16 tokens][128]; fp32 from the boundary, bf16 from the layer entry's
-// own prologue) as soon as the slot's previous chunk is done with; four set-up warps take a whole chunk each, round-robin (k, q
+// own prologue) as soon as the slot's previous chunk is done with; three set-up warps take a whole chunk each, round-robin (k, q
 // to bf16 tiles, the decay scan, k.k and q.k on the tensor cores, T in the warp's own fragments, P), and hand the slot to the
-// state warps through an mbarrier.  The eight state warps never meet a block barrier: each waits for the slot, runs its
-// products and signals the slot free.  Gamma and exp(G_C - G) are folded into accumulator columns, so the only operand tiles in
-// shared memory are k and q as bf16.  Only MMA operands are rounded to bf16; the state and all accumulation stay fp32.
-// Bound: the state warps' own chain, ~2,400 cycles per chunk against a tensor-pipe floor of ~900 (mma.sync.m16n8k16 issues at
-// one per 8 cycles and scheduler, 21 cycles dependent; 115 per chunk and scheduler); HBM traffic and FLOPs are far below their peaks.
+// state warps through an mbarrier.  The state warps never meet a block barrier: each waits for the slot, runs its products and
+// signals the slot free.  Eight warps in all: two per scheduler, so that a state warp can have its ~250 registers.  Gamma and
+// exp(G_C - G) are folded into accumulator columns, so the only operand tiles in shared memory are k and q as bf16.  Only MMA
+// operands are rounded to bf16; the state and all accumulation stay fp32.
+// Bound: the state warps' own chain, ~2,000 cycles per chunk.  Measured on this part: mma.sync.m16n8k16 issues at one per ~5 cycles
+// and scheduler (21 cycles dependent), a fp32 -> bf16x2 pack costs ~4 issue cycles beside MMAs and does not overlap with them,
+// so the first product alone (64 MMAs + 64 packs of the state) is ~600 cycles; HBM traffic and FLOPs are far below their peaks.
+// Tried and measured slower: RMSNormGated fused in through writer warps (twelve warps with setmaxnreg: the extra warps take
+// issue slots from the state warps, 14.4 -> 16.7 ms for three layers).
 //
 // Accuracy: bf16 operand rounding (2^-9 relative) enters every S-dependent product, so outputs agree with the fp32 rule
 // to ~1e-3, inside the path's stated tolerance (max-abs 2e-2, mean-abs 2e-3); hs_gdn_recurrent remains the fp32-exact form.
@@ -37,9 +42,9 @@ namespace hs {
 
 constexpr int kGcC = 16;          // tokens per chunk
 constexpr int kGcD = 128;         // head_k_dim = head_v_dim
-constexpr int kGcChain = 8;       // warps 0-7: one 16-column slice of the state each
-constexpr int kGcPrep = 4;        // warps 8-11: the S-independent set-up of a chunk, a whole chunk per warp, chunks dealt round-robin
-constexpr int kGcThreads = (kGcChain + kGcPrep + 1) * 32;  // warp 12: staging
+constexpr int kGcChain = 4;       // warps 0-3: a 32-column slice of the state each, one warp per scheduler
+constexpr int kGcPrep = 3;        // warps 4-6: the S-independent set-up of a chunk, a whole chunk per warp, chunks dealt round-robin
+constexpr int kGcThreads = (kGcChain + kGcPrep + 1) * 32;  // warp 7: staging (eight warps: two per scheduler, so that a state warp may hold its 128 state registers)
 // chunks in flight between the copies and the state warps: what fits beside fp32 (bf16) inputs
 template <typename TIn> constexpr int gc_slots() { return sizeof(TIn) == 4 ? 6 : 9; }
 constexpr int kGcRS = kGcD;       // fp32 row stride of the staged inputs (floats): dense, as the tensor copies write them
@@ -75,15 +80,18 @@ __device__ __forceinline__ bool gc_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // bounded; a wait that runs out raises the CTA's abort flag, which ends every other wait of the CTA at once
-__device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+// (the helper warps sleep `nap` ns between polls so that their waiting takes no issue slots from the state warp of their scheduler)
+__device__ __forceinline__ bool gc_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned nap = 0) {
     if (gc_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!gc_try_wait(bar, parity)) {
         if (*abort_flag) return false;
         if (clock64() - t0 > kGcWaitCycles) { *abort_flag = 1; return false; }
+        if (nap) __nanosleep(nap);
     }
     return true;
 }
+constexpr unsigned kGcNap = 200;
 __device__ __forceinline__ void gc_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -151,7 +159,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int c = 0; c < n_chunks; ++c) {
             const int s = c % kGcSlots, use = c / kGcSlots;
             Slot &sl = sm.slot[s];
-            if (use > 0 && !gc_wait(gc_s32(&sm.done[s]), (use - 1) & 1, abort_flag)) break;
+            if (use > 0 && !gc_wait(gc_s32(&sm.done[s]), (use - 1) & 1, abort_flag, kGcNap)) break;
             if (lane < kGcC) {
                 sl.g[lane] = gb_g;
                 sl.b[lane] = gb_b;
@@ -177,15 +185,15 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 
     if (warp >= kGcChain) {
-        // ================================ set-up (four warps, a whole chunk each) ================================
+        // ================================ set-up (three warps, a whole chunk each) ================================
         // Everything of a chunk that does not depend on the state: k, q -> bf16; the cumulative decay; k.k on the tensor cores,
         // the decay applied, T = (I + A')^-1 in the warp's own fragments; q.k, the decay applied, P.  Warp p takes chunks
-        // p, p + 4, ...: the warps never talk to each other, and the state warps never wait for any of this unless all four
+        // p, p + 3, ...: the warps never talk to each other, and the state warps never wait for any of this unless all three
         // fall behind.
         for (int c = warp - kGcChain; c < n_chunks; c += kGcPrep) {
             const int s = c % kGcSlots, use = c / kGcSlots;
             Slot &sl = sm.slot[s];
-            if (!gc_wait(gc_s32(&sm.full[s]), use & 1, abort_flag)) break;
+            if (!gc_wait(gc_s32(&sm.full[s]), use & 1, abort_flag, kGcNap)) break;
             // ---- k, q -> bf16 ----
 #pragma unroll
             for (int which = 0; which < 2; ++which)
@@ -297,96 +305,123 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         return;
     }
 
-    // ================================ state (eight warps, 16 value columns each) ================================
-    const int v0 = warp * 16;
-    // S^T accumulators: tile i covers k columns [8i, 8i+8): St[i] = {S^T[v0+gq][8i+2jq], [..+1], S^T[v0+gq+8][8i+2jq], [..+1]}
-    float St[16][4];
+    // ================================ state (four warps, 32 value columns each) ================================
+    // One state warp per scheduler: its 32 value columns are two 16-row MMA tiles (mt) that share every B operand (k, q, T, P)
+    // and give the tensor pipe eight independent accumulators to work on.
+    const int v0 = warp * 32;
+    // S^T accumulators: tile (mt, i) covers rows v0 + 16 mt + gq (+8), k columns [8i, 8i+8):
+    // St[mt][i] = {S^T[row][8i+2jq], [..+1], S^T[row+8][8i+2jq], [..+1]}
+    float St[2][16][4];
     float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * kGcD * kGcD;  // [k][v]
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        St[i][0] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq];
-        St[i][1] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq];
-        St[i][2] = sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8];
-        St[i][3] = sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8];
-    }
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int vr = v0 + 16 * mt + gq;
+            St[mt][i][0] = sp[(8 * i + 2 * jq) * kGcD + vr];
+            St[mt][i][1] = sp[(8 * i + 2 * jq + 1) * kGcD + vr];
+            St[mt][i][2] = sp[(8 * i + 2 * jq) * kGcD + vr + 8];
+            St[mt][i][3] = sp[(8 * i + 2 * jq + 1) * kGcD + vr + 8];
+        }
     bool failed = false;
-#ifdef HS_GC_STAGGER
-    if (warp >= 4) {  // the two state warps of a scheduler half a chunk apart: one's products under the other's dependent steps
-        const long long t0s = clock64();
-        while (clock64() - t0s < HS_GC_STAGGER) {}
-    }
-#endif
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % kGcSlots, use = c / kGcSlots;
         Slot &sl = sm.slot[s];
         if (!gc_wait(gc_s32(&sm.ready[s]), use & 1, abort_flag)) { failed = true; break; }
-        // ---- [K S0 | Q S0]^T = S^T . [K | Q]^T: rows = this warp's 16 value columns, columns = 16 tokens of k then 16 tokens of q ----
-        float X[4][4];
+        // ---- [K S0 | Q S0]^T = S^T . [K | Q]^T: rows = this warp's value columns, columns = 16 tokens of k then 16 tokens of q ----
+        float X[2][4][4];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) X[n][0] = X[n][1] = X[n][2] = X[n][3] = 0.0f;
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int n = 0; n < 4; ++n) X[mt][n][0] = X[mt][n][1] = X[mt][n][2] = X[mt][n][3] = 0.0f;
         // B operands: one ldmatrix.x4 per 16 state columns brings the four 8 x 8 blocks (tokens 0-7 / 8-15) x (columns +0 / +8) of k
         // (and one of q): lane -> row address of matrix (lane >> 3) = token 8 (lane >> 4) + (lane & 7), column block (lane >> 3) & 1
         const uint32_t xk_lane = gc_s32(&sl.Kb[8 * (lane >> 4) + (lane & 7)][8 * ((lane >> 3) & 1)]);
         const uint32_t xq_lane = gc_s32(&sl.Qb[8 * (lane >> 4) + (lane & 7)][8 * ((lane >> 3) & 1)]);
 #pragma unroll
         for (int kk8 = 0; kk8 < 8; ++kk8) {
-            const uint32_t a0 = gc_pack(St[2 * kk8][0], St[2 * kk8][1]), a1 = gc_pack(St[2 * kk8][2], St[2 * kk8][3]);
-            const uint32_t a2 = gc_pack(St[2 * kk8 + 1][0], St[2 * kk8 + 1][1]), a3 = gc_pack(St[2 * kk8 + 1][2], St[2 * kk8 + 1][3]);
             uint32_t kb[4], qb[4];
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(kb[0]), "=r"(kb[1]), "=r"(kb[2]), "=r"(kb[3]) : "r"(xk_lane + 32u * kk8));
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(qb[0]), "=r"(qb[1]), "=r"(qb[2]), "=r"(qb[3]) : "r"(xq_lane + 32u * kk8));
-            gc_mma(X[0], a0, a1, a2, a3, kb[0], kb[1]);
-            gc_mma(X[1], a0, a1, a2, a3, kb[2], kb[3]);
-            gc_mma(X[2], a0, a1, a2, a3, qb[0], qb[1]);
-            gc_mma(X[3], a0, a1, a2, a3, qb[2], qb[3]);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const uint32_t a0 = gc_pack(St[mt][2 * kk8][0], St[mt][2 * kk8][1]), a1 = gc_pack(St[mt][2 * kk8][2], St[mt][2 * kk8][3]);
+                const uint32_t a2 = gc_pack(St[mt][2 * kk8 + 1][0], St[mt][2 * kk8 + 1][1]), a3 = gc_pack(St[mt][2 * kk8 + 1][2], St[mt][2 * kk8 + 1][3]);
+                gc_mma(X[mt][0], a0, a1, a2, a3, kb[0], kb[1]);
+                gc_mma(X[mt][1], a0, a1, a2, a3, kb[2], kb[3]);
+                gc_mma(X[mt][2], a0, a1, a2, a3, qb[0], qb[1]);
+                gc_mma(X[mt][3], a0, a1, a2, a3, qb[2], qb[3]);
+            }
         }
         // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T;
         // (Gamma Q S0)^T = (Q S0)^T scaled per token column
-        uint32_t r[4];
+        uint32_t r[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int s0 = 8 * n + 2 * jq;
             const float b0 = sl.b[s0], b1 = sl.b[s0 + 1], g0 = sl.gam[s0], g1 = sl.gam[s0 + 1];
-            const float r00 = b0 * (gc_f32(sl.raw[2][s0][v0 + gq]) - g0 * X[n][0]), r01 = b1 * (gc_f32(sl.raw[2][s0 + 1][v0 + gq]) - g1 * X[n][1]);
-            const float r10 = b0 * (gc_f32(sl.raw[2][s0][v0 + gq + 8]) - g0 * X[n][2]), r11 = b1 * (gc_f32(sl.raw[2][s0 + 1][v0 + gq + 8]) - g1 * X[n][3]);
-            r[2 * n] = gc_pack(r00, r01);
-            r[2 * n + 1] = gc_pack(r10, r11);
-            X[2 + n][0] *= g0; X[2 + n][1] *= g1; X[2 + n][2] *= g0; X[2 + n][3] *= g1;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const int vr = v0 + 16 * mt + gq;
+                const float r00 = b0 * (gc_f32(sl.raw[2][s0][vr]) - g0 * X[mt][n][0]), r01 = b1 * (gc_f32(sl.raw[2][s0 + 1][vr]) - g1 * X[mt][n][1]);
+                const float r10 = b0 * (gc_f32(sl.raw[2][s0][vr + 8]) - g0 * X[mt][n][2]), r11 = b1 * (gc_f32(sl.raw[2][s0 + 1][vr + 8]) - g1 * X[mt][n][3]);
+                r[mt][2 * n] = gc_pack(r00, r01);
+                r[mt][2 * n + 1] = gc_pack(r10, r11);
+                X[mt][2 + n][0] *= g0; X[mt][2 + n][1] *= g1; X[mt][2 + n][2] *= g0; X[mt][2 + n][3] *= g1;
+            }
         }
         // ---- U^T = R^T . T^T; O^T = (Gamma Q S0)^T + U^T . P^T; S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K ----
-        float U[2][4];
+        float U[2][2][4];
+        {
+            const uint32_t t00 = gc_ld32(&sl.Tb[gq][2 * jq]), t01 = gc_ld32(&sl.Tb[gq][2 * jq + 8]);
+            const uint32_t t10 = gc_ld32(&sl.Tb[8 + gq][2 * jq]), t11 = gc_ld32(&sl.Tb[8 + gq][2 * jq + 8]);
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            U[n][0] = U[n][1] = U[n][2] = U[n][3] = 0.0f;
-            gc_mma(U[n], r[0], r[1], r[2], r[3], gc_ld32(&sl.Tb[8 * n + gq][2 * jq]), gc_ld32(&sl.Tb[8 * n + gq][2 * jq + 8]));
+            for (int mt = 0; mt < 2; ++mt) {
+                U[mt][0][0] = U[mt][0][1] = U[mt][0][2] = U[mt][0][3] = 0.0f;
+                U[mt][1][0] = U[mt][1][1] = U[mt][1][2] = U[mt][1][3] = 0.0f;
+                gc_mma(U[mt][0], r[mt][0], r[mt][1], r[mt][2], r[mt][3], t00, t01);
+                gc_mma(U[mt][1], r[mt][0], r[mt][1], r[mt][2], r[mt][3], t10, t11);
+            }
         }
-        const uint32_t u0 = gc_pack(U[0][0], U[0][1]), u1 = gc_pack(U[0][2], U[0][3]), u2 = gc_pack(U[1][0], U[1][1]), u3 = gc_pack(U[1][2], U[1][3]);
+        uint32_t w[2][4];
+        {
+            const uint32_t p00 = gc_ld32(&sl.P[gq][2 * jq]), p01 = gc_ld32(&sl.P[gq][2 * jq + 8]);
+            const uint32_t p10 = gc_ld32(&sl.P[8 + gq][2 * jq]), p11 = gc_ld32(&sl.P[8 + gq][2 * jq + 8]);
+            // token columns of U scaled by exp(G_C - G_s) for the state update
+            const float d00 = sl.dec[2 * jq], d01 = sl.dec[2 * jq + 1], d10 = sl.dec[8 + 2 * jq], d11 = sl.dec[8 + 2 * jq + 1];
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
-            gc_mma(X[2 + n], u0, u1, u2, u3, gc_ld32(&sl.P[8 * n + gq][2 * jq]), gc_ld32(&sl.P[8 * n + gq][2 * jq + 8]));
-        // token columns of U scaled by exp(G_C - G_s); k itself is the B operand, its 8 x 8 blocks transposed on load
-        const float d00 = sl.dec[2 * jq], d01 = sl.dec[2 * jq + 1], d10 = sl.dec[8 + 2 * jq], d11 = sl.dec[8 + 2 * jq + 1];
-        const uint32_t w0 = gc_pack(U[0][0] * d00, U[0][1] * d01), w1 = gc_pack(U[0][2] * d00, U[0][3] * d01);
-        const uint32_t w2 = gc_pack(U[1][0] * d10, U[1][1] * d11), w3 = gc_pack(U[1][2] * d10, U[1][3] * d11);
+            for (int mt = 0; mt < 2; ++mt) {
+                const uint32_t u0 = gc_pack(U[mt][0][0], U[mt][0][1]), u1 = gc_pack(U[mt][0][2], U[mt][0][3]);
+                const uint32_t u2 = gc_pack(U[mt][1][0], U[mt][1][1]), u3 = gc_pack(U[mt][1][2], U[mt][1][3]);
+                gc_mma(X[mt][2], u0, u1, u2, u3, p00, p01);
+                gc_mma(X[mt][3], u0, u1, u2, u3, p10, p11);
+                w[mt][0] = gc_pack(U[mt][0][0] * d00, U[mt][0][1] * d01); w[mt][1] = gc_pack(U[mt][0][2] * d00, U[mt][0][3] * d01);
+                w[mt][2] = gc_pack(U[mt][1][0] * d10, U[mt][1][1] * d11); w[mt][3] = gc_pack(U[mt][1][2] * d10, U[mt][1][3] * d11);
+            }
+        }
         const float gC = sl.gam[kGcC - 1];
-        // lane -> row address of ldmatrix.x4.trans: matrix (lane >> 3): rows s = (lane & 7) + 8 (matrix & 1), column block + (matrix >> 1)
+        // k itself is the B operand of the update, its 8 x 8 blocks transposed on load.  lane -> row address of ldmatrix.x4.trans:
+        // matrix (lane >> 3): rows s = (lane & 7) + 8 (matrix & 1), column block + (matrix >> 1)
         const uint32_t kb_lane = gc_s32(&sl.Kb[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
             uint32_t b0, b1, b2, b3;
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(kb_lane + 16u * i));
-            St[i][0] *= gC; St[i][1] *= gC; St[i][2] *= gC; St[i][3] *= gC;
-            gc_mma(St[i], w0, w1, w2, w3, b0, b1);
-            St[i + 1][0] *= gC; St[i + 1][1] *= gC; St[i + 1][2] *= gC; St[i + 1][3] *= gC;
-            gc_mma(St[i + 1], w0, w1, w2, w3, b2, b3);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                St[mt][i][0] *= gC; St[mt][i][1] *= gC; St[mt][i][2] *= gC; St[mt][i][3] *= gC;
+                gc_mma(St[mt][i], w[mt][0], w[mt][1], w[mt][2], w[mt][3], b0, b1);
+                St[mt][i + 1][0] *= gC; St[mt][i + 1][1] *= gC; St[mt][i + 1][2] *= gC; St[mt][i + 1][3] *= gC;
+                gc_mma(St[mt][i + 1], w[mt][0], w[mt][1], w[mt][2], w[mt][3], b2, b3);
+            }
         }
         // this warp is through with the slot
         __syncwarp();
         if (lane == 0) gc_arrive(gc_s32(&sm.done[s]));
-        // outputs: X[2 + n] = O^T rows v0+gq (+8), tokens 8n + 2jq (+1)
+        // outputs: X[mt][2 + n] = O^T rows v0 + 16 mt + gq (+8), tokens 8n + 2jq (+1)
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
@@ -394,8 +429,11 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const int t = c * kGcC + 8 * n + 2 * jq + e;
                 if (t < n_tokens) {
                     float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
-                    op[0] = X[2 + n][e];
-                    op[8] = X[2 + n][2 + e];
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        op[16 * mt] = X[mt][2 + n][e];
+                        op[16 * mt + 8] = X[mt][2 + n][2 + e];
+                    }
                 }
             }
     }
@@ -404,12 +442,15 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         return;  // the state is left as it was
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        sp[(8 * i + 2 * jq) * kGcD + v0 + gq] = St[i][0];
-        sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq] = St[i][1];
-        sp[(8 * i + 2 * jq) * kGcD + v0 + gq + 8] = St[i][2];
-        sp[(8 * i + 2 * jq + 1) * kGcD + v0 + gq + 8] = St[i][3];
-    }
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int vr = v0 + 16 * mt + gq;
+            sp[(8 * i + 2 * jq) * kGcD + vr] = St[mt][i][0];
+            sp[(8 * i + 2 * jq + 1) * kGcD + vr] = St[mt][i][1];
+            sp[(8 * i + 2 * jq) * kGcD + vr + 8] = St[mt][i][2];
+            sp[(8 * i + 2 * jq + 1) * kGcD + vr + 8] = St[mt][i][3];
+        }
 }
 
 }  // namespace hs
