@@ -791,6 +791,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--context", type=int, default=131072, help="--config 3: tokens per sequence")
     ap.add_argument("--decode-steps", type=int, default=64, help="--config 5: decode steps timed (BASELINE: 256)")
+    ap.add_argument("--prefill-tokens", type=int, default=32768, help="--config 5: prompt tokens per sequence")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -800,7 +801,7 @@ def main():
 
     ctx = Ctx()
     if args.config != 2:
-        kw = {3: {"context": args.context}, 4: {}, 5: {"decode_steps": args.decode_steps}}[args.config]
+        kw = {3: {"context": args.context}, 4: {}, 5: {"decode_steps": args.decode_steps, "prefill_tokens": args.prefill_tokens}}[args.config]
         rec = run_secondary(ctx, args.config, **kw)
         if ctx.rank == 0:
             print(json.dumps(rec))
