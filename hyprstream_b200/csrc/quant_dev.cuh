@@ -12,10 +12,13 @@ __device__ __forceinline__ float mid8(int j) { return __fmul_rn(0.5f, __fadd_rn(
 // Index of y in the 8-bit linear codebook.  The candidate round(y*127)+127 is exact unless y*127 sits
 // within 1e-3 of a half-integer; only then are the true f32 midpoints consulted (smid: the 255 midpoints in shared
 // memory, so the rare path costs two loads and not four divisions for every lane of the warp).
+// (rounding by the magic-number add: t + 1.5 * 2^23 is round-to-nearest-even of t in the low mantissa bits for |t| < 2^22 -
+// the same integer rintf gives - at full rate, where rintf and the float -> int conversion run on the quarter-rate pipe)
 __device__ __forceinline__ int index_int8(float y, const float *smid) {
     float t = __fmul_rn(y, 127.0f);
-    const float r = rintf(t);
-    int c = max(0, min(255, static_cast<int>(r) + 127));
+    const float tm = __fadd_rn(t, 12582912.0f);
+    const float r = __fadd_rn(tm, -12582912.0f);
+    int c = max(0, min(255, __float_as_int(tm) - 0x4B400000 + 127));
     if (fabsf(t - r) > 0.499f) {  // within 1e-3 of a half-integer
         if (c > 0 && !(y > smid[c - 1])) c--;
         else if (c < 255 && y > smid[c]) c++;
@@ -27,8 +30,9 @@ __device__ __forceinline__ int index_int8(float y, const float *smid) {
 // that has no table in shared memory.  mid8 is the function the table is filled from, so the results are identical.
 __device__ __forceinline__ int index_int8_direct(float y) {
     float t = __fmul_rn(y, 127.0f);
-    const float r = rintf(t);
-    int c = max(0, min(255, static_cast<int>(r) + 127));
+    const float tm = __fadd_rn(t, 12582912.0f);
+    const float r = __fadd_rn(tm, -12582912.0f);
+    int c = max(0, min(255, __float_as_int(tm) - 0x4B400000 + 127));
     if (fabsf(t - r) > 0.499f) {
         if (c > 0 && !(y > mid8(c - 1))) c--;
         else if (c < 255 && y > mid8(c)) c++;

@@ -79,6 +79,29 @@ def test_gdn_layer_prompt_then_decode_matches_oracle_and_serial(cuda):
     no_device_error()
 
 
+def test_gdn_layer_prompt_equals_the_three_boundary_calls_bit_for_bit(cuda):
+    """The layer entry hands q, k, v from its prologue to the chunked rule as bf16; the rule rounds q and k to bf16 itself and v is
+    a bf16 value already, so the entry must equal hs_gdn_prologue (fp32 tensors) -> hs_gdn_chunk_prefill -> hs_gdn_epilogue exactly,
+    output and both states; a ragged token count (tail chunk) and a continued prompt (carried states) included."""
+    from hyprstream_b200 import ops
+
+    b = 2
+    w, a_log, dt_bias, nw = _gdn_weights(5)
+    layer = ops.GdnLayer(w.to(cuda), a_log.to(cuda), dt_bias.to(cuda), nw.to(cuda), NK, NV)
+    x, z, a, bb = [u.to(cuda) for u in _gdn_inputs(b, 150, seed=6)]
+    conv, rec = layer.new_states(b, cuda)
+    conv2, rec2 = layer.new_states(b, cuda)
+    for i, (lo, hi) in enumerate(((0, 83), (83, 150))):
+        sl = [u[:, lo:hi].contiguous() for u in (x, z, a, bb)]
+        y = layer.forward(*sl, conv, rec, has_state=i > 0)
+        q, k, v, g, beta = ops.gdn_prologue(sl[0], layer.conv_weight, conv2, i > 0, sl[2], sl[3], layer.neg_a_exp, layer.dt_bias, NK, NV)
+        o = ops.gdn_chunk_prefill(q, k, v, g, beta, rec2)
+        y2 = ops.gdn_epilogue(o, sl[1], layer.norm_weight)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y2) and torch.equal(rec, rec2) and torch.equal(conv, conv2), i
+    no_device_error()
+
+
 def _attn_case(cuda, b, t, seed):
     from hyprstream_b200 import kv_cache as kc
 
