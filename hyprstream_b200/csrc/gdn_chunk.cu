@@ -26,8 +26,9 @@
 // exp(G_C - G) are folded into accumulator columns, so the only operand tiles in shared memory are k and q as bf16.  Only MMA
 // operands are rounded to bf16; the state and all accumulation stay fp32.
 // Bound: the state warps' own chain, ~2,000 cycles per chunk.  Measured on this part: mma.sync.m16n8k16 issues at one per ~5 cycles
-// and scheduler (21 cycles dependent), a fp32 -> bf16x2 pack costs ~4 issue cycles beside MMAs and does not overlap with them,
-// so the first product alone (64 MMAs + 64 packs of the state) is ~600 cycles; HBM traffic and FLOPs are far below their peaks.
+// and scheduler when its A registers repeat (21 cycles dependent), one per ~9.4 when every MMA brings fresh A registers - as the
+// state does, whether they are packed by cvt.rn.bf16x2 or by a single byte permute - so the first product alone (64 MMAs) is
+// ~600 cycles and the chunk's 115 MMAs per scheduler ~1,050; HBM traffic and FLOPs are far below their peaks.
 // Tried and measured slower: RMSNormGated fused in through writer warps (twelve warps with setmaxnreg: the extra warps take
 // issue slots from the state warps, 14.4 -> 16.7 ms for three layers).
 //
