@@ -69,11 +69,12 @@ class _Groups:
         self.h = []
 
 
+@pytest.mark.parametrize("world", [3, 8])
 @pytest.mark.parametrize("kind,block,sdt,hq,hkv,d", [(2, 64, 1, 32, 8, 128), (1, 128, 1, 32, 8, 128), (1, 64, 0, 16, 2, 256)])
-def test_virtual_ranks_merge_to_unsplit(cuda, kind, block, sdt, hq, hkv, d):
+def test_virtual_ranks_merge_to_unsplit(cuda, kind, block, sdt, hq, hkv, d, world):
     from hyprstream_b200 import ffi, kv_cache as kc, ops
 
-    world, lens = 3, [3000, 100, 2048, 5000]  # 100 tokens: one page, so ranks 1 and 2 hold empty shards of that sequence
+    lens = [3000, 100, 2048, 5000]  # 100 tokens: one page, so the later ranks hold empty shards of that sequence
     full, shards, local_lens = _make(cuda, kind, block, sdt, hq, hkv, d, lens, world, seed=31)
     fview, fkeep = kc.make_view(full)
     views = [kc.make_view(s) for s in shards]
@@ -82,7 +83,7 @@ def test_virtual_ranks_merge_to_unsplit(cuda, kind, block, sdt, hq, hkv, d):
     ws = ops.decode_workspace(len(lens), hq, d, cuda)
     grp = _Groups(cuda, world, len(lens), hq, d)
     try:
-        for step, last in enumerate((2, 0, 1, 2)):  # both inbox halves twice, a different rank finishing each time
+        for step, last in enumerate((world - 1, 0, 1, world - 1)):  # both inbox halves twice, a different rank finishing each time
             q = torch.randn(len(lens), hq, d, generator=torch.Generator().manual_seed(50 + step)).bfloat16().to(cuda)
             gate = torch.randn(len(lens), hq, d, generator=torch.Generator().manual_seed(70 + step)).bfloat16().to(cuda) if step == 1 else None
             ref = ops.decode_attention(q, fview, full_t, gate=gate)
