@@ -791,7 +791,9 @@ def main():
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--context", type=int, default=131072, help="--config 3: tokens per sequence")
     ap.add_argument("--decode-steps", type=int, default=64, help="--config 5: decode steps timed (BASELINE: 256)")
-    ap.add_argument("--prefill-tokens", type=int, default=32768, help="--config 5: prompt tokens per sequence")
+    ap.add_argument("--prefill-tokens", type=int, default=None, help="--config 4, 5: prompt tokens per sequence (default 8192, 32768)")
+    ap.add_argument("--prefill-batch", type=int, default=None, help="--config 4, 5: prompt sequences (default 8, 4)")
+    ap.add_argument("--decode-batch", type=int, default=64, help="--config 5: sequences of the decode steps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -801,7 +803,9 @@ def main():
 
     ctx = Ctx()
     if args.config != 2:
-        kw = {3: {"context": args.context}, 4: {}, 5: {"decode_steps": args.decode_steps, "prefill_tokens": args.prefill_tokens}}[args.config]
+        kw = {3: {"context": args.context}, 4: {"batch": args.prefill_batch or 8, "tokens": args.prefill_tokens or 8192},
+              5: {"decode_steps": args.decode_steps, "prefill_tokens": args.prefill_tokens or 32768, "prefill_batch": args.prefill_batch or 4,
+                  "decode_batch": args.decode_batch}}[args.config]
         rec = run_secondary(ctx, args.config, **kw)
         if ctx.rank == 0:
             print(json.dumps(rec))

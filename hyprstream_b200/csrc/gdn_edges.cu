@@ -228,10 +228,17 @@ int32_t gdn_prologue_impl(const void *mixed_qkv, const void *conv_weight, void *
     prof_end(s);
     if (int32_t e = check_launch("hs_gdn_prologue")) return e;
     // the new state is written by a second, stream-ordered launch: the first one still reads the old state
+    return gdn_conv_state_shift(mixed_qkv, has_state ? conv_state : nullptr, conv_state, n_seqs, n_tokens, conv_dim, kernel_size, stream);
+}
+
+// conv_state <- the last kernel_size - 1 frames of (old state | the new tokens); state_in == NULL: the old state is zeros.
+int32_t gdn_conv_state_shift(const void *mixed_qkv, const void *state_in, void *state_out, int32_t n_seqs, int32_t n_tokens, int32_t conv_dim,
+                             int32_t kernel_size, hs_stream_t stream) {
     const int ks1 = kernel_size - 1;
     const int64_t total = static_cast<int64_t>(n_seqs) * conv_dim;
-    gdn_conv_state_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
-        reinterpret_cast<const uint16_t *>(mixed_qkv), st_in, reinterpret_cast<uint16_t *>(conv_state), n_tokens, conv_dim, ks1, total);
+    gdn_conv_state_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint16_t *>(mixed_qkv), reinterpret_cast<const uint16_t *>(state_in), reinterpret_cast<uint16_t *>(state_out), n_tokens,
+        conv_dim, ks1, total);
     return check_launch("hs_gdn_prologue (conv state)");
 }
 

@@ -73,6 +73,20 @@ int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixe
     GdnScratch s = gdn_scratch(params, n_seqs, n_tokens, static_cast<unsigned char *>(workspace));
     if (workspace_bytes < static_cast<int64_t>(s.total))
         return fail(HS_ERR_WORKSPACE, "hs_gdn_layer_forward: workspace %lld < %lld bytes", static_cast<long long>(workspace_bytes), static_cast<long long>(s.total));
+    // a state that is being started is zero
+    if (!has_state) {
+        cudaError_t e = cudaMemsetAsync(rec_state, 0, static_cast<size_t>(n_seqs) * params->n_v_heads * params->head_k_dim * params->head_v_dim * 4, as_stream(stream));
+        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_layer_forward: %s", cudaGetErrorString(e));
+    }
+    if (n_tokens == 1 && n_seqs <= 65535) {
+        // a decode step: conv, gates, the recurrent rule and RMSNormGated in one kernel, then the conv_state shift
+        if (int32_t st = gdn_step_fused(mixed_qkv, params->conv_weight, has_state ? conv_state : nullptr, a_in, b_in, params->neg_a_exp, params->dt_bias, z,
+                                        params->norm_weight, params->norm_eps, rec_state, y, n_seqs, params->n_k_heads, params->n_v_heads,
+                                        params->kernel_size, stream))
+            return st;
+        const int conv_dim = 2 * params->n_k_heads * params->head_k_dim + params->n_v_heads * params->head_v_dim;
+        return gdn_conv_state_shift(mixed_qkv, has_state ? conv_state : nullptr, conv_state, n_seqs, 1, conv_dim, params->kernel_size, stream);
+    }
     // conv1d + SiLU + split + L2 norm + gates (qwen3_5.rs:627-701).  For a prompt q, k, v go to the chunked rule as bf16: that kernel
     // rounds q and k to bf16 first thing and v is a bf16 value already, so the results are the same and half the bytes move.
     const bool chunked = n_tokens > 1;
@@ -80,11 +94,7 @@ int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixe
                                        chunked, s.g, s.beta, n_seqs, n_tokens, params->n_k_heads, params->n_v_heads, params->head_k_dim, params->head_v_dim,
                                        params->kernel_size, stream))
         return st;
-    // the rule: recurrent for a decode step, chunked for a prompt (qwen3_5.rs:725-769); a state that is being started is zero
-    if (!has_state) {
-        cudaError_t e = cudaMemsetAsync(rec_state, 0, static_cast<size_t>(n_seqs) * params->n_v_heads * params->head_k_dim * params->head_v_dim * 4, as_stream(stream));
-        if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_layer_forward: %s", cudaGetErrorString(e));
-    }
+    // the rule: recurrent for a decode step, chunked for a prompt (qwen3_5.rs:725-769)
     int32_t st;
     if (n_tokens == 1)
         st = hs_gdn_recurrent(s.q, s.k, s.v, s.g, s.beta, rec_state, s.o, n_seqs, 1, params->n_k_heads, params->n_v_heads, params->head_k_dim,

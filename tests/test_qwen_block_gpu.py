@@ -102,6 +102,30 @@ def test_gdn_layer_prompt_equals_the_three_boundary_calls_bit_for_bit(cuda):
     no_device_error()
 
 
+def test_gdn_layer_decode_step_equals_the_three_boundary_calls_bit_for_bit(cuda):
+    """A decode step of the layer entry is one kernel (conv, gates, recurrent rule, RMSNormGated) plus the conv_state shift; it
+    must equal hs_gdn_prologue -> hs_gdn_recurrent -> hs_gdn_epilogue exactly - output, recurrent state and conv state - for a
+    sequence's very first token (no carried state) and for later ones."""
+    from hyprstream_b200 import ops
+
+    b = 5
+    w, a_log, dt_bias, nw = _gdn_weights(7)
+    layer = ops.GdnLayer(w.to(cuda), a_log.to(cuda), dt_bias.to(cuda), nw.to(cuda), NK, NV)
+    x, z, a, bb = [u.to(cuda) for u in _gdn_inputs(b, 6, seed=8)]
+    conv, rec = layer.new_states(b, cuda)
+    conv2, rec2 = layer.new_states(b, cuda)
+    rec.fill_(7.0)  # a state that is being started is cleared by the entry
+    for t in range(6):
+        sl = [u[:, t:t + 1].contiguous() for u in (x, z, a, bb)]
+        y = layer.forward(*sl, conv, rec, has_state=t > 0)
+        q, k, v, g, beta = ops.gdn_prologue(sl[0], layer.conv_weight, conv2, t > 0, sl[2], sl[3], layer.neg_a_exp, layer.dt_bias, NK, NV)
+        o = ops.gdn_recurrent(q, k, v, g, beta, rec2)
+        y2 = ops.gdn_epilogue(o, sl[1], layer.norm_weight)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y2) and torch.equal(rec, rec2) and torch.equal(conv, conv2), t
+    no_device_error()
+
+
 def _attn_case(cuda, b, t, seed):
     from hyprstream_b200 import kv_cache as kc
 
