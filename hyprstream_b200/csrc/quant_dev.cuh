@@ -2,6 +2,8 @@
 // kernels (quant.cu) and by the decode kernel that writes a step's new token itself (decode_tc.cu).  One definition, so
 // that every writer produces the same codes and scales bit for bit.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "hs_common.cuh"
 
 namespace hs {
@@ -141,21 +143,45 @@ __device__ __forceinline__ float rope_elem(float own, float partner, float s, fl
     return bf16_round(bf16_round(partner * s) + bf16_round(own * c));                 // x1*sin + x2*cos
 }
 
-// Loads the 8 bf16 elements [d0, d0+8) of a row, rotated when sin != NULL.
+// Loads the 8 bf16 elements [d0, d0+8) of a row, rotated when sin != NULL.  The rotation runs on packed bf16 pairs: a product
+// of two bf16 values is exact in fp32, so mul.rn.bf16x2 rounds it once exactly as "multiply in fp32, round to bf16" does, and
+// the difference / sum of two bf16 values rounds to the same bf16 either way - three instructions per pair instead of the
+// unpack, three roundings and two multiplies per element of rope_elem (which stays for callers that hold fp32 values).
 __device__ __forceinline__ void load_row8_rope(const uint16_t *row, int d0, const uint16_t *sin, const uint16_t *cos,
                                                int pos, int rotary_dim, float (&x)[8]) {
-    unpack8_bf16(*reinterpret_cast<const uint4 *>(row + d0), x);
+    uint4 ow = *reinterpret_cast<const uint4 *>(row + d0);
     if (sin != nullptr && d0 < rotary_dim) {
         const int half = rotary_dim >> 1;
         const bool first = d0 < half;
-        float p[8];
-        unpack8_bf16(*reinterpret_cast<const uint4 *>(row + (first ? d0 + half : d0 - half)), p);
+        const uint4 pw = *reinterpret_cast<const uint4 *>(row + (first ? d0 + half : d0 - half));
         const int j0 = first ? d0 : d0 - half;
         const uint16_t *srow = sin + static_cast<int64_t>(pos) * half + j0;
         const uint16_t *crow = cos + static_cast<int64_t>(pos) * half + j0;
+        uint32_t sw[4], cw[4];
+        if (((reinterpret_cast<uintptr_t>(srow) | reinterpret_cast<uintptr_t>(crow)) & 15u) == 0) {
+            const uint4 s4 = *reinterpret_cast<const uint4 *>(srow), c4 = *reinterpret_cast<const uint4 *>(crow);
+            sw[0] = s4.x; sw[1] = s4.y; sw[2] = s4.z; sw[3] = s4.w;
+            cw[0] = c4.x; cw[1] = c4.y; cw[2] = c4.z; cw[3] = c4.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = rope_elem(x[i], p[i], bf16_bits_to_f32(srow[i]), bf16_bits_to_f32(crow[i]), first);
+            for (int i = 0; i < 4; ++i) {
+                sw[i] = static_cast<uint32_t>(srow[2 * i]) | (static_cast<uint32_t>(srow[2 * i + 1]) << 16);
+                cw[i] = static_cast<uint32_t>(crow[2 * i]) | (static_cast<uint32_t>(crow[2 * i + 1]) << 16);
+            }
+        }
+        uint32_t o[4] = {ow.x, ow.y, ow.z, ow.w};
+        const uint32_t pp[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 own = *reinterpret_cast<const __nv_bfloat162 *>(&o[i]), par = *reinterpret_cast<const __nv_bfloat162 *>(&pp[i]);
+            const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&sw[i]), c2 = *reinterpret_cast<const __nv_bfloat162 *>(&cw[i]);
+            const __nv_bfloat162 oc = __hmul2(own, c2), ps = __hmul2(par, s2);
+            const __nv_bfloat162 r = first ? __hsub2(oc, ps) : __hadd2(ps, oc);  // x1*cos - x2*sin | x1*sin + x2*cos
+            o[i] = *reinterpret_cast<const uint32_t *>(&r);
+        }
+        ow = make_uint4(o[0], o[1], o[2], o[3]);
     }
+    unpack8_bf16(ow, x);
 }
 
 }  // namespace hs
