@@ -116,7 +116,10 @@ __device__ __forceinline__ float gc_f32(__nv_bfloat16 x) { return __bfloat162flo
 __device__ __forceinline__ uint32_t gc_ld32(const __nv_bfloat16 *p) { return *reinterpret_cast<const uint32_t *>(p); }
 
 
-template <typename TIn>
+// MT: 16-row MMA tiles per state warp.  2: a CTA holds a whole head (4 warps x 32 value columns).  1: a head is cut over two
+// CTAs of 64 columns (4 warps x 16): each repeats the set-up, and the state warps' chain per chunk is about half as long - for
+// launches that would leave more than half of the SMs idle (few sequences, or a head group per GPU).
+template <typename TIn, int MT>
 __global__ void __launch_bounds__(kGcThreads, 1)
 gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
@@ -125,7 +128,8 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     constexpr int kGcSlots = gc_slots<TIn>();
     using Slot = GcSlot<TIn>;
     GcSmem<TIn> &sm = *reinterpret_cast<GcSmem<TIn> *>((reinterpret_cast<uintptr_t>(gc_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
-    const int b = blockIdx.y, h = blockIdx.x, kh = h / (n_v_heads / n_k_heads);
+    const int b = blockIdx.y, h = blockIdx.x / (2 / MT), kh = h / (n_v_heads / n_k_heads);
+    const int col0 = (blockIdx.x % (2 / MT)) * 64;  // first value column of this CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, jq = lane & 3;
     const int n_chunks = (n_tokens + kGcC - 1) / kGcC;
     volatile int *abort_flag = &sm.abort;
@@ -309,13 +313,13 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // ================================ state (four warps, 32 value columns each) ================================
     // One state warp per scheduler: its 32 value columns are two 16-row MMA tiles (mt) that share every B operand (k, q, T, P)
     // and give the tensor pipe eight independent accumulators to work on.
-    const int v0 = warp * 32;
+    const int v0 = col0 + warp * 16 * MT;
     // S^T accumulators: tile (mt, i) covers rows v0 + 16 mt + gq (+8), k columns [8i, 8i+8):
     // St[mt][i] = {S^T[row][8i+2jq], [..+1], S^T[row+8][8i+2jq], [..+1]}
-    float St[2][16][4];
+    float St[MT][16][4];
     float *sp = state + (static_cast<int64_t>(b) * n_v_heads + h) * kGcD * kGcD;  // [k][v]
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int vr = v0 + 16 * mt + gq;
@@ -330,9 +334,9 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         Slot &sl = sm.slot[s];
         if (!gc_wait(gc_s32(&sm.ready[s]), use & 1, abort_flag)) { failed = true; break; }
         // ---- [K S0 | Q S0]^T = S^T . [K | Q]^T: rows = this warp's value columns, columns = 16 tokens of k then 16 tokens of q ----
-        float X[2][4][4];
+        float X[MT][4][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int n = 0; n < 4; ++n) X[mt][n][0] = X[mt][n][1] = X[mt][n][2] = X[mt][n][3] = 0.0f;
         // B operands: one ldmatrix.x4 per 16 state columns brings the four 8 x 8 blocks (tokens 0-7 / 8-15) x (columns +0 / +8) of k
@@ -347,7 +351,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(qb[0]), "=r"(qb[1]), "=r"(qb[2]), "=r"(qb[3]) : "r"(xq_lane + 32u * kk8));
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t a0 = gc_pack(St[mt][2 * kk8][0], St[mt][2 * kk8][1]), a1 = gc_pack(St[mt][2 * kk8][2], St[mt][2 * kk8][3]);
                 const uint32_t a2 = gc_pack(St[mt][2 * kk8 + 1][0], St[mt][2 * kk8 + 1][1]), a3 = gc_pack(St[mt][2 * kk8 + 1][2], St[mt][2 * kk8 + 1][3]);
                 gc_mma(X[mt][0], a0, a1, a2, a3, kb[0], kb[1]);
@@ -358,13 +362,13 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         // R^T = beta (V^T - Gamma (K S0)^T) in the accumulator layout = the A operand (k = tokens) of U^T = R^T . T^T;
         // (Gamma Q S0)^T = (Q S0)^T scaled per token column
-        uint32_t r[2][4];
+        uint32_t r[MT][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int s0 = 8 * n + 2 * jq;
             const float b0 = sl.b[s0], b1 = sl.b[s0 + 1], g0 = sl.gam[s0], g1 = sl.gam[s0 + 1];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 const int vr = v0 + 16 * mt + gq;
                 const float r00 = b0 * (gc_f32(sl.raw[2][s0][vr]) - g0 * X[mt][n][0]), r01 = b1 * (gc_f32(sl.raw[2][s0 + 1][vr]) - g1 * X[mt][n][1]);
                 const float r10 = b0 * (gc_f32(sl.raw[2][s0][vr + 8]) - g0 * X[mt][n][2]), r11 = b1 * (gc_f32(sl.raw[2][s0 + 1][vr + 8]) - g1 * X[mt][n][3]);
@@ -374,26 +378,26 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
         // ---- U^T = R^T . T^T; O^T = (Gamma Q S0)^T + U^T . P^T; S^T = Gamma_C S^T + (U^T diag(exp(G_C - G))) . K ----
-        float U[2][2][4];
+        float U[MT][2][4];
         {
             const uint32_t t00 = gc_ld32(&sl.Tb[gq][2 * jq]), t01 = gc_ld32(&sl.Tb[gq][2 * jq + 8]);
             const uint32_t t10 = gc_ld32(&sl.Tb[8 + gq][2 * jq]), t11 = gc_ld32(&sl.Tb[8 + gq][2 * jq + 8]);
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 U[mt][0][0] = U[mt][0][1] = U[mt][0][2] = U[mt][0][3] = 0.0f;
                 U[mt][1][0] = U[mt][1][1] = U[mt][1][2] = U[mt][1][3] = 0.0f;
                 gc_mma(U[mt][0], r[mt][0], r[mt][1], r[mt][2], r[mt][3], t00, t01);
                 gc_mma(U[mt][1], r[mt][0], r[mt][1], r[mt][2], r[mt][3], t10, t11);
             }
         }
-        uint32_t w[2][4];
+        uint32_t w[MT][4];
         {
             const uint32_t p00 = gc_ld32(&sl.P[gq][2 * jq]), p01 = gc_ld32(&sl.P[gq][2 * jq + 8]);
             const uint32_t p10 = gc_ld32(&sl.P[8 + gq][2 * jq]), p11 = gc_ld32(&sl.P[8 + gq][2 * jq + 8]);
             // token columns of U scaled by exp(G_C - G_s) for the state update
             const float d00 = sl.dec[2 * jq], d01 = sl.dec[2 * jq + 1], d10 = sl.dec[8 + 2 * jq], d11 = sl.dec[8 + 2 * jq + 1];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t u0 = gc_pack(U[mt][0][0], U[mt][0][1]), u1 = gc_pack(U[mt][0][2], U[mt][0][3]);
                 const uint32_t u2 = gc_pack(U[mt][1][0], U[mt][1][1]), u3 = gc_pack(U[mt][1][2], U[mt][1][3]);
                 gc_mma(X[mt][2], u0, u1, u2, u3, p00, p01);
@@ -412,7 +416,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(kb_lane + 16u * i));
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 St[mt][i][0] *= gC; St[mt][i][1] *= gC; St[mt][i][2] *= gC; St[mt][i][3] *= gC;
                 gc_mma(St[mt][i], w[mt][0], w[mt][1], w[mt][2], w[mt][3], b0, b1);
                 St[mt][i + 1][0] *= gC; St[mt][i + 1][1] *= gC; St[mt][i + 1][2] *= gC; St[mt][i + 1][3] *= gC;
@@ -431,7 +435,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (t < n_tokens) {
                     float *op = out + ((static_cast<int64_t>(b) * n_tokens + t) * n_v_heads + h) * kGcD + v0 + gq;
 #pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
+                    for (int mt = 0; mt < MT; ++mt) {
                         op[16 * mt] = X[mt][2 + n][e];
                         op[16 * mt + 8] = X[mt][2 + n][2 + e];
                     }
@@ -443,7 +447,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         return;  // the state is left as it was
     }
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int vr = v0 + 16 * mt + gq;
@@ -490,20 +494,20 @@ static bool gc_make_map(CUtensorMap *map, const void *base, bool bf16, int n_seq
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename TIn>
+template <typename TIn, int MT>
 static int32_t gc_launch(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const float *g, const float *beta, float *state, float *out,
                          int n_seqs, int n_tokens, int n_k_heads, int n_v_heads, int *err, cudaStream_t s) {
     static PerDeviceState configured;
     const int dev = current_device();
     constexpr int kBytes = static_cast<int>(sizeof(GcSmem<TIn>) + 128);
     if (!configured.get(dev)) {
-        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<TIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<TIn, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_chunk_prefill: %s", cudaGetErrorString(e));
         configured.set(dev, 1);
     }
-    dim3 grid(n_v_heads, n_seqs);
+    dim3 grid(n_v_heads * (2 / MT), n_seqs);
     prof_begin(s);
-    gdn_chunk_kernel<TIn><<<grid, kGcThreads, kBytes, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
+    gdn_chunk_kernel<TIn, MT><<<grid, kGcThreads, kBytes, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
     prof_end(s);
     return check_launch("hs_gdn_chunk_prefill");
 }
@@ -529,8 +533,12 @@ int32_t gdn_chunk_impl(const void *q, const void *k, const void *v, bool in_bf16
         !gc_make_map(&mv, v, in_bf16, n_seqs, n_tokens, n_v_heads))
         return fail(HS_ERR_UNSUPPORTED, "hs_gdn_chunk_prefill: the driver refused the tensor maps (use hs_gdn_recurrent)");
     cudaStream_t s = as_stream(stream);
-    return in_bf16 ? gc_launch<__nv_bfloat16>(mq, mk, mv, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, err, s)
-                   : gc_launch<float>(mq, mk, mv, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, err, s);
+    // a head over two CTAs when even so the launch fills at most one wave
+    const bool split = 2LL * n_seqs * n_v_heads <= sm_count();
+#define HS_GC(T, M) gc_launch<T, M>(mq, mk, mv, g, beta, state, out, n_seqs, n_tokens, n_k_heads, n_v_heads, err, s)
+    const int32_t st = in_bf16 ? (split ? HS_GC(__nv_bfloat16, 1) : HS_GC(__nv_bfloat16, 2)) : (split ? HS_GC(float, 1) : HS_GC(float, 2));
+#undef HS_GC
+    return st;
 }
 
 }  // namespace hs

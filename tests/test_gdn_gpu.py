@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import gdn_ref as gr
-from tests.util import GOLD
+from tests.util import GOLD, no_device_error
 
 pytestmark = pytest.mark.gpu
 
@@ -122,6 +122,28 @@ def test_chunk_prefill_matches_oracle_and_fp32_kernel(cuda, t):
         assert d.max().item() <= CHUNK_MAX_TOL and d.mean().item() <= CHUNK_MEAN_TOL, f"T={t} vs {what}: max {d.max().item():.3g} mean {d.mean().item():.3g}"
         sd = (state.cpu() - ref_s).abs().max().item() / max(ref_s.abs().max().item(), 1e-6)
         assert sd <= 1e-2, f"T={t} state vs {what}: rel {sd:.3g}"
+
+
+def test_chunk_prefill_whole_head_and_half_head_ctas_agree(cuda):
+    """The chunk kernel gives a head to one CTA, or - when the launch would leave most SMs idle - its two column halves to two
+    CTAs.  A value column's arithmetic is the same either way: a small batch (half heads) must equal, row for row, the same
+    sequences inside a batch large enough for whole-head CTAs; the large batch is also checked against the fp32 kernel."""
+    from hyprstream_b200 import ops
+
+    b, t, nk, nv = 6, 150, 8, 16  # 96 heads: whole-head CTAs on a 148-SM part; the first sequence alone: half-head CTAs
+    q, k, v, g, beta, s0 = _inputs(b, t, nk, nv, 128, 128, seed=77)
+    dev = [x.to(cuda) for x in (q, k, v, g, beta)]
+    state = s0.clone().to(cuda)
+    out = ops.gdn_chunk_prefill(*dev, state)
+    state1 = s0[:1].clone().to(cuda)
+    out1 = ops.gdn_chunk_prefill(*(x[:1].contiguous() for x in dev), state1)
+    state32 = s0.clone().to(cuda)
+    out32 = ops.gdn_recurrent(*dev, state32)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:1], out1) and torch.equal(state[:1], state1)
+    d = (out - out32).abs()
+    assert d.max().item() <= CHUNK_MAX_TOL and d.mean().item() <= CHUNK_MEAN_TOL, (d.max().item(), d.mean().item())
+    no_device_error()
 
 
 def test_chunk_prefill_long_run_stays_close(cuda):
