@@ -617,7 +617,8 @@ int32_t hs_attn_decode_step(const hs_kv_view *view, const void *host_in, void *d
     if (int32_t st = hs_attn_decode_append(qd, kd, vd, view, dst_pos, seq_lens, n_seqs, n_q_heads, softmax_scale, sin, cos, rotary_dim, n_positions, dev_out,
                                            nullptr, workspace, workspace_bytes, stream))
         return st;
-    // (letting the kernel store into mapped host memory instead of this copy was measured: 9 us slower per step)
+    // (letting the kernel store into mapped host memory instead of this copy was measured: 9 us slower per step; copy kernels over
+    // mapped pinned memory in place of the two cudaMemcpyAsync calls: 3 us faster of 102, not worth a second mechanism)
     e = cudaMemcpyAsync(host_out, dev_out, static_cast<size_t>(q_elems) * 2, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess && (flags & HS_STEP_SYNC)) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_attn_decode_step: %s", cudaGetErrorString(e));
