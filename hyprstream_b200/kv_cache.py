@@ -65,7 +65,7 @@ class BlockPool:
         return lib.hs_pool_num_free(self._h)
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # (lib is None when the interpreter is shutting down)
             lib.hs_pool_destroy(self._h)
             self._h = None
 
@@ -199,7 +199,7 @@ class LayerKVCache:
                 self._host_image = None
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.hs_cache_destroy(self._h)  # pages go back to the pool on drop (kv_cache.rs:1889-1898)
             self._h = None
 
@@ -209,7 +209,7 @@ class _ViewHandle:
         self.handle = handle
 
     def __del__(self):
-        if self.handle:
+        if self.handle and lib is not None:
             lib.hs_view_destroy(self.handle)
             self.handle = None
 

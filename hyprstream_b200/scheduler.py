@@ -70,6 +70,6 @@ class Scheduler:
         return s
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.hs_sched_destroy(self._h)
             self._h = None
