@@ -34,8 +34,8 @@ int32_t gdn_prologue_impl(const void *mixed_qkv, const void *conv_weight, void *
                           int32_t head_v_dim, int32_t kernel_size, hs_stream_t stream);
 int32_t gdn_conv_state_shift(const void *mixed_qkv, const void *state_in, void *state_out, int32_t n_seqs, int32_t n_tokens, int32_t conv_dim,
                              int32_t kernel_size, hs_stream_t stream);
-// One decode step of a DeltaNet layer in one kernel (gdn_step.cu); conv_state is read, not shifted.
-int32_t gdn_step_fused(const void *mixed_qkv, const void *conv_weight, const void *conv_state_in, const void *a_in, const void *b_in,
+// One decode step of a DeltaNet layer in one kernel (gdn_step.cu); conv_state is read (when has_state) and shifted in place.
+int32_t gdn_step_fused(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in, const void *b_in,
                        const float *neg_a_exp, const float *dt_bias, const void *z, const float *norm_weight, float eps, float *state, void *y,
                        int32_t n_seqs, int32_t n_k_heads, int32_t n_v_heads, int32_t kernel_size, hs_stream_t stream);
 int32_t gdn_chunk_impl(const void *q, const void *k, const void *v, bool in_bf16, const float *g, const float *beta, float *state, float *out,

@@ -79,13 +79,9 @@ int32_t hs_gdn_layer_forward(const hs_gdn_layer_params *params, const void *mixe
         if (e != cudaSuccess) return fail(static_cast<int32_t>(e), "hs_gdn_layer_forward: %s", cudaGetErrorString(e));
     }
     if (n_tokens == 1 && n_seqs <= 65535) {
-        // a decode step: conv, gates, the recurrent rule and RMSNormGated in one kernel, then the conv_state shift
-        if (int32_t st = gdn_step_fused(mixed_qkv, params->conv_weight, has_state ? conv_state : nullptr, a_in, b_in, params->neg_a_exp, params->dt_bias, z,
-                                        params->norm_weight, params->norm_eps, rec_state, y, n_seqs, params->n_k_heads, params->n_v_heads,
-                                        params->kernel_size, stream))
-            return st;
-        const int conv_dim = 2 * params->n_k_heads * params->head_k_dim + params->n_v_heads * params->head_v_dim;
-        return gdn_conv_state_shift(mixed_qkv, has_state ? conv_state : nullptr, conv_state, n_seqs, 1, conv_dim, params->kernel_size, stream);
+        // a decode step: conv (with the conv_state shift), gates, the recurrent rule and RMSNormGated in one kernel
+        return gdn_step_fused(mixed_qkv, params->conv_weight, conv_state, has_state, a_in, b_in, params->neg_a_exp, params->dt_bias, z, params->norm_weight,
+                              params->norm_eps, rec_state, y, n_seqs, params->n_k_heads, params->n_v_heads, params->kernel_size, stream);
     }
     // conv1d + SiLU + split + L2 norm + gates (qwen3_5.rs:627-701).  For a prompt q, k, v go to the chunked rule as bf16: that kernel
     // rounds q and k to bf16 first thing and v is a bf16 value already, so the results are the same and half the bytes move.
