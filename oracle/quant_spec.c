@@ -23,7 +23,7 @@
  *   A3  4-bit packing: even-indexed element in the HIGH nibble
  *   A4  an all-zero block stores absmax 0 and the codeword index of the value 0
  *   A5  the 4-bit entry points use the built-in table; no `code` pointer is consulted
- *   A6  f16-scale mode (BASELINE.json configs 2, 3): absmax is rounded to f16 (nearest even,
+ *   A6  f16-scale mode (the 2-byte scales of the ragged-decode and long-context workloads): absmax is rounded to f16 (nearest even,
  *       saturating at 65504) BEFORE it is used to normalise, so codes and the stored scale
  *       stay self-consistent
  * NaN/Inf inputs are outside the contract.
