@@ -104,6 +104,15 @@ __device__ __forceinline__ void t5_st32(uint32_t taddr, const uint32_t (&r)[32])
           "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 8-column forms for the rare rescale of O, which runs while a whole score row is held in registers
+__device__ __forceinline__ void t5_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void t5_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
 __device__ __forceinline__ void t5_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -315,8 +324,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int lim = min(kv_len - 1, off + row) - n0;  // last visible column of this row inside the tile
             // ---- pass 1: row maximum (all four loads in flight, one wait) ----
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            // (the score row stays in registers for the second pass: one trip to tensor memory per tile and row)
+            uint32_t r[4][32];
             {
-                uint32_t r[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) t5_ld32(tS + 32 * c, r[c]);
                 t5_wait_ld();
@@ -352,13 +362,13 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     t5_fence_after();
                     const float f = need ? exp2f(m_used - m_new) : 1.0f;
 #pragma unroll
-                    for (int c0 = 0; c0 < kT5D; c0 += 32) {
-                        uint32_t r[32];
-                        t5_ld32(tO + c0, r);
+                    for (int c0 = 0; c0 < kT5D; c0 += 8) {
+                        uint32_t ro[8];
+                        t5_ld8(tO + c0, ro);
                         t5_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-                        t5_st32(tO + c0, r);
+                        for (int i = 0; i < 8; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+                        t5_st8(tO + c0, ro);
                     }
                     t5_wait_st();
                     l *= f;
@@ -370,10 +380,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
             float ps0 = 0.0f, ps1 = 0.0f;
             {
-                uint32_t r[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) t5_ld32(tS + 32 * c, r[c]);
-                t5_wait_ld();  // the whole score row is in registers: P may now overwrite it
                 if (!masked) {
                     const uint64_t sc2 = t5_pack2(scale_log2, scale_log2), nm2 = t5_pack2(neg_m, neg_m);
                     uint64_t acc_a = t5_pack2(0.0f, 0.0f), acc_b = acc_a;
