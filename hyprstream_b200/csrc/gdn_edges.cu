@@ -20,6 +20,14 @@ constexpr int kEdgeTokens = 96;   // tokens per CTA tile (a multiple of the unro
 constexpr int kEdgeMaxTaps = 8;
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// Round to nearest-even bf16 and back, in integer arithmetic: the same value cvt.rn.bf16.f32 gives for every finite input, on
+// the integer pipe instead of the conversion unit, which this kernel's two roundings, exponential and reciprocal per element
+// would otherwise saturate (measured: 66 % busy against 36 % for the integer pipe).
+__device__ __forceinline__ float bf16_round_alu(float f) {
+    uint32_t u = __float_as_uint(f);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return __uint_as_float(u & 0xffff0000u);
+}
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(__expf(x)); }  // libtorch: beta 1, threshold 20
 
 // Thread = 4 consecutive channels of one 128-channel group: a warp is one head, 8 heads per CTA; a CTA walks kEdgeTokens
@@ -102,7 +110,7 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
 #pragma unroll
                 for (int j = 0; j < KS - 1; ++j) acc = fmaf(wt[c][j], hist[c][(u + j) % (KS - 1)], acc);  // frame t - (KS-1) + j
                 acc = fmaf(wt[c][KS - 1], cur[c], acc);
-                y[u][c] = bf16_round(silu_f(bf16_round(acc)));
+                y[u][c] = bf16_round_alu(silu_f(bf16_round_alu(acc)));
                 ss[u] = fmaf(y[u][c], y[u][c], ss[u]);
                 hist[c][u % (KS - 1)] = cur[c];  // replaces the oldest frame
             }
