@@ -44,8 +44,11 @@ namespace hs {
 constexpr int kGcC = 16;          // tokens per chunk
 constexpr int kGcD = 128;         // head_k_dim = head_v_dim
 constexpr int kGcChain = 4;       // warps 0-3: a 32-column slice of the state each, one warp per scheduler
-constexpr int kGcPrep = 3;        // warps 4-6: the S-independent set-up of a chunk, a whole chunk per warp, chunks dealt round-robin
-constexpr int kGcThreads = (kGcChain + kGcPrep + 1) * 32;  // warp 7: staging (eight warps: two per scheduler, so that a state warp may hold its 128 state registers)
+// set-up warps (after the state warps): the S-independent set-up of a chunk, a whole chunk per warp, chunks dealt round-robin; then one
+// staging warp.  Whole-head CTAs (MT = 2): three, eight warps in all - two per scheduler, so that a state warp may hold its 128 state
+// registers.  Half-head CTAs (MT = 1): the state warps' chain is shorter and they need fewer registers: six set-up warps keep up.
+template <int MT> constexpr int gc_prep() { return MT == 2 ? 3 : 6; }
+template <int MT> constexpr int gc_threads() { return (kGcChain + gc_prep<MT>() + 1) * 32; }
 // chunks in flight between the copies and the state warps: what fits beside fp32 (bf16) inputs
 template <typename TIn> constexpr int gc_slots() { return sizeof(TIn) == 4 ? 6 : 9; }
 constexpr int kGcRS = kGcD;       // fp32 row stride of the staged inputs (floats): dense, as the tensor copies write them
@@ -120,7 +123,7 @@ __device__ __forceinline__ uint32_t gc_ld32(const __nv_bfloat16 *p) { return *re
 // CTAs of 64 columns (4 warps x 16): each repeats the set-up, and the state warps' chain per chunk is about half as long - for
 // launches that would leave more than half of the SMs idle (few sequences, or a head group per GPU).
 template <typename TIn, int MT>
-__global__ void __launch_bounds__(kGcThreads, 1)
+__global__ void __launch_bounds__(gc_threads<MT>(), 1)
 gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const float *__restrict__ g, const float *__restrict__ beta, float *__restrict__ state, float *__restrict__ out, int n_tokens, int n_k_heads,
                  int n_v_heads, int *__restrict__ err) {
@@ -145,6 +148,7 @@ gdn_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     __syncthreads();
 
+    constexpr int kGcPrep = gc_prep<MT>();
     if (warp == kGcChain + kGcPrep) {
         // ================================ staging (one warp) ================================
         // Chunk c goes into slot c mod kGcSlots once the state warps are through with the chunk that used the slot before: one
@@ -507,7 +511,7 @@ static int32_t gc_launch(const CUtensorMap &mq, const CUtensorMap &mk, const CUt
     }
     dim3 grid(n_v_heads * (2 / MT), n_seqs);
     prof_begin(s);
-    gdn_chunk_kernel<TIn, MT><<<grid, kGcThreads, kBytes, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
+    gdn_chunk_kernel<TIn, MT><<<grid, gc_threads<MT>(), kBytes, s>>>(mq, mk, mv, g, beta, state, out, n_tokens, n_k_heads, n_v_heads, err);
     prof_end(s);
     return check_launch("hs_gdn_chunk_prefill");
 }
