@@ -19,7 +19,7 @@ constexpr int kEdgeThreads = 256;
 constexpr int kEdgeTokens = 96;   // tokens per CTA tile (a multiple of the unroll of 6)
 constexpr int kEdgeMaxTaps = 8;
 
-__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return silu_fast(x); }
 // Round to nearest-even bf16 and back, in integer arithmetic: the same value cvt.rn.bf16.f32 gives for every finite input, on
 // the integer pipe instead of the conversion unit, which this kernel's two roundings, exponential and reciprocal per element
 // would otherwise saturate (measured: 66 % busy against 36 % for the integer pipe).
@@ -36,7 +36,7 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // TOut: float (the boundary's tensors) or uint16_t = bf16 bits (the layer entry's route to the chunked rule, which rounds q and k
 // to bf16 itself and finds v a bf16 value already: half the bytes written here and read there, same results).
 template <int KS, typename TOut>
-__global__ void __launch_bounds__(kEdgeThreads)
+__global__ void __launch_bounds__(kEdgeThreads, 3)
 gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, const uint16_t *__restrict__ state_in,
                     const uint16_t *__restrict__ a_in, const uint16_t *__restrict__ b_in, const float *__restrict__ neg_a_exp,
                     const float *__restrict__ dt_bias, TOut *__restrict__ q, TOut *__restrict__ k, TOut *__restrict__ v,
@@ -86,11 +86,17 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
     // U tokens' loads are in flight together; U is a multiple of KS-1 so that the ring is indexed by constants after unrolling
     constexpr int U = (KS - 1) * (KS == 4 ? 2 : 6);  // (deeper batches measured no faster: 9 tokens the same, 12 slower)
     // ... and the next U tokens' loads are issued before this batch is worked on: the kernel is bound by bytes in flight
+    // (a batch that lies wholly inside the tile is loaded and stored without per-token tests)
+    const uint16_t *xt = x + (static_cast<int64_t>(b) * n_tokens + t0) * conv_dim + c0;
     auto load_batch = [&](int tb, uint2 (&r)[U]) {
+        if (tb + U <= nt) {
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-            r[u] = tb + u < nt ? *reinterpret_cast<const uint2 *>(x + (static_cast<int64_t>(b) * n_tokens + t0 + tb + u) * conv_dim + c0)
-                               : make_uint2(0u, 0u);
+            for (int u = 0; u < U; ++u) r[u] = *reinterpret_cast<const uint2 *>(xt + static_cast<int64_t>(tb + u) * conv_dim);
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                r[u] = tb + u < nt ? *reinterpret_cast<const uint2 *>(xt + static_cast<int64_t>(tb + u) * conv_dim) : make_uint2(0u, 0u);
+        }
     };
     uint2 rawn[U];
     load_batch(0, rawn);
@@ -121,10 +127,11 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
 #pragma unroll
                 for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], off);
         }
+        const int n_store = min(U, nt - tb);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int t = tb + u;
-            if (t >= nt) break;
+            if (u >= n_store) break;
             float mul = 1.0f;
             if (!is_v) {
                 mul = 1.0f / fmaxf(sqrtf(ss[u]), 1e-3f);  // x / clamp_min(norm, 1e-3), as a multiply by the reciprocal

@@ -20,7 +20,7 @@ constexpr int kGsThreads = 256;
 constexpr int kGsWarps = kGsThreads / 32;
 constexpr int kGsD = 128;  // head_k_dim = head_v_dim
 
-__device__ __forceinline__ float gs_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float gs_silu(float x) { return silu_fast(x); }
 __device__ __forceinline__ float gs_softplus(float x) { return x > 20.0f ? x : log1pf(__expf(x)); }  // libtorch: beta 1, threshold 20
 
 // grid (n_k_heads, n_seqs): a CTA takes a key head's q / k channels once and then its value heads one after the other - so every
