@@ -20,13 +20,13 @@ constexpr int kEdgeTokens = 96;   // tokens per CTA tile (a multiple of the unro
 constexpr int kEdgeMaxTaps = 8;
 
 __device__ __forceinline__ float silu_f(float x) { return silu_fast(x); }
-// Round to nearest-even bf16 and back, in integer arithmetic: the same value cvt.rn.bf16.f32 gives for every finite input, on
-// the integer pipe instead of the conversion unit, which this kernel's two roundings, exponential and reciprocal per element
-// would otherwise saturate (measured: 66 % busy against 36 % for the integer pipe).
-__device__ __forceinline__ float bf16_round_alu(float f) {
-    uint32_t u = __float_as_uint(f);
-    u += 0x7fffu + ((u >> 16) & 1u);
-    return __uint_as_float(u & 0xffff0000u);
+// two values rounded to bf16 (nearest even) and back by one packed conversion and two integer operations (scalar conversions,
+// one per value, kept the conversion unit 66 % busy; this form measured fastest)
+__device__ __forceinline__ void bf16_round_pair(float &a, float &b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    a = __uint_as_float(r << 16);
+    b = __uint_as_float(r & 0xffff0000u);
 }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(__expf(x)); }  // libtorch: beta 1, threshold 20
 
@@ -110,16 +110,23 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
         for (int u = 0; u < U; ++u) {  // (tokens past the end compute on zeros and are not stored)
             const float cur[C] = {bf16lo(rawu[u].x), bf16hi(rawu[u].x), bf16lo(rawu[u].y), bf16hi(rawu[u].y)};
             ss[u] = 0.0f;
+            float acc[C];
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                float acc = 0.0f;
+                acc[c] = 0.0f;
 #pragma unroll
-                for (int j = 0; j < KS - 1; ++j) acc = fmaf(wt[c][j], hist[c][(u + j) % (KS - 1)], acc);  // frame t - (KS-1) + j
-                acc = fmaf(wt[c][KS - 1], cur[c], acc);
-                y[u][c] = bf16_round_alu(silu_f(bf16_round_alu(acc)));
-                ss[u] = fmaf(y[u][c], y[u][c], ss[u]);
+                for (int j = 0; j < KS - 1; ++j) acc[c] = fmaf(wt[c][j], hist[c][(u + j) % (KS - 1)], acc[c]);  // frame t - (KS-1) + j
+                acc[c] = fmaf(wt[c][KS - 1], cur[c], acc[c]);
                 hist[c][u % (KS - 1)] = cur[c];  // replaces the oldest frame
             }
+            bf16_round_pair(acc[0], acc[1]);
+            bf16_round_pair(acc[2], acc[3]);
+#pragma unroll
+            for (int c = 0; c < C; ++c) y[u][c] = silu_f(acc[c]);
+            bf16_round_pair(y[u][0], y[u][1]);
+            bf16_round_pair(y[u][2], y[u][3]);
+#pragma unroll
+            for (int c = 0; c < C; ++c) ss[u] = fmaf(y[u][c], y[u][c], ss[u]);
         }
         if (!is_v) {  // L2 norm over the 128 channels of the head = this warp (warp-uniform branch); the U reductions interleave
 #pragma unroll
@@ -134,7 +141,7 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
             if (u >= n_store) break;
             float mul = 1.0f;
             if (!is_v) {
-                mul = 1.0f / fmaxf(sqrtf(ss[u]), 1e-3f);  // x / clamp_min(norm, 1e-3), as a multiply by the reciprocal
+                mul = inv_l2_norm(ss[u]);  // x / clamp_min(norm, 1e-3), as a multiply by the reciprocal
                 if (is_q) mul *= q_scale;
             }
             if constexpr (sizeof(TOut) == 4) {

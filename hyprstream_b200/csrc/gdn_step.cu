@@ -76,7 +76,7 @@ gdn_step_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, 
         float ss = conv4(warp == 0 ? kh : nk + kh, yv);
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-        float mul = 1.0f / fmaxf(sqrtf(ss), 1e-3f);
+        float mul = inv_l2_norm(ss);
         if (warp == 0) mul *= q_scale;
         *reinterpret_cast<float4 *>(&s_qk[warp][4 * lane]) = make_float4(yv[0] * mul, yv[1] * mul, yv[2] * mul, yv[3] * mul);
     }

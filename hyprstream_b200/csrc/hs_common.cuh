@@ -113,6 +113,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 // x * sigmoid(x) on the approximate exponential and reciprocal: the values of __fdividef(x, 1 + __expf(-x)) without the
 // denormal handling of the two intrinsics (three more instructions per value; 1 + tiny is 1 either way)
+// 1 / max(sqrt(ss), 1e-3) = min(rsqrt(ss), 1e3) on the approximate reciprocal square root (relative error 2^-22; ss = 0 gives 1e3)
+__device__ __forceinline__ float inv_l2_norm(float ss) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ss));
+    return fminf(r, 1e3f);
+}
 __device__ __forceinline__ float silu_fast(float x) {
     float e, r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
