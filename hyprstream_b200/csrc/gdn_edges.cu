@@ -105,12 +105,9 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
 #pragma unroll
         for (int u = 0; u < U; ++u) rawu[u] = rawn[u];
         if (tb + U < nt) load_batch(tb + U, rawn);
-        float y[U][C], ss[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {  // (tokens past the end compute on zeros and are not stored)
+        // the conv sum of token u of the batch, rounded to bf16
+        auto conv_token = [&](int u, float (&acc)[C]) {
             const float cur[C] = {bf16lo(rawu[u].x), bf16hi(rawu[u].x), bf16lo(rawu[u].y), bf16hi(rawu[u].y)};
-            ss[u] = 0.0f;
-            float acc[C];
 #pragma unroll
             for (int c = 0; c < C; ++c) {
                 acc[c] = 0.0f;
@@ -121,6 +118,32 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
             }
             bf16_round_pair(acc[0], acc[1]);
             bf16_round_pair(acc[2], acc[3]);
+        };
+        const int n_store = min(U, nt - tb);
+        if constexpr (sizeof(TOut) == 2) {
+            if (is_v) {  // (warp-uniform) v as bf16 is SiLU's output rounded once: the packed conversion's result is what is stored
+                uint2 yw[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    float acc[C];
+                    conv_token(u, acc);
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(silu_f(acc[0]), silu_f(acc[1])), hi = __floats2bfloat162_rn(silu_f(acc[2]), silu_f(acc[3]));
+                    yw[u] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (u >= n_store) break;
+                    *reinterpret_cast<uint2 *>(dst + (t0 + tb + u) * tok_stride + lane * C) = yw[u];
+                }
+                continue;
+            }
+        }
+        float y[U][C], ss[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {  // (tokens past the end compute on zeros and are not stored)
+            ss[u] = 0.0f;
+            float acc[C];
+            conv_token(u, acc);
 #pragma unroll
             for (int c = 0; c < C; ++c) y[u][c] = silu_f(acc[c]);
             bf16_round_pair(y[u][0], y[u][1]);
@@ -134,7 +157,6 @@ gdn_prologue_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__
 #pragma unroll
                 for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], off);
         }
-        const int n_store = min(U, nt - tb);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int t = tb + u;
