@@ -688,21 +688,26 @@ def run_qwen_block(ctx: Ctx, prefill_batch: int = 4, prefill_tokens: int = 32768
         ws = torch.empty(max(layers[0].workspace_bytes(b, t), attn.workspace_bytes(b, t)), dtype=torch.uint8, device=dev)
         # warm-up (also builds tensor maps, sets attributes): the whole block through the one block-level call
         ops.qwen_block_forward(layers, gin, attn, ain, False, b, t, dev, workspace=ws)
-    ctx.barrier()
-    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    e[0].record()
-    if units:
-        ops.qwen_block_forward(layers, gin, None, None, False, b, t, dev, workspace=ws)   # the three DeltaNet layers
-    e[1].record()
-    if units:
-        ops.qwen_block_forward([], [], attn, ain, False, b, t, dev, workspace=ws)         # the full-attention layer
-    e[2].record()
-    ctx.barrier()
-    gdn_ms, attn_ms = ctx.max(e[0].elapsed_time(e[1])), ctx.max(e[1].elapsed_time(e[2]))
-    block_ms = ctx.max(e[0].elapsed_time(e[2]))
+    # three timed passes of the block, the median pass reported (one pass is 40 ms; the DeltaNet layers' chain follows the SM clock,
+    # which the power cap moves from pass to pass)
+    passes = []
+    for _ in range(3):
+        ctx.barrier()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        if units:
+            ops.qwen_block_forward(layers, gin, None, None, False, b, t, dev, workspace=ws)   # the three DeltaNet layers
+        e[1].record()
+        if units:
+            ops.qwen_block_forward([], [], attn, ain, False, b, t, dev, workspace=ws)         # the full-attention layer
+        e[2].record()
+        ctx.barrier()
+        passes.append((ctx.max(e[0].elapsed_time(e[2])), ctx.max(e[0].elapsed_time(e[1])), ctx.max(e[1].elapsed_time(e[2]))))
+    block_ms, gdn_ms, attn_ms = sorted(passes)[1]
     attn_flops = 4.0 * prefill_batch * HQ5 * D5 * t * (t + 1) / 2
     res["prefill"] = {"batch": prefill_batch, "tokens": t, "units_per_gpu": f"{b} x ({nv} v heads, {hq} q heads)",
                       "api": "hs_qwen_block_forward", "gdn_layers_ms": gdn_ms, "full_attention_layer_ms": attn_ms, "block_ms": block_ms,
+                      "block_ms_passes": [round(p[0], 3) for p in passes],
                       "tokens_per_s": prefill_batch * t / block_ms * 1e3,
                       "full_attention_useful_tflops_incl_edges": attn_flops / attn_ms / 1e9}
     if units:

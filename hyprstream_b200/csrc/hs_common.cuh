@@ -38,6 +38,10 @@ int32_t gdn_conv_state_shift(const void *mixed_qkv, const void *state_in, void *
 int32_t gdn_step_fused(const void *mixed_qkv, const void *conv_weight, void *conv_state, int32_t has_state, const void *a_in, const void *b_in,
                        const float *neg_a_exp, const float *dt_bias, const void *z, const float *norm_weight, float eps, float *state, void *y,
                        int32_t n_seqs, int32_t n_k_heads, int32_t n_v_heads, int32_t kernel_size, hs_stream_t stream);
+// hs_attn_prefill_causal with the gate's strides given (elements between tokens / between heads); prefill.cu
+int32_t prefill_causal_impl(const void *q, const void *k, const void *v, void *out, const void *gate, int64_t gate_ts, int64_t gate_hs,
+                            int32_t n_seqs, int32_t q_len, int32_t kv_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                            float softmax_scale, hs_stream_t stream);
 int32_t gdn_chunk_impl(const void *q, const void *k, const void *v, bool in_bf16, const float *g, const float *beta, float *state, float *out,
                        int32_t n_seqs, int32_t n_tokens, int32_t n_k_heads, int32_t n_v_heads, int32_t head_k_dim, int32_t head_v_dim, hs_stream_t stream);
 

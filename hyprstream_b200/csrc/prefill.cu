@@ -59,8 +59,8 @@ __device__ __forceinline__ void load_tile(uint32_t smem_tile, const uint16_t *ba
 template <int D, int BN>
 __global__ void __launch_bounds__(kPfThreads)
 prefill_mma_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k, const uint16_t *__restrict__ v,
-                   uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, int q_len, int kv_len, int n_q_heads,
-                   int n_kv_heads, float scale_log2) {
+                   uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, int64_t gate_ts, int64_t gate_hs, int q_len, int kv_len,
+                   int n_q_heads, int n_kv_heads, float scale_log2) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int kQBytes = kPfM * D * 2, kTile = BN * D * 2;
     const uint32_t sQ = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -190,12 +190,13 @@ prefill_mma_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ 
         const int row = r ? row_hi : row_lo;
         if (row >= q_len) continue;
         const int64_t base = (static_cast<int64_t>(b) * q_len + row) * q_stride + static_cast<int64_t>(h) * D;
+        const int64_t gbase = (static_cast<int64_t>(b) * q_len + row) * gate_ts + static_cast<int64_t>(h) * gate_hs;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
             float x0 = o[i][2 * r] * l[r], x1 = o[i][2 * r + 1] * l[r];
             const int col = i * 8 + 2 * j;
             if (gate != nullptr) {
-                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + base + col);
+                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + gbase + col);
                 x0 = bf16_round(x0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
                 x1 = bf16_round(x1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
             }
@@ -206,7 +207,7 @@ prefill_mma_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ 
 
 template <int D, int BN>
 static int32_t launch_prefill(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate,
-                              int n_seqs, int q_len, int kv_len, int hq, int hkv, float scale_log2, cudaStream_t s) {
+                              int64_t gate_ts, int64_t gate_hs, int n_seqs, int q_len, int kv_len, int hq, int hkv, float scale_log2, cudaStream_t s) {
     constexpr int smem = kPfM * D * 2 + 4 * BN * D * 2;
     auto kern = prefill_mma_kernel<D, BN>;
     static PerDeviceState configured;  // per instantiation and device
@@ -217,13 +218,48 @@ static int32_t launch_prefill(const uint16_t *q, const uint16_t *k, const uint16
         configured.set(dev, 1);
     }
     dim3 grid((q_len + kPfM - 1) / kPfM, hq, n_seqs);
-    kern<<<grid, kPfThreads, smem, s>>>(q, k, v, out, gate, q_len, kv_len, hq, hkv, scale_log2);
+    kern<<<grid, kPfThreads, smem, s>>>(q, k, v, out, gate, gate_ts, gate_hs, q_len, kv_len, hq, hkv, scale_log2);
     return HS_OK;
 }
 
 // prefill_tc5.cu: tcgen05 / TMEM / TMA kernel for head_dim 128
-int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int n_seqs,
-                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2, cudaStream_t s, int *taken);
+int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int64_t gate_ts,
+                        int64_t gate_hs, int n_seqs, int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2,
+                        cudaStream_t s, int *taken);
+
+// The body of hs_attn_prefill_causal with the gate's strides spelled out (elements between tokens and between heads): the Qwen3.5
+// layer entry reads the gate halves where the projection left them.
+int32_t prefill_causal_impl(const void *q, const void *k, const void *v, void *out, const void *gate, int64_t gate_ts, int64_t gate_hs,
+                            int32_t n_seqs, int32_t q_len, int32_t kv_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                            float softmax_scale, hs_stream_t stream) {
+    if (int32_t st = check_device()) return st;
+    if (n_seqs < 0 || q_len < 0 || kv_len < 0 || n_q_heads <= 0 || n_kv_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: bad sizes");
+    if (n_q_heads % n_kv_heads != 0) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: n_q_heads %d not a multiple of n_kv_heads %d", n_q_heads, n_kv_heads);
+    if (kv_len < q_len) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: kv_len %d < q_len %d", kv_len, q_len);
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(HS_ERR_UNSUPPORTED, "hs_attn_prefill_causal: head_dim %d (supported: 64, 128, 256)", head_dim);
+    if (n_seqs == 0 || q_len == 0) return HS_OK;
+    if (!q || !k || !v || !out) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: NULL pointer");
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(out, 4) || (gate && !aligned(gate, 4)))
+        return fail(HS_ERR_ARG, "hs_attn_prefill_causal: q, k, v must be 16-byte aligned");
+    if (gate && (gate_ts % 2 != 0 || gate_hs % 2 != 0)) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: gate strides must be even");
+    if (n_seqs > 65535 || n_q_heads > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_attn_prefill_causal: grid too large");
+    const float sl2 = softmax_scale * 1.4426950408889634f;
+    cudaStream_t s = as_stream(stream);
+    const uint16_t *qp = reinterpret_cast<const uint16_t *>(q), *kp = reinterpret_cast<const uint16_t *>(k), *vp = reinterpret_cast<const uint16_t *>(v);
+    uint16_t *op = reinterpret_cast<uint16_t *>(out);
+    const uint16_t *gp = reinterpret_cast<const uint16_t *>(gate);
+    int32_t st;
+    int taken = 0;
+    prof_begin(s);
+    st = prefill_tc5_try(qp, kp, vp, op, gp, gate_ts, gate_hs, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, head_dim, sl2, s, &taken);
+    if (st != HS_OK || taken) {
+    } else if (head_dim == 64) st = launch_prefill<64, 64>(qp, kp, vp, op, gp, gate_ts, gate_hs, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
+    else if (head_dim == 128) st = launch_prefill<128, 64>(qp, kp, vp, op, gp, gate_ts, gate_hs, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
+    else st = launch_prefill<256, 32>(qp, kp, vp, op, gp, gate_ts, gate_hs, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
+    prof_end(s);
+    if (st != HS_OK) return st;
+    return check_launch("hs_attn_prefill_causal");
+}
 
 }  // namespace hs
 
@@ -234,32 +270,8 @@ extern "C" {
 int32_t hs_attn_prefill_causal(const void *q, const void *k, const void *v, void *out, const void *gate, int32_t n_seqs,
                                int32_t q_len, int32_t kv_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
                                float softmax_scale, hs_stream_t stream) {
-    if (int32_t st = check_device()) return st;
-    if (n_seqs < 0 || q_len < 0 || kv_len < 0 || n_q_heads <= 0 || n_kv_heads <= 0) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: bad sizes");
-    if (n_q_heads % n_kv_heads != 0) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: n_q_heads %d not a multiple of n_kv_heads %d", n_q_heads, n_kv_heads);
-    if (kv_len < q_len) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: kv_len %d < q_len %d", kv_len, q_len);
-    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(HS_ERR_UNSUPPORTED, "hs_attn_prefill_causal: head_dim %d (supported: 64, 128, 256)", head_dim);
-    if (n_seqs == 0 || q_len == 0) return HS_OK;
-    if (!q || !k || !v || !out) return fail(HS_ERR_ARG, "hs_attn_prefill_causal: NULL pointer");
-    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(out, 4) || (gate && !aligned(gate, 4)))
-        return fail(HS_ERR_ARG, "hs_attn_prefill_causal: q, k, v must be 16-byte aligned");
-    if (n_seqs > 65535 || n_q_heads > 65535) return fail(HS_ERR_UNSUPPORTED, "hs_attn_prefill_causal: grid too large");
-    const float sl2 = softmax_scale * 1.4426950408889634f;
-    cudaStream_t s = as_stream(stream);
-    const uint16_t *qp = reinterpret_cast<const uint16_t *>(q), *kp = reinterpret_cast<const uint16_t *>(k), *vp = reinterpret_cast<const uint16_t *>(v);
-    uint16_t *op = reinterpret_cast<uint16_t *>(out);
-    const uint16_t *gp = reinterpret_cast<const uint16_t *>(gate);
-    int32_t st;
-    int taken = 0;
-    prof_begin(s);
-    st = prefill_tc5_try(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, head_dim, sl2, s, &taken);
-    if (st != HS_OK || taken) {
-    } else if (head_dim == 64) st = launch_prefill<64, 64>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
-    else if (head_dim == 128) st = launch_prefill<128, 64>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
-    else st = launch_prefill<256, 32>(qp, kp, vp, op, gp, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads, sl2, s);
-    prof_end(s);
-    if (st != HS_OK) return st;
-    return check_launch("hs_attn_prefill_causal");
+    return prefill_causal_impl(q, k, v, out, gate, static_cast<int64_t>(n_q_heads) * head_dim, head_dim, n_seqs, q_len, kv_len, n_q_heads, n_kv_heads,
+                               head_dim, softmax_scale, stream);
 }
 
 }  // extern "C"

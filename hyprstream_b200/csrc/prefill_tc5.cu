@@ -175,8 +175,8 @@ __device__ __forceinline__ float t5_ex2(float x) {
 // tile 1, warp 8: loader, warp 9: MMA issuer.  TMEM columns: S/P of tile x at 128x, O of tile x at 256 + 128x.
 __global__ void __launch_bounds__(kT5Threads, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
-                   int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
+                   const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, int64_t gate_ts,
+                   int64_t gate_hs, int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) T5Bars bars;
     __shared__ uint32_t s_tmem;
@@ -425,6 +425,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             t5_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kT5D;
+            const int64_t gbase = (static_cast<int64_t>(b) * q_len + row) * gate_ts + h * gate_hs;
 #pragma unroll
             for (int c0 = 0; c0 < kT5D; c0 += 32) {
                 uint32_t r[32];
@@ -438,7 +439,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         for (int i = 0; i < 4; ++i) {
                             float x0 = __uint_as_float(r[v4 * 8 + 2 * i]) * inv, x1 = __uint_as_float(r[v4 * 8 + 2 * i + 1]) * inv;
                             if (gate != nullptr) {
-                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + base + c0 + v4 * 8 + 2 * i);
+                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + gbase + c0 + v4 * 8 + 2 * i);
                                 x0 = bf16_round(x0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
                                 x1 = bf16_round(x1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
                             }
@@ -491,8 +492,8 @@ struct W5Bars {
 
 __global__ void __launch_bounds__(kW5Threads, 1)
 prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate,
-                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
+                        const __grid_constant__ CUtensorMap map_v, uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, int64_t gate_ts,
+                        int64_t gate_hs, int q_len, int kv_len, int n_q_heads, int n_kv_heads, float scale_log2, int *__restrict__ err, uint32_t launch_id) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) W5Bars bars;
     __shared__ uint32_t s_tmem;
@@ -792,6 +793,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
             const int64_t base = ((static_cast<int64_t>(b) * q_len + row) * n_q_heads + h) * kW5D;
+            const int64_t gbase = (static_cast<int64_t>(b) * q_len + row) * gate_ts + h * gate_hs;
 #pragma unroll 1
             for (int c0 = grp * (kW5D / 2); c0 < (grp + 1) * (kW5D / 2); c0 += 32) {
                 uint32_t o[32];
@@ -805,7 +807,7 @@ prefill_tc5_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         for (int i = 0; i < 4; ++i) {
                             float x0 = __uint_as_float(o[v4 * 8 + 2 * i]) * inv, x1 = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
                             if (gate != nullptr) {
-                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + base + c0 + v4 * 8 + 2 * i);
+                                const uint32_t gw = *reinterpret_cast<const uint32_t *>(gate + gbase + c0 + v4 * 8 + 2 * i);
                                 x0 = bf16_round(x0) * bf16_round(1.0f / (1.0f + __expf(-bf16lo(gw))));
                                 x1 = bf16_round(x1) * bf16_round(1.0f / (1.0f + __expf(-bf16hi(gw))));
                             }
@@ -864,8 +866,9 @@ static bool make_map(CUtensorMap *map, const void *base, int n_seqs, int n_token
 
 // Returns HS_OK with *taken = 1 when this kernel took the launch, *taken = 0 when the caller should use the
 // mma.sync kernel (head_dim != 128, or no tensor-map encoder in the driver).
-int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int n_seqs,
-                        int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2, cudaStream_t s, int *taken) {
+int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *out, const uint16_t *gate, int64_t gate_ts,
+                        int64_t gate_hs, int n_seqs, int q_len, int kv_len, int n_q_heads, int n_kv_heads, int head_dim, float scale_log2,
+                        cudaStream_t s, int *taken) {
     *taken = 0;
     if (q_len < 2) return HS_OK;
     if (head_dim == kW5D) {
@@ -883,7 +886,7 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
             configured_w.set(dev, 1);
         }
         dim3 gridw((q_len + kW5M - 1) / kW5M, n_q_heads, n_seqs);
-        prefill_tc5_wide_kernel<<<gridw, kW5Threads, kW5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, errw, next_launch_id());
+        prefill_tc5_wide_kernel<<<gridw, kW5Threads, kW5SmemBytes, s>>>(mq, mk, mv, out, gate, gate_ts, gate_hs, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, errw, next_launch_id());
         *taken = 1;
         return HS_OK;
     }
@@ -902,7 +905,7 @@ int32_t prefill_tc5_try(const uint16_t *q, const uint16_t *k, const uint16_t *v,
         configured.set(dev, 1);
     }
     dim3 grid((q_len + kT5BlockM - 1) / kT5BlockM, n_q_heads, n_seqs);
-    prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err, next_launch_id());
+    prefill_tc5_kernel<<<grid, kT5Threads, kT5SmemBytes, s>>>(mq, mk, mv, out, gate, gate_ts, gate_hs, q_len, kv_len, n_q_heads, n_kv_heads, scale_log2, err, next_launch_id());
     *taken = 1;
     return HS_OK;
 }

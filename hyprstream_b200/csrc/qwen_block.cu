@@ -133,8 +133,9 @@ int32_t hs_qwen_attn_layer_forward(const hs_qwen_attn_params *params, const void
     unsigned char *w = static_cast<unsigned char *>(workspace);
     const size_t qb = up256(static_cast<size_t>(rows) * hq * d * 2), kb = up256(static_cast<size_t>(rows) * hkv * d * 2);
     void *query = w, *gate = w + qb, *k_rot = w + 2 * qb, *dec_ws = w + 2 * qb + kb;
-    // q_proj rows are [n_q_heads, 2 * head_dim]: query half | gate half (qwen3_5.rs:965-967); (1 + w) QK-norm, partial RoPE
-    if (int32_t st = hs_qk_norm_rope(q_proj, static_cast<int64_t>(hq) * 2 * d, 2 * d, query, gate, params->q_norm_weight, params->norm_eps, 1, params->sin,
+    // q_proj rows are [n_q_heads, 2 * head_dim]: query half | gate half (qwen3_5.rs:965-967); (1 + w) QK-norm, partial RoPE.
+    // A decode step copies the gate halves out (its kernel wants them dense); a prompt's attention reads them in place.
+    if (int32_t st = hs_qk_norm_rope(q_proj, static_cast<int64_t>(hq) * 2 * d, 2 * d, query, n_tokens == 1 ? gate : nullptr, params->q_norm_weight, params->norm_eps, 1, params->sin,
                                      params->cos, positions, params->n_positions, params->rotary_dim, rows, hq, d, stream))
         return st;
     // K: norm + rotation + cache update in one pass over the new keys (qwen3_5.rs:971-999); a prompt also keeps the normed,
@@ -146,7 +147,8 @@ int32_t hs_qwen_attn_layer_forward(const hs_qwen_attn_params *params, const void
     if (n_tokens == 1)
         return hs_attn_decode(query, view, seq_lens, n_seqs, hq, params->softmax_scale, out, gate, dec_ws,
                               hs_attn_decode_workspace_bytes(n_seqs, hq, d), nullptr, nullptr, stream);
-    return hs_attn_prefill_causal(query, k_rot, v_proj, out, gate, n_seqs, n_tokens, n_tokens, hq, hkv, d, params->softmax_scale, stream);
+    return hs::prefill_causal_impl(query, k_rot, v_proj, out, static_cast<const uint16_t *>(q_proj) + d, static_cast<int64_t>(hq) * 2 * d, 2 * d, n_seqs, n_tokens,
+                                   n_tokens, hq, hkv, d, params->softmax_scale, stream);
 }
 
 int64_t hs_qwen_block_workspace_bytes(const hs_gdn_layer_params *gdn, int32_t n_gdn, const hs_qwen_attn_params *attn, int32_t n_seqs,
