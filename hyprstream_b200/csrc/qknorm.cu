@@ -11,16 +11,14 @@
 // One pass over HBM: head_dim/8 lanes hold one (token, head) row, 8 elements each; the row's sum of squares and the
 // rotation partners travel by shuffles.  Input rows may be strided (the query half of a [.., 2 head_dim] projection);
 // outputs are dense [n_tokens, n_heads, head_dim].
+#include <cuda_bf16.h>
+
 #include "hs_common.cuh"
 
 namespace hs {
 
 constexpr int kNormThreads = 256;
 
-__device__ __forceinline__ float qkn_rope_elem(float own, float partner, float s, float c, bool first_half) {
-    if (first_half) return bf16_round(bf16_round(own * c) - bf16_round(partner * s));  // x1*cos - x2*sin
-    return bf16_round(bf16_round(partner * s) + bf16_round(own * c));                 // x1*sin + x2*cos
-}
 
 // LPR: lanes per row = head_dim / 8
 template <int LPR>
@@ -33,19 +31,26 @@ qk_norm_rope_kernel(const uint16_t *__restrict__ x, int64_t token_stride, int64_
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * kNormThreads + threadIdx.x) / LPR;  // (token, head)
     const int l = threadIdx.x % LPR, d0 = l * 8;
     const bool live = row < n_tokens * n_heads;  // dead lanes still take part in the shuffles
-    const int64_t tok = live ? row / n_heads : 0;
-    const int h = live ? static_cast<int>(row % n_heads) : 0;
-    const uint16_t *src = x + tok * token_stride + h * head_stride;
-    float v[8];
-    {
-        const uint4 w4 = live ? *reinterpret_cast<const uint4 *>(src + d0) : make_uint4(0u, 0u, 0u, 0u);
-        v[0] = bf16lo(w4.x); v[1] = bf16hi(w4.x); v[2] = bf16lo(w4.y); v[3] = bf16hi(w4.y);
-        v[4] = bf16lo(w4.z); v[5] = bf16hi(w4.z); v[6] = bf16lo(w4.w); v[7] = bf16hi(w4.w);
+    int64_t tok = 0;
+    int h = 0;
+    if (live) {
+        if (row <= 0x7fffffffLL) {  // (a 64-bit division is several dozen instructions)
+            const unsigned r32 = static_cast<unsigned>(row), t32 = r32 / static_cast<unsigned>(n_heads);
+            tok = t32;
+            h = static_cast<int>(r32 - t32 * static_cast<unsigned>(n_heads));
+        } else {
+            tok = row / n_heads;
+            h = static_cast<int>(row % n_heads);
+        }
     }
+    const uint16_t *src = x + tok * token_stride + h * head_stride;
+    const uint4 w4 = live ? *reinterpret_cast<const uint4 *>(src + d0) : make_uint4(0u, 0u, 0u, 0u);
     if (gate_out != nullptr && live)
         *reinterpret_cast<uint4 *>(gate_out + row * D + d0) = *reinterpret_cast<const uint4 *>(src + D + d0);
-    float n[8];
+    // n: the normed row as bf16 pairs (one packed conversion per pair = the one rounding to the model dtype)
+    uint32_t n[4] = {w4.x, w4.y, w4.z, w4.w};
     if (weight != nullptr) {
+        const float v[8] = {bf16lo(w4.x), bf16hi(w4.x), bf16lo(w4.y), bf16hi(w4.y), bf16lo(w4.z), bf16hi(w4.z), bf16lo(w4.w), bf16hi(w4.w)};
         float ss = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
@@ -56,10 +61,7 @@ qk_norm_rope_kernel(const uint16_t *__restrict__ x, int64_t token_stride, int64_
         const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         const float add = plus_one ? 1.0f : 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) n[i] = bf16_round(v[i] * rrms * (wv[i] + add));
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) n[i] = v[i];
+        for (int i = 0; i < 4; ++i) n[i] = pack_bf16(v[2 * i] * rrms * (wv[2 * i] + add), v[2 * i + 1] * rrms * (wv[2 * i + 1] + add));
     }
     if (sin != nullptr) {
         const int half = rotary_dim >> 1;
@@ -69,24 +71,28 @@ qk_norm_rope_kernel(const uint16_t *__restrict__ x, int64_t token_stride, int64_
         const bool rot = d0 < rotary_dim, first = d0 < half;
         // the partner chunk (d0 +- half) sits half/8 lanes away in the same row
         const int partner_lane = (threadIdx.x & 31) + (first ? half / 8 : -(half / 8));
-        float p[8];
+        uint32_t p[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) p[i] = __shfl_sync(0xffffffffu, n[i], rot ? partner_lane : (threadIdx.x & 31));
+        for (int i = 0; i < 4; ++i) p[i] = __shfl_sync(0xffffffffu, n[i], rot ? partner_lane : (threadIdx.x & 31));
         if (rot && in_table && live) {
+            // In packed bf16 arithmetic: the product of two bf16 values is exact in fp32, so mul.rn.bf16x2 rounds it once exactly as
+            // "multiply in fp32, round to bf16" does, and the difference / sum of two bf16 values rounds to the same bf16 either way
+            // (runtime/rope.rs:206-248 rounds every product, difference and sum to bf16).
             const int j0 = first ? d0 : d0 - half;
             const uint4 s4 = *reinterpret_cast<const uint4 *>(sin + static_cast<int64_t>(pos) * half + j0);
             const uint4 c4 = *reinterpret_cast<const uint4 *>(cos + static_cast<int64_t>(pos) * half + j0);
             const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, cw[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                n[2 * i] = qkn_rope_elem(n[2 * i], p[2 * i], bf16lo(sw[i]), bf16lo(cw[i]), first);
-                n[2 * i + 1] = qkn_rope_elem(n[2 * i + 1], p[2 * i + 1], bf16hi(sw[i]), bf16hi(cw[i]), first);
+                const __nv_bfloat162 own = *reinterpret_cast<const __nv_bfloat162 *>(&n[i]), par = *reinterpret_cast<const __nv_bfloat162 *>(&p[i]);
+                const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&sw[i]), c2 = *reinterpret_cast<const __nv_bfloat162 *>(&cw[i]);
+                const __nv_bfloat162 oc = __hmul2(own, c2), ps = __hmul2(par, s2);
+                const __nv_bfloat162 r = first ? __hsub2(oc, ps) : __hadd2(ps, oc);  // x1*cos - x2*sin | x1*sin + x2*cos
+                n[i] = *reinterpret_cast<const uint32_t *>(&r);
             }
         }
     }
-    if (live)
-        *reinterpret_cast<uint4 *>(out + row * D + d0) =
-            make_uint4(pack_bf16(n[0], n[1]), pack_bf16(n[2], n[3]), pack_bf16(n[4], n[5]), pack_bf16(n[6], n[7]));
+    if (live) *reinterpret_cast<uint4 *>(out + row * D + d0) = make_uint4(n[0], n[1], n[2], n[3]);
 }
 
 }  // namespace hs
