@@ -185,8 +185,12 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
 #pragma unroll
             for (int part = 0; part < E / 8; ++part) {
                 const int dd = d0 + 8 * part;
+                // the normed chunk as bf16 pairs (one packed conversion per pair = the one rounding to the model dtype), rotated in
+                // packed bf16 arithmetic like load_row8_rope: the same values as the scalar form, bit for bit
+                uint32_t ow[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x[8 * part + i] = bf16_round(x[8 * part + i] * rrms * (kn.weight[dd + i] + add));
+                for (int i = 0; i < 4; ++i)
+                    ow[i] = pack_bf16(x[8 * part + 2 * i] * rrms * (kn.weight[dd + 2 * i] + add), x[8 * part + 2 * i + 1] * rrms * (kn.weight[dd + 2 * i + 1] + add));
                 if (rope && dd < rotary_dim) {
                     const bool first = dd < half;
                     const int pd = first ? dd + half : dd - half;  // the rotation partner's chunk, normed the same way
@@ -196,17 +200,21 @@ __global__ void __launch_bounds__(kQThreads) kv_write_kernel(ViewDev view, const
                     const uint16_t *srow = sin + static_cast<int64_t>(pos) * half + j0;
                     const uint16_t *crow = cos + static_cast<int64_t>(pos) * half + j0;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float pn = bf16_round(p8[i] * rrms * (kn.weight[pd + i] + add));
-                        x[8 * part + i] = rope_elem(x[8 * part + i], pn, bf16_bits_to_f32(srow[i]), bf16_bits_to_f32(crow[i]), first);
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t pw = pack_bf16(p8[2 * i] * rrms * (kn.weight[pd + 2 * i] + add), p8[2 * i + 1] * rrms * (kn.weight[pd + 2 * i + 1] + add));
+                        const uint32_t sw = static_cast<uint32_t>(srow[2 * i]) | (static_cast<uint32_t>(srow[2 * i + 1]) << 16);
+                        const uint32_t cw = static_cast<uint32_t>(crow[2 * i]) | (static_cast<uint32_t>(crow[2 * i + 1]) << 16);
+                        const __nv_bfloat162 own = *reinterpret_cast<const __nv_bfloat162 *>(&ow[i]), par = *reinterpret_cast<const __nv_bfloat162 *>(&pw);
+                        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&sw), c2 = *reinterpret_cast<const __nv_bfloat162 *>(&cw);
+                        const __nv_bfloat162 oc = __hmul2(own, c2), ps = __hmul2(par, s2);
+                        const __nv_bfloat162 r = first ? __hsub2(oc, ps) : __hadd2(ps, oc);  // x1*cos - x2*sin | x1*sin + x2*cos
+                        ow[i] = *reinterpret_cast<const uint32_t *>(&r);
                     }
                 }
-                if (kn.k_out != nullptr && ok) {  // the normed, rotated keys in bf16, for a prompt's own attention
-                    uint4 w;
-                    w.x = pack_bf16(x[8 * part], x[8 * part + 1]); w.y = pack_bf16(x[8 * part + 2], x[8 * part + 3]);
-                    w.z = pack_bf16(x[8 * part + 4], x[8 * part + 5]); w.w = pack_bf16(x[8 * part + 6], x[8 * part + 7]);
-                    *reinterpret_cast<uint4 *>(kn.k_out + row * D + dd) = w;
-                }
+                if (kn.k_out != nullptr && ok)  // the normed, rotated keys in bf16, for a prompt's own attention
+                    *reinterpret_cast<uint4 *>(kn.k_out + row * D + dd) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { x[8 * part + 2 * i] = bf16lo(ow[i]); x[8 * part + 2 * i + 1] = bf16hi(ow[i]); }
             }
         } else {
 #pragma unroll
